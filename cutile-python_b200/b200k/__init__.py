@@ -1,0 +1,11 @@
+"""b200k — B200 (sm_100a) kernels behind the entry points of the cuTile samples.
+
+Importing this package needs only torch; the first operator call loads
+``libb200k.so`` (built by ``cutile-python_b200/build.py``) and raises if it is missing.
+"""
+from ._lib import B200KError, device_status, raise_on_device_error  # noqa: F401
+from .matmul import (bmm, cutile_batch_matmul, cutile_matmul,  # noqa: F401
+                     cutile_persistent_matmul)
+from .block_scaled import (block_quantize, cutile_block_scaled_matmul,  # noqa: F401
+                           cutile_nvfp4_matmul, cutile_swizzled_scaled_matmul, nvfp4_quantize,
+                           swizzle_32_4_4)

@@ -1,0 +1,147 @@
+"""ctypes binding of libb200k.so (the C ABI declared in include/b200k.h).
+
+The shared library is the only compute path of this package: if it is missing or
+fails to load, importing an operator raises — there is no fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libb200k.so")
+
+# enum b200k_dtype
+F16, BF16, F32, E4M3, E5M2, E2M1X2 = range(6)
+# enum b200k_b_layout
+B_KN, B_NK = 0, 1
+# enum b200k_epilogue
+EPI_STORE, EPI_SWIGLU = 0, 1
+# enum b200k_status
+OK, INVALID_ARG, UNSUPPORTED, CUDA_ERROR, TIMEOUT = 0, -1, -2, -3, -4
+
+
+class B200KError(RuntimeError):
+    """A b200k entry point returned a negative status."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"b200k error {code}: {message}")
+        self.code = code
+
+
+class GemmArgs(Structure):
+    _fields_ = [
+        ("a", c_void_p), ("b", c_void_p), ("c", c_void_p),
+        ("m", c_int64), ("n", c_int64), ("k", c_int64), ("batch", c_int64),
+        ("lda", c_int64), ("ldb", c_int64), ("ldc", c_int64),
+        ("stride_a", c_int64), ("stride_b", c_int64), ("stride_c", c_int64),
+        ("ab_dtype", c_int32), ("c_dtype", c_int32), ("b_layout", c_int32), ("epilogue", c_int32),
+        ("alpha", c_float), ("max_ctas", c_int32),
+        ("tile_group", c_void_p), ("num_row_tiles", c_void_p),
+        ("row_map", c_void_p), ("row_scale", c_void_p), ("c_rows", c_int64),
+    ]
+
+
+class BlockScaledGemmArgs(Structure):
+    _fields_ = [
+        ("a", c_void_p), ("b", c_void_p), ("sfa", c_void_p), ("sfb", c_void_p), ("c", c_void_p),
+        ("m", c_int64), ("n", c_int64), ("k", c_int64), ("batch", c_int64),
+        ("lda", c_int64), ("ldb", c_int64), ("ldc", c_int64),
+        ("stride_a", c_int64), ("stride_b", c_int64), ("stride_c", c_int64),
+        ("sf_k_atoms", c_int64), ("stride_sfa", c_int64), ("stride_sfb", c_int64),
+        ("ab_dtype", c_int32), ("c_dtype", c_int32), ("epilogue", c_int32), ("alpha", c_float),
+        ("alpha_a", c_void_p), ("alpha_b", c_void_p),
+        ("max_ctas", c_int32),
+        ("tile_group", c_void_p), ("num_row_tiles", c_void_p),
+        ("row_map", c_void_p), ("row_scale", c_void_p), ("c_rows", c_int64),
+    ]
+
+
+class QuantizeArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("q", c_void_p), ("sf_logical", c_void_p), ("sf_swizzled", c_void_p),
+        ("tensor_scale", c_void_p), ("scratch", c_void_p),
+        ("rows", c_int64), ("k", c_int64), ("ldx", c_int64), ("ldq", c_int64),
+        ("sf_k_atoms", c_int64),
+        ("x_dtype", c_int32), ("q_dtype", c_int32),
+    ]
+
+
+# name -> (restype, argtypes); every symbol include/b200k.h declares
+SIGNATURES = {
+    "b200k_version": (c_char_p, []),
+    "b200k_last_error": (c_char_p, []),
+    "b200k_sm_count": (c_int, []),
+    "b200k_device_status": (c_int, [POINTER(c_int), POINTER(c_int)]),
+    "b200k_gemm": (c_int, [POINTER(GemmArgs), c_void_p]),
+    "b200k_block_scaled_gemm": (c_int, [POINTER(BlockScaledGemmArgs), c_void_p]),
+    "b200k_mxfp8_quantize": (c_int, [POINTER(QuantizeArgs), c_void_p]),
+    "b200k_nvfp4_quantize": (c_int, [POINTER(QuantizeArgs), c_void_p]),
+    "b200k_sf_swizzle": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int32,
+                                 c_void_p]),
+}
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the shared library once; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python cutile-python_b200/build.py` "
+                "(b200k has no fallback path)")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+    return _lib
+
+
+def check(code: int) -> None:
+    if code < 0:
+        raise B200KError(code, lib().b200k_last_error().decode("utf-8", "replace"))
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def device_status() -> tuple[int, int]:
+    """(code, info) of the current device's status word; synchronise the stream first."""
+    code, info = c_int(0), c_int(0)
+    check(lib().b200k_device_status(ctypes.byref(code), ctypes.byref(info)))
+    return code.value, info.value
+
+
+def raise_on_device_error() -> None:
+    code, info = device_status()
+    if code != 0:
+        raise B200KError(code, f"device-side wait gave up (role {(info >> 8) & 0xff}, "
+                               f"detail {(info >> 16) & 0xffff})")
+
+
+_TORCH_TO_ENUM = {
+    torch.float16: F16,
+    torch.bfloat16: BF16,
+    torch.float32: F32,
+    torch.float8_e4m3fn: E4M3,
+    torch.float8_e5m2: E5M2,
+}
+
+
+def dtype_enum(dt: torch.dtype) -> int:
+    try:
+        return _TORCH_TO_ENUM[dt]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {dt}") from None
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()

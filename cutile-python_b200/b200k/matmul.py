@@ -1,0 +1,155 @@
+"""Dense matmul entry points with the signatures of the reference's samples.
+
+cutile_matmul            samples/MatMul.py:179-251
+bmm                      samples/BatchMatMul.py:53-92
+cutile_persistent_matmul test/bench_matmul.py:396-410 (bench form, output passed in)
+cutile_batch_matmul      test/bench_matmul.py:323-329 (bench form)
+
+All of them run the tcgen05 GEMM behind ``b200k_gemm``; tile sizes are fixed by the
+kernel (128 x 256 x one 128-byte K atom), so the reference's tile-size choice by dtype
+has no counterpart here.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+def _row_major_2d(t: torch.Tensor) -> bool:
+    return t.stride(-1) == 1
+
+
+def _aligned(t: torch.Tensor, ld: int) -> bool:
+    return (ld * t.element_size()) % 16 == 0 and t.data_ptr() % 16 == 0
+
+
+def _pad_last(t: torch.Tensor) -> torch.Tensor:
+    """Copies ``t`` (..., R, C) into a buffer whose rows start on 16-byte boundaries.
+    TMA cannot address rows at other pitches; the logical shape is unchanged."""
+    per = 16 // t.element_size()
+    cols = t.shape[-1]
+    padded = (cols + per - 1) // per * per
+    buf = torch.zeros(*t.shape[:-1], padded, dtype=t.dtype, device=t.device)
+    buf[..., :cols].copy_(t)
+    return buf[..., :cols]
+
+
+def _gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, alpha: float = 1.0,
+          max_ctas: int = 0) -> torch.Tensor:
+    """a: (B, M, K) or (M, K); b: (B, K, N) or (K, N) as a view; c likewise (M, N)."""
+    batched = a.dim() == 3
+    if not batched:
+        a3, b3, c3 = a.unsqueeze(0), b.unsqueeze(0), c.unsqueeze(0)
+    else:
+        a3, b3, c3 = a, b, c
+    nb, m, k = a3.shape
+    n = b3.shape[2]
+    if a3.dtype != b3.dtype:
+        raise TypeError(f"operand dtypes differ: {a3.dtype} vs {b3.dtype}")
+
+    # A must be K-contiguous
+    if a3.stride(2) != 1 or not _aligned(a3, a3.stride(1)) or (nb > 1 and (a3.stride(0) * a3.element_size()) % 16):
+        a3 = _pad_last(a3.contiguous() if a3.stride(2) != 1 else a3)
+    # B: (K, N) N-contiguous, or a transposed view of an (N, K) K-contiguous tensor
+    if b3.stride(2) == 1 and (b3.stride(1) != 1 or n == 1):
+        layout = _lib.B_KN
+        ldb = b3.stride(1)
+        if not _aligned(b3, ldb) or (nb > 1 and (b3.stride(0) * b3.element_size()) % 16):
+            b3 = _pad_last(b3)
+            ldb = b3.stride(1)
+    elif b3.stride(1) == 1:
+        layout = _lib.B_NK
+        ldb = b3.stride(2)
+        if not _aligned(b3, ldb) or (nb > 1 and (b3.stride(0) * b3.element_size()) % 16):
+            b3 = _pad_last(b3.transpose(1, 2)).transpose(1, 2)
+            ldb = b3.stride(2)
+    else:
+        b3 = _pad_last(b3.contiguous())
+        layout = _lib.B_KN
+        ldb = b3.stride(1)
+    if c3.stride(2) != 1:
+        raise ValueError("output must be row-major")
+
+    args = _lib.GemmArgs()
+    args.a, args.b, args.c = a3.data_ptr(), b3.data_ptr(), c3.data_ptr()
+    args.m, args.n, args.k, args.batch = m, n, k, nb
+    args.lda, args.ldb, args.ldc = a3.stride(1), ldb, c3.stride(1)
+    args.stride_a, args.stride_b, args.stride_c = a3.stride(0), b3.stride(0), c3.stride(0)
+    args.ab_dtype = _lib.dtype_enum(a3.dtype)
+    args.c_dtype = _lib.dtype_enum(c3.dtype)
+    args.b_layout = layout
+    args.epilogue = _lib.EPI_STORE
+    args.alpha = alpha
+    args.max_ctas = max_ctas
+    with torch.cuda.device(a.device):
+        _lib.check(_lib.lib().b200k_gemm(ctypes.byref(args), _lib.stream_ptr(a.device)))
+    return c
+
+
+def _validate(A: torch.Tensor, B: torch.Tensor) -> None:
+    # same checks and messages as samples/MatMul.py:201-207
+    if A.shape[-1] != B.shape[-2]:
+        raise ValueError(f"Incompatible matrices: K dimension of A ({A.shape[-1]}) "
+                         f"must match K dimension of B ({B.shape[-2]})")
+    if A.device != B.device:
+        raise ValueError("Input tensors must be on the same device.")
+    if not A.is_cuda or not B.is_cuda:
+        raise ValueError("Input tensors must be on a CUDA device.")
+
+
+def cutile_matmul(A: torch.Tensor, B: torch.Tensor, persistent: bool = False,
+                  C: torch.Tensor | None = None) -> torch.Tensor:
+    """C = A @ B with fp32 accumulation; C has A's dtype and shape (M, N).
+
+    fp32 operands are multiplied as tf32, like the reference kernel
+    (test/kernels/matmul.py:74).  ``persistent`` is accepted for signature
+    compatibility; the kernel is always persistent (one CTA per SM).
+    """
+    _validate(A, B)
+    if A.dim() != 2 or B.dim() != 2:
+        raise ValueError("cutile_matmul expects 2-D operands")
+    m, n = A.shape[0], B.shape[1]
+    if C is None:
+        C = torch.empty((m, n), device=A.device, dtype=A.dtype)
+    if m == 0 or n == 0:
+        return C
+    if A.shape[1] == 0:
+        return C.zero_()
+    return _gemm(A, B, C)
+
+
+def cutile_persistent_matmul(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor) -> torch.Tensor:
+    return cutile_matmul(A, B, persistent=True, C=C)
+
+
+def bmm(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """Batched C[i] = a[i] @ b[i]; a (Batch, M, K), b (Batch, K, N).
+
+    fp16/bf16 operands give an output of the same dtype; fp8 operands accumulate in
+    fp32 and default to an fp32 output (samples/BatchMatMul.py:72-81).
+    """
+    if a.dim() != 3 or b.dim() != 3:
+        raise ValueError("bmm expects 3-D operands")
+    if a.shape[0] != b.shape[0]:
+        raise ValueError(f"Batch dimensions differ: {a.shape[0]} vs {b.shape[0]}")
+    _validate(a, b)
+    if out_dtype is None:
+        out_dtype = torch.float32 if a.element_size() == 1 else a.dtype
+    nb, m, _ = a.shape
+    n = b.shape[2]
+    c = torch.empty((nb, m, n), device=a.device, dtype=out_dtype)
+    if nb == 0 or m == 0 or n == 0:
+        return c
+    if a.shape[2] == 0:
+        return c.zero_()
+    return _gemm(a, b, c)
+
+
+def cutile_batch_matmul(bs: int, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor) -> torch.Tensor:
+    if A.shape[0] != bs:
+        raise ValueError("batch size does not match A")
+    _validate(A, B)
+    return _gemm(A, B, C)

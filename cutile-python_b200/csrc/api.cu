@@ -1,0 +1,157 @@
+// Library-level entry points: version, error text, device status, tensor-map
+// encoding.  See include/b200k.h for the contract.
+#include <stdarg.h>
+#include <stdio.h>
+#include <mutex>
+
+#include "host.h"
+
+namespace b200k {
+
+namespace {
+thread_local char g_error[512] = "";
+
+// One status word per device, resident in the library image.
+__device__ int g_status_word;
+
+constexpr int kMaxDevices = 64;
+int* g_status_addr[kMaxDevices];
+int g_sm_count[kMaxDevices];
+std::mutex g_mutex;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+EncodeTiledFn get_encode() {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) {
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+  }
+  return g_encode;
+}
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int* device_status_word() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_status_addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+    g_status_addr[dev] = static_cast<int*>(p);
+  }
+  return g_status_addr[dev];
+}
+
+int current_sm_count() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_sm_count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+    g_sm_count[dev] = n;
+  }
+  return g_sm_count[dev];
+}
+
+static bool encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base,
+                        const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                        CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = get_encode();
+  if (fn == nullptr) {
+    fail(B200K_CUDA_ERROR, "cuTensorMapEncodeTiled entry point unavailable");
+    return false;
+  }
+  cuuint64_t gdim[5];
+  cuuint64_t gstride[4];
+  cuuint32_t gbox[5];
+  cuuint32_t estride[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    gbox[i] = box[i];
+    estride[i] = 1;
+  }
+  for (int i = 0; i + 1 < rank; ++i) gstride[i] = strides_bytes[i];
+  CUresult r = fn(out, dtype, rank, const_cast<void*>(base), gdim, gstride, gbox, estride,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fail(B200K_INVALID_ARG,
+         "tensor map rejected (CUresult %d): base %p dims [%llu,%llu,%llu] strides [%llu,%llu] "
+         "box [%u,%u,%u]",
+         static_cast<int>(r), base, (unsigned long long)dims[0], (unsigned long long)dims[1],
+         (unsigned long long)(rank > 2 ? dims[2] : 0), (unsigned long long)strides_bytes[0],
+         (unsigned long long)(rank > 2 ? strides_bytes[1] : 0), box[0], box[1],
+         rank > 2 ? box[2] : 0);
+    return false;
+  }
+  return true;
+}
+
+bool encode_tmap_3d(CUtensorMap* out, CUtensorMapDataType dtype, const void* base, uint64_t d0,
+                    uint64_t d1, uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes,
+                    uint32_t box0, uint32_t box1, uint32_t box2, CUtensorMapSwizzle swizzle) {
+  uint64_t dims[3] = {d0, d1, d2};
+  uint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  uint32_t box[3] = {box0, box1, box2};
+  return encode_tmap(out, dtype, 3, base, dims, strides, box, swizzle);
+}
+
+bool encode_tmap_4d(CUtensorMap* out, CUtensorMapDataType dtype, const void* base, uint64_t d0,
+                    uint64_t d1, uint64_t d2, uint64_t d3, uint64_t stride1_bytes,
+                    uint64_t stride2_bytes, uint64_t stride3_bytes, uint32_t box0, uint32_t box1,
+                    uint32_t box2, uint32_t box3, CUtensorMapSwizzle swizzle) {
+  uint64_t dims[4] = {d0, d1, d2, d3};
+  uint64_t strides[3] = {stride1_bytes, stride2_bytes, stride3_bytes};
+  uint32_t box[4] = {box0, box1, box2, box3};
+  return encode_tmap(out, dtype, 4, base, dims, strides, box, swizzle);
+}
+
+}  // namespace b200k
+
+extern "C" {
+
+const char* b200k_version(void) { return "b200k 0.1 (sm_100a)"; }
+
+const char* b200k_last_error(void) { return b200k::g_error; }
+
+int b200k_sm_count(void) {
+  int n = b200k::current_sm_count();
+  if (n < 0) return b200k::fail(B200K_CUDA_ERROR, "no current CUDA device");
+  return n;
+}
+
+int b200k_device_status(int* code, int* info) {
+  int* word = b200k::device_status_word();
+  if (word == nullptr) return b200k::fail(B200K_CUDA_ERROR, "status word unavailable");
+  int value = 0;
+  cudaError_t e = cudaMemcpy(&value, word, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess)
+    return b200k::fail(B200K_CUDA_ERROR, "reading status word: %s", cudaGetErrorString(e));
+  if (value != 0) {
+    int zero = 0;
+    cudaMemcpy(word, &zero, sizeof(int), cudaMemcpyHostToDevice);
+  }
+  if (code) *code = (value & 0xff) ? B200K_TIMEOUT : B200K_OK;
+  if (info) *info = value & ~0xff;
+  return B200K_OK;
+}
+
+}  // extern "C"

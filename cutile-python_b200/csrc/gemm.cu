@@ -1,0 +1,684 @@
+// Dense and block-scaled GEMM for sm_100a: one persistent, warp-specialised kernel
+// template built on TMA loads, an mbarrier ring and tcgen05 MMA with the
+// accumulator in tensor memory.
+//
+//   warp 0      TMA producer (one lane): A / B / scale-factor tiles -> shared memory
+//   warp 1      MMA issuer (one lane): [scale factors smem -> TMEM,] 4 MMAs per stage
+//   warps 2..5  epilogue: TMEM -> registers -> global (each warp owns 32 TMEM lanes)
+//
+// CTA tile: 128 x BN, one 128-byte swizzle atom of K per stage (64 f16 / 32 tf32 /
+// 128 fp8 / 256 fp4 elements).  Tiles are walked persistently in the grouped
+// raster order of the reference (GROUP_SIZE_M = 8, test/kernels/matmul.py:13-23).
+//
+// Semantics follow the reference kernels: fp32 accumulation, zero padding of
+// partial tiles (TMA out-of-bounds fill), result rounded once to the output type
+// (test/kernels/matmul.py:70-100, test/kernels/scaled_matmul.py:71-114).
+#include "common.cuh"
+#include "host.h"
+
+namespace b200k {
+
+constexpr int kBM = 128;
+constexpr int kStages = 4;
+constexpr int kGroupM = 8;
+constexpr int kNumThreads = 192;
+constexpr int kTmemCols = 512;
+
+enum OutType : int { kOutF16 = 0, kOutBF16 = 1, kOutF32 = 2 };
+
+struct GemmParams {
+  void* c;
+  int m, n, k;          // k in elements
+  int batch;
+  int64_t ldc;          // elements
+  int64_t stride_c;     // elements
+  int tiles_m, tiles_n;
+  int k_iters;
+  int k_tail_mmas;      // MMAs of the last k iteration (1..4)
+  uint32_t idesc;
+  float alpha;
+  const float* alpha_a;
+  const float* alpha_b;
+  // scale factors (swizzled atoms of 512 bytes)
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  int sf_k_atoms;
+  int sfb_row_tiles;    // 128-row tiles present in sfb (reads are clamped to it)
+  int64_t stride_sfa, stride_sfb;
+  // grouped mode
+  const int* tile_group;
+  const int* num_row_tiles;
+  const int* row_map;
+  const float* row_scale;
+  int64_t c_rows;
+  int epilogue;
+  int* status;
+};
+
+template <int KIND>
+struct KindTraits;
+template <> struct KindTraits<kKindF16>  { static constexpr int kElemBits = 16; static constexpr bool kScaled = false; };
+template <> struct KindTraits<kKindTF32> { static constexpr int kElemBits = 32; static constexpr bool kScaled = false; };
+template <> struct KindTraits<kKindF8>   { static constexpr int kElemBits = 8;  static constexpr bool kScaled = false; };
+template <> struct KindTraits<kKindMXF8> { static constexpr int kElemBits = 8;  static constexpr bool kScaled = true;
+                                           static constexpr int kSfBlock = 32; };
+template <> struct KindTraits<kKindNVF4> { static constexpr int kElemBits = 4;  static constexpr bool kScaled = true;
+                                           static constexpr int kSfBlock = 16; };
+
+template <int KIND, int BN, bool B_MN>
+struct GemmCfg {
+  using T = KindTraits<KIND>;
+  static constexpr int kBKElems = 128 * 8 / T::kElemBits;  // K elements per stage
+  static constexpr int kMmaK = kBKElems / 4;               // 32 bytes of K per MMA
+  static constexpr int kABytes = kBM * 128;
+  static constexpr int kBBytes = BN * 128;
+  // MN-major B: boxes of (128 bytes of N) x (kBKElems rows of K)
+  static constexpr int kBBoxN = 128 * 8 / T::kElemBits;    // N elements per 128-byte row
+  static constexpr int kBBoxBytes = kBKElems * 128;
+  static constexpr int kBBoxes = B_MN ? BN / kBBoxN : BN / 128;
+  static constexpr bool kScaled = T::kScaled;
+  static constexpr int kSfaAtoms = kScaled ? (KIND == kKindNVF4 ? 4 : 1) : 0;  // per stage
+  static constexpr int kSfbAtoms = kSfaAtoms * (BN / 128);
+  static constexpr int kSfBytes = (kSfaAtoms + kSfbAtoms) * 512;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kNumAcc = kScaled ? 1 : (BN <= 256 ? 512 / 256 : 1);
+  static constexpr int kAccStride = 256;
+  static constexpr int kSfTmemBase = 256;
+  static constexpr int kSfaCols = kSfaAtoms * 4;
+  static constexpr int kSfbCols = kSfbAtoms * 4;
+  static constexpr int kSmemBytes =
+      1024 /*alignment slack*/ + kStages * (kStageBytes + kSfBytes) + 256 /*barriers*/;
+  static_assert(!kScaled || kSfTmemBase + kStages * (kSfaCols + kSfbCols) <= kTmemCols,
+                "scale factors do not fit in tensor memory");
+  static_assert(!(B_MN && KIND == kKindNVF4), "fp4 operands are K-major only");
+};
+
+struct TileCoord {
+  int batch, pid_m, pid_n;
+};
+
+// Grouped raster order: consecutive tile ids walk kGroupM row tiles before moving to
+// the next column tile, which keeps a band of A and one B tile hot in L2.
+__device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles_n) {
+  int per_batch = tiles_m * tiles_n;
+  TileCoord c;
+  c.batch = tile / per_batch;
+  int t = tile - c.batch * per_batch;
+  int group_tiles = kGroupM * tiles_n;
+  int group = t / group_tiles;
+  int first_m = group * kGroupM;
+  int rows = min(kGroupM, tiles_m - first_m);
+  int in_group = t - group * group_tiles;
+  c.pid_m = first_m + in_group % rows;
+  c.pid_n = in_group / rows;
+  return c;
+}
+
+template <int OUT>
+__device__ __forceinline__ void store_row_chunk(void* c_row, int col0, int n_limit,
+                                                const float (&v)[32], bool vec_ok) {
+  // 32 consecutive output columns of one row, starting at col0.
+  if constexpr (OUT == kOutF32) {
+    float* dst = static_cast<float*>(c_row) + col0;
+    if (vec_ok && col0 + 32 <= n_limit) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < n_limit) dst[i] = v[i];
+    }
+  } else {
+    uint16_t* dst = static_cast<uint16_t*>(c_row) + col0;
+    if (vec_ok && col0 + 32 <= n_limit) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 q;
+        if constexpr (OUT == kOutBF16) {
+          q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+          q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+          q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+          q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+        } else {
+          q.x = pack_f16x2(v[8 * i + 0], v[8 * i + 1]);
+          q.y = pack_f16x2(v[8 * i + 2], v[8 * i + 3]);
+          q.z = pack_f16x2(v[8 * i + 4], v[8 * i + 5]);
+          q.w = pack_f16x2(v[8 * i + 6], v[8 * i + 7]);
+        }
+        reinterpret_cast<uint4*>(dst)[i] = q;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (col0 + i < n_limit) {
+          if constexpr (OUT == kOutBF16) {
+            __nv_bfloat16 h = __float2bfloat16_rn(v[i]);
+            dst[i] = *reinterpret_cast<uint16_t*>(&h);
+          } else {
+            __half h = __float2half_rn(v[i]);
+            dst[i] = *reinterpret_cast<uint16_t*>(&h);
+          }
+        }
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+template <int KIND, int BN, bool B_MN, int OUT>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const GemmParams p) {
+  using Cfg = GemmCfg<KIND, BN, B_MN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  // carve-up
+  const uint32_t tiles_base = smem_base;
+  const uint32_t sf_base = tiles_base + kStages * Cfg::kStageBytes;
+  uint8_t* tail = smem + kStages * (Cfg::kStageBytes + Cfg::kSfBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
+  const uint32_t bar_base = smem_u32(bars);
+  // full[kStages], empty[kStages], acc_full[2], acc_empty[2]
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+  auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * kStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8 * (2 * kStages + 4) + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  int tiles_m = p.tiles_m;
+  if (p.num_row_tiles != nullptr) tiles_m = min(tiles_m, *p.num_row_tiles);
+  const int num_tiles = tiles_m * p.tiles_n * p.batch;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
+        int group = tc.batch;
+        if (p.tile_group != nullptr) {
+          group = p.tile_group[tc.pid_m];
+          if (group < 0) continue;
+        }
+        const int m0 = tc.pid_m * kBM;
+        const int n0 = tc.pid_n * BN;
+        for (int kb = 0; kb < p.k_iters; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) {
+            report_status(p.status, 1, s);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint32_t tx = Cfg::kStageBytes;
+          int sfa_atoms = 0;
+          if constexpr (Cfg::kScaled) {
+            sfa_atoms = min(Cfg::kSfaAtoms, p.sf_k_atoms - kb * Cfg::kSfaAtoms);
+            tx += sfa_atoms * 512 * (1 + BN / 128);
+          }
+          mbar_arrive_expect_tx(full_bar(s), tx);
+          const uint32_t a_dst = tiles_base + s * Cfg::kStageBytes;
+          const uint32_t b_dst = a_dst + Cfg::kABytes;
+          // TMA x coordinate in tensor-map elements (fp4 maps are byte typed)
+          const int kx = kb * (KIND == kKindNVF4 ? 128 : Cfg::kBKElems);
+          tma_load_3d(a_dst, &tmap_a, full_bar(s), kx, m0, p.tile_group ? 0 : tc.batch);
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int j = 0; j < Cfg::kBBoxes; ++j)
+              tma_load_3d(b_dst + j * Cfg::kBBoxBytes, &tmap_b, full_bar(s),
+                          n0 + j * Cfg::kBBoxN, kb * Cfg::kBKElems, group);
+          } else {
+#pragma unroll
+            for (int j = 0; j < Cfg::kBBoxes; ++j) {
+              int row = n0 + j * 128;
+              // SwiGLU: the second half of the tile holds the "up" columns, which
+              // live N/2 rows further down in B.
+              if (p.epilogue == B200K_EPI_SWIGLU) row = n0 / 2 + (j >= Cfg::kBBoxes / 2 ? p.n / 2 + (j - Cfg::kBBoxes / 2) * 128 : j * 128);
+              tma_load_3d(b_dst + j * 128 * 128, &tmap_b, full_bar(s), kx, row, group);
+            }
+          }
+          if constexpr (Cfg::kScaled) {
+            const uint32_t sfa_dst = sf_base + s * Cfg::kSfBytes;
+            const uint32_t sfb_dst = sfa_dst + Cfg::kSfaAtoms * 512;
+            const uint8_t* sfa_src = p.sfa + (p.tile_group ? 0 : tc.batch) * p.stride_sfa +
+                                     (static_cast<int64_t>(tc.pid_m) * p.sf_k_atoms + kb * Cfg::kSfaAtoms) * 512;
+            bulk_load(sfa_dst, sfa_src, sfa_atoms * 512, full_bar(s));
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j) {
+              int row_tile = (n0 >> 7) + j;
+              if (p.epilogue == B200K_EPI_SWIGLU)
+                row_tile = (n0 >> 8) + (j >= BN / 256 ? (p.n >> 8) + (j - BN / 256) : j);
+              row_tile = min(row_tile, p.sfb_row_tiles - 1);
+              const uint8_t* sfb_src = p.sfb + group * p.stride_sfb +
+                                       (static_cast<int64_t>(row_tile) * p.sf_k_atoms + kb * Cfg::kSfaAtoms) * 512;
+              bulk_load(sfb_dst + j * Cfg::kSfaAtoms * 512, sfb_src, sfa_atoms * 512, full_bar(s));
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      uint32_t local_tile = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (p.tile_group != nullptr) {
+          TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
+          if (p.tile_group[tc.pid_m] < 0) continue;
+        }
+        const int as = local_tile % Cfg::kNumAcc;
+        const uint32_t aph = (local_tile / Cfg::kNumAcc) & 1;
+        if (!mbar_wait(acc_empty_bar(as), aph ^ 1, abort_flag)) {
+          report_status(p.status, 2, 100 + as);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t tmem_acc = tmem_base + as * Cfg::kAccStride;
+        for (int kb = 0; kb < p.k_iters; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(full_bar(s), ph, abort_flag)) {
+            report_status(p.status, 2, s);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = tiles_base + s * Cfg::kStageBytes;
+          const uint32_t b_addr = a_addr + Cfg::kABytes;
+          const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024, kSwizzle128B);
+          const uint64_t b_desc = B_MN ? make_smem_desc(b_addr, Cfg::kBBoxBytes, 1024, kSwizzle128B)
+                                       : make_smem_desc(b_addr, 16, 1024, kSwizzle128B);
+          const int n_mma = (kb == p.k_iters - 1) ? p.k_tail_mmas : 4;
+          uint32_t tsfa = 0, tsfb = 0;
+          if constexpr (Cfg::kScaled) {
+            tsfa = tmem_base + Cfg::kSfTmemBase + s * Cfg::kSfaCols;
+            tsfb = tmem_base + Cfg::kSfTmemBase + kStages * Cfg::kSfaCols + s * Cfg::kSfbCols;
+            const uint32_t sfa_addr = sf_base + s * Cfg::kSfBytes;
+            const uint32_t sfb_addr = sfa_addr + Cfg::kSfaAtoms * 512;
+            const int atoms = min(Cfg::kSfaAtoms, p.sf_k_atoms - kb * Cfg::kSfaAtoms);
+            for (int ka = 0; ka < atoms; ++ka) {
+              tmem_cp_sf_atom(tsfa + ka * 4, make_smem_desc(sfa_addr + ka * 512, 128, 128, kSwizzleNone));
+#pragma unroll
+              for (int j = 0; j < BN / 128; ++j)
+                tmem_cp_sf_atom(tsfb + ka * (BN / 128) * 4 + j * 4,
+                                make_smem_desc(sfb_addr + (j * Cfg::kSfaAtoms + ka) * 512, 128, 128, kSwizzleNone));
+            }
+          }
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            if (kk < n_mma) {
+              const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
+              // K-major: 32 bytes of K per MMA inside the 128-byte swizzle atom.
+              // MN-major B: kMmaK rows of 128 bytes per MMA.
+              const uint64_t a_d = a_desc + static_cast<uint64_t>(kk * 2);
+              const uint64_t b_d = b_desc + static_cast<uint64_t>(B_MN ? kk * (Cfg::kMmaK * 128 / 16) : kk * 2);
+              if constexpr (KIND == kKindMXF8) {
+                // one scale byte per 32-element block: block kk of this stage
+                umma_block_scaled<KIND>(tmem_acc, a_d, b_d, p.idesc | (uint32_t(kk) << 29) | (uint32_t(kk) << 4),
+                                        acc, tsfa, tsfb);
+              } else if constexpr (KIND == kKindNVF4) {
+                // four scale bytes per MMA: atom kk of this stage
+                umma_block_scaled<KIND>(tmem_acc, a_d, b_d, p.idesc, acc, tsfa + kk * 4,
+                                        tsfb + kk * (BN / 128) * 4);
+              } else {
+                umma<KIND>(tmem_acc, a_d, b_d, p.idesc, acc);
+              }
+            }
+          }
+          tc_commit(empty_bar(s));
+        }
+        if (ok) tc_commit(acc_full_bar(as));
+        ++local_tile;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue ----------------
+    const int quarter = warp & 3;  // TMEM lanes [32 * quarter, 32 * quarter + 32)
+    float alpha = p.alpha;
+    if (p.alpha_a != nullptr) alpha *= *p.alpha_a;
+    if (p.alpha_b != nullptr) alpha *= *p.alpha_b;
+    const int elem_bytes = (OUT == kOutF32) ? 4 : 2;
+    const bool swiglu = p.epilogue == B200K_EPI_SWIGLU;
+    const int n_out = swiglu ? p.n / 2 : p.n;
+    const bool vec_ok = ((p.ldc * elem_bytes) % 16 == 0) && ((p.stride_c * elem_bytes) % 16 == 0) &&
+                        (reinterpret_cast<uintptr_t>(p.c) % 16 == 0);
+    uint32_t local_tile = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
+      if (p.tile_group != nullptr && p.tile_group[tc.pid_m] < 0) continue;
+      const int as = local_tile % Cfg::kNumAcc;
+      const uint32_t aph = (local_tile / Cfg::kNumAcc) & 1;
+      if (!mbar_wait(acc_full_bar(as), aph, abort_flag)) {
+        report_status(p.status, 3, as);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = tc.pid_m * kBM + quarter * 32 + lane;
+      int64_t out_row = row;
+      bool row_ok = row < p.m;
+      if (p.row_map != nullptr && row_ok) {
+        out_row = p.row_map[row];
+        row_ok = out_row >= 0 && out_row < p.c_rows;
+      }
+      float scale = alpha;
+      if (p.row_scale != nullptr && row_ok) scale *= p.row_scale[out_row];
+      uint8_t* c_row = static_cast<uint8_t*>(p.c) +
+                       (static_cast<int64_t>(p.tile_group ? 0 : tc.batch) * p.stride_c + out_row * p.ldc) * elem_bytes;
+      const uint32_t taddr = tmem_base + as * Cfg::kAccStride + (uint32_t(quarter * 32) << 16);
+      if (!swiglu) {
+        const int n0 = tc.pid_n * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (row_ok && n0 + c * 32 < p.n) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * scale;
+            store_row_chunk<OUT>(c_row, n0 + c * 32, p.n, v, vec_ok);
+          }
+        }
+      } else {
+        const int n0 = tc.pid_n * (BN / 2);
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, g);
+          tmem_ld_32x32b_x32(taddr + BN / 2 + c * 32, u);
+          tmem_ld_wait();
+          if (row_ok && n0 + c * 32 < n_out) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              v[i] = silu(__uint_as_float(g[i]) * scale) * (__uint_as_float(u[i]) * scale);
+            store_row_chunk<OUT>(c_row, n0 + c * 32, n_out, v, vec_ok);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(as));
+      ++local_tile;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+namespace {
+
+template <int KIND, int BN, bool B_MN, int OUT>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+           cudaStream_t stream) {
+  using Cfg = GemmCfg<KIND, BN, B_MN>;
+  auto kernel = gemm_kernel<KIND, BN, B_MN, OUT>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if (e != cudaSuccess)
+      return fail(B200K_CUDA_ERROR, "cudaFuncSetAttribute(%d bytes): %s", Cfg::kSmemBytes,
+                  cudaGetErrorString(e));
+    configured[dev] = true;
+  }
+  kernel<<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  B200K_CHECK_LAUNCH("gemm launch");
+  return B200K_OK;
+}
+
+template <int KIND, int BN, bool B_MN>
+int launch_out(int out, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+               int grid, cudaStream_t stream) {
+  switch (out) {
+    case B200K_F16: return launch<KIND, BN, B_MN, kOutF16>(ta, tb, p, grid, stream);
+    case B200K_BF16: return launch<KIND, BN, B_MN, kOutBF16>(ta, tb, p, grid, stream);
+    case B200K_F32: return launch<KIND, BN, B_MN, kOutF32>(ta, tb, p, grid, stream);
+    default: return fail(B200K_INVALID_ARG, "unsupported output dtype %d", out);
+  }
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+}  // namespace b200k
+
+using namespace b200k;
+
+extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
+  if (a == nullptr) return fail(B200K_INVALID_ARG, "null args");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a->m < 0 || a->n < 0 || a->k < 0 || a->batch < 0)
+    return fail(B200K_INVALID_ARG, "negative dimension");
+  if (a->m == 0 || a->n == 0 || a->batch == 0) return B200K_OK;
+  if (a->a == nullptr || a->b == nullptr || a->c == nullptr)
+    return fail(B200K_INVALID_ARG, "null operand pointer");
+  if (a->k == 0) return fail(B200K_UNSUPPORTED, "K == 0 is not supported (C would be all zeros)");
+
+  int kind, elem_bytes;
+  uint32_t fmt;
+  CUtensorMapDataType tdt;
+  switch (a->ab_dtype) {
+    case B200K_F16: kind = kKindF16; elem_bytes = 2; fmt = kFmtF16; tdt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
+    case B200K_BF16: kind = kKindF16; elem_bytes = 2; fmt = kFmtBF16; tdt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; break;
+    case B200K_F32: kind = kKindTF32; elem_bytes = 4; fmt = kFmtTF32; tdt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; break;
+    case B200K_E4M3: kind = kKindF8; elem_bytes = 1; fmt = kFmtE4M3; tdt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+    case B200K_E5M2: kind = kKindF8; elem_bytes = 1; fmt = kFmtE5M2; tdt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+    default: return fail(B200K_INVALID_ARG, "unsupported operand dtype %d", a->ab_dtype);
+  }
+  const bool b_mn = a->b_layout == B200K_B_KN;
+  if (a->epilogue == B200K_EPI_SWIGLU && (b_mn || a->n % 256 != 0))
+    return fail(B200K_UNSUPPORTED, "SwiGLU epilogue needs B stored (N, K) and N a multiple of 256");
+  if ((a->lda * elem_bytes) % 16 || (a->ldb * elem_bytes) % 16 || !aligned16(a->a) || !aligned16(a->b))
+    return fail(B200K_UNSUPPORTED,
+                "operand rows must start on 16-byte boundaries (lda %lld, ldb %lld, %d-byte elements)",
+                (long long)a->lda, (long long)a->ldb, elem_bytes);
+  if (a->batch > 1 && ((a->stride_a * elem_bytes) % 16 || (a->stride_b * elem_bytes) % 16))
+    return fail(B200K_UNSUPPORTED, "batch strides must be multiples of 16 bytes");
+  if (a->m > INT32_MAX || a->n > INT32_MAX || a->k > INT32_MAX)
+    return fail(B200K_UNSUPPORTED, "dimension exceeds 2^31 - 1");
+
+  constexpr int BN = 256;
+  const int bk = 128 / elem_bytes;
+  GemmParams p = {};
+  p.c = a->c;
+  p.m = static_cast<int>(a->m);
+  p.n = static_cast<int>(a->n);
+  p.k = static_cast<int>(a->k);
+  p.batch = static_cast<int>(a->batch);
+  p.ldc = a->ldc;
+  p.stride_c = a->stride_c;
+  p.tiles_m = static_cast<int>(ceil_div(a->m, kBM));
+  p.tiles_n = static_cast<int>(ceil_div(a->n, BN));
+  p.k_iters = static_cast<int>(ceil_div(a->k, bk));
+  {
+    int rem = static_cast<int>(a->k - static_cast<int64_t>(p.k_iters - 1) * bk);
+    p.k_tail_mmas = static_cast<int>(ceil_div(rem, bk / 4));
+  }
+  p.idesc = make_idesc(fmt, fmt, false, b_mn, kBM, BN);
+  p.alpha = a->alpha;
+  p.tile_group = a->tile_group;
+  p.num_row_tiles = a->num_row_tiles;
+  p.row_map = a->row_map;
+  p.row_scale = a->row_scale;
+  p.c_rows = a->row_map ? a->c_rows : a->m;
+  p.epilogue = a->epilogue;
+  p.status = device_status_word();
+  const bool grouped = a->tile_group != nullptr;
+  if (grouped) p.batch = 1;
+
+  CUtensorMap ta, tb;
+  const uint64_t a_batches = grouped ? 1 : a->batch;
+  const uint64_t sa = (a_batches > 1 ? a->stride_a : a->m * a->lda) * elem_bytes;
+  if (!encode_tmap_3d(&ta, tdt, a->a, a->k, a->m, a_batches, a->lda * elem_bytes, sa, bk, kBM, 1,
+                      CU_TENSOR_MAP_SWIZZLE_128B))
+    return B200K_INVALID_ARG;
+  const uint64_t b_batches = a->batch;
+  if (b_mn) {
+    const uint64_t sb = (b_batches > 1 ? a->stride_b : a->k * a->ldb) * elem_bytes;
+    if (!encode_tmap_3d(&tb, tdt, a->b, a->n, a->k, b_batches, a->ldb * elem_bytes, sb, bk, bk, 1,
+                        CU_TENSOR_MAP_SWIZZLE_128B))
+      return B200K_INVALID_ARG;
+  } else {
+    const uint64_t sb = (b_batches > 1 ? a->stride_b : a->n * a->ldb) * elem_bytes;
+    if (!encode_tmap_3d(&tb, tdt, a->b, a->k, a->n, b_batches, a->ldb * elem_bytes, sb, bk, 128, 1,
+                        CU_TENSOR_MAP_SWIZZLE_128B))
+      return B200K_INVALID_ARG;
+  }
+
+  int sms = current_sm_count();
+  if (sms <= 0) return fail(B200K_CUDA_ERROR, "no current CUDA device");
+  int64_t total_tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n * p.batch;
+  int grid = static_cast<int>(total_tiles < sms ? total_tiles : sms);
+  if (a->max_ctas > 0 && grid > a->max_ctas) grid = a->max_ctas;
+
+  const int out = a->c_dtype;
+  if (kind == kKindF16)
+    return b_mn ? launch_out<kKindF16, BN, true>(out, ta, tb, p, grid, stream)
+                : launch_out<kKindF16, BN, false>(out, ta, tb, p, grid, stream);
+  if (kind == kKindTF32)
+    return b_mn ? launch_out<kKindTF32, BN, true>(out, ta, tb, p, grid, stream)
+                : launch_out<kKindTF32, BN, false>(out, ta, tb, p, grid, stream);
+  return b_mn ? launch_out<kKindF8, BN, true>(out, ta, tb, p, grid, stream)
+              : launch_out<kKindF8, BN, false>(out, ta, tb, p, grid, stream);
+}
+
+extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
+                                       b200k_stream stream_) {
+  if (a == nullptr) return fail(B200K_INVALID_ARG, "null args");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a->m < 0 || a->n < 0 || a->k < 0 || a->batch < 0)
+    return fail(B200K_INVALID_ARG, "negative dimension");
+  if (a->m == 0 || a->n == 0 || a->batch == 0) return B200K_OK;
+  if (!a->a || !a->b || !a->c || !a->sfa || !a->sfb)
+    return fail(B200K_INVALID_ARG, "null operand pointer");
+  if (a->k == 0) return fail(B200K_UNSUPPORTED, "K == 0 is not supported");
+
+  const bool fp4 = a->ab_dtype == B200K_E2M1X2;
+  if (!fp4 && a->ab_dtype != B200K_E4M3 && a->ab_dtype != B200K_E5M2)
+    return fail(B200K_INVALID_ARG, "block-scaled operands must be e4m3, e5m2 or e2m1x2 (got %d)",
+                a->ab_dtype);
+  const int sf_block = fp4 ? 16 : 32;
+  const int bk = fp4 ? 256 : 128;              // K elements per stage
+  const int64_t kbytes = fp4 ? a->k / 2 : a->k;
+  if (fp4 && (a->k % 2)) return fail(B200K_UNSUPPORTED, "fp4 K must be even");
+  const int64_t lda_b = fp4 ? a->lda / 2 : a->lda;
+  const int64_t ldb_b = fp4 ? a->ldb / 2 : a->ldb;
+  if (lda_b % 16 || ldb_b % 16 || !aligned16(a->a) || !aligned16(a->b) || !aligned16(a->sfa) ||
+      !aligned16(a->sfb))
+    return fail(B200K_UNSUPPORTED, "operand rows and scale tensors must start on 16-byte boundaries");
+  if (a->sf_k_atoms < ceil_div(a->k, 4 * sf_block))
+    return fail(B200K_INVALID_ARG, "sf_k_atoms %lld too small for K %lld", (long long)a->sf_k_atoms,
+                (long long)a->k);
+  if (a->epilogue == B200K_EPI_SWIGLU && a->n % 256 != 0)
+    return fail(B200K_UNSUPPORTED, "SwiGLU epilogue needs N a multiple of 256");
+  if (a->m > INT32_MAX || a->n > INT32_MAX || a->k > INT32_MAX)
+    return fail(B200K_UNSUPPORTED, "dimension exceeds 2^31 - 1");
+
+  constexpr int BN = 256;
+  GemmParams p = {};
+  p.c = a->c;
+  p.m = static_cast<int>(a->m);
+  p.n = static_cast<int>(a->n);
+  p.k = static_cast<int>(a->k);
+  p.batch = static_cast<int>(a->batch);
+  p.ldc = a->ldc;
+  p.stride_c = a->stride_c;
+  p.tiles_m = static_cast<int>(ceil_div(a->m, kBM));
+  p.tiles_n = static_cast<int>(ceil_div(a->n, BN));
+  p.k_iters = static_cast<int>(ceil_div(a->k, bk));
+  {
+    int rem = static_cast<int>(a->k - static_cast<int64_t>(p.k_iters - 1) * bk);
+    p.k_tail_mmas = static_cast<int>(ceil_div(rem, bk / 4));
+  }
+  const uint32_t fmt = fp4 ? kFmtE2M1_MXF4 : (a->ab_dtype == B200K_E4M3 ? kFmtE4M3 : kFmtE5M2);
+  p.idesc = make_idesc_block_scaled(fmt, fmt, kBM, BN, /*ue8m0=*/!fp4, 0, 0);
+  p.alpha = a->alpha;
+  p.alpha_a = a->alpha_a;
+  p.alpha_b = a->alpha_b;
+  p.sfa = static_cast<const uint8_t*>(a->sfa);
+  p.sfb = static_cast<const uint8_t*>(a->sfb);
+  p.sf_k_atoms = static_cast<int>(a->sf_k_atoms);
+  p.sfb_row_tiles = static_cast<int>(ceil_div(a->n, 128));
+  p.stride_sfa = a->stride_sfa;
+  p.stride_sfb = a->stride_sfb;
+  p.tile_group = a->tile_group;
+  p.num_row_tiles = a->num_row_tiles;
+  p.row_map = a->row_map;
+  p.row_scale = a->row_scale;
+  p.c_rows = a->row_map ? a->c_rows : a->m;
+  p.epilogue = a->epilogue;
+  p.status = device_status_word();
+  const bool grouped = a->tile_group != nullptr;
+  if (grouped) p.batch = 1;
+
+  CUtensorMap ta, tb;
+  const uint64_t a_batches = grouped ? 1 : a->batch;
+  const uint64_t sa = a_batches > 1 ? (fp4 ? a->stride_a / 2 : a->stride_a) : a->m * lda_b;
+  const uint64_t sb = a->batch > 1 ? (fp4 ? a->stride_b / 2 : a->stride_b) : a->n * ldb_b;
+  if (!encode_tmap_3d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, kbytes, a->m, a_batches, lda_b, sa,
+                      128, kBM, 1, CU_TENSOR_MAP_SWIZZLE_128B))
+    return B200K_INVALID_ARG;
+  if (!encode_tmap_3d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b, kbytes, a->n, a->batch, ldb_b, sb,
+                      128, 128, 1, CU_TENSOR_MAP_SWIZZLE_128B))
+    return B200K_INVALID_ARG;
+
+  int sms = current_sm_count();
+  if (sms <= 0) return fail(B200K_CUDA_ERROR, "no current CUDA device");
+  int64_t total_tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n * p.batch;
+  int grid = static_cast<int>(total_tiles < sms ? total_tiles : sms);
+  if (a->max_ctas > 0 && grid > a->max_ctas) grid = a->max_ctas;
+
+  if (fp4) return launch_out<kKindNVF4, BN, false>(a->c_dtype, ta, tb, p, grid, stream);
+  return launch_out<kKindMXF8, BN, false>(a->c_dtype, ta, tb, p, grid, stream);
+}

@@ -1,0 +1,346 @@
+// Block quantisers and the scale-factor relayout that sit either side of the
+// block-scaled GEMM.  All three are HBM-bound byte shuffles: one pass over the input,
+// 16-byte vector loads and stores, no shared-memory staging needed.
+//
+//   mxfp8_quantize : x (rows, K) f32|bf16|f16 -> e4m3 bytes + one ue8m0 scale per 32
+//                    elements, bit-for-bit the result of the reference's
+//                    block_quantize(x.float(), 32) (test/kernels/kernel_utils.py:38-80)
+//   sf_swizzle     : logical (rows, K/block) scale bytes -> swizzle_32_4_4 atoms
+//                    (test/kernels/kernel_utils.py:83-98)
+//   nvfp4_quantize : x -> e2m1 pairs + one ue4m3 scale per 16 elements + one fp32
+//                    per-tensor scale (the reference has no such quantiser; the rule is
+//                    stated at b200k_nvfp4_quantize in include/b200k.h)
+#include <cuda_fp8.h>
+#include <cuda_fp4.h>
+
+#include "common.cuh"
+#include "host.h"
+
+namespace b200k {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+// Loads N consecutive elements (N * sizeof(T) a multiple of 16, address 16-byte aligned
+// when `vec` is true) and widens them to fp32.
+template <typename T, int N>
+__device__ __forceinline__ void load_block(const T* src, float (&v)[N], bool vec, int valid) {
+  if (vec && valid == N) {
+    constexpr int kPer = 16 / sizeof(T);
+    constexpr int kVecs = N / kPer;
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+    for (int i = 0; i < kVecs; ++i) {
+      uint4 q = s4[i];
+      const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) v[i * kPer + j] = to_f32<T>(e[j]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) v[i] = i < valid ? to_f32<T>(src[i]) : 0.0f;
+  }
+}
+
+__device__ __forceinline__ int64_t swizzled_sf_offset(int64_t row, int64_t kblk, int64_t k_atoms) {
+  return ((row >> 7) * k_atoms + (kblk >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 +
+         (kblk & 3);
+}
+
+// ceil(log2(q)) for q > 0 as the reference computes it in fp32:
+// ceil(float(log2(q))).  Away from powers of two this is the exponent of q plus one;
+// within a few ulps above a power of two the fp32 rounding of the logarithm decides,
+// which the double-precision logarithm rounded to fp32 reproduces.
+__device__ __forceinline__ int ceil_log2_f32(float q) {
+  const uint32_t bits = __float_as_uint(q);
+  int e = static_cast<int>((bits >> 23) & 0xff);
+  uint32_t man = bits & 0x7fffff;
+  if (e == 0) {  // subnormal: not reachable after the 1e-12 clamp, kept for completeness
+    return static_cast<int>(ceilf(static_cast<float>(log2(static_cast<double>(q)))));
+  }
+  e -= 127;
+  if (man == 0) return e;
+  if (man > 64) return e + 1;
+  return static_cast<int>(ceilf(static_cast<float>(log2(static_cast<double>(q)))));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+mxfp8_quantize_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t ldx,
+                      uint8_t* __restrict__ q, int64_t ldq, uint8_t* __restrict__ sf_logical,
+                      uint8_t* __restrict__ sf_swizzled, int64_t k_atoms, int fmt_e5m2) {
+  const int64_t kblocks = (k + 31) >> 5;
+  const int64_t total = rows * kblocks;
+  const bool vec_in = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && ((ldx * sizeof(T)) % 16 == 0);
+  const bool vec_out = (reinterpret_cast<uintptr_t>(q) % 16 == 0) && (ldq % 16 == 0);
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = idx / kblocks;
+    const int64_t kb = idx - row * kblocks;
+    const int valid = static_cast<int>(k - kb * 32 < 32 ? k - kb * 32 : 32);
+    float v[32];
+    load_block<T, 32>(x + row * ldx + kb * 32, v, vec_in, valid);
+    float amax = 0.0f;
+    bool has_nan = false;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      amax = fmaxf(amax, fabsf(v[i]));
+      has_nan |= (v[i] != v[i]);
+    }
+    uint8_t sf_byte;
+    float inv_scale;
+    if (has_nan || amax == __int_as_float(0x7f800000)) {
+      sf_byte = 0xff;  // the reference propagates NaN / inf into the scale
+      inv_scale = __int_as_float(0x7fc00000);
+    } else {
+      float s = __fdiv_rn(amax, 448.0f);
+      s = fmaxf(s, 1e-12f);
+      const int e = ceil_log2_f32(s);
+      sf_byte = static_cast<uint8_t>(e + 127);
+      // 2^-e, exact: e is in [-39, 120]
+      inv_scale = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+      if (127 - e <= 0) inv_scale = ldexpf(1.0f, -e);
+    }
+    uint32_t packed[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      uint32_t w = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float y = v[4 * i + j] * inv_scale;
+        const uint8_t b = fmt_e5m2 ? __nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E5M2)
+                                   : __nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3);
+        w |= static_cast<uint32_t>(b) << (8 * j);
+      }
+      packed[i] = w;
+    }
+    uint8_t* dst = q + row * ldq + kb * 32;
+    if (vec_out && valid == 32) {
+      reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    } else {
+      for (int i = 0; i < valid; ++i) dst[i] = (packed[i >> 2] >> (8 * (i & 3))) & 0xff;
+    }
+    if (sf_logical != nullptr) sf_logical[row * kblocks + kb] = sf_byte;
+    if (sf_swizzled != nullptr) sf_swizzled[swizzled_sf_offset(row, kb, k_atoms)] = sf_byte;
+  }
+}
+
+// One thread per 16 output bytes of the swizzled tensor (one row of an atom).
+__global__ void __launch_bounds__(256)
+sf_swizzle_kernel(const uint8_t* __restrict__ src, int64_t rows, int64_t kblocks, int64_t ld,
+                  uint8_t* __restrict__ dst, int64_t row_tiles, int64_t k_atoms, int fill) {
+  const int64_t total = row_tiles * k_atoms * 32;
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r32 = idx & 31;
+    const int64_t atom = idx >> 5;
+    const int64_t ka = atom % k_atoms;
+    const int64_t rt = atom / k_atoms;
+    uint32_t w[4];
+#pragma unroll
+    for (int m2 = 0; m2 < 4; ++m2) {
+      const int64_t row = rt * 128 + m2 * 32 + r32;
+      uint32_t word = 0;
+#pragma unroll
+      for (int k1 = 0; k1 < 4; ++k1) {
+        const int64_t kb = ka * 4 + k1;
+        uint32_t b = (row < rows && kb < kblocks) ? src[row * ld + kb] : static_cast<uint32_t>(fill);
+        word |= b << (8 * k1);
+      }
+      w[m2] = word;
+    }
+    reinterpret_cast<uint4*>(dst)[idx] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// ---- NVFP4 ----------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+absmax_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t ldx,
+              uint32_t* __restrict__ amax_bits) {
+  float m = 0.0f;
+  const int64_t total = rows * k;
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = idx / k;
+    const int64_t col = idx - row * k;
+    m = fmaxf(m, fabsf(to_f32<T>(x[row * ldx + col])));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  __shared__ float part[8];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) m = fmaxf(m, part[i]);
+    // non-negative floats order like their bit patterns
+    atomicMax(amax_bits, __float_as_uint(m));
+  }
+}
+
+__device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(b, __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+nvfp4_quantize_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t ldx,
+                      uint8_t* __restrict__ q, int64_t ldq_bytes, uint8_t* __restrict__ sf_logical,
+                      uint8_t* __restrict__ sf_swizzled, int64_t k_atoms,
+                      const uint32_t* __restrict__ amax_bits, float* __restrict__ tensor_scale) {
+  const float amax_t = __uint_as_float(*amax_bits);
+  const float s_t = __fdiv_rn(amax_t, 2688.0f);  // 448 * 6
+  if (blockIdx.x == 0 && threadIdx.x == 0 && tensor_scale != nullptr) *tensor_scale = s_t;
+  const float six_st = __fmul_rn(6.0f, s_t);
+  const int64_t kblocks = (k + 15) >> 4;
+  const int64_t total = rows * kblocks;
+  const bool vec_in = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && ((ldx * sizeof(T)) % 16 == 0);
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = idx / kblocks;
+    const int64_t kb = idx - row * kblocks;
+    const int valid = static_cast<int>(k - kb * 16 < 16 ? k - kb * 16 : 16);
+    float v[16];
+    load_block<T, 16>(x + row * ldx + kb * 16, v, vec_in, valid);
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    uint8_t sf_byte = 0;
+    float denom = 0.0f;
+    if (amax > 0.0f && six_st > 0.0f) {
+      const float r = __fdiv_rn(amax, six_st);
+      sf_byte = __nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
+      denom = __fmul_rn(e4m3_to_f32(sf_byte), s_t);
+    }
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float a = 0.0f, b = 0.0f;
+      if (denom > 0.0f) {
+        a = __fdiv_rn(v[2 * i], denom);
+        b = __fdiv_rn(v[2 * i + 1], denom);
+      }
+      // low nibble = even element
+      const uint32_t byte = __nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest);
+      if (i < 4) lo |= (byte & 0xff) << (8 * i);
+      else hi |= (byte & 0xff) << (8 * (i - 4));
+    }
+    uint8_t* dst = q + row * ldq_bytes + kb * 8;
+    if (valid == 16 && (reinterpret_cast<uintptr_t>(dst) % 8 == 0)) {
+      *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+    } else {
+      for (int i = 0; i < (valid + 1) / 2; ++i)
+        dst[i] = ((i < 4 ? lo >> (8 * i) : hi >> (8 * (i - 4))) & 0xff);
+    }
+    if (sf_logical != nullptr) sf_logical[row * kblocks + kb] = sf_byte;
+    if (sf_swizzled != nullptr) sf_swizzled[swizzled_sf_offset(row, kb, k_atoms)] = sf_byte;
+  }
+}
+
+int grid_for(int64_t work_items, int threads) {
+  int sms = current_sm_count();
+  if (sms <= 0) sms = 148;
+  int64_t blocks = ceil_div(work_items, threads);
+  int64_t cap = static_cast<int64_t>(sms) * 8;
+  return static_cast<int>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+}  // namespace
+}  // namespace b200k
+
+using namespace b200k;
+
+extern "C" int b200k_mxfp8_quantize(const b200k_quantize_args* a, b200k_stream stream_) {
+  if (a == nullptr) return fail(B200K_INVALID_ARG, "null args");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a->rows < 0 || a->k < 0) return fail(B200K_INVALID_ARG, "negative dimension");
+  if (a->rows == 0 || a->k == 0) return B200K_OK;
+  if (!a->x || !a->q) return fail(B200K_INVALID_ARG, "null pointer");
+  if (a->q_dtype != B200K_E4M3 && a->q_dtype != B200K_E5M2)
+    return fail(B200K_INVALID_ARG, "q_dtype must be e4m3 or e5m2");
+  if (a->sf_swizzled && (reinterpret_cast<uintptr_t>(a->sf_swizzled) % 16))
+    return fail(B200K_UNSUPPORTED, "swizzled scale tensor must be 16-byte aligned");
+  const int64_t kblocks = ceil_div(a->k, 32);
+  if (a->sf_swizzled && a->sf_k_atoms < ceil_div(kblocks, 4))
+    return fail(B200K_INVALID_ARG, "sf_k_atoms too small");
+  const int grid = grid_for(a->rows * kblocks, 256);
+  const int e5m2 = a->q_dtype == B200K_E5M2;
+  uint8_t* q = static_cast<uint8_t*>(a->q);
+  uint8_t* sl = static_cast<uint8_t*>(a->sf_logical);
+  uint8_t* ss = static_cast<uint8_t*>(a->sf_swizzled);
+  switch (a->x_dtype) {
+    case B200K_F32:
+      mxfp8_quantize_kernel<float><<<grid, 256, 0, stream>>>(
+          static_cast<const float*>(a->x), a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, e5m2);
+      break;
+    case B200K_BF16:
+      mxfp8_quantize_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+          static_cast<const __nv_bfloat16*>(a->x), a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, e5m2);
+      break;
+    case B200K_F16:
+      mxfp8_quantize_kernel<__half><<<grid, 256, 0, stream>>>(
+          static_cast<const __half*>(a->x), a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, e5m2);
+      break;
+    default:
+      return fail(B200K_INVALID_ARG, "x_dtype must be f32, bf16 or f16");
+  }
+  B200K_CHECK_LAUNCH("mxfp8_quantize launch");
+  return B200K_OK;
+}
+
+extern "C" int b200k_sf_swizzle(const void* sf, int64_t rows, int64_t kblocks, int64_t ld,
+                                void* out, int64_t k_atoms, int32_t fill, b200k_stream stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (rows < 0 || kblocks < 0) return fail(B200K_INVALID_ARG, "negative dimension");
+  if (rows == 0 || kblocks == 0) return B200K_OK;
+  if (!sf || !out) return fail(B200K_INVALID_ARG, "null pointer");
+  if (reinterpret_cast<uintptr_t>(out) % 16) return fail(B200K_UNSUPPORTED, "output must be 16-byte aligned");
+  if (k_atoms < ceil_div(kblocks, 4)) return fail(B200K_INVALID_ARG, "k_atoms too small");
+  const int64_t row_tiles = ceil_div(rows, 128);
+  const int grid = grid_for(row_tiles * k_atoms * 32, 256);
+  sf_swizzle_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(sf), rows, kblocks, ld,
+                                              static_cast<uint8_t*>(out), row_tiles, k_atoms, fill);
+  B200K_CHECK_LAUNCH("sf_swizzle launch");
+  return B200K_OK;
+}
+
+extern "C" int b200k_nvfp4_quantize(const b200k_quantize_args* a, b200k_stream stream_) {
+  if (a == nullptr) return fail(B200K_INVALID_ARG, "null args");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a->rows < 0 || a->k < 0) return fail(B200K_INVALID_ARG, "negative dimension");
+  if (a->rows == 0 || a->k == 0) return B200K_OK;
+  if (!a->x || !a->q || !a->scratch) return fail(B200K_INVALID_ARG, "null pointer");
+  if (a->k % 2) return fail(B200K_UNSUPPORTED, "K must be even (two e2m1 values per byte)");
+  const int64_t kblocks = ceil_div(a->k, 16);
+  if (a->sf_swizzled && a->sf_k_atoms < ceil_div(kblocks, 4))
+    return fail(B200K_INVALID_ARG, "sf_k_atoms too small");
+  uint32_t* amax = static_cast<uint32_t*>(a->scratch);
+  cudaError_t e = cudaMemsetAsync(amax, 0, sizeof(uint32_t), stream);
+  if (e != cudaSuccess) return fail(B200K_CUDA_ERROR, "memset: %s", cudaGetErrorString(e));
+  const int grid_r = grid_for(a->rows * a->k / 4, 256);
+  const int grid_q = grid_for(a->rows * kblocks, 256);
+  uint8_t* q = static_cast<uint8_t*>(a->q);
+  uint8_t* sl = static_cast<uint8_t*>(a->sf_logical);
+  uint8_t* ss = static_cast<uint8_t*>(a->sf_swizzled);
+#define B200K_NVFP4_CASE(T)                                                                       \
+  absmax_kernel<T><<<grid_r, 256, 0, stream>>>(static_cast<const T*>(a->x), a->rows, a->k, a->ldx, \
+                                               amax);                                             \
+  nvfp4_quantize_kernel<T><<<grid_q, 256, 0, stream>>>(static_cast<const T*>(a->x), a->rows, a->k, \
+                                                       a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms,  \
+                                                       amax, a->tensor_scale)
+  switch (a->x_dtype) {
+    case B200K_F32: B200K_NVFP4_CASE(float); break;
+    case B200K_BF16: B200K_NVFP4_CASE(__nv_bfloat16); break;
+    case B200K_F16: B200K_NVFP4_CASE(__half); break;
+    default: return fail(B200K_INVALID_ARG, "x_dtype must be f32, bf16 or f16");
+  }
+#undef B200K_NVFP4_CASE
+  B200K_CHECK_LAUNCH("nvfp4_quantize launch");
+  return B200K_OK;
+}

@@ -1,0 +1,178 @@
+/*
+ * b200k — C ABI of the B200 (sm_100a) dense-contraction kernels.
+ *
+ * This is the boundary a host program binds instead of the cuTile launch path
+ * `ct.launch(stream, grid, kernel, args)` (reference: cext/tile_kernel.cpp:4569-4577)
+ * for the kernels the reference's samples put first.  Every entry point
+ *   - takes plain pointers, sizes and enums (no torch / Python types),
+ *   - enqueues its work on the caller's stream and returns without synchronising,
+ *   - borrows all buffers (the caller owns inputs, outputs and workspaces and keeps
+ *     them alive until the stream has passed the call; array arguments must not alias),
+ *   - returns 0 or a negative b200k_status; b200k_last_error() gives the message.
+ *
+ * Device-side trouble (a pipeline wait that ran out of its time budget) is recorded
+ * in a per-device status word that b200k_device_status() reads after the caller has
+ * synchronised the stream.
+ */
+#ifndef B200K_H_
+#define B200K_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* b200k_stream;  /* a cudaStream_t */
+
+typedef enum {
+  B200K_OK = 0,
+  B200K_INVALID_ARG = -1,
+  B200K_UNSUPPORTED = -2,
+  B200K_CUDA_ERROR = -3,
+  B200K_TIMEOUT = -4
+} b200k_status;
+
+typedef enum {
+  B200K_F16 = 0,
+  B200K_BF16 = 1,
+  B200K_F32 = 2,   /* as a GEMM operand: multiplied as tf32 */
+  B200K_E4M3 = 3,
+  B200K_E5M2 = 4,
+  B200K_E2M1X2 = 5 /* two e2m1 values per byte, low nibble = even element */
+} b200k_dtype;
+
+typedef enum {
+  B200K_B_KN = 0, /* B is (K, N), N contiguous (row-major K x N) */
+  B200K_B_NK = 1  /* B is stored as (N, K), K contiguous (a transposed view) */
+} b200k_b_layout;
+
+typedef enum {
+  B200K_EPI_STORE = 0,  /* C = alpha * acc */
+  B200K_EPI_SWIGLU = 1  /* C[:, j] = silu(acc[:, j]) * acc[:, j + N/2]; C has N/2 columns */
+} b200k_epilogue;
+
+/* ---- library ---------------------------------------------------------- */
+const char* b200k_version(void);
+const char* b200k_last_error(void);             /* thread-local message of the last failure */
+int b200k_sm_count(void);                       /* SMs of the current device, <0 on error */
+/* Reads and clears the current device's status word.  *code is 0 or B200K_TIMEOUT,
+ * *info packs (role << 8 | detail << 16) of the wait that gave up. */
+int b200k_device_status(int* code, int* info);
+
+/* ---- dense GEMM -------------------------------------------------------
+ * C[b] = A[b] . B[b], fp32 accumulation, result rounded to c_dtype.
+ * Replaces matmul_kernel / persistent_matmul_kernel / batch_matmul_kernel
+ * (reference: test/kernels/matmul.py:32-100, 142-178, 181-253) behind
+ * cutile_matmul (samples/MatMul.py:179-251) and bmm (samples/BatchMatMul.py:53-92).
+ * With `tile_group` set it is the grouped (MoE) GEMM of fused_moe_kernel
+ * (test/kernels/fused_moe.py:14-82) over an expert-sorted, tile-padded row list. */
+typedef struct {
+  const void* a;      /* (batch, M, K), K contiguous */
+  const void* b;      /* per b_layout */
+  void* c;            /* (batch, M, N) row-major */
+  int64_t m, n, k, batch;
+  int64_t lda, ldb, ldc;                 /* leading dimensions in elements */
+  int64_t stride_a, stride_b, stride_c;  /* batch strides in elements */
+  int32_t ab_dtype;   /* B200K_F16 | BF16 | F32 | E4M3 | E5M2 */
+  int32_t c_dtype;    /* B200K_F16 | BF16 | F32 */
+  int32_t b_layout;   /* b200k_b_layout */
+  int32_t epilogue;   /* b200k_epilogue */
+  float alpha;        /* scalar applied to the accumulator */
+  int32_t max_ctas;   /* 0 = one CTA per SM (persistent) */
+  /* Grouped mode (all optional, NULL = off).  `tile_group[i]` is the B batch index
+   * (expert) of the i-th 128-row tile of A, or a negative value for a tile to skip;
+   * `num_row_tiles` points at the device-side count of row tiles in use. */
+  const int32_t* tile_group;
+  const int32_t* num_row_tiles;
+  /* Output row remap: row i of the product goes to row row_map[i] of C; rows whose
+   * target is outside [0, c_rows) are dropped (scatter semantics).  `row_scale[r]`
+   * multiplies target row r (fp32). */
+  const int32_t* row_map;
+  const float* row_scale;
+  int64_t c_rows;
+} b200k_gemm_args;
+
+int b200k_gemm(const b200k_gemm_args* args, b200k_stream stream);
+
+/* ---- block-scaled GEMM ------------------------------------------------
+ * C = alpha * (A (.) sA) . (B (.) sB), fp32 accumulation.  Replaces
+ * block_scaled_matmul_kernel / ct.mma_scaled (reference:
+ * test/kernels/scaled_matmul.py:12-114, src/cuda/tile/_stub.py:2198-2329) behind
+ * cutile_block_scaled_matmul (samples/BlockScaledMatMul.py:229-297).
+ *   MXFP8 : ab_dtype E4M3|E5M2, scales ue8m0, one per 32 elements of K
+ *   NVFP4 : ab_dtype E2M1X2,    scales ue4m3, one per 16 elements of K
+ * Both operands are K-contiguous: A is (M, K), B is stored (N, K).
+ * Scales use the swizzle_32_4_4 layout (reference: test/kernels/kernel_utils.py:83-98):
+ * [rows/128][sf_k_atoms][32][16] bytes with rows padded to 128 and sf_k_atoms =
+ * ceil(K / (4 * block)). */
+typedef struct {
+  const void* a;
+  const void* b;
+  const void* sfa;
+  const void* sfb;
+  void* c;
+  int64_t m, n, k, batch;
+  int64_t lda, ldb, ldc;                 /* in elements (e2m1: two per byte) */
+  int64_t stride_a, stride_b, stride_c;  /* batch strides in elements */
+  int64_t sf_k_atoms;                    /* atoms along K in sfa / sfb */
+  int64_t stride_sfa, stride_sfb;        /* batch strides of the scale tensors in bytes */
+  int32_t ab_dtype;
+  int32_t c_dtype;
+  int32_t epilogue;
+  float alpha;
+  const float* alpha_a;  /* optional device scalars multiplied into alpha */
+  const float* alpha_b;
+  int32_t max_ctas;
+  const int32_t* tile_group;
+  const int32_t* num_row_tiles;
+  const int32_t* row_map;
+  const float* row_scale;
+  int64_t c_rows;
+} b200k_block_scaled_gemm_args;
+
+int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* args, b200k_stream stream);
+
+/* ---- block quantisers --------------------------------------------------
+ * x is (rows, K) with row stride ldx (elements); q is (rows, K) with row stride ldq
+ * (bytes).  Scales are written to `sf_logical` ((rows, ceil(K/block)) bytes, dense)
+ * and/or to `sf_swizzled` (swizzle_32_4_4 atoms, [ceil(rows/128)][sf_k_atoms][32][16]);
+ * either may be NULL.  Padding bytes of the swizzled tensor are left untouched. */
+typedef struct {
+  const void* x;
+  void* q;
+  void* sf_logical;
+  void* sf_swizzled;
+  float* tensor_scale;   /* nvfp4 only: receives the fp32 per-tensor scale (device) */
+  void* scratch;         /* nvfp4 only: at least 4 bytes of device memory, 4-byte aligned */
+  int64_t rows, k;
+  int64_t ldx, ldq;
+  int64_t sf_k_atoms;
+  int32_t x_dtype;       /* B200K_F32 | BF16 | F16 */
+  int32_t q_dtype;       /* mxfp8: B200K_E4M3 | E5M2 */
+} b200k_quantize_args;
+
+/* MXFP8: replaces block_quantize(x, 32) (reference: test/kernels/kernel_utils.py:38-80)
+ * evaluated in fp32: scale = 2^ceil(log2(max(amax/448, 1e-12))), q = rn_e4m3(x/scale),
+ * scale byte = exponent + 127 (ue8m0). */
+int b200k_mxfp8_quantize(const b200k_quantize_args* args, b200k_stream stream);
+
+/* NVFP4 (no counterpart in the reference, which only consumes such operands through
+ * ct.mma_scaled, test/test_mma_scaled.py:149-183).  Rule, all in fp32 with IEEE
+ * round-to-nearest operations:
+ *   s_t   = amax(x) / 2688                      (448 * 6)
+ *   s_blk = rn_e4m3(amax_blk / (6 * s_t))       one per 16 elements, 0 for a zero block
+ *   q     = rn_e2m1(x / (f32(s_blk) * s_t))     ties to even, saturating at +-6
+ * x ~= q * s_blk * s_t.  Byte i of a row holds elements 2i (low nibble) and 2i+1. */
+int b200k_nvfp4_quantize(const b200k_quantize_args* args, b200k_stream stream);
+
+/* Logical (rows, kblocks) scale bytes (row stride ld) -> swizzle_32_4_4 atoms; replaces
+ * swizzle_32_4_4 (reference: test/kernels/kernel_utils.py:83-98).  Rows beyond `rows`
+ * and blocks beyond `kblocks` inside the padded atoms are set to `fill`. */
+int b200k_sf_swizzle(const void* sf, int64_t rows, int64_t kblocks, int64_t ld, void* out,
+                     int64_t k_atoms, int32_t fill, b200k_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200K_H_ */
