@@ -1,0 +1,504 @@
+"""Benchmark of the hot path on B200: TFLOPS of the block-scaled / dense contraction kernels.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload mxfp8_gemm|nvfp4_gemm|dense_f16]
+
+One step = one pass of the workload's kernel over one batch of seeded synthetic input.
+The default workload is BASELINE config 2: MXFP8 GEMM, M = N = K = 8192, e4m3 operands
+with ue8m0 scales per 32 elements of K, fp32 accumulation, bf16 output.  With N > 1 every
+rank runs the same problem on its own GPU (the GEMM does not shard: replicas only) and the
+value is the sum over ranks divided by the slowest rank's time.
+
+`--impl reference` times the reference's CPU ground truth for the same workload (the
+de-quantised fp32 matmul of samples/BlockScaledMatMul.py:359-361, restated in oracle/) on
+the host cores, on a bounded block of the output.
+
+Prints ONE JSON line (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "cutile-python_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch  # noqa: E402
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"bf16_tflops": float(d["bf16_tflops"]), "hbm_gbs": float(d["hbm_gbs"]),
+                "source": "measured"}
+    return {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------------------
+# Workloads
+# --------------------------------------------------------------------------------------
+class Workload:
+    name = ""
+    dtype = ""
+    tensor_rate_vs_bf16 = 1.0   # tensor-core rate of the operand format relative to bf16
+
+    def config(self):
+        raise NotImplementedError
+
+
+class Mxfp8Gemm(Workload):
+    """BASELINE config 2."""
+    name = "mxfp8_gemm_8192x8192x8192_bf16out"
+    dtype = "e4m3 x e4m3 (ue8m0 scale / 32) -> fp32 accumulate -> bf16"
+    tensor_rate_vs_bf16 = 2.0
+    M = N = K = 8192
+    seed = 1
+    sets = 2   # rotating operand/output sets, so that no step finds its inputs in L2
+    cpu_block_limit = 8192
+
+    def flops(self):
+        return 2.0 * self.M * self.N * self.K
+
+    def algorithmic_bytes(self):
+        ks = self.K // 32
+        return self.M * self.K + self.N * self.K + (self.M + self.N) * ks + 2 * self.M * self.N
+
+    def setup(self, device):
+        import b200k
+        g = torch.Generator(device=device).manual_seed(self.seed)
+        self.inputs = []
+        for i in range(self.sets):
+            a = torch.randn(self.M, self.K, device=device, generator=g).bfloat16()
+            b = torch.randn(self.N, self.K, device=device, generator=g).bfloat16()
+            aq, sa = b200k.block_quantize(a, 32, swizzled_scale=True)
+            bq, sb = b200k.block_quantize(b, 32, swizzled_scale=True)
+            c = torch.empty(self.M, self.N, device=device, dtype=torch.bfloat16)
+            self.inputs.append((aq, sa, bq, sb, c))
+            del a, b
+        self.b200k = b200k
+        self.i = 0
+
+    def step(self):
+        aq, sa, bq, sb, c = self.inputs[self.i % self.sets]
+        self.i += 1
+        self.b200k.cutile_block_scaled_matmul(aq, sa, bq.T, sb, C=c)
+        return c
+
+    launches_per_step = 1
+
+    # ---- end-to-end: host buffers in, host buffer out, through the public call
+    def setup_e2e(self, device):
+        aq, sa, bq, sb, c = self.inputs[0]
+        self.host_in = [t.cpu().pin_memory() for t in (aq, sa, bq, sb)]
+        self.host_out = torch.empty_like(c, device="cpu").pin_memory()
+        self.dev_in = [torch.empty_like(t) for t in (aq, sa, bq, sb)]
+        self.dev_out = torch.empty_like(c)
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host_in)
+        self.d2h = self.host_out.numel() * self.host_out.element_size()
+
+    def step_e2e(self):
+        for d, h in zip(self.dev_in, self.host_in):
+            d.copy_(h, non_blocking=True)
+        aq, sa, bq, sb = self.dev_in
+        self.b200k.cutile_block_scaled_matmul(aq, sa, bq.T, sb, C=self.dev_out)
+        self.host_out.copy_(self.dev_out, non_blocking=True)
+
+    # ---- CPU ground truth on an S x S block of the output
+    def cpu_setup(self):
+        import oracle
+        g = torch.Generator().manual_seed(self.seed)
+        s = self.cpu_block_limit
+        a = torch.randn(s, self.K, generator=g).bfloat16()
+        b = torch.randn(s, self.K, generator=g).bfloat16()
+        self.cpu_ops = oracle.block_quantize_ref(a) + oracle.block_quantize_ref(b)
+        self.oracle = oracle
+
+    def cpu_step(self, s):
+        aq, sa, bq, sb = self.cpu_ops
+        return self.oracle.block_scaled_matmul_ref(aq[:s], sa[:s], bq[:s], sb[:s])
+
+    def cpu_flops(self, s):
+        return 2.0 * s * s * self.K
+
+    def cpu_sample_desc(self, s):
+        return (f"{s}x{s} block of the {self.M}x{self.N} output, K={self.K}: de-quantise both "
+                f"operand blocks to fp32 and matmul (torch CPU)")
+
+    def config(self):
+        return {"workload": self.name, "M": self.M, "N": self.N, "K": self.K,
+                "scale_block": 32, "out": "bf16", "seed": self.seed,
+                "l2": f"{self.sets} rotating operand/output sets of "
+                      f"{self.algorithmic_bytes() / 2**20:.0f} MiB each (> 126 MiB L2)"}
+
+
+class Nvfp4Gemm(Mxfp8Gemm):
+    """BASELINE config 3 on one GPU (the per-rank problem of the AllGather GEMM)."""
+    name = "nvfp4_gemm_8192x28672x8192_bf16out"
+    dtype = "e2m1 x e2m1 (ue4m3 scale / 16, fp32 tensor scale) -> fp32 accumulate -> bf16"
+    tensor_rate_vs_bf16 = 4.0
+    M, N, K = 8192, 28672, 8192
+    seed = 2
+
+    def algorithmic_bytes(self):
+        return (self.M + self.N) * (self.K // 2 + self.K // 16) + 2 * self.M * self.N
+
+    def setup(self, device):
+        import b200k
+        g = torch.Generator(device=device).manual_seed(self.seed)
+        self.inputs = []
+        for i in range(self.sets):
+            a = torch.randn(self.M, self.K, device=device, generator=g).bfloat16()
+            b = (0.02 * torch.randn(self.N, self.K, device=device, generator=g)).bfloat16()
+            qa = b200k.nvfp4_quantize(a)
+            qb = b200k.nvfp4_quantize(b)
+            c = torch.empty(self.M, self.N, device=device, dtype=torch.bfloat16)
+            self.inputs.append((qa, qb, c))
+            del a, b
+        self.b200k = b200k
+        self.i = 0
+
+    def step(self):
+        qa, qb, c = self.inputs[self.i % self.sets]
+        self.i += 1
+        self.b200k.cutile_nvfp4_matmul(*qa, *qb, C=c)
+        return c
+
+    def setup_e2e(self, device):
+        qa, qb, c = self.inputs[0]
+        flat = list(qa) + list(qb)
+        self.host_in = [t.cpu().pin_memory() for t in flat]
+        self.host_out = torch.empty_like(c, device="cpu").pin_memory()
+        self.dev_in = [torch.empty_like(t) for t in flat]
+        self.dev_out = torch.empty_like(c)
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host_in)
+        self.d2h = self.host_out.numel() * self.host_out.element_size()
+
+    def step_e2e(self):
+        for d, h in zip(self.dev_in, self.host_in):
+            d.copy_(h, non_blocking=True)
+        self.b200k.cutile_nvfp4_matmul(*self.dev_in, C=self.dev_out)
+        self.host_out.copy_(self.dev_out, non_blocking=True)
+
+    def cpu_setup(self):
+        import oracle
+        g = torch.Generator().manual_seed(self.seed)
+        s = 2048
+        a = torch.randn(s, self.K, generator=g).bfloat16()
+        b = (0.02 * torch.randn(s, self.K, generator=g)).bfloat16()
+        self.cpu_ops = (oracle.nvfp4_quantize_ref(a), oracle.nvfp4_quantize_ref(b))
+        self.oracle = oracle
+
+    def cpu_step(self, s):
+        (aq, asf, ats), (bq, bsf, bts) = self.cpu_ops
+        return self.oracle.nvfp4_matmul_ref(aq[:s], asf[:s], ats, bq[:s], bsf[:s], bts)
+
+    def config(self):
+        c = super().config()
+        c["scale_block"] = 16
+        return c
+
+
+class DenseF16(Mxfp8Gemm):
+    """BASELINE config 1."""
+    name = "dense_f16_gemm_2048x2048x2048"
+    dtype = "f16 x f16 -> fp32 accumulate -> f16"
+    tensor_rate_vs_bf16 = 1.0
+    M = N = K = 2048
+    seed = 0
+    sets = 12   # 12 x 24 MiB > L2
+
+    def algorithmic_bytes(self):
+        return 2 * (self.M * self.K + self.K * self.N + self.M * self.N)
+
+    def setup(self, device):
+        import b200k
+        g = torch.Generator(device=device).manual_seed(self.seed)
+        self.inputs = []
+        for i in range(self.sets):
+            a = torch.randn(self.M, self.K, device=device, generator=g).half()
+            b = torch.randn(self.K, self.N, device=device, generator=g).half()
+            self.inputs.append((a, b, torch.empty(self.M, self.N, device=device, dtype=torch.float16)))
+        self.b200k = b200k
+        self.i = 0
+
+    def step(self):
+        a, b, c = self.inputs[self.i % self.sets]
+        self.i += 1
+        return self.b200k.cutile_matmul(a, b, C=c)
+
+    def setup_e2e(self, device):
+        a, b, c = self.inputs[0]
+        self.host_in = [t.cpu().pin_memory() for t in (a, b)]
+        self.host_out = torch.empty_like(c, device="cpu").pin_memory()
+        self.dev_in = [torch.empty_like(t) for t in (a, b)]
+        self.dev_out = torch.empty_like(c)
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host_in)
+        self.d2h = self.host_out.numel() * self.host_out.element_size()
+
+    def step_e2e(self):
+        for d, h in zip(self.dev_in, self.host_in):
+            d.copy_(h, non_blocking=True)
+        self.b200k.cutile_matmul(self.dev_in[0], self.dev_in[1], C=self.dev_out)
+        self.host_out.copy_(self.dev_out, non_blocking=True)
+
+    def cpu_setup(self):
+        import oracle
+        g = torch.Generator().manual_seed(self.seed)
+        self.cpu_ops = (torch.randn(self.M, self.K, generator=g).half(),
+                        torch.randn(self.K, self.N, generator=g).half())
+        self.oracle = oracle
+
+    def cpu_step(self, s):
+        a, b = self.cpu_ops
+        return self.oracle.matmul_ref(a[:s], b[:, :s])
+
+    def cpu_sample_desc(self, s):
+        return f"{s}x{s} block of the output, K={self.K}: A.float() @ B.float() (torch CPU)"
+
+    def config(self):
+        c = super().config()
+        c.pop("scale_block")
+        c["out"] = "f16"
+        return c
+
+
+WORKLOADS = {"mxfp8_gemm": Mxfp8Gemm, "nvfp4_gemm": Nvfp4Gemm, "dense_f16": DenseF16}
+
+
+# --------------------------------------------------------------------------------------
+# Clock sampling (read-only NVML queries during the timed region)
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {
+        0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap",
+        0x8: "hw_slowdown", 0x10: "sync_boost", 0x20: "sw_thermal_slowdown",
+        0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting",
+    }
+
+    def __init__(self, device):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(device).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception as e:  # pragma: no cover - depends on the box
+            self.err = repr(e)
+
+    def _run(self):
+        while not self._stop.is_set():
+            self.sample()
+            time.sleep(0.02)
+
+    def sample(self):
+        if not self.ok:
+            return
+        try:
+            self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+            mask = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+            for bit, name in self.REASONS.items():
+                if mask & bit and name != "gpu_idle":
+                    self.reasons.add(name)
+        except Exception:
+            pass
+
+    def start(self):
+        if self.ok:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.ok or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# --------------------------------------------------------------------------------------
+def time_cpu(w, steps, warmup, budget_s=120.0):
+    """Times the CPU ground truth on an S x S output block sized so the run fits the budget."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    w.cpu_setup()
+    probe = 256
+    t0 = time.perf_counter()
+    w.cpu_step(probe)
+    t_probe = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    w.cpu_step(probe)
+    t_probe = min(t_probe, time.perf_counter() - t0)
+    limit = len(w.cpu_ops[0][0]) if isinstance(w.cpu_ops[0], tuple) else w.cpu_ops[0].shape[0]
+    per_step = budget_s / max(1, steps + warmup)
+    # cost grows about quadratically with the block edge
+    s = int(probe * max(1.0, (per_step / max(t_probe, 1e-4)) ** 0.5))
+    s = max(256, min(limit, s // 128 * 128))
+    for _ in range(warmup):
+        w.cpu_step(s)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        w.cpu_step(s)
+    dt = (time.perf_counter() - t0) / steps
+    return dt, s
+
+
+def run_reference(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    dt, s = time_cpu(w, args.steps, args.warmup)
+    tflops = w.cpu_flops(s) / dt / 1e12
+    line = {
+        "impl": "reference", "metric": "tflops", "value": tflops, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 (de-quantised operands)", "data": "synthetic",
+        "config": w.config(),
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": w.cpu_sample_desc(s)},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, w):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    import b200k
+    w.setup(device)
+    for _ in range(max(3, args.warmup)):
+        w.step()
+    barrier()
+    sampler = ClockSampler(device)
+    sampler.start()
+    ev0 = torch.cuda.Event(enable_timing=True)
+    ev1 = torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        w.step()
+    ev1.record()
+    barrier()
+    sampler.sample()
+    sampler.stop()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    b200k.raise_on_device_error()
+
+    # end to end: pinned host buffers -> device -> kernel -> pinned host buffer
+    e2e_steps = max(3, min(args.steps, 10))
+    if args.kernel_only:
+        ms_e2e, w.h2d, w.d2h = float("nan"), 0, 0
+    else:
+        w.setup_e2e(device)
+        for _ in range(2):
+            w.step_e2e()
+        barrier()
+        ev0.record()
+        for _ in range(e2e_steps):
+            w.step_e2e()
+        ev1.record()
+        barrier()
+        ms_e2e = ev0.elapsed_time(ev1) / e2e_steps
+
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = t.tolist()
+
+    if rank == 0:
+        peaks = load_peaks()
+        flops = w.flops()
+        value = world * flops / (ms * 1e-3) / 1e12
+        per_gpu = flops / (ms * 1e-3) / 1e12
+        peak = peaks["bf16_tflops"] * w.tensor_rate_vs_bf16
+        line = {
+            "metric": "tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": w.dtype, "data": "synthetic", "config": w.config(),
+            "e2e": {"value": world * flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h,
+                    "ms_per_step": ms_e2e, "steps": e2e_steps},
+            "gpu_launches": args.steps * w.launches_per_step,
+            "clocks": sampler.summary(),
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
+                         "frac": per_gpu / peak,
+                         "peak_source": f"{peaks['source']} cuBLAS bf16 burst x "
+                                        f"{w.tensor_rate_vs_bf16:g} (tensor-core rate of the "
+                                        f"operand format relative to bf16)",
+                         "traffic": TRAFFIC_BYTES.get(w.name),
+                         "algorithmic_bytes": w.algorithmic_bytes()},
+        }
+        if args.kernel_only:
+            line["e2e"] = None
+        if world == 1 and not args.no_cpu_baseline and not args.kernel_only:
+            dt, s = time_cpu(w, 1, 1, budget_s=30.0)
+            line["cpu_baseline"] = {"value": w.cpu_flops(s) / dt / 1e12, "unit": "TFLOP/s",
+                                    "cores": torch.get_num_threads(), "kind": "port",
+                                    "sample": w.cpu_sample_desc(s)}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
+# ncu captures summarised under profiles/ (None until captured)
+TRAFFIC_BYTES: dict[str, float | None] = {}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="mxfp8_gemm")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the end-to-end and CPU legs (for profiler runs)")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]()
+    if args.impl == "reference":
+        run_reference(args, w)
+    else:
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+        run_ours(args, w)
+
+
+if __name__ == "__main__":
+    main()

@@ -18,10 +18,6 @@ import torch
 from . import _lib
 
 
-def _row_major_2d(t: torch.Tensor) -> bool:
-    return t.stride(-1) == 1
-
-
 def _aligned(t: torch.Tensor, ld: int) -> bool:
     return (ld * t.element_size()) % 16 == 0 and t.data_ptr() % 16 == 0
 
@@ -52,23 +48,25 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, alpha: float = 1
 
     # A must be K-contiguous
     if a3.stride(2) != 1 or not _aligned(a3, a3.stride(1)) or (nb > 1 and (a3.stride(0) * a3.element_size()) % 16):
-        a3 = _pad_last(a3.contiguous() if a3.stride(2) != 1 else a3)
-    # B: (K, N) N-contiguous, or a transposed view of an (N, K) K-contiguous tensor
-    if b3.stride(2) == 1 and (b3.stride(1) != 1 or n == 1):
-        layout = _lib.B_KN
-        ldb = b3.stride(1)
-        if not _aligned(b3, ldb) or (nb > 1 and (b3.stride(0) * b3.element_size()) % 16):
-            b3 = _pad_last(b3)
-            ldb = b3.stride(1)
-    elif b3.stride(1) == 1:
+        a3 = _pad_last(a3)
+    # B: (K, N) N-contiguous, or a transposed view of an (N, K) K-contiguous tensor.
+    # tf32 operands exist only K-contiguous on the tensor core, so an N-contiguous fp32 B
+    # is re-laid out once here.
+    def rows_ok(t):
+        return (t.stride(2) == 1 and _aligned(t, t.stride(1))
+                and (nb == 1 or (t.stride(0) * t.element_size()) % 16 == 0))
+
+    is_kn, is_nk = b3.stride(2) == 1, b3.stride(1) == 1
+    if b3.dtype == torch.float32 or (is_nk and (not is_kn or n == 1)):
         layout = _lib.B_NK
-        ldb = b3.stride(2)
-        if not _aligned(b3, ldb) or (nb > 1 and (b3.stride(0) * b3.element_size()) % 16):
-            b3 = _pad_last(b3.transpose(1, 2)).transpose(1, 2)
-            ldb = b3.stride(2)
+        bt = b3.transpose(1, 2)
+        if not rows_ok(bt):
+            bt = _pad_last(bt)
+        b3, ldb = bt, bt.stride(1)
     else:
-        b3 = _pad_last(b3.contiguous())
         layout = _lib.B_KN
+        if not rows_ok(b3):
+            b3 = _pad_last(b3)
         ldb = b3.stride(1)
     if c3.stride(2) != 1:
         raise ValueError("output must be row-major")
@@ -113,6 +111,8 @@ def cutile_matmul(A: torch.Tensor, B: torch.Tensor, persistent: bool = False,
         raise ValueError("cutile_matmul expects 2-D operands")
     m, n = A.shape[0], B.shape[1]
     if C is None:
+        if A.element_size() == 1:
+            raise TypeError("fp8 operands need an explicit fp16/bf16/fp32 output: pass C=")
         C = torch.empty((m, n), device=A.device, dtype=A.dtype)
     if m == 0 or n == 0:
         return C

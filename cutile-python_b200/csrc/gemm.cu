@@ -517,6 +517,10 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
     default: return fail(B200K_INVALID_ARG, "unsupported operand dtype %d", a->ab_dtype);
   }
   const bool b_mn = a->b_layout == B200K_B_KN;
+  if (b_mn && kind == kKindTF32)
+    return fail(B200K_UNSUPPORTED,
+                "fp32 (tf32) operands need B stored (N, K): the N-contiguous layout is only "
+                "available for 8- and 16-bit operands");
   if (a->epilogue == B200K_EPI_SWIGLU && (b_mn || a->n % 256 != 0))
     return fail(B200K_UNSUPPORTED, "SwiGLU epilogue needs B stored (N, K) and N a multiple of 256");
   if ((a->lda * elem_bytes) % 16 || (a->ldb * elem_bytes) % 16 || !aligned16(a->a) || !aligned16(a->b))
@@ -586,9 +590,7 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
   if (kind == kKindF16)
     return b_mn ? launch_out<kKindF16, BN, true>(out, ta, tb, p, grid, stream)
                 : launch_out<kKindF16, BN, false>(out, ta, tb, p, grid, stream);
-  if (kind == kKindTF32)
-    return b_mn ? launch_out<kKindTF32, BN, true>(out, ta, tb, p, grid, stream)
-                : launch_out<kKindTF32, BN, false>(out, ta, tb, p, grid, stream);
+  if (kind == kKindTF32) return launch_out<kKindTF32, BN, false>(out, ta, tb, p, grid, stream);
   return b_mn ? launch_out<kKindF8, BN, true>(out, ta, tb, p, grid, stream)
               : launch_out<kKindF8, BN, false>(out, ta, tb, p, grid, stream);
 }

@@ -1,0 +1,156 @@
+"""Parity of the block-scaled GEMMs (MXFP8, NVFP4) with the de-quantised fp32 oracle.
+
+Follows samples/BlockScaledMatMul.py:318-365 (512x512x768, logical and swizzled scales,
+atol 1e-4 / rtol 1e-3 on fp32 output), test/test_mma_scaled.py:94-183 (reference
+expression, fp4 nibble order, scale/block combinations), the docstring known answers of
+src/cuda/tile/_stub.py:2248-2328 and the non-uniform-exponent case of
+experimental/cuda-lang/test/examples/tk/test_mxfp8_b200_gemm.py:749-755.
+"""
+import numpy as np
+import pytest
+import torch
+
+import b200k
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _quantised_pair(m, n, k, seed, pattern=None):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(m, k, generator=g)
+    b = torch.randn(n, k, generator=g)
+    if pattern == "exponents":
+        kb = -(-k // 32)
+        ea = ((torch.arange(m)[:, None] + torch.arange(kb)[None, :]) % 5 - 2).float()
+        eb = ((3 * torch.arange(n)[:, None] + torch.arange(kb)[None, :]) % 7 - 3).float()
+        a = a * torch.exp2(ea).repeat_interleave(32, 1)[:, :k]
+        b = b * torch.exp2(eb).repeat_interleave(32, 1)[:, :k]
+    aq, sa = oracle.block_quantize_ref(a)
+    bq, sb = oracle.block_quantize_ref(b)
+    return aq, sa, bq, sb
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 512, 768), (128, 256, 128), (256, 512, 1024),
+                                   (200, 300, 160), (1, 8, 32), (640, 1280, 4096)])
+@pytest.mark.parametrize("pattern", [None, "exponents"])
+def test_mxfp8_logical_scales(m, n, k, pattern, device_ok):
+    aq, sa, bq, sb = _quantised_pair(m, n, k, 10 + m, pattern)
+    ref = oracle.block_scaled_matmul_ref(aq, sa, bq, sb)
+    c = b200k.cutile_block_scaled_matmul(aq.cuda(), sa.cuda(), bq.cuda().T, sb.cuda().T)
+    assert c.dtype == torch.float32 and c.shape == (m, n)
+    # products and scales are exact in fp32; only the summation order differs
+    torch.testing.assert_close(c.cpu(), ref, atol=1e-4 * float(ref.abs().max()), rtol=1e-3)
+
+
+def test_mxfp8_swizzled_scales_and_bench_form(device_ok):
+    m = n = 512
+    k = 768
+    aq, sa, bq, sb = _quantised_pair(m, n, k, 3)
+    ref = oracle.block_scaled_matmul_ref(aq, sa, bq, sb)
+    sa_sw = oracle.swizzle_32_4_4_ref(sa).cuda()
+    sb_sw = oracle.swizzle_32_4_4_ref(sb).cuda()
+    c = b200k.cutile_block_scaled_matmul(aq.cuda(), sa_sw, bq.cuda().T, sb_sw)
+    torch.testing.assert_close(c.cpu(), ref, atol=1e-4, rtol=1e-3)
+    out = torch.empty(m, n, dtype=torch.float32, device="cuda")
+    assert b200k.cutile_swizzled_scaled_matmul(aq.cuda(), sa_sw, bq.cuda().T, sb_sw, out) is out
+    torch.testing.assert_close(out.cpu(), ref, atol=1e-4, rtol=1e-3)
+
+
+def test_mxfp8_known_answers(device_ok):
+    # ones with every scale = 2: each 32-block contributes 2 * 2 * 32 = 128
+    for k, want in ((64, 256.0), (128, 512.0)):
+        a = torch.ones(128, k, device="cuda").to(torch.float8_e4m3fn)
+        s = torch.full((128, k // 32), 128, dtype=torch.uint8, device="cuda").view(torch.float8_e8m0fnu)
+        c = b200k.cutile_block_scaled_matmul(a, s, a.T, s.T)
+        assert torch.all(c == want)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
+def test_mxfp8_half_outputs(out_dtype, device_ok):
+    aq, sa, bq, sb = _quantised_pair(384, 512, 512, 5)
+    ref = oracle.block_scaled_matmul_ref(aq, sa, bq, sb)
+    c = b200k.cutile_block_scaled_matmul(aq.cuda(), sa.cuda(), bq.cuda().T, sb.cuda().T,
+                                         out_dtype=out_dtype)
+    torch.testing.assert_close(c.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+
+
+def test_mxfp8_e5m2(device_ok):
+    g = torch.Generator().manual_seed(8)
+    a = torch.randn(256, 256, generator=g)
+    b = torch.randn(256, 256, generator=g)
+    aq, sa = oracle.block_quantize_ref(a, 32, torch.float8_e5m2)
+    bq, sb = oracle.block_quantize_ref(b, 32, torch.float8_e5m2)
+    ref = oracle.block_scaled_matmul_ref(aq, sa, bq, sb)
+    c = b200k.cutile_block_scaled_matmul(aq.cuda(), sa.cuda(), bq.cuda().T, sb.cuda().T)
+    torch.testing.assert_close(c.cpu(), ref, atol=1e-3, rtol=1e-3)
+
+
+def test_mxfp8_validation():
+    a = torch.zeros(128, 64, device="cuda").to(torch.float8_e4m3fn)
+    s = torch.zeros(128, 2, dtype=torch.uint8, device="cuda").view(torch.float8_e8m0fnu)
+    with pytest.raises(ValueError, match="Incompatible matrices"):
+        b200k.cutile_block_scaled_matmul(a, s, torch.zeros(32, 8, device="cuda").to(torch.float8_e4m3fn), s.T)
+    with pytest.raises(ValueError, match="CUDA device"):
+        b200k.cutile_block_scaled_matmul(a.cpu(), s.cpu(), a.T.cpu(), s.T.cpu())
+
+
+def _t(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 256), (512, 512, 768), (200, 300, 320), (256, 256, 64),
+                                   (384, 1024, 2048)])
+def test_nvfp4_matmul(m, n, k, device_ok):
+    g = torch.Generator().manual_seed(m + k)
+    a = torch.randn(m, k, generator=g)
+    b = 0.02 * torch.randn(n, k, generator=g)
+    aq, asf, ats = oracle.nvfp4_quantize_ref(a)
+    bq, bsf, bts = oracle.nvfp4_quantize_ref(b)
+    ref = oracle.nvfp4_matmul_ref(aq, asf, ats, bq, bsf, bts)
+    asw = b200k.swizzle_32_4_4(_t(asf).view(torch.float8_e4m3fn))
+    bsw = b200k.swizzle_32_4_4(_t(bsf).view(torch.float8_e4m3fn))
+    c = b200k.cutile_nvfp4_matmul(_t(aq), asw, torch.tensor([float(ats)], device="cuda"),
+                                  _t(bq), bsw, torch.tensor([float(bts)], device="cuda"),
+                                  out_dtype=torch.float32)
+    # against the de-quantised operands the kernel is exact up to fp32 summation order
+    torch.testing.assert_close(c.cpu(), ref, atol=1e-4 * float(ref.abs().max()), rtol=1e-3)
+    # against the unquantised product: BASELINE's 5e-2 bound is on bf16 outputs of the
+    # quantised pipeline; fp4 quantisation noise itself is ~13 % per operand pair
+    assert oracle.rel_frobenius(c, a @ b.T) < 0.2
+
+
+def test_nvfp4_end_to_end_bf16(device_ok):
+    g = torch.Generator().manual_seed(2)
+    a = torch.randn(256, 1024, generator=g).bfloat16()
+    b = (0.02 * torch.randn(512, 1024, generator=g)).bfloat16()
+    aq, asf, ats = b200k.nvfp4_quantize(a.cuda())
+    bq, bsf, bts = b200k.nvfp4_quantize(b.cuda())
+    c = b200k.cutile_nvfp4_matmul(aq, asf, ats, bq, bsf, bts)
+    assert c.dtype == torch.bfloat16
+    qa = oracle.nvfp4_quantize_ref(a)
+    qb = oracle.nvfp4_quantize_ref(b)
+    ref = oracle.nvfp4_matmul_ref(*qa, *qb)
+    assert oracle.rel_frobenius(c, ref) < 5e-2
+    torch.testing.assert_close(c.float().cpu(), ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2)
+
+
+def test_mxfp8_sampled_rows_at_full_size(device_ok):
+    # BASELINE config 2 (8192^3, bf16 out): sampled rows against the oracle and a
+    # row-sum identity over the whole output
+    n = 8192
+    g = torch.Generator(device="cuda").manual_seed(1)
+    a = torch.randn(n, n, device="cuda", generator=g).bfloat16()
+    b = torch.randn(n, n, device="cuda", generator=g).bfloat16()
+    aq, sa = b200k.block_quantize(a, 32)
+    bq, sb = b200k.block_quantize(b, 32)
+    c = b200k.cutile_block_scaled_matmul(aq, sa, bq.T, sb.T, out_dtype=torch.bfloat16)
+    rows = torch.tensor([0, 1, 127, 128, 4097, 8191])
+    ref = oracle.block_scaled_matmul_ref(aq[rows].cpu(), sa[rows].cpu(), bq.cpu(), sb.cpu())
+    torch.testing.assert_close(c[rows].float().cpu(), ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2)
+    # sum_j C[i, j] == A_deq[i, :] . (sum_j B_deq[j, :])
+    bsum = (bq.float() * torch.exp2(sb.view(torch.uint8).float() - 127).repeat_interleave(32, 1)).sum(0)
+    adeq = aq.float() * torch.exp2(sa.view(torch.uint8).float() - 127).repeat_interleave(32, 1)
+    want = adeq @ bsum
+    got = c.float().sum(1)
+    torch.testing.assert_close(got, want, atol=0.02 * float(want.abs().max()), rtol=2e-2)

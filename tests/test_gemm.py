@@ -1,0 +1,124 @@
+"""Parity of the dense tcgen05 GEMM (through the C ABI) with the fp32 CPU oracle.
+
+Shapes and tolerances follow the reference: samples/MatMul.py:268-330 (512x512x768 and the
+ragged 1000x500x700), samples/BatchMatMul.py:128-163, test/test_mma.py:46-59 (per-dtype
+tolerances), and the all-ones known answers of src/cuda/tile/_stub.py:2171-2193.
+"""
+import pytest
+import torch
+
+import b200k
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+# |err| <= atol + rtol * |ref|, fp32 accumulation over K <= 2048 of N(0,1) products
+TOL = {
+    torch.float16: dict(atol=2e-2, rtol=2e-2),
+    torch.bfloat16: dict(atol=2e-2, rtol=2e-2),
+    torch.float32: dict(atol=5e-2, rtol=1e-2),   # multiplied as tf32
+}
+
+
+def _rand(shape, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("m,n,k", [(512, 512, 768), (1000, 500, 700), (128, 256, 64), (1, 1, 8),
+                                   (130, 264, 72), (2048, 2048, 2048)])
+def test_cutile_matmul_row_major_b(dtype, m, n, k, device_ok):
+    a = _rand((m, k), dtype, 0)
+    b = _rand((k, n), dtype, 1)
+    c = b200k.cutile_matmul(a.cuda(), b.cuda())
+    assert c.shape == (m, n) and c.dtype == dtype
+    torch.testing.assert_close(c.float().cpu(), oracle.matmul_ref(a, b), **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_cutile_matmul_transposed_b_view(dtype, device_ok):
+    a = _rand((300, 520), dtype, 2)
+    b_nk = _rand((260, 520), dtype, 3)
+    c = b200k.cutile_matmul(a.cuda(), b_nk.cuda().T, persistent=True)
+    torch.testing.assert_close(c.float().cpu(), oracle.matmul_ref(a, b_nk.T), **TOL[dtype])
+
+
+def test_all_ones_known_answer(device_ok):
+    # mma of all-ones tiles: every output equals K
+    a = torch.ones(128, 448, dtype=torch.float16, device="cuda")
+    b = torch.ones(448, 256, dtype=torch.float16, device="cuda")
+    assert torch.all(b200k.cutile_matmul(a, b) == 448.0)
+
+
+def test_one_hot_rows_pick_columns(device_ok):
+    # A one-hot in K selects rows of B exactly: catches any operand-layout mix-up
+    k, n = 192, 320
+    idx = torch.arange(256) % k
+    a = torch.nn.functional.one_hot(idx, k).to(torch.float16)
+    b = _rand((k, n), torch.float16, 4)
+    c = b200k.cutile_matmul(a.cuda(), b.cuda())
+    assert torch.equal(c.cpu(), b[idx])
+
+
+def test_unaligned_leading_dimensions_are_repacked(device_ok):
+    a = _rand((64, 100), torch.float16, 5)     # 200-byte rows
+    b = _rand((100, 36), torch.float16, 6)     # 72-byte rows
+    c = b200k.cutile_matmul(a.cuda(), b.cuda())
+    torch.testing.assert_close(c.float().cpu(), oracle.matmul_ref(a, b), **TOL[torch.float16])
+
+
+def test_empty_and_zero_k():
+    a = torch.zeros(0, 64, dtype=torch.float16, device="cuda")
+    b = torch.zeros(64, 32, dtype=torch.float16, device="cuda")
+    assert b200k.cutile_matmul(a, b).shape == (0, 32)
+    a = torch.zeros(16, 0, dtype=torch.float16, device="cuda")
+    b = torch.zeros(0, 32, dtype=torch.float16, device="cuda")
+    assert torch.all(b200k.cutile_matmul(a, b) == 0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_bmm_half(dtype, device_ok):
+    a = _rand((4, 512, 256), dtype, 7)
+    b = _rand((4, 256, 1024), dtype, 8)
+    c = b200k.bmm(a.cuda(), b.cuda(), dtype)
+    assert c.shape == (4, 512, 1024)
+    torch.testing.assert_close(c.float().cpu(), oracle.matmul_ref(a, b), **TOL[dtype])
+
+
+@pytest.mark.parametrize("fp8", [torch.float8_e4m3fn, torch.float8_e5m2])
+def test_bmm_fp8_fp32_out(fp8, device_ok):
+    a = _rand((4, 512, 256), torch.float32, 9).to(fp8)
+    b = _rand((4, 256, 1024), torch.float32, 10).to(fp8)
+    c = b200k.bmm(a.cuda(), b.cuda(), torch.float32)
+    # fp8 products are exact in fp32; only the summation order differs
+    torch.testing.assert_close(c.cpu(), oracle.matmul_ref(a, b), atol=1e-3, rtol=1e-4)
+
+
+def test_bench_forms_write_into_c(device_ok):
+    a = _rand((256, 128), torch.bfloat16, 11).cuda()
+    b = _rand((128, 256), torch.bfloat16, 12).cuda()
+    c = torch.empty(256, 256, dtype=torch.bfloat16, device="cuda")
+    assert b200k.cutile_persistent_matmul(a, b, c) is c
+    torch.testing.assert_close(c.float().cpu(), oracle.matmul_ref(a, b), **TOL[torch.bfloat16])
+    a3, b3 = a.unsqueeze(0).repeat(2, 1, 1), b.unsqueeze(0).repeat(2, 1, 1)
+    c3 = torch.empty(2, 256, 256, dtype=torch.bfloat16, device="cuda")
+    b200k.cutile_batch_matmul(2, a3, b3, c3)
+    torch.testing.assert_close(c3[1].float().cpu(), oracle.matmul_ref(a, b), **TOL[torch.bfloat16])
+
+
+def test_linearity_at_full_size(device_ok):
+    # size-independent property at a bench-sized problem: (A1 + A2) B == A1 B + A2 B up to
+    # one rounding of each output, and a sampled block against the oracle
+    m = n = k = 4096
+    g = torch.Generator(device="cuda").manual_seed(13)
+    a1 = torch.randn(m, k, device="cuda", generator=g).half()
+    a2 = torch.randn(m, k, device="cuda", generator=g).half()
+    b = torch.randn(k, n, device="cuda", generator=g).half()
+    c12 = b200k.cutile_matmul(a1 + a2, b).float()
+    c1 = b200k.cutile_matmul(a1, b).float()
+    c2 = b200k.cutile_matmul(a2, b).float()
+    torch.testing.assert_close(c12, c1 + c2, atol=0.5, rtol=1e-2)
+    rows = torch.tensor([0, 127, 128, 2049, 4095])
+    ref = oracle.matmul_ref(a1[rows].cpu(), b.cpu())
+    torch.testing.assert_close(c1[rows].cpu(), ref, **TOL[torch.float16])
