@@ -33,7 +33,12 @@ def test_cutile_matmul_row_major_b(dtype, m, n, k, device_ok):
     b = _rand((k, n), dtype, 1)
     c = b200k.cutile_matmul(a.cuda(), b.cuda())
     assert c.shape == (m, n) and c.dtype == dtype
-    torch.testing.assert_close(c.float().cpu(), oracle.matmul_ref(a, b), **TOL[dtype])
+    tol = dict(TOL[dtype])
+    if dtype == torch.float32:
+        # tf32 keeps 10 mantissa bits of each operand: the error of a K-term sum of N(0,1)
+        # products grows like sqrt(K) * 2^-10
+        tol["atol"] = max(tol["atol"], 6e-3 * k ** 0.5)
+    torch.testing.assert_close(c.float().cpu(), oracle.matmul_ref(a, b), **tol)
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
