@@ -9,3 +9,4 @@ from .matmul import (bmm, cutile_batch_matmul, cutile_matmul,  # noqa: F401
 from .block_scaled import (block_quantize, cutile_block_scaled_matmul,  # noqa: F401
                            cutile_nvfp4_matmul, cutile_swizzled_scaled_matmul, nvfp4_quantize,
                            swizzle_32_4_4)
+from .fmha import cutile_fmha, cutile_fmha_into  # noqa: F401

@@ -70,6 +70,21 @@ class QuantizeArgs(Structure):
     ]
 
 
+class FmhaArgs(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("out", c_void_p),
+        ("batch", c_int64), ("heads_q", c_int64), ("heads_kv", c_int64),
+        ("seq_q", c_int64), ("seq_kv", c_int64),
+        ("q_stride_b", c_int64), ("q_stride_h", c_int64), ("q_stride_s", c_int64),
+        ("k_stride_b", c_int64), ("k_stride_h", c_int64), ("k_stride_s", c_int64),
+        ("v_stride_b", c_int64), ("v_stride_h", c_int64), ("v_stride_s", c_int64),
+        ("o_stride_b", c_int64), ("o_stride_h", c_int64), ("o_stride_s", c_int64),
+        ("input_pos", c_int64),
+        ("head_dim", c_int32), ("dtype", c_int32), ("query_group_size", c_int32),
+        ("causal", c_int32), ("qk_scale", c_float),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/b200k.h declares
 SIGNATURES = {
     "b200k_version": (c_char_p, []),
@@ -80,6 +95,7 @@ SIGNATURES = {
     "b200k_block_scaled_gemm": (c_int, [POINTER(BlockScaledGemmArgs), c_void_p]),
     "b200k_mxfp8_quantize": (c_int, [POINTER(QuantizeArgs), c_void_p]),
     "b200k_nvfp4_quantize": (c_int, [POINTER(QuantizeArgs), c_void_p]),
+    "b200k_fmha_fwd": (c_int, [POINTER(FmhaArgs), c_void_p]),
     "b200k_sf_swizzle": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int32,
                                  c_void_p]),
 }

@@ -172,6 +172,34 @@ int b200k_nvfp4_quantize(const b200k_quantize_args* args, b200k_stream stream);
 int b200k_sf_swizzle(const void* sf, int64_t rows, int64_t kblocks, int64_t ld, void* out,
                      int64_t k_atoms, int32_t fill, b200k_stream stream);
 
+/* ---- attention forward ------------------------------------------------
+ * Out = softmax(qk_scale * Q K^T + mask) V per (batch, head); replaces fmha_kernel
+ * (reference: test/kernels/attention.py:20-128) behind cutile_fmha
+ * (samples/AttentionFMHA.py:138-210).  Q (B, Hq, Sq, D), K / V (B, Hkv, Sk, D), Out
+ * (B, Hq, Sq, D), all f16 or all bf16, addressed through element strides so that
+ * (B, S, H, D) storage works too; the head dimension is contiguous and 64 or 128.
+ * `causal` masks key j for query i when j > i + input_pos; query head h reads
+ * key/value head h / query_group_size. */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  int64_t batch, heads_q, heads_kv, seq_q, seq_kv;
+  int64_t q_stride_b, q_stride_h, q_stride_s;
+  int64_t k_stride_b, k_stride_h, k_stride_s;
+  int64_t v_stride_b, v_stride_h, v_stride_s;
+  int64_t o_stride_b, o_stride_h, o_stride_s;
+  int64_t input_pos;
+  int32_t head_dim;
+  int32_t dtype;            /* B200K_F16 | B200K_BF16 */
+  int32_t query_group_size;
+  int32_t causal;
+  float qk_scale;
+} b200k_fmha_args;
+
+int b200k_fmha_fwd(const b200k_fmha_args* args, b200k_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

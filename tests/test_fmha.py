@@ -1,0 +1,117 @@
+"""Parity of the attention forward kernel with the fp32 CPU oracle.
+
+Shapes follow test/test_attention.py:13-64 (batch {1,4}, q heads {8,16} over 8 kv heads,
+ragged q/k lengths, causal with input_pos) scaled to this kernel's head dims, plus
+BASELINE-shaped slices; tolerances are the reference's for 16-bit inputs
+(atol 1e-2, rtol 5e-2, test/test_attention.py:62-63).
+"""
+import math
+
+import pytest
+import torch
+
+import b200k
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = dict(atol=1e-2, rtol=5e-2)
+
+
+def _qkv(b, hq, hkv, sq, sk, d, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(b, hq, sq, d, generator=g).to(dtype)
+    k = torch.randn(b, hkv, sk, d, generator=g).to(dtype)
+    v = torch.randn(b, hkv, sk, d, generator=g).to(dtype)
+    return q, k, v
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("sq,sk", [(128, 128), (256, 384), (100, 100), (129, 300), (512, 512)])
+@pytest.mark.parametrize("d", [64, 128])
+def test_fmha_matches_oracle(dtype, causal, sq, sk, d, device_ok):
+    q, k, v = _qkv(2, 4, 4, sq, sk, d, dtype, sq + sk + d)
+    input_pos = sk - sq if (causal and sk > sq) else 0
+    out = b200k.cutile_fmha(q.cuda(), k.cuda(), v.cuda(), causal=causal, input_pos=input_pos)
+    assert out.shape == (2, 4, sq, d) and out.dtype == dtype
+    ref = oracle.fmha_ref(q, k, v, causal=causal, input_pos=input_pos)
+    torch.testing.assert_close(out.float().cpu(), ref, **TOL)
+
+
+@pytest.mark.parametrize("batch", [1, 4])
+@pytest.mark.parametrize("q_heads", [8, 16])
+@pytest.mark.parametrize("q_len,k_len", [(1, 32), (15, 63), (32, 32)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_fmha_reference_test_shapes_gqa(batch, q_heads, q_len, k_len, causal, device_ok):
+    # D = 32 as in the reference test: zero-padded to the kernel's 64 by the wrapper
+    q, k, v = _qkv(batch, q_heads, 8, q_len, k_len, 32, torch.bfloat16, q_heads + q_len)
+    group = q_heads // 8
+    input_pos = k_len - q_len if causal else 0
+    out = b200k.cutile_fmha(q.cuda(), k.cuda(), v.cuda(), query_group_size=group, causal=causal,
+                            input_pos=input_pos)
+    ref = oracle.fmha_ref(q, k, v, causal=causal, input_pos=input_pos, query_group_size=group)
+    torch.testing.assert_close(out.float().cpu(), ref, **TOL)
+
+
+def test_fmha_bshd_storage_and_scale(device_ok):
+    # (B, S, H, D) storage viewed as (B, H, S, D), explicit scale
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(2, 200, 4, 128, generator=g).bfloat16().transpose(1, 2)
+    k = torch.randn(2, 200, 4, 128, generator=g).bfloat16().transpose(1, 2)
+    v = torch.randn(2, 200, 4, 128, generator=g).bfloat16().transpose(1, 2)
+    out = b200k.cutile_fmha(q.cuda(), k.cuda(), v.cuda(), qk_scale=0.05, causal=True)
+    ref = oracle.fmha_ref(q, k, v, causal=True, qk_scale=0.05)
+    torch.testing.assert_close(out.float().cpu(), ref, **TOL)
+
+
+def test_fmha_large_score_range_exercises_rescale(device_ok):
+    # growing score magnitudes along the keys force the running maximum up by far more
+    # than the deferred-rescale threshold
+    g = torch.Generator().manual_seed(6)
+    q = torch.randn(1, 2, 256, 128, generator=g)
+    k = torch.randn(1, 2, 1024, 128, generator=g) * torch.linspace(0.2, 6.0, 1024)[None, None, :, None]
+    v = torch.randn(1, 2, 1024, 128, generator=g)
+    q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    out = b200k.cutile_fmha(q.cuda(), k.cuda(), v.cuda(), qk_scale=1.0 / math.sqrt(128))
+    ref = oracle.fmha_ref(q, k, v)
+    torch.testing.assert_close(out.float().cpu(), ref, atol=2e-2, rtol=5e-2)
+
+
+def test_fmha_uniform_values_known_answer(device_ok):
+    # identical keys -> uniform attention -> output = mean of the visible values
+    q = torch.ones(1, 1, 128, 64, dtype=torch.float16)
+    k = torch.ones(1, 1, 256, 64, dtype=torch.float16)
+    v = torch.arange(256, dtype=torch.float32).remainder(16).reshape(1, 1, 256, 1).expand(1, 1, 256, 64).half()
+    out = b200k.cutile_fmha(q.cuda(), k.cuda(), v.cuda().contiguous())
+    torch.testing.assert_close(out.float().cpu(), torch.full((1, 1, 128, 64), 7.5), atol=1e-2, rtol=1e-2)
+
+
+def test_fmha_bench_form_and_validation(device_ok):
+    q, k, v = _qkv(1, 4, 2, 1, 256, 128, torch.float16, 9)     # decode with GQA
+    o = torch.empty(1, 4, 1, 128, dtype=torch.float16, device="cuda")
+    b200k.cutile_fmha_into(q.cuda(), k.cuda(), v.cuda(), o, True, True)
+    ref = oracle.fmha_ref(q, k, v, causal=True, input_pos=255, query_group_size=2)
+    torch.testing.assert_close(o.float().cpu(), ref, **TOL)
+    with pytest.raises(ValueError, match="must be 4D"):
+        b200k.cutile_fmha(q[0].cuda(), k.cuda(), v.cuda())
+    with pytest.raises(ValueError, match="query_group_size must equal"):
+        b200k.cutile_fmha(q.cuda(), k.cuda(), v.cuda())
+
+
+def test_fmha_baseline_shape_slice(device_ok):
+    # BASELINE config 4 is (4, 32, 8192, 128) causal; one batch and 2 heads of it at full
+    # sequence length against the oracle on sampled query rows, plus the row-sum property
+    # that attention over a constant V returns that constant
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(1, 2, 8192, 128, generator=g).bfloat16()
+    k = torch.randn(1, 2, 8192, 128, generator=g).bfloat16()
+    v = torch.randn(1, 2, 8192, 128, generator=g).bfloat16()
+    out = b200k.cutile_fmha(q.cuda(), k.cuda(), v.cuda(), causal=True).float().cpu()
+    rows = torch.tensor([0, 1, 127, 128, 4095, 4096, 8191])
+    for r in rows.tolist():
+        ref = oracle.fmha_ref(q[:, :, r:r + 1], k[:, :, :r + 1], v[:, :, :r + 1])
+        torch.testing.assert_close(out[:, :, r:r + 1], ref, **TOL)
+    ones = torch.ones_like(v)
+    const = b200k.cutile_fmha(q.cuda(), k.cuda(), ones.cuda(), causal=True).float().cpu()
+    torch.testing.assert_close(const, torch.ones_like(const), atol=1e-2, rtol=1e-2)
