@@ -95,6 +95,7 @@ SIGNATURES = {
     "b200k_block_scaled_gemm": (c_int, [POINTER(BlockScaledGemmArgs), c_void_p]),
     "b200k_mxfp8_quantize": (c_int, [POINTER(QuantizeArgs), c_void_p]),
     "b200k_nvfp4_quantize": (c_int, [POINTER(QuantizeArgs), c_void_p]),
+    "b200k_nvfp4_quantize_noalloc": (c_int, [POINTER(QuantizeArgs), c_void_p]),
     "b200k_fmha_fwd": (c_int, [POINTER(FmhaArgs), c_void_p]),
     "b200k_sf_swizzle": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int32,
                                  c_void_p]),

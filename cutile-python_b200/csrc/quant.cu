@@ -13,6 +13,8 @@
 #include <cuda_fp8.h>
 #include <cuda_fp4.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "host.h"
 
@@ -243,6 +245,77 @@ nvfp4_quantize_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t 
   }
 }
 
+// ---- scratch that lives in the library image (for b200k_nvfp4_quantize_noalloc) ----
+// One partial |x| maximum per slab of kNoAllocSlabElems elements.  64 KB per GPU that
+// loads the library, held until the process exits.
+constexpr int kNoAllocSlots = 16384;
+constexpr int64_t kNoAllocSlabElems = 65536;
+static __device__ __align__(256) uint32_t g_noalloc_amax[kNoAllocSlots];
+
+// Block b reduces elements [b * slab, (b + 1) * slab) of the row-major index space and
+// overwrites slot b: every slot a call reads is written by that call first.
+template <typename T>
+__global__ void __launch_bounds__(256)
+absmax_slab_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t ldx,
+                   uint32_t* __restrict__ slots) {
+  const int64_t total = rows * k;
+  const int64_t begin = static_cast<int64_t>(blockIdx.x) * kNoAllocSlabElems;
+  const int64_t end = begin + kNoAllocSlabElems < total ? begin + kNoAllocSlabElems : total;
+  float m = 0.0f;
+  for (int64_t idx = begin + threadIdx.x; idx < end; idx += blockDim.x) {
+    const int64_t row = idx / k;
+    m = fmaxf(m, fabsf(to_f32<T>(x[row * ldx + (idx - row * k)])));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  __shared__ float part[8];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) m = fmaxf(m, part[i]);
+    slots[blockIdx.x] = __float_as_uint(m);
+  }
+}
+
+// Single block: folds slots [0, n) into slot 0.
+__global__ void __launch_bounds__(256) fold_slots_kernel(uint32_t* __restrict__ slots, int n) {
+  uint32_t m = 0;  // non-negative floats order like their bit patterns
+  for (int i = threadIdx.x; i < n; i += blockDim.x) m = max(m, slots[i]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+  __shared__ uint32_t part[8];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) m = max(m, part[i]);
+    slots[0] = m;
+  }
+}
+
+// Device address of g_noalloc_amax per device.  In host code the array's name is only a
+// handle for the runtime, so the address a kernel can use is asked for once per device,
+// with that device current.
+uint32_t* noalloc_slots() {
+  static uint32_t* addr[64] = {};
+  static std::mutex mu;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    fail(B200K_CUDA_ERROR, "no current CUDA device");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    uint32_t* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_amax);
+    if (e != cudaSuccess || p == nullptr) {
+      fail(B200K_CUDA_ERROR, "cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    addr[dev] = p;
+  }
+  return addr[dev];
+}
+
 int grid_for(int64_t work_items, int threads) {
   int sms = current_sm_count();
   if (sms <= 0) sms = 148;
@@ -342,5 +415,45 @@ extern "C" int b200k_nvfp4_quantize(const b200k_quantize_args* a, b200k_stream s
   }
 #undef B200K_NVFP4_CASE
   B200K_CHECK_LAUNCH("nvfp4_quantize launch");
+  return B200K_OK;
+}
+
+extern "C" int b200k_nvfp4_quantize_noalloc(const b200k_quantize_args* a, b200k_stream stream_) {
+  if (a == nullptr) return fail(B200K_INVALID_ARG, "null args");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a->rows < 0 || a->k < 0) return fail(B200K_INVALID_ARG, "negative dimension");
+  if (a->rows == 0 || a->k == 0) return B200K_OK;
+  if (!a->x || !a->q) return fail(B200K_INVALID_ARG, "null pointer");
+  if (a->k % 2) return fail(B200K_UNSUPPORTED, "K must be even (two e2m1 values per byte)");
+  const int64_t kblocks = ceil_div(a->k, 16);
+  if (a->sf_swizzled && a->sf_k_atoms < ceil_div(kblocks, 4))
+    return fail(B200K_INVALID_ARG, "sf_k_atoms too small");
+  const int64_t slabs = ceil_div(a->rows * a->k, kNoAllocSlabElems);
+  if (slabs > kNoAllocSlots)
+    return fail(B200K_UNSUPPORTED,
+                "tensor of %lld elements exceeds the built-in scratch of this entry point "
+                "(%lld elements at most); use b200k_nvfp4_quantize with caller scratch",
+                (long long)(a->rows * a->k), (long long)(kNoAllocSlots * kNoAllocSlabElems));
+  uint32_t* slots = noalloc_slots();
+  if (slots == nullptr) return B200K_CUDA_ERROR;
+  const int grid_q = grid_for(a->rows * kblocks, 256);
+  uint8_t* q = static_cast<uint8_t*>(a->q);
+  uint8_t* sl = static_cast<uint8_t*>(a->sf_logical);
+  uint8_t* ss = static_cast<uint8_t*>(a->sf_swizzled);
+#define B200K_NVFP4_NOALLOC_CASE(T)                                                               \
+  absmax_slab_kernel<T><<<static_cast<int>(slabs), 256, 0, stream>>>(                             \
+      static_cast<const T*>(a->x), a->rows, a->k, a->ldx, slots);                                 \
+  fold_slots_kernel<<<1, 256, 0, stream>>>(slots, static_cast<int>(slabs));                       \
+  nvfp4_quantize_kernel<T><<<grid_q, 256, 0, stream>>>(static_cast<const T*>(a->x), a->rows, a->k, \
+                                                       a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms,  \
+                                                       slots, a->tensor_scale)
+  switch (a->x_dtype) {
+    case B200K_F32: B200K_NVFP4_NOALLOC_CASE(float); break;
+    case B200K_BF16: B200K_NVFP4_NOALLOC_CASE(__nv_bfloat16); break;
+    case B200K_F16: B200K_NVFP4_NOALLOC_CASE(__half); break;
+    default: return fail(B200K_INVALID_ARG, "x_dtype must be f32, bf16 or f16");
+  }
+#undef B200K_NVFP4_NOALLOC_CASE
+  B200K_CHECK_LAUNCH("nvfp4_quantize_noalloc launch");
   return B200K_OK;
 }

@@ -166,6 +166,23 @@ int b200k_mxfp8_quantize(const b200k_quantize_args* args, b200k_stream stream);
  * x ~= q * s_blk * s_t.  Byte i of a row holds elements 2i (low nibble) and 2i+1. */
 int b200k_nvfp4_quantize(const b200k_quantize_args* args, b200k_stream stream);
 
+/* Same result as b200k_nvfp4_quantize, for callers that cannot allocate device memory
+ * (it has no counterpart in the reference).  Some hosts of this library may not call
+ * cudaMalloc where they call us: a plugin running inside another framework's stream
+ * callback or memory-pool-owned region, a process whose device memory is fully
+ * pre-partitioned, code between the nodes of a captured launch sequence.  This entry
+ * point allocates nothing and ignores `scratch`: its temporary (one partial maximum per
+ * 65536 elements) lives in a 64 KB array inside the library image, which every GPU that
+ * loads the library keeps until the process exits.
+ *   - Limit: rows * K <= 16384 * 65536 (2^30) elements; larger tensors are rejected with
+ *     B200K_UNSUPPORTED and a message naming the limit.
+ *   - The first call on each device looks up the array's device address (a host-side
+ *     runtime query, no allocation); make that first call outside any stream capture.
+ *   - All calls on a device share the array.  Each call overwrites the slots it later
+ *     reads, so nothing needs clearing, but two calls that overlap on the GPU (different
+ *     streams) race on it: serialise them. */
+int b200k_nvfp4_quantize_noalloc(const b200k_quantize_args* args, b200k_stream stream);
+
 /* Logical (rows, kblocks) scale bytes (row stride ld) -> swizzle_32_4_4 atoms; replaces
  * swizzle_32_4_4 (reference: test/kernels/kernel_utils.py:83-98).  Rows beyond `rows`
  * and blocks beyond `kblocks` inside the padded atoms are set to `fill`. */
