@@ -10,3 +10,6 @@ from .block_scaled import (block_quantize, cutile_block_scaled_matmul,  # noqa: 
                            cutile_nvfp4_matmul, cutile_swizzled_scaled_matmul, nvfp4_quantize,
                            swizzle_32_4_4)
 from .fmha import cutile_fmha, cutile_fmha_into  # noqa: F401
+from .moe import (cutile_moe, cutile_moe_mxfp8, invoke_fused_moe_kernel,  # noqa: F401
+                  invoke_silu_and_mul_kernel, moe_align_device, moe_align_tile_size_torch,
+                  quantize_expert_weights)

@@ -67,6 +67,17 @@ class QuantizeArgs(Structure):
         ("rows", c_int64), ("k", c_int64), ("ldx", c_int64), ("ldq", c_int64),
         ("sf_k_atoms", c_int64),
         ("x_dtype", c_int32), ("q_dtype", c_int32),
+        ("gather_index", c_void_p), ("gather_divisor", c_int32), ("tile_m", c_int32),
+        ("src_rows", c_int64), ("live_blocks", c_void_p),
+    ]
+
+
+class MoeAlignArgs(Structure):
+    _fields_ = [
+        ("topk_ids", c_void_p), ("sorted_token_ids", c_void_p), ("sorted_expert_ids", c_void_p),
+        ("num_blocks", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_int64),
+        ("num_replicas", c_int64), ("capacity", c_int64), ("block_capacity", c_int64),
+        ("num_experts", c_int32), ("tile_m", c_int32), ("ids_are_int64", c_int32),
     ]
 
 
@@ -96,6 +107,13 @@ SIGNATURES = {
     "b200k_mxfp8_quantize": (c_int, [POINTER(QuantizeArgs), c_void_p]),
     "b200k_nvfp4_quantize": (c_int, [POINTER(QuantizeArgs), c_void_p]),
     "b200k_nvfp4_quantize_noalloc": (c_int, [POINTER(QuantizeArgs), c_void_p]),
+    "b200k_moe_align_workspace_bytes": (c_int64, [c_int64, c_int32]),
+    "b200k_moe_align": (c_int, [POINTER(MoeAlignArgs), c_void_p]),
+    "b200k_gather_rows": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int32, c_void_p,
+                                  c_int32, c_int64, c_void_p, c_int64, c_void_p]),
+    "b200k_silu_and_mul": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int32,
+                                   c_void_p]),
+    "b200k_topk_sum": (c_int, [c_void_p, c_int64, c_int32, c_int64, c_void_p, c_int32, c_void_p]),
     "b200k_fmha_fwd": (c_int, [POINTER(FmhaArgs), c_void_p]),
     "b200k_sf_swizzle": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int32,
                                  c_void_p]),

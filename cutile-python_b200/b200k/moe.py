@@ -1,0 +1,280 @@
+"""Mixture-of-experts FFN with the entry points of the reference's sample.
+
+cutile_moe                   samples/MoE.py:197-288
+moe_align_tile_size_torch    test/kernels/fused_moe.py:113-173
+invoke_fused_moe_kernel      samples/MoE.py:338-375
+invoke_silu_and_mul_kernel   samples/MoE.py:378-393
+cutile_moe_mxfp8             the same FFN with MXFP8 expert weights and activations (the
+                             reference has only the bf16 form)
+
+Pipeline of cutile_moe (no host synchronisation anywhere): device-side alignment ->
+row gather of the hidden states into expert order -> grouped GEMM with fused SiLU-and-
+multiply epilogue -> grouped GEMM with routed-weight scaling and row scatter -> top-k sum.
+The grouped GEMM's row tile is 128, so the alignment always uses tile_m = 128 internally;
+`tile_m/tile_n/tile_k` are accepted for signature compatibility.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from .block_scaled import _as_u8, swizzled_shape
+
+ROW_TILE = 128
+
+
+def _cdiv(a: int, b: int) -> int:
+    return (a + b - 1) // b
+
+
+def moe_align_device(topk_ids: torch.Tensor, tile_m: int, num_experts: int):
+    """Device-side alignment.  Returns (sorted_token_ids [capacity] int32,
+    sorted_expert_ids [capacity / tile_m] int32, num_blocks int32 device scalar)."""
+    if topk_ids.dim() != 2:
+        raise ValueError("topk_ids must be (num_tokens, topk)")
+    if not topk_ids.is_cuda:
+        raise ValueError("Input tensors must be on a CUDA device.")
+    if topk_ids.dtype not in (torch.int32, torch.int64):
+        raise TypeError("topk_ids must be int32 or int64")
+    ids = topk_ids.contiguous()
+    total = ids.numel()
+    blocks = _cdiv(total + num_experts * (tile_m - 1), tile_m)
+    dev = ids.device
+    sorted_ids = torch.empty(blocks * tile_m, dtype=torch.int32, device=dev)
+    expert_ids = torch.empty(blocks, dtype=torch.int32, device=dev)
+    num_blocks = torch.empty(1, dtype=torch.int32, device=dev)
+    ws_bytes = _lib.lib().b200k_moe_align_workspace_bytes(total, num_experts)
+    ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
+    a = _lib.MoeAlignArgs()
+    a.topk_ids = ids.data_ptr()
+    a.sorted_token_ids, a.sorted_expert_ids = sorted_ids.data_ptr(), expert_ids.data_ptr()
+    a.num_blocks, a.workspace, a.workspace_bytes = num_blocks.data_ptr(), ws.data_ptr(), ws.numel()
+    a.num_replicas, a.capacity, a.block_capacity = total, sorted_ids.numel(), blocks
+    a.num_experts, a.tile_m = num_experts, tile_m
+    a.ids_are_int64 = 1 if ids.dtype == torch.int64 else 0
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().b200k_moe_align(ctypes.byref(a), _lib.stream_ptr(dev)))
+    return sorted_ids, expert_ids, num_blocks
+
+
+def moe_align_tile_size_torch(topk_ids: torch.Tensor, tile_m: int, num_experts: int):
+    """Same outputs as the reference function (exact lengths), computed on the device.
+    Reading the block count back is the one host synchronisation; cutile_moe avoids it by
+    using moe_align_device."""
+    sorted_ids, expert_ids, num_blocks = moe_align_device(topk_ids, tile_m, num_experts)
+    n = int(num_blocks.item())
+    return sorted_ids[: n * tile_m], expert_ids[:n]
+
+
+def _gather_rows(src: torch.Tensor, index: torch.Tensor, divisor: int, rows: int,
+                 num_blocks: torch.Tensor | None) -> torch.Tensor:
+    if src.stride(1) != 1 or (src.stride(0) * src.element_size()) % 16 or src.data_ptr() % 16 \
+            or (src.shape[1] * src.element_size()) % 16:
+        raise ValueError("gather source rows must be contiguous multiples of 16 bytes")
+    dst = torch.empty((rows, src.shape[1]), dtype=src.dtype, device=src.device)
+    with torch.cuda.device(src.device):
+        _lib.check(_lib.lib().b200k_gather_rows(
+            src.data_ptr(), src.shape[0], src.shape[1] * src.element_size(),
+            src.stride(0) * src.element_size(), index.data_ptr(), divisor,
+            _lib.ptr(num_blocks), ROW_TILE, rows, dst.data_ptr(),
+            dst.stride(0) * dst.element_size(), _lib.stream_ptr(src.device)))
+    return dst
+
+
+def _grouped_gemm(a_sorted, w, c, expert_ids, *, num_blocks=None, row_map=None, row_scale=None,
+                  c_rows=0, swiglu=False):
+    """a_sorted (Mp, K) x w (E, N, K)^T with the expert of each 128-row tile in expert_ids."""
+    mp, k = a_sorted.shape
+    e, n, _ = w.shape
+    args = _lib.GemmArgs()
+    args.a, args.b, args.c = a_sorted.data_ptr(), w.data_ptr(), c.data_ptr()
+    args.m, args.n, args.k, args.batch = mp, n, k, e
+    args.lda, args.ldb, args.ldc = a_sorted.stride(0), w.stride(1), c.stride(0)
+    args.stride_a, args.stride_b, args.stride_c = 0, w.stride(0), 0
+    args.ab_dtype = _lib.dtype_enum(a_sorted.dtype)
+    args.c_dtype = _lib.dtype_enum(c.dtype)
+    args.b_layout = _lib.B_NK
+    args.epilogue = _lib.EPI_SWIGLU if swiglu else _lib.EPI_STORE
+    args.alpha = 1.0
+    args.tile_group = expert_ids.data_ptr()
+    args.num_row_tiles = _lib.ptr(num_blocks)
+    args.row_map = _lib.ptr(row_map)
+    args.row_scale = _lib.ptr(row_scale)
+    args.c_rows = c_rows
+    with torch.cuda.device(c.device):
+        _lib.check(_lib.lib().b200k_gemm(ctypes.byref(args), _lib.stream_ptr(c.device)))
+    return c
+
+
+def _check_weight(w: torch.Tensor) -> torch.Tensor:
+    if w.stride(2) != 1 or (w.stride(1) * w.element_size()) % 16 or (w.stride(0) * w.element_size()) % 16:
+        w = w.contiguous()
+    if (w.shape[2] * w.element_size()) % 16:
+        raise ValueError("expert weight rows must be multiples of 16 bytes")
+    return w
+
+
+def invoke_fused_moe_kernel(A, B, C, topk_weights, sorted_token_ids, sorted_expert_ids,
+                            mul_routed_weight: bool, num_token_replicas: int,
+                            tile_m: int = ROW_TILE, tile_n: int = 128, tile_k: int = 64) -> None:
+    """C.view(-1, N)[r] = (A[r // num_token_replicas] @ B[expert(r)].T) [* topk_weights[r]] for
+    every replica id r in sorted_token_ids; sentinel ids are skipped."""
+    if tile_m != ROW_TILE:
+        raise ValueError(f"this kernel's row tile is {ROW_TILE}: align with tile_m={ROW_TILE}")
+    if sorted_token_ids.numel() != sorted_expert_ids.numel() * tile_m:
+        raise ValueError("sorted_token_ids / sorted_expert_ids lengths disagree")
+    c2 = C.view(-1, C.shape[-1])
+    rows = sorted_token_ids.numel()
+    if rows == 0:
+        return
+    a_sorted = _gather_rows(A, sorted_token_ids, num_token_replicas, rows, None)
+    scale = topk_weights.reshape(-1).float().contiguous() if mul_routed_weight else None
+    _grouped_gemm(a_sorted, _check_weight(B), c2, sorted_expert_ids, row_map=sorted_token_ids,
+                  row_scale=scale, c_rows=c2.shape[0])
+
+
+def invoke_silu_and_mul_kernel(AB: torch.Tensor, C: torch.Tensor) -> None:
+    rows, two_n = AB.shape
+    with torch.cuda.device(AB.device):
+        _lib.check(_lib.lib().b200k_silu_and_mul(AB.data_ptr(), rows, two_n // 2, AB.stride(0),
+                                                 C.data_ptr(), C.stride(0),
+                                                 _lib.dtype_enum(AB.dtype),
+                                                 _lib.stream_ptr(AB.device)))
+
+
+def _topk_sum(x: torch.Tensor, tokens: int, topk: int, hidden: int) -> torch.Tensor:
+    out = torch.empty((tokens, hidden), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().b200k_topk_sum(x.data_ptr(), tokens, topk, hidden, out.data_ptr(),
+                                             _lib.dtype_enum(x.dtype), _lib.stream_ptr(x.device)))
+    return out
+
+
+def _validate(hidden_states, w1, w2, topk_weights, topk_ids):
+    if w1.shape[1] != w2.shape[2] * 2:
+        raise ValueError("w1 must have 2 * intermediate_size rows (gate + up projection)")
+    if hidden_states.shape[1] != w1.shape[2] or hidden_states.shape[1] != w2.shape[1]:
+        raise ValueError("hidden size of the activations and the expert weights differ")
+    if topk_ids.shape != topk_weights.shape or topk_ids.shape[0] != hidden_states.shape[0]:
+        raise ValueError("topk_ids / topk_weights must be (num_tokens, topk)")
+    if not hidden_states.is_cuda:
+        raise ValueError("Input tensors must be on a CUDA device.")
+
+
+def cutile_moe(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
+               topk_weights: torch.Tensor, topk_ids: torch.Tensor,
+               tile_m: int = 128, tile_n: int = 128, tile_k: int = 64) -> torch.Tensor:
+    """MoE FFN forward: out[t] = sum_j w[t, j] * W2[e] (silu(W1g[e] x_t) * (W1u[e] x_t)),
+    e = topk_ids[t, j].  hidden_states (T, H) f16/bf16; w1 (E, 2I, H); w2 (E, H, I)."""
+    _validate(hidden_states, w1, w2, topk_weights, topk_ids)
+    tokens, hidden = hidden_states.shape
+    experts, _, inter = w2.shape
+    topk = topk_ids.shape[1]
+    dtype, dev = hidden_states.dtype, hidden_states.device
+    if tokens == 0:
+        return torch.empty_like(hidden_states)
+    x = hidden_states if hidden_states.stride(1) == 1 else hidden_states.contiguous()
+    w1c, w2c = _check_weight(w1), _check_weight(w2)
+
+    sorted_ids, expert_ids, num_blocks = moe_align_device(topk_ids, ROW_TILE, experts)
+    cap = sorted_ids.numel()
+    a_sorted = _gather_rows(x, sorted_ids, topk, cap, num_blocks)
+    act = torch.empty((cap, inter), dtype=dtype, device=dev)
+    if inter % 128 == 0:
+        _grouped_gemm(a_sorted, w1c, act, expert_ids, num_blocks=num_blocks, swiglu=True)
+    else:
+        gate_up = torch.empty((cap, 2 * inter), dtype=dtype, device=dev)
+        _grouped_gemm(a_sorted, w1c, gate_up, expert_ids, num_blocks=num_blocks)
+        invoke_silu_and_mul_kernel(gate_up, act)
+    per_replica = torch.empty((tokens * topk, hidden), dtype=dtype, device=dev)
+    _grouped_gemm(act, w2c, per_replica, expert_ids, num_blocks=num_blocks, row_map=sorted_ids,
+                  row_scale=topk_weights.reshape(-1).float().contiguous(), c_rows=tokens * topk)
+    return _topk_sum(per_replica, tokens, topk, hidden)
+
+
+# ---- MXFP8 experts -----------------------------------------------------------------
+def quantize_expert_weights(w: torch.Tensor):
+    """(E, N, K) f16/bf16/f32 -> (e4m3 (E, N, K), swizzled ue8m0 scales (E, N/128, K/128, 32, 16)).
+    N must be a multiple of 128 and K of 128 so that no scale atom straddles two experts."""
+    from .block_scaled import block_quantize
+    e, n, k = w.shape
+    if n % 128 or k % 128:
+        raise ValueError("expert weight dims must be multiples of 128 for MXFP8")
+    q, sf = block_quantize(w.reshape(e * n, k), 32, swizzled_scale=True)
+    return q.reshape(e, n, k), sf.reshape(e, n // 128, k // 128, 32, 16)
+
+
+def _quantize_rows(x, *, rows, gather=None, divisor=1, num_blocks=None):
+    """MXFP8 quantisation of (optionally gathered) rows with swizzled scales."""
+    k = x.shape[1]
+    q = torch.empty((rows, k), dtype=torch.uint8, device=x.device)
+    shape = swizzled_shape(rows, k // 32)
+    sf = torch.empty(shape, dtype=torch.uint8, device=x.device)
+    a = _lib.QuantizeArgs()
+    a.x, a.q, a.sf_swizzled = x.data_ptr(), q.data_ptr(), sf.data_ptr()
+    a.rows, a.k, a.ldx, a.ldq, a.sf_k_atoms = rows, k, x.stride(0), k, shape[1]
+    a.x_dtype, a.q_dtype = _lib.dtype_enum(x.dtype), _lib.E4M3
+    a.gather_index = _lib.ptr(gather)
+    a.gather_divisor, a.tile_m, a.src_rows = divisor, ROW_TILE, x.shape[0]
+    a.live_blocks = _lib.ptr(num_blocks)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().b200k_mxfp8_quantize(ctypes.byref(a), _lib.stream_ptr(x.device)))
+    return q.view(torch.float8_e4m3fn), sf
+
+
+def _grouped_scaled_gemm(a_q, a_sf, w_q, w_sf, c, expert_ids, *, num_blocks, row_map=None,
+                         row_scale=None, c_rows=0, swiglu=False):
+    mp, k = a_q.shape
+    e, n, _ = w_q.shape
+    args = _lib.BlockScaledGemmArgs()
+    args.a, args.b, args.c = a_q.data_ptr(), w_q.data_ptr(), c.data_ptr()
+    args.sfa, args.sfb = a_sf.data_ptr(), w_sf.data_ptr()
+    args.m, args.n, args.k, args.batch = mp, n, k, e
+    args.lda, args.ldb, args.ldc = a_q.stride(0), w_q.stride(1), c.stride(0)
+    args.stride_a, args.stride_b, args.stride_c = 0, w_q.stride(0), 0
+    args.sf_k_atoms = a_sf.shape[1]
+    args.stride_sfa, args.stride_sfb = 0, w_sf.stride(0)
+    args.ab_dtype, args.c_dtype = _lib.E4M3, _lib.dtype_enum(c.dtype)
+    args.epilogue = _lib.EPI_SWIGLU if swiglu else _lib.EPI_STORE
+    args.alpha = 1.0
+    args.tile_group = expert_ids.data_ptr()
+    args.num_row_tiles = _lib.ptr(num_blocks)
+    args.row_map = _lib.ptr(row_map)
+    args.row_scale = _lib.ptr(row_scale)
+    args.c_rows = c_rows
+    with torch.cuda.device(c.device):
+        _lib.check(_lib.lib().b200k_block_scaled_gemm(ctypes.byref(args), _lib.stream_ptr(c.device)))
+    return c
+
+
+def cutile_moe_mxfp8(hidden_states: torch.Tensor, w1_q: torch.Tensor, w1_sf: torch.Tensor,
+                     w2_q: torch.Tensor, w2_sf: torch.Tensor, topk_weights: torch.Tensor,
+                     topk_ids: torch.Tensor) -> torch.Tensor:
+    """The MoE FFN with MXFP8 expert weights (from quantize_expert_weights).  Activations are
+    quantised to MXFP8 on the fly, fused with the permutation; the SiLU-and-multiply
+    output is rounded to the activation dtype and re-quantised before the down projection."""
+    _validate(hidden_states, w1_q, w2_q, topk_weights, topk_ids)
+    tokens, hidden = hidden_states.shape
+    experts, _, inter = w2_q.shape
+    topk = topk_ids.shape[1]
+    dtype, dev = hidden_states.dtype, hidden_states.device
+    if hidden % 128 or inter % 128:
+        raise ValueError("hidden and intermediate sizes must be multiples of 128 for MXFP8")
+    if tokens == 0:
+        return torch.empty_like(hidden_states)
+    x = hidden_states if hidden_states.stride(1) == 1 else hidden_states.contiguous()
+    sorted_ids, expert_ids, num_blocks = moe_align_device(topk_ids, ROW_TILE, experts)
+    cap = sorted_ids.numel()
+    a_q, a_sf = _quantize_rows(x, rows=cap, gather=sorted_ids, divisor=topk, num_blocks=num_blocks)
+    act = torch.empty((cap, inter), dtype=dtype, device=dev)
+    _grouped_scaled_gemm(a_q, a_sf, w1_q, _as_u8(w1_sf), act, expert_ids, num_blocks=num_blocks,
+                         swiglu=True)
+    act_q, act_sf = _quantize_rows(act, rows=cap, num_blocks=num_blocks)
+    per_replica = torch.empty((tokens * topk, hidden), dtype=dtype, device=dev)
+    _grouped_scaled_gemm(act_q, act_sf, w2_q, _as_u8(w2_sf), per_replica, expert_ids,
+                         num_blocks=num_blocks, row_map=sorted_ids,
+                         row_scale=topk_weights.reshape(-1).float().contiguous(),
+                         c_rows=tokens * topk)
+    return _topk_sum(per_replica, tokens, topk, hidden)

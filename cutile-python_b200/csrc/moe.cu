@@ -1,0 +1,365 @@
+// Mixture-of-experts plumbing around the grouped GEMM: routing alignment (a stable
+// counting sort of token replicas by expert, padded per expert to the GEMM's row tile),
+// row gather, SiLU-and-multiply and the top-k reduction.  All of it is integer / byte
+// work bound by HBM (or by launch latency at small sizes); nothing here touches the
+// tensor cores.
+//
+//   moe_align      follows moe_align_tile_size_torch (reference:
+//                  test/kernels/fused_moe.py:113-173) without its host loop and device
+//                  syncs: same sorted_token_ids / sorted_expert_ids, bit for bit, written
+//                  into worst-case-sized buffers with the block count left on the device
+//   gather_rows    A_sorted[i] = A[sorted_token_ids[i] / replicas], zero rows for the
+//                  sentinel (the gather of fused_moe_kernel, test/kernels/fused_moe.py:56-68)
+//   silu_and_mul   silu_and_mul_kernel (test/kernels/fused_moe.py:85-108)
+//   topk_sum       torch.sum(intermediate_cache3, dim=1) (samples/MoE.py:288)
+#include "common.cuh"
+#include "host.h"
+
+namespace b200k {
+namespace {
+
+constexpr int kChunk = 512;          // token replicas per warp
+constexpr int kAlignWarps = 4;       // warps per block in the count / scatter kernels
+
+template <typename IdT>
+__device__ __forceinline__ int load_expert(const IdT* ids, int64_t i, int num_experts, int* status) {
+  const long long e = static_cast<long long>(ids[i]);
+  if (e < 0 || e >= num_experts) {
+    report_status(status, 40, 0);   // routing entry outside [0, num_experts): dropped
+    return -1;
+  }
+  return static_cast<int>(e);
+}
+
+// Pass 1: per-chunk histogram over experts.  counts[chunk * E + e].
+template <typename IdT>
+__global__ void __launch_bounds__(kAlignWarps * 32)
+moe_count_kernel(const IdT* __restrict__ ids, int64_t total, int num_experts,
+                 int* __restrict__ counts, int* status) {
+  extern __shared__ int smem_counts[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int* mine = smem_counts + warp * num_experts;
+  const int64_t chunk = static_cast<int64_t>(blockIdx.x) * kAlignWarps + warp;
+  const int64_t begin = chunk * kChunk;
+  if (begin >= total) return;
+  for (int e = lane; e < num_experts; e += 32) mine[e] = 0;
+  __syncwarp();
+  const int64_t end = begin + kChunk < total ? begin + kChunk : total;
+  for (int64_t i = begin + lane; i - lane < end; i += 32) {
+    const bool active = i < end;
+    const int e = active ? load_expert(ids, i, num_experts, status) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    if (e >= 0 && (peers & ((1u << lane) - 1)) == 0) mine[e] += __popc(peers);
+    __syncwarp();
+  }
+  for (int e = lane; e < num_experts; e += 32) counts[chunk * num_experts + e] = mine[e];
+}
+
+// Pass 2 (one block): turns the histograms into write offsets, emits the per-block expert
+// ids, the block count and every sentinel slot.
+__global__ void __launch_bounds__(1024)
+moe_offsets_kernel(int* __restrict__ counts, int num_chunks, int num_experts, int tile_m,
+                   int64_t total, int* __restrict__ sorted_token_ids, int64_t capacity,
+                   int* __restrict__ sorted_expert_ids, int64_t block_capacity,
+                   int* __restrict__ num_blocks_out) {
+  extern __shared__ int sm[];
+  int* totals = sm;                      // [E] replicas per expert
+  int* starts = sm + num_experts;        // [E] first slot of the expert's padded run
+  __shared__ int total_blocks;
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < num_chunks; ++c) {
+      const int v = counts[c * num_experts + e];
+      counts[c * num_experts + e] = run;   // exclusive prefix inside the expert
+      run += v;
+    }
+    totals[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int slot = 0;
+    for (int e = 0; e < num_experts; ++e) {
+      starts[e] = slot;
+      slot += (totals[e] + tile_m - 1) / tile_m * tile_m;
+    }
+    total_blocks = slot / tile_m;
+    *num_blocks_out = total_blocks;
+  }
+  __syncthreads();
+  const int sentinel = static_cast<int>(total);
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+    for (int c = 0; c < num_chunks; ++c) counts[c * num_experts + e] += starts[e];
+  }
+  // expert id of every tile_m block, -1 beyond the blocks in use
+  for (int64_t b = threadIdx.x; b < block_capacity; b += blockDim.x) {
+    int owner = -1;
+    if (b < total_blocks) {
+      // experts are few: linear search of the run that holds block b
+      const int slot = static_cast<int>(b) * tile_m;
+      for (int e = 0; e < num_experts; ++e) {
+        const int padded = (totals[e] + tile_m - 1) / tile_m * tile_m;
+        if (slot >= starts[e] && slot < starts[e] + padded) { owner = e; break; }
+      }
+    }
+    sorted_expert_ids[b] = owner;
+  }
+  // sentinels: the padding tail of every run and everything beyond the last block
+  for (int e = 0; e < num_experts; ++e) {
+    const int padded = (totals[e] + tile_m - 1) / tile_m * tile_m;
+    for (int i = totals[e] + threadIdx.x; i < padded; i += blockDim.x)
+      sorted_token_ids[starts[e] + i] = sentinel;
+  }
+  for (int64_t i = static_cast<int64_t>(total_blocks) * tile_m + threadIdx.x; i < capacity;
+       i += blockDim.x)
+    sorted_token_ids[i] = sentinel;
+}
+
+// Pass 3: stable scatter.  A warp walks its chunk in index order, so replicas of one
+// expert keep their original order (the order torch.argsort(stable=True) gives).
+template <typename IdT>
+__global__ void __launch_bounds__(kAlignWarps * 32)
+moe_scatter_kernel(const IdT* __restrict__ ids, int64_t total, int num_experts,
+                   const int* __restrict__ offsets, int* __restrict__ sorted_token_ids,
+                   int* status) {
+  extern __shared__ int smem_counts[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int* next = smem_counts + warp * num_experts;
+  const int64_t chunk = static_cast<int64_t>(blockIdx.x) * kAlignWarps + warp;
+  const int64_t begin = chunk * kChunk;
+  if (begin >= total) return;
+  for (int e = lane; e < num_experts; e += 32) next[e] = offsets[chunk * num_experts + e];
+  __syncwarp();
+  const int64_t end = begin + kChunk < total ? begin + kChunk : total;
+  for (int64_t i = begin + lane; i - lane < end; i += 32) {
+    const bool active = i < end;
+    const int e = active ? load_expert(ids, i, num_experts, status) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const unsigned before = peers & ((1u << lane) - 1);
+    if (e >= 0) sorted_token_ids[next[e] + __popc(before)] = static_cast<int>(i);
+    __syncwarp();
+    if (e >= 0 && before == 0) next[e] += __popc(peers);
+    __syncwarp();
+  }
+}
+
+// One block per destination row; 16-byte copies.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint8_t* __restrict__ src, int64_t src_rows, int64_t row_bytes,
+                   int64_t src_stride, const int* __restrict__ index, int divisor,
+                   const int* __restrict__ num_blocks, int tile_m, int64_t max_rows,
+                   uint8_t* __restrict__ dst, int64_t dst_stride) {
+  int64_t rows = max_rows;
+  if (num_blocks != nullptr) {
+    const int64_t live = static_cast<int64_t>(*num_blocks) * tile_m;
+    rows = live < rows ? live : rows;
+  }
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const int64_t s = index[r] / divisor;
+    uint4* out = reinterpret_cast<uint4*>(dst + r * dst_stride);
+    const int64_t vecs = row_bytes / 16;
+    if (s >= 0 && s < src_rows && index[r] >= 0) {
+      const uint4* in = reinterpret_cast<const uint4*>(src + s * src_stride);
+      for (int64_t i = threadIdx.x; i < vecs; i += blockDim.x) out[i] = in[i];
+    } else {
+      for (int64_t i = threadIdx.x; i < vecs; i += blockDim.x) out[i] = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
+template <bool BF16>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+  if constexpr (BF16) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+  } else {
+    return __half22float2(*reinterpret_cast<const __half2*>(&w));
+  }
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  return BF16 ? pack_bf16x2(a, b) : pack_f16x2(a, b);
+}
+
+// C[r, j] = silu(AB[r, j]) * AB[r, j + n]; fp32 math, one rounding.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+silu_and_mul_kernel(const uint16_t* __restrict__ ab, int64_t rows, int64_t n, int64_t ld_ab,
+                    uint16_t* __restrict__ c, int64_t ld_c) {
+  const int64_t pairs = n / 2;
+  const int64_t total = rows * pairs;
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = idx / pairs;
+    const int64_t j = (idx - r * pairs) * 2;
+    const uint32_t g = *reinterpret_cast<const uint32_t*>(ab + r * ld_ab + j);
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(ab + r * ld_ab + n + j);
+    const float2 gf = unpack2<BF16>(g), uf = unpack2<BF16>(u);
+    const float a = gf.x / (1.0f + __expf(-gf.x)) * uf.x;
+    const float b = gf.y / (1.0f + __expf(-gf.y)) * uf.y;
+    *reinterpret_cast<uint32_t*>(c + r * ld_c + j) = pack2<BF16>(a, b);
+  }
+}
+
+// out[t, :] = sum_j x[t, j, :], fp32 accumulation, 8 columns per thread.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+topk_sum_kernel(const uint16_t* __restrict__ x, int64_t tokens, int topk, int64_t h,
+                uint16_t* __restrict__ out) {
+  const int64_t vecs = h / 8;
+  const int64_t total = tokens * vecs;
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t t = idx / vecs;
+    const int64_t v = idx - t * vecs;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < topk; ++j) {
+      const uint4 q = *reinterpret_cast<const uint4*>(x + (t * topk + j) * h + v * 8);
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = unpack2<BF16>(w[i]);
+        acc[2 * i] += f.x;
+        acc[2 * i + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack2<BF16>(acc[0], acc[1]);
+    o.y = pack2<BF16>(acc[2], acc[3]);
+    o.z = pack2<BF16>(acc[4], acc[5]);
+    o.w = pack2<BF16>(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + t * h + v * 8) = o;
+  }
+}
+
+int blocks_for(int64_t items, int threads, int per_sm = 8) {
+  int sms = current_sm_count();
+  if (sms <= 0) sms = 148;
+  int64_t b = ceil_div(items, threads);
+  int64_t cap = static_cast<int64_t>(sms) * per_sm;
+  if (b < 1) b = 1;
+  return static_cast<int>(b < cap ? b : cap);
+}
+
+}  // namespace
+}  // namespace b200k
+
+using namespace b200k;
+
+extern "C" int64_t b200k_moe_align_workspace_bytes(int64_t num_replicas, int32_t num_experts) {
+  if (num_replicas < 0 || num_experts <= 0) return 0;
+  const int64_t chunks = ceil_div(num_replicas > 0 ? num_replicas : 1, kChunk);
+  return chunks * num_experts * static_cast<int64_t>(sizeof(int));
+}
+
+extern "C" int b200k_moe_align(const b200k_moe_align_args* a, b200k_stream stream_) {
+  if (a == nullptr) return fail(B200K_INVALID_ARG, "null args");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a->num_replicas < 0 || a->num_experts <= 0 || a->tile_m <= 0)
+    return fail(B200K_INVALID_ARG, "bad sizes");
+  if (a->num_experts > 2048) return fail(B200K_UNSUPPORTED, "at most 2048 experts");
+  if (a->num_replicas >= INT32_MAX) return fail(B200K_UNSUPPORTED, "too many token replicas");
+  if (!a->sorted_token_ids || !a->sorted_expert_ids || !a->num_blocks || !a->workspace)
+    return fail(B200K_INVALID_ARG, "null pointer");
+  if (a->num_replicas > 0 && !a->topk_ids) return fail(B200K_INVALID_ARG, "null topk_ids");
+  // worst case: every expert wastes tile_m - 1 slots
+  const int64_t need = a->num_replicas + static_cast<int64_t>(a->num_experts) * (a->tile_m - 1);
+  const int64_t need_blocks = ceil_div(need, a->tile_m);
+  if (a->capacity < need_blocks * a->tile_m || a->block_capacity < need_blocks)
+    return fail(B200K_INVALID_ARG, "capacity %lld / %lld too small: need %lld slots, %lld blocks",
+                (long long)a->capacity, (long long)a->block_capacity,
+                (long long)(need_blocks * a->tile_m), (long long)need_blocks);
+  const int chunks = static_cast<int>(ceil_div(a->num_replicas > 0 ? a->num_replicas : 1, kChunk));
+  if (a->workspace_bytes < static_cast<int64_t>(chunks) * a->num_experts * 4)
+    return fail(B200K_INVALID_ARG, "workspace too small");
+  int* counts = static_cast<int*>(a->workspace);
+  int* status = device_status_word();
+  const int grid = static_cast<int>(ceil_div(chunks, kAlignWarps));
+  const size_t smem = static_cast<size_t>(kAlignWarps) * a->num_experts * sizeof(int);
+  cudaError_t e = cudaMemsetAsync(counts, 0, static_cast<size_t>(chunks) * a->num_experts * 4, stream);
+  if (e != cudaSuccess) return fail(B200K_CUDA_ERROR, "memset: %s", cudaGetErrorString(e));
+  if (a->num_replicas > 0) {
+    if (a->ids_are_int64)
+      moe_count_kernel<long long><<<grid, kAlignWarps * 32, smem, stream>>>(
+          static_cast<const long long*>(a->topk_ids), a->num_replicas, a->num_experts, counts, status);
+    else
+      moe_count_kernel<int><<<grid, kAlignWarps * 32, smem, stream>>>(
+          static_cast<const int*>(a->topk_ids), a->num_replicas, a->num_experts, counts, status);
+  }
+  moe_offsets_kernel<<<1, 1024, 2 * a->num_experts * sizeof(int), stream>>>(
+      counts, chunks, a->num_experts, a->tile_m, a->num_replicas, a->sorted_token_ids, a->capacity,
+      a->sorted_expert_ids, a->block_capacity, a->num_blocks);
+  if (a->num_replicas > 0) {
+    if (a->ids_are_int64)
+      moe_scatter_kernel<long long><<<grid, kAlignWarps * 32, smem, stream>>>(
+          static_cast<const long long*>(a->topk_ids), a->num_replicas, a->num_experts, counts,
+          a->sorted_token_ids, status);
+    else
+      moe_scatter_kernel<int><<<grid, kAlignWarps * 32, smem, stream>>>(
+          static_cast<const int*>(a->topk_ids), a->num_replicas, a->num_experts, counts,
+          a->sorted_token_ids, status);
+  }
+  B200K_CHECK_LAUNCH("moe_align launch");
+  return B200K_OK;
+}
+
+extern "C" int b200k_gather_rows(const void* src, int64_t src_rows, int64_t row_bytes,
+                                 int64_t src_stride_bytes, const int32_t* index, int32_t divisor,
+                                 const int32_t* num_blocks, int32_t tile_m, int64_t max_rows,
+                                 void* dst, int64_t dst_stride_bytes, b200k_stream stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (max_rows < 0 || row_bytes < 0 || divisor <= 0) return fail(B200K_INVALID_ARG, "bad sizes");
+  if (max_rows == 0 || row_bytes == 0) return B200K_OK;
+  if (!src || !index || !dst) return fail(B200K_INVALID_ARG, "null pointer");
+  if (row_bytes % 16 || src_stride_bytes % 16 || dst_stride_bytes % 16 ||
+      (reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) % 16)
+    return fail(B200K_UNSUPPORTED, "rows must be multiples of 16 bytes on 16-byte boundaries");
+  const int grid = blocks_for(max_rows * 256, 256, 16);
+  gather_rows_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(src), src_rows, row_bytes,
+                                               src_stride_bytes, index, divisor, num_blocks, tile_m,
+                                               max_rows, static_cast<uint8_t*>(dst), dst_stride_bytes);
+  B200K_CHECK_LAUNCH("gather_rows launch");
+  return B200K_OK;
+}
+
+extern "C" int b200k_silu_and_mul(const void* ab, int64_t rows, int64_t n, int64_t ld_ab, void* c,
+                                  int64_t ld_c, int32_t dtype, b200k_stream stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (rows < 0 || n < 0) return fail(B200K_INVALID_ARG, "negative dimension");
+  if (rows == 0 || n == 0) return B200K_OK;
+  if (!ab || !c) return fail(B200K_INVALID_ARG, "null pointer");
+  if (n % 2 || ld_ab % 2 || ld_c % 2 ||
+      (reinterpret_cast<uintptr_t>(ab) | reinterpret_cast<uintptr_t>(c)) % 4)
+    return fail(B200K_UNSUPPORTED, "columns and leading dimensions must be even");
+  const int grid = blocks_for(rows * n / 2, 256);
+  if (dtype == B200K_BF16)
+    silu_and_mul_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(ab), rows, n, ld_ab,
+                                                        static_cast<uint16_t*>(c), ld_c);
+  else if (dtype == B200K_F16)
+    silu_and_mul_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(ab), rows, n, ld_ab,
+                                                         static_cast<uint16_t*>(c), ld_c);
+  else
+    return fail(B200K_INVALID_ARG, "dtype must be f16 or bf16");
+  B200K_CHECK_LAUNCH("silu_and_mul launch");
+  return B200K_OK;
+}
+
+extern "C" int b200k_topk_sum(const void* x, int64_t tokens, int32_t topk, int64_t hidden, void* out,
+                              int32_t dtype, b200k_stream stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (tokens < 0 || topk <= 0 || hidden < 0) return fail(B200K_INVALID_ARG, "bad sizes");
+  if (tokens == 0 || hidden == 0) return B200K_OK;
+  if (!x || !out) return fail(B200K_INVALID_ARG, "null pointer");
+  if (hidden % 8 || (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) % 16)
+    return fail(B200K_UNSUPPORTED, "hidden must be a multiple of 8 and buffers 16-byte aligned");
+  const int grid = blocks_for(tokens * hidden / 8, 256);
+  if (dtype == B200K_BF16)
+    topk_sum_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), tokens, topk, hidden,
+                                                    static_cast<uint16_t*>(out));
+  else if (dtype == B200K_F16)
+    topk_sum_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), tokens, topk, hidden,
+                                                     static_cast<uint16_t*>(out));
+  else
+    return fail(B200K_INVALID_ARG, "dtype must be f16 or bf16");
+  B200K_CHECK_LAUNCH("topk_sum launch");
+  return B200K_OK;
+}

@@ -74,8 +74,14 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 mxfp8_quantize_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t ldx,
                       uint8_t* __restrict__ q, int64_t ldq, uint8_t* __restrict__ sf_logical,
-                      uint8_t* __restrict__ sf_swizzled, int64_t k_atoms, int fmt_e5m2) {
+                      uint8_t* __restrict__ sf_swizzled, int64_t k_atoms, int fmt_e5m2,
+                      const int* __restrict__ gather_index, int gather_div, int64_t src_rows,
+                      const int* __restrict__ live_blocks, int tile_m) {
   const int64_t kblocks = (k + 31) >> 5;
+  if (live_blocks != nullptr) {
+    const int64_t live = static_cast<int64_t>(*live_blocks) * tile_m;
+    rows = live < rows ? live : rows;
+  }
   const int64_t total = rows * kblocks;
   const bool vec_in = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && ((ldx * sizeof(T)) % 16 == 0);
   const bool vec_out = (reinterpret_cast<uintptr_t>(q) % 16 == 0) && (ldq % 16 == 0);
@@ -85,7 +91,17 @@ mxfp8_quantize_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t 
     const int64_t kb = idx - row * kblocks;
     const int valid = static_cast<int>(k - kb * 32 < 32 ? k - kb * 32 : 32);
     float v[32];
-    load_block<T, 32>(x + row * ldx + kb * 32, v, vec_in, valid);
+    int64_t src_row = row;
+    if (gather_index != nullptr) {
+      const int g = gather_index[row];
+      src_row = (g >= 0 && g / gather_div < src_rows) ? g / gather_div : -1;
+    }
+    if (src_row >= 0) {
+      load_block<T, 32>(x + src_row * ldx + kb * 32, v, vec_in, valid);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+    }
     float amax = 0.0f;
     bool has_nan = false;
 #pragma unroll
@@ -350,15 +366,21 @@ extern "C" int b200k_mxfp8_quantize(const b200k_quantize_args* a, b200k_stream s
   switch (a->x_dtype) {
     case B200K_F32:
       mxfp8_quantize_kernel<float><<<grid, 256, 0, stream>>>(
-          static_cast<const float*>(a->x), a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, e5m2);
+          static_cast<const float*>(a->x), a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, e5m2,
+          a->gather_index, a->gather_divisor > 0 ? a->gather_divisor : 1, a->src_rows, a->live_blocks,
+          a->tile_m);
       break;
     case B200K_BF16:
       mxfp8_quantize_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
-          static_cast<const __nv_bfloat16*>(a->x), a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, e5m2);
+          static_cast<const __nv_bfloat16*>(a->x), a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, e5m2,
+          a->gather_index, a->gather_divisor > 0 ? a->gather_divisor : 1, a->src_rows, a->live_blocks,
+          a->tile_m);
       break;
     case B200K_F16:
       mxfp8_quantize_kernel<__half><<<grid, 256, 0, stream>>>(
-          static_cast<const __half*>(a->x), a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, e5m2);
+          static_cast<const __half*>(a->x), a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, e5m2,
+          a->gather_index, a->gather_divisor > 0 ? a->gather_divisor : 1, a->src_rows, a->live_blocks,
+          a->tile_m);
       break;
     default:
       return fail(B200K_INVALID_ARG, "x_dtype must be f32, bf16 or f16");

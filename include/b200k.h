@@ -150,6 +150,15 @@ typedef struct {
   int64_t sf_k_atoms;
   int32_t x_dtype;       /* B200K_F32 | BF16 | F16 */
   int32_t q_dtype;       /* mxfp8: B200K_E4M3 | E5M2 */
+  /* mxfp8 only, optional row gather (MoE permute fused into the quantiser): output row i
+   * is quantised from x row gather_index[i] / gather_divisor; an index outside
+   * [0, src_rows * gather_divisor) gives an all-zero row.  `live_blocks` (device) limits the
+   * work to the first *live_blocks * tile_m output rows. */
+  const int32_t* gather_index;
+  int32_t gather_divisor;
+  int32_t tile_m;
+  int64_t src_rows;
+  const int32_t* live_blocks;
 } b200k_quantize_args;
 
 /* MXFP8: replaces block_quantize(x, 32) (reference: test/kernels/kernel_utils.py:38-80)
@@ -188,6 +197,51 @@ int b200k_nvfp4_quantize_noalloc(const b200k_quantize_args* args, b200k_stream s
  * and blocks beyond `kblocks` inside the padded atoms are set to `fill`. */
 int b200k_sf_swizzle(const void* sf, int64_t rows, int64_t kblocks, int64_t ld, void* out,
                      int64_t k_atoms, int32_t fill, b200k_stream stream);
+
+/* ---- mixture-of-experts plumbing ---------------------------------------
+ * b200k_moe_align replaces moe_align_tile_size_torch (reference:
+ * test/kernels/fused_moe.py:113-173): token replicas (token * topk + slot) are sorted by
+ * expert (stable), every expert's run is padded to a multiple of tile_m with the sentinel
+ * num_replicas, and each tile_m block gets its expert id.  Unlike the reference it runs
+ * entirely on the device: outputs are worst-case sized (capacity >= num_replicas +
+ * num_experts * (tile_m - 1), rounded up to tile_m; block_capacity = capacity / tile_m),
+ * *num_blocks receives the number of blocks in use, slots beyond them hold the sentinel and
+ * block ids beyond them hold -1.  The first *num_blocks * tile_m ids and *num_blocks block
+ * ids equal the reference's outputs. */
+typedef struct {
+  const void* topk_ids;        /* (num_replicas) int32 or int64 expert ids */
+  int32_t* sorted_token_ids;   /* [capacity] */
+  int32_t* sorted_expert_ids;  /* [block_capacity] */
+  int32_t* num_blocks;         /* device scalar */
+  void* workspace;             /* b200k_moe_align_workspace_bytes() bytes of device memory */
+  int64_t workspace_bytes;
+  int64_t num_replicas;
+  int64_t capacity, block_capacity;
+  int32_t num_experts;
+  int32_t tile_m;
+  int32_t ids_are_int64;
+} b200k_moe_align_args;
+
+int64_t b200k_moe_align_workspace_bytes(int64_t num_replicas, int32_t num_experts);
+int b200k_moe_align(const b200k_moe_align_args* args, b200k_stream stream);
+
+/* dst row i = src row index[i] / divisor (zero row when the index is out of range): the
+ * row gather of fused_moe_kernel (reference: test/kernels/fused_moe.py:56-68).  With
+ * `num_blocks` only the first *num_blocks * tile_m rows are produced. */
+int b200k_gather_rows(const void* src, int64_t src_rows, int64_t row_bytes,
+                      int64_t src_stride_bytes, const int32_t* index, int32_t divisor,
+                      const int32_t* num_blocks, int32_t tile_m, int64_t max_rows, void* dst,
+                      int64_t dst_stride_bytes, b200k_stream stream);
+
+/* C[r, j] = silu(AB[r, j]) * AB[r, j + n], f16/bf16; replaces silu_and_mul_kernel
+ * (reference: test/kernels/fused_moe.py:85-108). */
+int b200k_silu_and_mul(const void* ab, int64_t rows, int64_t n, int64_t ld_ab, void* c,
+                       int64_t ld_c, int32_t dtype, b200k_stream stream);
+
+/* out[t, :] = sum over slot of x[t, slot, :] with fp32 accumulation; replaces
+ * torch.sum(intermediate_cache3, dim=1) (reference: samples/MoE.py:288). */
+int b200k_topk_sum(const void* x, int64_t tokens, int32_t topk, int64_t hidden, void* out,
+                   int32_t dtype, b200k_stream stream);
 
 /* ---- attention forward ------------------------------------------------
  * Out = softmax(qk_scale * Q K^T + mask) V per (batch, head); replaces fmha_kernel

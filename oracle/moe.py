@@ -13,7 +13,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-__all__ = ["moe_align_ref", "moe_ref", "moe_route_ref"]
+__all__ = ["moe_align_ref", "moe_ref", "moe_route_ref", "moe_mxfp8_ref"]
 
 
 def moe_align_ref(topk_ids: torch.Tensor, tile_m: int, num_experts: int):
@@ -55,3 +55,27 @@ def moe_route_ref(logits: torch.Tensor, topk: int):
     """top-k experts per token and softmax over the selected logits."""
     vals, ids = torch.topk(logits.detach().cpu().float(), topk, dim=-1)
     return torch.softmax(vals, dim=-1), ids
+
+
+def moe_mxfp8_ref(hidden, w1_q, w1_scale, w2_q, w2_scale, topk_weights, topk_ids,
+                  act_dtype=torch.bfloat16) -> torch.Tensor:
+    """The FFN of moe_ref with MXFP8 quantisation points made explicit (no counterpart in the
+    reference, which has only the bf16 form): expert weights given as (e4m3, ue8m0 / 32)
+    pairs, activations quantised per 32 elements before each projection, the SiLU-and-
+    multiply result rounded to `act_dtype` before it is re-quantised."""
+    from .quantize import block_quantize_ref, mxfp8_dequantize_ref
+    x = mxfp8_dequantize_ref(*block_quantize_ref(hidden))
+    w1 = mxfp8_dequantize_ref(w1_q, w1_scale)
+    w2 = mxfp8_dequantize_ref(w2_q, w2_scale)
+    tw = topk_weights.detach().cpu().float()
+    ids = topk_ids.detach().cpu()
+    inter = w2.shape[2]
+    out = torch.zeros(hidden.shape, dtype=torch.float32)
+    for e in ids.unique().tolist():
+        tok, slot = torch.where(ids == e)
+        h = x[tok] @ w1[e].T
+        act = (torch.nn.functional.silu(h[:, :inter]) * h[:, inter:]).to(act_dtype)
+        act = mxfp8_dequantize_ref(*block_quantize_ref(act))
+        y = ((act @ w2[e].T) * tw[tok, slot].unsqueeze(-1)).to(act_dtype).float()
+        out.index_add_(0, tok, y)
+    return out
