@@ -96,6 +96,15 @@ class FmhaArgs(Structure):
     ]
 
 
+class PeerGatherArgs(Structure):
+    _fields_ = [
+        ("shards", POINTER(c_void_p)), ("dst", c_void_p),
+        ("rows", c_int64), ("row_bytes", c_int64),
+        ("src_stride_bytes", c_int64), ("dst_stride_bytes", c_int64),
+        ("world", c_int32), ("rank", c_int32), ("round_tf32", c_int32),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/b200k.h declares
 SIGNATURES = {
     "b200k_version": (c_char_p, []),
@@ -114,6 +123,7 @@ SIGNATURES = {
     "b200k_silu_and_mul": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int32,
                                    c_void_p]),
     "b200k_topk_sum": (c_int, [c_void_p, c_int64, c_int32, c_int64, c_void_p, c_int32, c_void_p]),
+    "b200k_peer_gather": (c_int, [POINTER(PeerGatherArgs), c_void_p]),
     "b200k_fmha_fwd": (c_int, [POINTER(FmhaArgs), c_void_p]),
     "b200k_sf_swizzle": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int32,
                                  c_void_p]),

@@ -1,0 +1,133 @@
+"""AllGather + matmul with the entry point of the reference's sample.
+
+cutile_gather_matmul   samples/AllGatherMatmul.py:85-120
+    out[(p * M + m), :] = inp_p[m, :] @ w  for every rank p, on every rank.
+
+Each rank pulls the other ranks' shards out of their symmetric-memory buffers into a local
+staging buffer with one kernel (plain peer loads over NVLink, all peers at once) and runs
+the tcgen05 GEMM on the staged A.  As in the sample, the caller makes the peers' inputs
+visible first (a barrier) and keeps them unchanged until every rank has finished.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .block_scaled import _as_u8, _scaled_gemm
+from .matmul import _gemm
+
+
+def shard_rows(total_rows: int, world: int, rank: int) -> tuple[int, int]:
+    """[begin, end) of the rows rank owns when `total_rows` are split evenly."""
+    if total_rows % world:
+        raise ValueError(f"{total_rows} rows do not split evenly over {world} ranks")
+    per = total_rows // world
+    return rank * per, (rank + 1) * per
+
+
+def peer_buffers(t: torch.Tensor, group) -> list[torch.Tensor]:
+    """The same symmetric-memory tensor as seen on every rank (index = rank)."""
+    import torch.distributed._symmetric_memory as symm_mem
+    handle = symm_mem.rendezvous(t, group.group_name)
+    return [handle.get_buffer(r, t.shape, t.dtype, 0) for r in range(handle.world_size)]
+
+
+def peer_gather(shards: list[torch.Tensor], rank: int, *, round_tf32: bool = False,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """Concatenates `shards` (one (rows, cols) tensor per rank, peer-mapped) along dim 0 into
+    a local tensor."""
+    world = len(shards)
+    mine = shards[rank]
+    rows, cols = mine.shape
+    if any(s.shape != mine.shape or s.dtype != mine.dtype or s.stride() != mine.stride() for s in shards):
+        raise ValueError("all shards must have the same shape, dtype and strides")
+    if mine.stride(1) != 1:
+        raise ValueError("shards must have contiguous rows")
+    if out is None:
+        out = torch.empty((world * rows, cols), dtype=mine.dtype, device=mine.device)
+    ptrs = (ctypes.c_void_p * world)(*[s.data_ptr() for s in shards])
+    a = _lib.PeerGatherArgs()
+    a.shards = ctypes.cast(ptrs, ctypes.POINTER(ctypes.c_void_p))
+    a.dst = out.data_ptr()
+    a.rows, a.row_bytes = rows, cols * mine.element_size()
+    a.src_stride_bytes = mine.stride(0) * mine.element_size()
+    a.dst_stride_bytes = out.stride(0) * out.element_size()
+    a.world, a.rank = world, rank
+    a.round_tf32 = 1 if (round_tf32 and mine.dtype == torch.float32) else 0
+    with torch.cuda.device(mine.device):
+        _lib.check(_lib.lib().b200k_peer_gather(ctypes.byref(a), _lib.stream_ptr(mine.device)))
+    return out
+
+
+def _round_tf32(t: torch.Tensor) -> torch.Tensor:
+    """fp32 -> nearest tf32 value (ties away from zero), still stored as fp32."""
+    bits = t.contiguous().view(torch.int32)
+    return ((bits + 0x1000) & ~0x1FFF).view(torch.float32)
+
+
+def cutile_gather_matmul(inp: torch.Tensor, w: torch.Tensor, group=None, *,
+                         transport: str = "p2p") -> torch.Tensor:
+    """out (M * world, N) = concat over ranks of inp_p (M, K) @ w (K, N).
+
+    ``inp`` must live in symmetric memory (``torch.distributed._symmetric_memory.empty``)
+    for the default "p2p" transport; "nccl" gathers with ``all_gather_into_tensor``
+    instead and accepts any tensor.  fp32 operands are rounded to tf32 and multiplied on
+    the tensor cores, as in the reference kernel (samples/AllGatherMatmul.py:57)."""
+    if group is None:
+        group = dist.group.WORLD
+    if inp.dim() != 2 or w.dim() != 2:
+        raise ValueError("inp and w must be 2-D")
+    if inp.shape[1] != w.shape[0]:
+        raise ValueError("reduction dimension mismatch")
+    if not inp.is_cuda or inp.device != w.device:
+        raise ValueError("Input tensors must be on the same CUDA device.")
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    m, k = inp.shape
+    n = w.shape[1]
+    fp32 = inp.dtype == torch.float32
+    if transport == "p2p":
+        staged = peer_gather(peer_buffers(inp, group), rank, round_tf32=fp32)
+    elif transport == "nccl":
+        staged = torch.empty((world * m, k), dtype=inp.dtype, device=inp.device)
+        dist.all_gather_into_tensor(staged, inp.contiguous(), group=group)
+        if fp32:
+            staged = _round_tf32(staged)
+    else:
+        raise ValueError("transport must be 'p2p' or 'nccl'")
+    if fp32:
+        w = _round_tf32(w.T).T      # (N, K) K-contiguous storage, viewed as (K, N)
+    out = torch.empty((world * m, n), dtype=inp.dtype, device=inp.device)
+    if world * m == 0 or n == 0:
+        return out
+    return _gemm(staged, w, out)
+
+
+def cutile_gather_matmul_nvfp4(a_q: torch.Tensor, a_sf: torch.Tensor, a_ts: torch.Tensor,
+                               w_q: torch.Tensor, w_sf: torch.Tensor, w_ts: torch.Tensor,
+                               group=None, *, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """AllGather GEMM on NVFP4 operands: each rank contributes the quantised rows it owns —
+    a_q (M, K/2) packed e2m1, a_sf its swizzled ue4m3 scales (M/128, K/64, 32, 16), a_ts its
+    fp32 tensor scale (1,) — all three in symmetric memory; w_q (N, K/2), w_sf, w_ts are this
+    rank's weights.  M must be a multiple of 128 so that scale atoms do not straddle ranks.
+    Returns (M * world, N)."""
+    if group is None:
+        group = dist.group.WORLD
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    m = a_q.shape[0]
+    if m % 128:
+        raise ValueError("rows per rank must be a multiple of 128")
+    q = peer_gather(peer_buffers(_as_u8(a_q), group), rank)
+    sf_flat = _as_u8(a_sf).reshape(a_sf.shape[0], -1)
+    sf = peer_gather(peer_buffers(sf_flat, group), rank)
+    sf = sf.reshape(world * a_sf.shape[0], *a_sf.shape[1:])
+    ts_all = torch.cat([t.reshape(1) for t in peer_buffers(a_ts, group)])
+    row_scale = ts_all.repeat_interleave(m)
+    n = w_q.shape[0]
+    out = torch.empty((world * m, n), dtype=out_dtype, device=a_q.device)
+    return _scaled_gemm(q, sf, _as_u8(w_q), _as_u8(w_sf), out, fp4=True, alpha_b=w_ts,
+                        row_scale=row_scale)

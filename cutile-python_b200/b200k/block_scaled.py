@@ -159,7 +159,7 @@ def nvfp4_quantize(x: torch.Tensor, *, swizzled_scale: bool = True):
 
 
 def _scaled_gemm(a_km, sfa, b_nk, sfb, c, *, fp4: bool, alpha: float = 1.0, alpha_a=None,
-                 alpha_b=None, max_ctas: int = 0):
+                 alpha_b=None, max_ctas: int = 0, row_scale=None):
     """a_km (M, Kp), b_nk (N, Kp) K-contiguous byte tensors (Kp = K or K/2 bytes);
     sfa/sfb swizzled 4-D byte tensors."""
     m, kp = a_km.shape
@@ -181,6 +181,7 @@ def _scaled_gemm(a_km, sfa, b_nk, sfb, c, *, fp4: bool, alpha: float = 1.0, alph
     args.alpha_a = _lib.ptr(alpha_a)
     args.alpha_b = _lib.ptr(alpha_b)
     args.max_ctas = max_ctas
+    args.row_scale = _lib.ptr(row_scale)
     with torch.cuda.device(c.device):
         _lib.check(_lib.lib().b200k_block_scaled_gemm(ctypes.byref(args), _lib.stream_ptr(c.device)))
     return c

@@ -243,6 +243,23 @@ int b200k_silu_and_mul(const void* ab, int64_t rows, int64_t n, int64_t ld_ab, v
 int b200k_topk_sum(const void* x, int64_t tokens, int32_t topk, int64_t hidden, void* out,
                    int32_t dtype, b200k_stream stream);
 
+/* ---- peer-memory gather (AllGather GEMM) -------------------------------
+ * dst rows [p * rows, (p + 1) * rows) = shard p, read through `shards[p]`, a pointer this
+ * process can dereference (its own buffer for p == rank, peer-mapped buffers otherwise).
+ * Together with b200k_gemm / b200k_block_scaled_gemm on `dst` this replaces
+ * gather_matmul_kernel (reference: samples/AllGatherMatmul.py:28-120).  `round_tf32`
+ * rounds fp32 payload to tf32 (nearest) on the way, as the reference kernel's cast does. */
+typedef struct {
+  const void* const* shards;   /* host array of `world` device pointers */
+  void* dst;
+  int64_t rows, row_bytes;
+  int64_t src_stride_bytes, dst_stride_bytes;
+  int32_t world, rank;
+  int32_t round_tf32;
+} b200k_peer_gather_args;
+
+int b200k_peer_gather(const b200k_peer_gather_args* args, b200k_stream stream);
+
 /* ---- attention forward ------------------------------------------------
  * Out = softmax(qk_scale * Q K^T + mask) V per (batch, head); replaces fmha_kernel
  * (reference: test/kernels/attention.py:20-128) behind cutile_fmha
