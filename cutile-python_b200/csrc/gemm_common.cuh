@@ -1,0 +1,156 @@
+// Pieces shared by the GEMM kernels: launch parameters, per-kind traits, the grouped tile
+// raster and the row-chunk store of the epilogue.
+#pragma once
+#include "common.cuh"
+#include "host.h"
+
+namespace b200k {
+
+constexpr int kBM = 128;
+constexpr int kStages = 4;
+constexpr int kGroupM = 8;
+constexpr int kNumThreads = 192;
+constexpr int kTmemCols = 512;
+
+enum OutType : int { kOutF16 = 0, kOutBF16 = 1, kOutF32 = 2 };
+
+struct GemmParams {
+  void* c;
+  int m, n, k;          // k in elements
+  int batch;
+  int64_t ldc;          // elements
+  int64_t stride_c;     // elements
+  int tiles_m, tiles_n;
+  int k_iters;
+  int k_tail_mmas;      // MMAs of the last k iteration (1..4)
+  uint32_t idesc;
+  float alpha;
+  const float* alpha_a;
+  const float* alpha_b;
+  // scale factors (swizzled atoms of 512 bytes)
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  int sf_k_atoms;
+  int sfb_row_tiles;    // 128-row tiles present in sfb (reads are clamped to it)
+  int64_t stride_sfa, stride_sfb;
+  // grouped mode
+  const int* tile_group;
+  const int* num_row_tiles;
+  const int* row_map;
+  const float* row_scale;
+  int64_t c_rows;
+  int epilogue;
+  int* status;
+};
+
+template <int KIND>
+struct KindTraits;
+template <> struct KindTraits<kKindF16>  { static constexpr int kElemBits = 16; static constexpr bool kScaled = false; };
+template <> struct KindTraits<kKindTF32> { static constexpr int kElemBits = 32; static constexpr bool kScaled = false; };
+template <> struct KindTraits<kKindF8>   { static constexpr int kElemBits = 8;  static constexpr bool kScaled = false; };
+template <> struct KindTraits<kKindMXF8> { static constexpr int kElemBits = 8;  static constexpr bool kScaled = true;
+                                           static constexpr int kSfBlock = 32; };
+template <> struct KindTraits<kKindNVF4> { static constexpr int kElemBits = 4;  static constexpr bool kScaled = true;
+                                           static constexpr int kSfBlock = 16; };
+
+template <int KIND, int BN, bool B_MN>
+struct GemmCfg {
+  using T = KindTraits<KIND>;
+  static constexpr int kBKElems = 128 * 8 / T::kElemBits;  // K elements per stage
+  static constexpr int kMmaK = kBKElems / 4;               // 32 bytes of K per MMA
+  static constexpr int kABytes = kBM * 128;
+  static constexpr int kBBytes = BN * 128;
+  // MN-major B: boxes of (128 bytes of N) x (kBKElems rows of K)
+  static constexpr int kBBoxN = 128 * 8 / T::kElemBits;    // N elements per 128-byte row
+  static constexpr int kBBoxBytes = kBKElems * 128;
+  static constexpr int kBBoxes = B_MN ? BN / kBBoxN : BN / 128;
+  static constexpr bool kScaled = T::kScaled;
+  static constexpr int kSfaAtoms = kScaled ? (KIND == kKindNVF4 ? 4 : 1) : 0;  // per stage
+  static constexpr int kSfbAtoms = kSfaAtoms * (BN / 128);
+  static constexpr int kSfBytes = (kSfaAtoms + kSfbAtoms) * 512;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kNumAcc = kScaled ? 1 : (BN <= 256 ? 512 / 256 : 1);
+  static constexpr int kAccStride = 256;
+  static constexpr int kSfTmemBase = 256;
+  static constexpr int kSfaCols = kSfaAtoms * 4;
+  static constexpr int kSfbCols = kSfbAtoms * 4;
+  static constexpr int kSmemBytes =
+      1024 /*alignment slack*/ + kStages * (kStageBytes + kSfBytes) + 256 /*barriers*/;
+  static_assert(!kScaled || kSfTmemBase + kStages * (kSfaCols + kSfbCols) <= kTmemCols,
+                "scale factors do not fit in tensor memory");
+  static_assert(!(B_MN && KIND == kKindNVF4), "fp4 operands are K-major only");
+};
+
+struct TileCoord {
+  int batch, pid_m, pid_n;
+};
+
+// Grouped raster order: consecutive tile ids walk kGroupM row tiles before moving to
+// the next column tile, which keeps a band of A and one B tile hot in L2.
+__device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles_n) {
+  int per_batch = tiles_m * tiles_n;
+  TileCoord c;
+  c.batch = tile / per_batch;
+  int t = tile - c.batch * per_batch;
+  int group_tiles = kGroupM * tiles_n;
+  int group = t / group_tiles;
+  int first_m = group * kGroupM;
+  int rows = min(kGroupM, tiles_m - first_m);
+  int in_group = t - group * group_tiles;
+  c.pid_m = first_m + in_group % rows;
+  c.pid_n = in_group / rows;
+  return c;
+}
+
+template <int OUT>
+__device__ __forceinline__ void store_row_chunk(void* c_row, int col0, int n_limit,
+                                                const float (&v)[32], bool vec_ok) {
+  // 32 consecutive output columns of one row, starting at col0.
+  if constexpr (OUT == kOutF32) {
+    float* dst = static_cast<float*>(c_row) + col0;
+    if (vec_ok && col0 + 32 <= n_limit) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < n_limit) dst[i] = v[i];
+    }
+  } else {
+    uint16_t* dst = static_cast<uint16_t*>(c_row) + col0;
+    if (vec_ok && col0 + 32 <= n_limit) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 q;
+        if constexpr (OUT == kOutBF16) {
+          q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+          q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+          q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+          q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+        } else {
+          q.x = pack_f16x2(v[8 * i + 0], v[8 * i + 1]);
+          q.y = pack_f16x2(v[8 * i + 2], v[8 * i + 3]);
+          q.z = pack_f16x2(v[8 * i + 4], v[8 * i + 5]);
+          q.w = pack_f16x2(v[8 * i + 6], v[8 * i + 7]);
+        }
+        reinterpret_cast<uint4*>(dst)[i] = q;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (col0 + i < n_limit) {
+          if constexpr (OUT == kOutBF16) {
+            __nv_bfloat16 h = __float2bfloat16_rn(v[i]);
+            dst[i] = *reinterpret_cast<uint16_t*>(&h);
+          } else {
+            __half h = __float2half_rn(v[i]);
+            dst[i] = *reinterpret_cast<uint16_t*>(&h);
+          }
+        }
+      }
+    }
+  }
+}
+
+}  // namespace b200k

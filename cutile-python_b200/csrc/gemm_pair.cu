@@ -1,0 +1,337 @@
+// GEMM on CTA pairs (tcgen05 cta_group::2): two CTAs of a cluster share one 256 x 256
+// output tile.  Each CTA loads its 128 rows of A and its 128 of the 256 rows of B per
+// stage (32 KB instead of 48 KB, and 4.3 GB instead of 6.4 GB out of L2 for an 8192^3
+// problem), the pair's leader issues 256 x 256 MMAs that read both halves, and each CTA
+// drains its own 128 accumulator rows from its own tensor memory.
+//
+// No load in this file is a multicast: every CTA fetches its own tiles (scale-factor
+// atoms of B are simply fetched by both) and reports the bytes to the leader's mbarrier.
+//
+//   warp 0      TMA producer, one lane, in both CTAs
+//   warp 1      MMA issuer, one lane, leader CTA only (allocates TMEM in both)
+//   warps 2..5  epilogue, both CTAs
+//
+// Two accumulator windows let a tile's epilogue overlap the next tile's mainloop.  The
+// block-scaled kinds also need TMEM columns for scale factors, so their windows overlap
+// by 32 (MXFP8) or 64 (NVFP4) columns: the epilogue drains the shared columns first and
+// releases them early; the next tile's first MMA waits only for that.
+#include "gemm_common.cuh"
+#include "gemm_pair.h"
+
+namespace b200k {
+
+template <int KIND>
+struct PairCfg {
+  using T = KindTraits<KIND>;
+  static constexpr bool kScaled = T::kScaled;
+  static constexpr int kBKElems = 128 * 8 / T::kElemBits;
+  static constexpr int kStages = (KIND == kKindNVF4) ? 5 : 6;
+  static constexpr int kABytes = 128 * 128;
+  static constexpr int kBBytes = 128 * 128;          // this CTA's half of the 256 B rows
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kSfAtoms = kScaled ? (KIND == kKindNVF4 ? 4 : 1) : 0;  // along K, per stage
+  static constexpr int kSfBytes = kSfAtoms * 512 * 3;                       // SFA + both SFB row tiles
+  static constexpr int kAccStride = !kScaled ? 256 : (KIND == kKindNVF4 ? 192 : 224);
+  static constexpr int kOverlapChunks = (256 - kAccStride) / 32;
+  static constexpr int kSfBase = 2 * kAccStride + 32 * kOverlapChunks;     // 480 / 448
+  static constexpr int kSfSlots = (KIND == kKindMXF8) ? 2 : 1;
+  static constexpr int kSfaCols = kSfAtoms * 4;
+  static constexpr int kSfSlotCols = kSfAtoms * 12;
+  static constexpr int kSmemBytes = 1024 + kStages * (kStageBytes + kSfBytes) + 256;
+  static_assert(!kScaled || kSfBase + kSfSlots * kSfSlotCols <= 512, "TMEM budget");
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
+};
+
+template <int KIND, int OUT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_sfa,
+                 const __grid_constant__ CUtensorMap tmap_sfb, const GemmParams p) {
+  using Cfg = PairCfg<KIND>;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t tiles_base = smem_base;
+  const uint32_t sf_base = tiles_base + S * Cfg::kStageBytes;
+  uint8_t* tail = smem + S * (Cfg::kStageBytes + Cfg::kSfBytes);
+  const uint32_t bar_base = smem_u32(tail);
+  // full[S], empty[S], acc_full[2], acc_empty[2], ovl_free
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
+  auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * S + a); };
+  auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * S + 2 + a); };
+  const uint32_t ovl_free_bar = bar_base + 8u * (2 * S + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * S + 5));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8 * (2 * S + 5) + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 8);   // 4 epilogue warps in each CTA of the pair
+    }
+    mbar_init(ovl_free_bar, 8);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_m = (p.m + 255) / 256;
+  const int num_tiles = tiles_m * p.tiles_n * p.batch;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
+        const int m0 = tc.pid_m * 256 + rank * 128;
+        const int nb = tc.pid_n * 256 + rank * 128;
+        for (int kb = 0; kb < p.k_iters; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) {
+            report_status(p.status, 51, s);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          // the leader's barrier collects the bytes of both CTAs
+          const uint32_t lead_full = map_to_cta(full_bar(s), 0);
+          if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * (Cfg::kStageBytes + Cfg::kSfBytes));
+          const uint32_t a_dst = tiles_base + s * Cfg::kStageBytes;
+          const uint32_t b_dst = a_dst + Cfg::kABytes;
+          const int kx = kb * (KIND == kKindNVF4 ? 128 : Cfg::kBKElems);
+          tma_load_3d_pair(a_dst, &tmap_a, lead_full, kx, m0, tc.batch);
+          tma_load_3d_pair(b_dst, &tmap_b, lead_full, kx, nb, tc.batch);
+          if constexpr (Cfg::kScaled) {
+            const uint32_t sfa_dst = sf_base + s * Cfg::kSfBytes;
+            const uint32_t sfb_dst = sfa_dst + Cfg::kSfAtoms * 512;
+            tma_load_4d_pair(sfa_dst, &tmap_sfa, lead_full, 0, 0, kb * Cfg::kSfAtoms, tc.pid_m * 2 + rank);
+            tma_load_4d_pair(sfb_dst, &tmap_sfb, lead_full, 0, 0, kb * Cfg::kSfAtoms, tc.pid_n * 2);
+            tma_load_4d_pair(sfb_dst + Cfg::kSfAtoms * 512, &tmap_sfb, lead_full, 0, 0,
+                             kb * Cfg::kSfAtoms, tc.pid_n * 2 + 1);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader only) ----------------
+    if (lane == 0 && leader) {
+      uint32_t it = 0;
+      uint32_t lt = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++lt) {
+        const int w = lt & 1;
+        if (!mbar_wait(acc_empty_bar(w), ((lt >> 1) & 1) ^ 1, abort_flag)) {
+          report_status(p.status, 52, 100 + w);
+          *abort_flag = 1;
+          break;
+        }
+        if (Cfg::kOverlapChunks > 0 && lt > 0) {
+          if (!mbar_wait(ovl_free_bar, (lt - 1) & 1, abort_flag)) {
+            report_status(p.status, 52, 200);
+            *abort_flag = 1;
+            break;
+          }
+        }
+        tc_fence_after_sync();
+        const uint32_t tmem_acc = tmem_base + w * Cfg::kAccStride;
+        for (int kb = 0; kb < p.k_iters; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait(full_bar(s), ph, abort_flag)) {
+            report_status(p.status, 52, s);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = tiles_base + s * Cfg::kStageBytes;
+          const uint32_t b_addr = a_addr + Cfg::kABytes;
+          const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024, kSwizzle128B);
+          const uint64_t b_desc = make_smem_desc(b_addr, 16, 1024, kSwizzle128B);
+          const int n_mma = (kb == p.k_iters - 1) ? p.k_tail_mmas : 4;
+          uint32_t tsfa = 0, tsfb = 0;
+          if constexpr (Cfg::kScaled) {
+            const int slot = (Cfg::kSfSlots == 2) ? (it & 1) : 0;
+            tsfa = tmem_base + Cfg::kSfBase + slot * Cfg::kSfSlotCols;
+            tsfb = tsfa + Cfg::kSfaCols;
+            const uint32_t sfa_addr = sf_base + s * Cfg::kSfBytes;
+            const uint32_t sfb_addr = sfa_addr + Cfg::kSfAtoms * 512;
+#pragma unroll
+            for (int ka = 0; ka < Cfg::kSfAtoms; ++ka) {
+              tmem_cp_sf_atom_pair(tsfa + ka * 4, make_smem_desc(sfa_addr + ka * 512, 128, 128, kSwizzleNone));
+#pragma unroll
+              for (int j = 0; j < 2; ++j)
+                tmem_cp_sf_atom_pair(tsfb + ka * 8 + j * 4,
+                                     make_smem_desc(sfb_addr + (j * Cfg::kSfAtoms + ka) * 512, 128, 128, kSwizzleNone));
+            }
+          }
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            if (kk < n_mma) {
+              const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
+              const uint64_t a_d = a_desc + static_cast<uint64_t>(kk * 2);
+              const uint64_t b_d = b_desc + static_cast<uint64_t>(kk * 2);
+              if constexpr (KIND == kKindMXF8) {
+                umma_block_scaled_pair<KIND>(tmem_acc, a_d, b_d,
+                                             p.idesc | (uint32_t(kk) << 29) | (uint32_t(kk) << 4), acc, tsfa, tsfb);
+              } else if constexpr (KIND == kKindNVF4) {
+                umma_block_scaled_pair<KIND>(tmem_acc, a_d, b_d, p.idesc, acc, tsfa + kk * 4, tsfb + kk * 8);
+              } else {
+                umma_pair<KIND>(tmem_acc, a_d, b_d, p.idesc, acc);
+              }
+            }
+          }
+          // release the stage in both CTAs
+          tc_commit_pair(map_to_cta(empty_bar(s), 0));
+          tc_commit_pair(map_to_cta(empty_bar(s), 1));
+        }
+        if (ok) {
+          tc_commit_pair(map_to_cta(acc_full_bar(w), 0));
+          tc_commit_pair(map_to_cta(acc_full_bar(w), 1));
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue (both CTAs) ----------------
+    const int quarter = warp & 3;
+    float alpha = p.alpha;
+    if (p.alpha_a != nullptr) alpha *= *p.alpha_a;
+    if (p.alpha_b != nullptr) alpha *= *p.alpha_b;
+    const int elem_bytes = (OUT == kOutF32) ? 4 : 2;
+    const bool vec_ok = ((p.ldc * elem_bytes) % 16 == 0) && ((p.stride_c * elem_bytes) % 16 == 0) &&
+                        (reinterpret_cast<uintptr_t>(p.c) % 16 == 0);
+    const uint32_t lead_ovl = map_to_cta(ovl_free_bar, 0);
+    uint32_t lt = 0;
+    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++lt) {
+      const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
+      const int w = lt & 1;
+      if (!mbar_wait(acc_full_bar(w), (lt >> 1) & 1, abort_flag)) {
+        report_status(p.status, 53, w);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = tc.pid_m * 256 + rank * 128 + quarter * 32 + lane;
+      const bool row_ok = row < p.m;
+      float scale = alpha;
+      if (p.row_scale != nullptr && row_ok) scale *= p.row_scale[row];
+      uint8_t* c_row = static_cast<uint8_t*>(p.c) +
+                       (static_cast<int64_t>(tc.batch) * p.stride_c + static_cast<int64_t>(row) * p.ldc) * elem_bytes;
+      const uint32_t taddr = tmem_base + w * Cfg::kAccStride + (uint32_t(quarter * 32) << 16);
+      const int n0 = tc.pid_n * 256;
+      // columns shared with the other window first: the last chunks of window 0, the first
+      // chunks of window 1
+      const int first = (w == 0) ? (8 - Cfg::kOverlapChunks) & 7 : 0;
+      if (Cfg::kOverlapChunks == 0) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(lead_ovl);
+      }
+#pragma unroll 1
+      for (int ci = 0; ci < 8; ++ci) {
+        const int c = (first + ci) & 7;
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (Cfg::kOverlapChunks > 0 && ci == Cfg::kOverlapChunks - 1) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(lead_ovl);
+        }
+        if (row_ok && n0 + c * 32 < p.n) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * scale;
+          store_row_chunk<OUT>(c_row, n0 + c * 32, p.n, v, vec_ok);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(w), 0));
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();   // the peer may still be reading our barriers / TMEM pairing
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+namespace {
+
+template <int KIND, int OUT>
+int launch_pair(const CUtensorMap* maps, const GemmParams& p, int grid, cudaStream_t stream) {
+  using Cfg = PairCfg<KIND>;
+  auto kernel = gemm_pair_kernel<KIND, OUT>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess)
+      return fail(B200K_CUDA_ERROR, "cudaFuncSetAttribute(%d bytes): %s", Cfg::kSmemBytes, cudaGetErrorString(e));
+    configured[dev] = true;
+  }
+  kernel<<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+  B200K_CHECK_LAUNCH("gemm (CTA pair) launch");
+  return B200K_OK;
+}
+
+template <int KIND>
+int launch_pair_out(int out, const CUtensorMap* maps, const GemmParams& p, int grid, cudaStream_t stream) {
+  switch (out) {
+    case B200K_F16: return launch_pair<KIND, kOutF16>(maps, p, grid, stream);
+    case B200K_BF16: return launch_pair<KIND, kOutBF16>(maps, p, grid, stream);
+    case B200K_F32: return launch_pair<KIND, kOutF32>(maps, p, grid, stream);
+    default: return fail(B200K_INVALID_ARG, "unsupported output dtype %d", out);
+  }
+}
+
+}  // namespace
+
+int launch_gemm_pair(int kind, int out_dtype, const CUtensorMap* maps, const GemmParams& p, int sms,
+                     cudaStream_t stream) {
+  const int64_t tiles = static_cast<int64_t>((p.m + 255) / 256) * p.tiles_n * p.batch;
+  int clusters = static_cast<int>(tiles < sms / 2 ? tiles : sms / 2);
+  if (clusters < 1) clusters = 1;
+  const int grid = clusters * 2;
+  switch (kind) {
+    case kKindF16: return launch_pair_out<kKindF16>(out_dtype, maps, p, grid, stream);
+    case kKindTF32: return launch_pair_out<kKindTF32>(out_dtype, maps, p, grid, stream);
+    case kKindF8: return launch_pair_out<kKindF8>(out_dtype, maps, p, grid, stream);
+    case kKindMXF8: return launch_pair_out<kKindMXF8>(out_dtype, maps, p, grid, stream);
+    case kKindNVF4: return launch_pair_out<kKindNVF4>(out_dtype, maps, p, grid, stream);
+    default: return fail(B200K_INVALID_ARG, "unknown kind %d", kind);
+  }
+}
+
+}  // namespace b200k
