@@ -12,7 +12,8 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int6
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libb200k.so")
+# B200K_LIB points at an alternative build of the library (e.g. one with tracing compiled in)
+LIB_PATH = os.environ.get("B200K_LIB") or os.path.join(_HERE, "libb200k.so")
 
 # enum b200k_dtype
 F16, BF16, F32, E4M3, E5M2, E2M1X2 = range(6)

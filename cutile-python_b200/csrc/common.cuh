@@ -119,6 +119,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   }
 }
 
+// Same contract, for roles whose wake-up latency does not matter (epilogue warps waiting
+// for a whole tile, producers waiting for a free stage): the thread sleeps between polls,
+// so a waiting warp costs no issue slots and little power.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
+                                                  volatile int* abort_flag, uint32_t sleep_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = 0;
+  for (uint32_t it = 1;; ++it) {
+    __nanosleep(sleep_ns);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 0xff) == 0) {
+      if (*abort_flag) return false;
+      uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitBudgetNs) return false;
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // TMA (bulk tensor copies, never with cluster multicast)
 // ---------------------------------------------------------------------------

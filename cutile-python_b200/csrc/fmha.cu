@@ -219,9 +219,14 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         for (int i = 0; i < 128; ++i)
           if (key0 + i > limit) s[i] = -INFINITY;
       }
-      float mx = s[0];
+      // eight independent chains keep the max / sum reductions off the critical path
+      float mx8[8];
 #pragma unroll
-      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+      for (int i = 0; i < 8; ++i) mx8[i] = s[i];
+#pragma unroll
+      for (int i = 8; i < 128; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], s[i]);
+      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       // Deferred rescale: keep the stale maximum while the true one is less than 2^8
       // above it.  A row whose maximum is still -inf has seen no key yet.
@@ -246,7 +251,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
       }
       const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
-      float sum = 0.0f;
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t pk[32];
@@ -254,12 +259,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         for (int i = 0; i < 32; ++i) {
           const float p0 = fast_exp2(fmaf(s[c * 64 + 2 * i], p.scale_log2, neg_m));
           const float p1 = fast_exp2(fmaf(s[c * 64 + 2 * i + 1], p.scale_log2, neg_m));
-          sum += p0 + p1;
+          sum4[i & 3] += p0 + p1;
           pk[i] = BF16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
         }
         tmem_st_32x32b_x32(tmem_s + lane_addr + c * 32, pk);
       }
-      l += sum;
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();

@@ -20,6 +20,20 @@
 
 namespace b200k {
 
+#ifdef B200K_TRACE
+// Debug build only: cycle counters summed over all CTAs.
+// 0 producer wait(empty), 1 producer total, 2 mma wait(full), 3 mma wait(acc), 4 mma total,
+// 5 epilogue wait(acc_full), 6 epilogue total, 7 mma issue (descs + cp + mma + commit)
+__device__ unsigned long long g_trace[16];
+#define TRACE_T0(var) long long var = clock64()
+#define TRACE_ADD(idx, var) atomicAdd(&g_trace[idx], static_cast<unsigned long long>(clock64() - (var)))
+#define TRACE_ACC(acc, var) acc += clock64() - (var)
+#else
+#define TRACE_T0(var)
+#define TRACE_ADD(idx, var)
+#define TRACE_ACC(acc, var)
+#endif
+
 template <int KIND>
 struct PairCfg {
   using T = KindTraits<KIND>;
@@ -105,6 +119,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      TRACE_T0(t_total);
+#ifdef B200K_TRACE
+      long long w_empty = 0;
+#endif
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
         const int m0 = tc.pid_m * 256 + rank * 128;
@@ -112,12 +130,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int kb = 0; kb < p.k_iters; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) {
+          TRACE_T0(t_w);
+          if (!mbar_wait_relaxed(empty_bar(s), ph ^ 1, abort_flag, 64)) {
             report_status(p.status, 51, s);
             *abort_flag = 1;
             ok = false;
             break;
           }
+          TRACE_ACC(w_empty, t_w);
           // the leader's barrier collects the bytes of both CTAs
           const uint32_t lead_full = map_to_cta(full_bar(s), 0);
           if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * (Cfg::kStageBytes + Cfg::kSfBytes));
@@ -136,6 +156,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
       }
+#ifdef B200K_TRACE
+      atomicAdd(&g_trace[0], static_cast<unsigned long long>(w_empty));
+      TRACE_ADD(1, t_total);
+#endif
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -144,8 +168,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t it = 0;
       uint32_t lt = 0;
       bool ok = true;
+      TRACE_T0(t_total);
+#ifdef B200K_TRACE
+      long long w_full = 0, w_acc = 0, t_issue = 0;
+#endif
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++lt) {
         const int w = lt & 1;
+        TRACE_T0(t_a);
         if (!mbar_wait(acc_empty_bar(w), ((lt >> 1) & 1) ^ 1, abort_flag)) {
           report_status(p.status, 52, 100 + w);
           *abort_flag = 1;
@@ -159,16 +188,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
         tc_fence_after_sync();
+        TRACE_ACC(w_acc, t_a);
         const uint32_t tmem_acc = tmem_base + w * Cfg::kAccStride;
         for (int kb = 0; kb < p.k_iters; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
+          TRACE_T0(t_f);
           if (!mbar_wait(full_bar(s), ph, abort_flag)) {
             report_status(p.status, 52, s);
             *abort_flag = 1;
             ok = false;
             break;
           }
+          TRACE_ACC(w_full, t_f);
+          TRACE_T0(t_i);
           tc_fence_after_sync();
           const uint32_t a_addr = tiles_base + s * Cfg::kStageBytes;
           const uint32_t b_addr = a_addr + Cfg::kABytes;
@@ -210,12 +243,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           // release the stage in both CTAs
           tc_commit_pair(map_to_cta(empty_bar(s), 0));
           tc_commit_pair(map_to_cta(empty_bar(s), 1));
+          TRACE_ACC(t_issue, t_i);
         }
         if (ok) {
           tc_commit_pair(map_to_cta(acc_full_bar(w), 0));
           tc_commit_pair(map_to_cta(acc_full_bar(w), 1));
         }
       }
+#ifdef B200K_TRACE
+      atomicAdd(&g_trace[2], static_cast<unsigned long long>(w_full));
+      atomicAdd(&g_trace[3], static_cast<unsigned long long>(w_acc));
+      atomicAdd(&g_trace[7], static_cast<unsigned long long>(t_issue));
+      TRACE_ADD(4, t_total);
+#endif
     }
     __syncwarp();
   } else {
@@ -229,14 +269,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         (reinterpret_cast<uintptr_t>(p.c) % 16 == 0);
     const uint32_t lead_ovl = map_to_cta(ovl_free_bar, 0);
     uint32_t lt = 0;
+    TRACE_T0(t_total);
+#ifdef B200K_TRACE
+    long long w_accf = 0;
+#endif
     for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++lt) {
       const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
       const int w = lt & 1;
-      if (!mbar_wait(acc_full_bar(w), (lt >> 1) & 1, abort_flag)) {
+      TRACE_T0(t_e);
+      if (!mbar_wait_relaxed(acc_full_bar(w), (lt >> 1) & 1, abort_flag, 256)) {
         report_status(p.status, 53, w);
         *abort_flag = 1;
         break;
       }
+      TRACE_ACC(w_accf, t_e);
       tc_fence_after_sync();
       const int row = tc.pid_m * 256 + rank * 128 + quarter * 32 + lane;
       const bool row_ok = row < p.m;
@@ -275,6 +321,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(w), 0));
     }
+#ifdef B200K_TRACE
+    if (threadIdx.x == 64) {
+      atomicAdd(&g_trace[5], static_cast<unsigned long long>(w_accf));
+      TRACE_ADD(6, t_total);
+    }
+#endif
   }
 
   tc_fence_before_sync();
@@ -335,3 +387,13 @@ int launch_gemm_pair(int kind, int out_dtype, const CUtensorMap* maps, const Gem
 }
 
 }  // namespace b200k
+
+#ifdef B200K_TRACE
+extern "C" int b200k_debug_trace(unsigned long long* out16) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out16, b200k::g_trace, sizeof(unsigned long long) * 16);
+  unsigned long long zero[16] = {};
+  cudaMemcpyToSymbol(b200k::g_trace, zero, sizeof(zero));
+  return 0;
+}
+#endif
