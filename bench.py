@@ -1,7 +1,7 @@
 """Benchmark of the hot path on B200: TFLOPS of the block-scaled / dense contraction kernels.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload mxfp8_gemm|nvfp4_gemm|dense_f16]
+                    [--workload mxfp8_gemm|nvfp4_gemm|dense_f16|ag_nvfp4_gemm]
 
 One step = one pass of the workload's kernel over one batch of seeded synthetic input.
 The default workload is BASELINE config 2: MXFP8 GEMM, M = N = K = 8192, e4m3 operands
@@ -51,6 +51,7 @@ class Workload:
     name = ""
     dtype = ""
     tensor_rate_vs_bf16 = 1.0   # tensor-core rate of the operand format relative to bf16
+    distributed = False         # needs a process group even on one GPU
 
     def config(self):
         raise NotImplementedError
@@ -208,6 +209,60 @@ class Nvfp4Gemm(Mxfp8Gemm):
         return c
 
 
+class AgNvfp4Gemm(Nvfp4Gemm):
+    """BASELINE config 3 as the AllGather GEMM: A row-sharded M / world per rank, gathered
+    over NVLink from the peers' symmetric-memory buffers, every rank computing the full
+    (M, N) product against its own weights (fixed work per rank: weak scaling)."""
+    name = "allgather_nvfp4_gemm_8192x28672x8192_bf16out"
+    distributed = True
+    sets = 1
+    launches_per_step = 3   # two gather kernels + the GEMM
+
+    def setup(self, device):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        import b200k
+        world, rank = dist.get_world_size(), dist.get_rank()
+        rows = self.M // world
+        g = torch.Generator(device=device).manual_seed(self.seed + 1000 * rank)
+        a = torch.randn(rows, self.K, device=device, generator=g).bfloat16()
+        gw = torch.Generator(device=device).manual_seed(self.seed)
+        b = (0.02 * torch.randn(self.N, self.K, device=device, generator=gw)).bfloat16()
+        aq, asf, ats = b200k.nvfp4_quantize(a)
+        self.wq = b200k.nvfp4_quantize(b)
+        del a, b
+        self.s_q = symm_mem.empty(aq.shape, device=device, dtype=torch.uint8).copy_(aq)
+        self.s_sf = symm_mem.empty(asf.shape, device=device, dtype=torch.uint8).copy_(asf.view(torch.uint8))
+        self.s_ts = symm_mem.empty(1, device=device, dtype=torch.float32).copy_(ats)
+        self.plan = b200k.Nvfp4GatherMatmul(self.s_q, self.s_sf, self.s_ts)
+        self.c = torch.empty(self.M, self.N, device=device, dtype=torch.bfloat16)
+        self.flush = torch.empty(L2_BYTES * 2, dtype=torch.uint8, device=device)
+        dist.barrier()
+        torch.cuda.synchronize()
+        self.b200k = b200k
+
+    def step(self):
+        return self.plan.run(*self.wq, out=self.c)
+
+    def setup_e2e(self, device):
+        self.host_in = [t.cpu().pin_memory() for t in (self.s_q, self.s_sf, self.s_ts)]
+        self.host_out = torch.empty_like(self.c, device="cpu").pin_memory()
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host_in)
+        self.d2h = self.host_out.numel() * self.host_out.element_size()
+
+    def step_e2e(self):
+        for d, h in zip((self.s_q, self.s_sf, self.s_ts), self.host_in):
+            d.copy_(h, non_blocking=True)
+        self.plan.run(*self.wq, out=self.c)
+        self.host_out.copy_(self.c, non_blocking=True)
+
+    def config(self):
+        c = super().config()
+        c["l2"] = "operands and output of one step are 610 MiB (> 126 MiB L2)"
+        c["sharding"] = "A rows M/world per rank, gathered by peer loads; B replicated"
+        return c
+
+
 class DenseF16(Mxfp8Gemm):
     """BASELINE config 1."""
     name = "dense_f16_gemm_2048x2048x2048"
@@ -272,7 +327,8 @@ class DenseF16(Mxfp8Gemm):
         return c
 
 
-WORKLOADS = {"mxfp8_gemm": Mxfp8Gemm, "nvfp4_gemm": Nvfp4Gemm, "dense_f16": DenseF16}
+WORKLOADS = {"mxfp8_gemm": Mxfp8Gemm, "nvfp4_gemm": Nvfp4Gemm, "dense_f16": DenseF16,
+             "ag_nvfp4_gemm": AgNvfp4Gemm}
 
 
 # --------------------------------------------------------------------------------------
@@ -391,11 +447,16 @@ def run_ours(args, w):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
-    if world > 1:
+    distributed = world > 1 or getattr(w, "distributed", False)
+    if distributed:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29531")
+        os.environ.setdefault("RANK", "0")
+        os.environ.setdefault("WORLD_SIZE", "1")
         dist.init_process_group("nccl", device_id=device)
 
     def barrier():
-        if world > 1:
+        if distributed:
             dist.barrier()
         torch.cuda.synchronize()
 
@@ -471,7 +532,7 @@ def run_ours(args, w):
                                     "cores": torch.get_num_threads(), "kind": "port",
                                     "sample": w.cpu_sample_desc(s)}
         print(json.dumps(line), flush=True)
-    if world > 1:
+    if distributed:
         dist.destroy_process_group()
 
 

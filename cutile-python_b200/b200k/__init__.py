@@ -13,5 +13,5 @@ from .fmha import cutile_fmha, cutile_fmha_into  # noqa: F401
 from .moe import (cutile_moe, cutile_moe_mxfp8, invoke_fused_moe_kernel,  # noqa: F401
                   invoke_silu_and_mul_kernel, moe_align_device, moe_align_tile_size_torch,
                   quantize_expert_weights)
-from .allgather import (cutile_gather_matmul, cutile_gather_matmul_nvfp4, peer_buffers,  # noqa: F401
+from .allgather import (Nvfp4GatherMatmul, cutile_gather_matmul, cutile_gather_matmul_nvfp4, peer_buffers,  # noqa: F401
                         peer_gather, shard_rows)

@@ -106,28 +106,54 @@ def cutile_gather_matmul(inp: torch.Tensor, w: torch.Tensor, group=None, *,
     return _gemm(staged, w, out)
 
 
+class Nvfp4GatherMatmul:
+    """AllGather GEMM on NVFP4 operands with the peer mappings and staging buffers set up
+    once: ``run()`` is then one gather kernel per operand part plus the GEMM, with no host
+    synchronisation.  Each rank contributes the quantised rows it owns — a_q (M, K/2) packed
+    e2m1, a_sf its swizzled ue4m3 scales (M/128, K/64, 32, 16), a_ts its fp32 tensor scale
+    (1,) — all three whole symmetric-memory allocations; M a multiple of 128 so that scale
+    atoms do not straddle ranks."""
+
+    def __init__(self, a_q: torch.Tensor, a_sf: torch.Tensor, a_ts: torch.Tensor, group=None):
+        if group is None:
+            group = dist.group.WORLD
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.m = a_q.shape[0]
+        if self.m % 128:
+            raise ValueError("rows per rank must be a multiple of 128")
+        self.sf_shape = tuple(a_sf.shape)
+        self.q_peers = peer_buffers(_as_u8(a_q), group)
+        self.sf_peers = peer_buffers(_as_u8(a_sf).reshape(a_sf.shape[0], -1), group)
+        self.ts_peers = peer_buffers(a_ts.reshape(1, 1), group)
+        dev = a_q.device
+        self.q = torch.empty((self.world * self.m, a_q.shape[1]), dtype=torch.uint8, device=dev)
+        self.sf = torch.empty((self.world * a_sf.shape[0], self.sf_peers[0].shape[1]),
+                              dtype=torch.uint8, device=dev)
+        self.ts = torch.empty((self.world, 1), dtype=torch.float32, device=dev)
+        self.row_scale = torch.empty(self.world * self.m, dtype=torch.float32, device=dev)
+
+    def gather(self):
+        peer_gather(self.q_peers, self.rank, out=self.q)
+        peer_gather(self.sf_peers, self.rank, out=self.sf)
+        # one float per rank: a 16-byte-row gather does not apply, torch copies do
+        for r, t in enumerate(self.ts_peers):
+            self.ts[r].copy_(t[0])
+        self.row_scale.copy_(self.ts.expand(self.world, self.m).reshape(-1))
+
+    def run(self, w_q, w_sf, w_ts, out: torch.Tensor | None = None,
+            out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        self.gather()
+        n = w_q.shape[0]
+        if out is None:
+            out = torch.empty((self.world * self.m, n), dtype=out_dtype, device=self.q.device)
+        sf = self.sf.reshape(self.world * self.sf_shape[0], *self.sf_shape[1:])
+        return _scaled_gemm(self.q, sf, _as_u8(w_q), _as_u8(w_sf), out, fp4=True, alpha_b=w_ts,
+                            row_scale=self.row_scale)
+
+
 def cutile_gather_matmul_nvfp4(a_q: torch.Tensor, a_sf: torch.Tensor, a_ts: torch.Tensor,
                                w_q: torch.Tensor, w_sf: torch.Tensor, w_ts: torch.Tensor,
                                group=None, *, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-    """AllGather GEMM on NVFP4 operands: each rank contributes the quantised rows it owns —
-    a_q (M, K/2) packed e2m1, a_sf its swizzled ue4m3 scales (M/128, K/64, 32, 16), a_ts its
-    fp32 tensor scale (1,) — all three in symmetric memory; w_q (N, K/2), w_sf, w_ts are this
-    rank's weights.  M must be a multiple of 128 so that scale atoms do not straddle ranks.
-    Returns (M * world, N)."""
-    if group is None:
-        group = dist.group.WORLD
-    world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
-    m = a_q.shape[0]
-    if m % 128:
-        raise ValueError("rows per rank must be a multiple of 128")
-    q = peer_gather(peer_buffers(_as_u8(a_q), group), rank)
-    sf_flat = _as_u8(a_sf).reshape(a_sf.shape[0], -1)
-    sf = peer_gather(peer_buffers(sf_flat, group), rank)
-    sf = sf.reshape(world * a_sf.shape[0], *a_sf.shape[1:])
-    ts_all = torch.cat([t.reshape(1) for t in peer_buffers(a_ts, group)])
-    row_scale = ts_all.repeat_interleave(m)
-    n = w_q.shape[0]
-    out = torch.empty((world * m, n), dtype=out_dtype, device=a_q.device)
-    return _scaled_gemm(q, sf, _as_u8(w_q), _as_u8(w_sf), out, fp4=True, alpha_b=w_ts,
-                        row_scale=row_scale)
+    """One-shot form of Nvfp4GatherMatmul: returns (M * world, N)."""
+    return Nvfp4GatherMatmul(a_q, a_sf, a_ts, group).run(w_q, w_sf, w_ts, out_dtype=out_dtype)
