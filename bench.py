@@ -4,7 +4,7 @@
                     [--workload mxfp8_gemm|nvfp4_gemm|dense_f16|ag_nvfp4_gemm]
 
 One step = one pass of the workload's kernel over one batch of seeded synthetic input.
-The default workload is BASELINE config 2: MXFP8 GEMM, M = N = K = 8192, e4m3 operands
+The default workload is the headline configuration: MXFP8 GEMM, M = N = K = 8192, e4m3 operands
 with ue8m0 scales per 32 elements of K, fp32 accumulation, bf16 output.  With N > 1 every
 rank runs the same problem on its own GPU (the GEMM does not shard: replicas only) and the
 value is the sum over ranks divided by the slowest rank's time.
@@ -58,7 +58,7 @@ class Workload:
 
 
 class Mxfp8Gemm(Workload):
-    """BASELINE config 2."""
+    """The headline MXFP8 configuration (8192 cubed, bf16 output)."""
     name = "mxfp8_gemm_8192x8192x8192_bf16out"
     dtype = "e4m3 x e4m3 (ue8m0 scale / 32) -> fp32 accumulate -> bf16"
     tensor_rate_vs_bf16 = 2.0
@@ -143,7 +143,8 @@ class Mxfp8Gemm(Workload):
 
 
 class Nvfp4Gemm(Mxfp8Gemm):
-    """BASELINE config 3 on one GPU (the per-rank problem of the AllGather GEMM)."""
+    """The NVFP4 FFN up-projection (8192 x 28672 x 8192) on one GPU: the per-rank problem of
+    the AllGather GEMM."""
     name = "nvfp4_gemm_8192x28672x8192_bf16out"
     dtype = "e2m1 x e2m1 (ue4m3 scale / 16, fp32 tensor scale) -> fp32 accumulate -> bf16"
     tensor_rate_vs_bf16 = 4.0
@@ -210,7 +211,7 @@ class Nvfp4Gemm(Mxfp8Gemm):
 
 
 class AgNvfp4Gemm(Nvfp4Gemm):
-    """BASELINE config 3 as the AllGather GEMM: A row-sharded M / world per rank, gathered
+    """The NVFP4 FFN up-projection as the AllGather GEMM: A row-sharded M / world per rank, gathered
     over NVLink from the peers' symmetric-memory buffers, every rank computing the full
     (M, N) product against its own weights (fixed work per rank: weak scaling)."""
     name = "allgather_nvfp4_gemm_8192x28672x8192_bf16out"
@@ -264,7 +265,7 @@ class AgNvfp4Gemm(Nvfp4Gemm):
 
 
 class DenseF16(Mxfp8Gemm):
-    """BASELINE config 1."""
+    """The sample-sized dense fp16 matmul (2048 cubed)."""
     name = "dense_f16_gemm_2048x2048x2048"
     dtype = "f16 x f16 -> fp32 accumulate -> f16"
     tensor_rate_vs_bf16 = 1.0

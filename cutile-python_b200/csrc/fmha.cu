@@ -16,6 +16,8 @@
 // out-of-range keys masked, fp32 running max / sum, P rounded to the input type before
 // P V, output = accumulator / sum rounded to the input type, grouped-query heads by
 // integer division.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "host.h"
 
@@ -43,6 +45,147 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// One softmax warp group (4 warps, one query row per thread) working on the 128-row query
+// tile that starts at row q0 of (batch b, head h): for each of its n_kv key tiles it reads S
+// from tensor memory, updates the running maximum / sum, writes P back over S as 16-bit
+// pairs, rescales O when needed, and finally writes O / l.
+template <int D, bool BF16>
+__device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int lane, int b, int h,
+                                             int q0, int n_kv, uint32_t tmem_s, uint32_t tmem_o,
+                                             uint32_t s_full, uint32_t p_full, uint32_t pv_done,
+                                             volatile int* abort_flag) {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
+    const int q_pos = p.input_pos + q0 + row;
+    float m_used = -INFINITY;
+    float l = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const uint32_t ph = j & 1;
+      if (!mbar_wait(s_full, ph, abort_flag)) {
+        report_status(p.status, 31, j);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      float s[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_s + lane_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]);
+      }
+      const int key0 = j * kFmhaBN;
+      const bool need_mask = (key0 + kFmhaBN > p.sk) || (p.causal && key0 + kFmhaBN - 1 > p.input_pos + q0);
+      if (need_mask) {
+        const int limit = p.causal ? min(p.sk - 1, q_pos) : p.sk - 1;  // last visible key
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (key0 + i > limit) s[i] = -INFINITY;
+      }
+      // eight independent chains keep the max / sum reductions off the critical path
+      float mx8[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx8[i] = s[i];
+#pragma unroll
+      for (int i = 8; i < 128; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], s[i]);
+      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      const float m_new = fmaxf(m_used, mx * p.scale_log2);
+      // Deferred rescale: keep the stale maximum while the true one is less than 2^8
+      // above it.  A row whose maximum is still -inf has seen no key yet.
+      bool grow = (m_new - m_used > kRescaleThreshold) || (m_used == -INFINITY && m_new > -INFINITY);
+      const bool any_grow = __any_sync(0xffffffffu, grow);
+      float alpha = 1.0f;
+      if (grow) {
+        alpha = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_new);
+        m_used = m_new;
+      }
+      if (any_grow && j > 0) {
+        // S_FULL of tile j was committed after P V of tile j-1, so O is quiescent here
+        l *= alpha;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_o + lane_addr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st_32x32b_x32(tmem_o + lane_addr + c * 32, r);
+        }
+      }
+      const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = fast_exp2(fmaf(s[c * 64 + 2 * i], p.scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(s[c * 64 + 2 * i + 1], p.scale_log2, neg_m));
+          sum4[i & 3] += p0 + p1;
+          pk[i] = BF16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
+        }
+        tmem_st_32x32b_x32(tmem_s + lane_addr + c * 32, pk);
+      }
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    // epilogue: O / l
+    if (ok && n_kv > 0) {
+      if (!mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag)) {
+        report_status(p.status, 32, 0);
+        *abort_flag = 1;
+        ok = false;
+      }
+    }
+    tc_fence_after_sync();
+    const bool row_ok = (q0 + row) < p.sq;
+    uint16_t* o_row = static_cast<uint16_t*>(p.out) + b * p.o_stride_b + h * p.o_stride_h +
+                      static_cast<int64_t>(q0 + row) * p.o_stride_s;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0) && (p.o_stride_b % 8 == 0) &&
+                        (p.o_stride_h % 8 == 0) && (p.o_stride_s % 8 == 0);
+    const float inv_l = (l > 0.0f) ? __fdividef(1.0f, l) : 0.0f;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t r[32];
+      if (ok && n_kv > 0) {
+        tmem_ld_32x32b_x32(tmem_o + lane_addr + c * 32, r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = 0;
+      }
+      if (row_ok) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float a = __uint_as_float(r[2 * i]) * inv_l;
+          const float c2 = __uint_as_float(r[2 * i + 1]) * inv_l;
+          pk[i] = BF16 ? pack_bf16x2(a, c2) : pack_f16x2(a, c2);
+        }
+        if (vec_ok) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            reinterpret_cast<uint4*>(o_row + c * 32)[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            o_row[c * 32 + 2 * i] = static_cast<uint16_t>(pk[i] & 0xffff);
+            o_row[c * 32 + 2 * i + 1] = static_cast<uint16_t>(pk[i] >> 16);
+          }
+        }
+      }
+    }
 }
 
 template <int D, bool BF16>
@@ -186,136 +329,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
     __syncwarp();
   } else {
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
-    const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
-    const int q_pos = p.input_pos + q0 + row;
-    float m_used = -INFINITY;
-    float l = 0.0f;
-    bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      const uint32_t ph = j & 1;
-      if (!mbar_wait(bar(S_FULL), ph, abort_flag)) {
-        report_status(p.status, 31, j);
-        *abort_flag = 1;
-        ok = false;
-        break;
-      }
-      tc_fence_after_sync();
-      float s[128];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_s + lane_addr + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]);
-      }
-      const int key0 = j * kFmhaBN;
-      const bool need_mask = (key0 + kFmhaBN > p.sk) || (p.causal && key0 + kFmhaBN - 1 > p.input_pos + q0);
-      if (need_mask) {
-        const int limit = p.causal ? min(p.sk - 1, q_pos) : p.sk - 1;  // last visible key
-#pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (key0 + i > limit) s[i] = -INFINITY;
-      }
-      // eight independent chains keep the max / sum reductions off the critical path
-      float mx8[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) mx8[i] = s[i];
-#pragma unroll
-      for (int i = 8; i < 128; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], s[i]);
-      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-      const float m_new = fmaxf(m_used, mx * p.scale_log2);
-      // Deferred rescale: keep the stale maximum while the true one is less than 2^8
-      // above it.  A row whose maximum is still -inf has seen no key yet.
-      bool grow = (m_new - m_used > kRescaleThreshold) || (m_used == -INFINITY && m_new > -INFINITY);
-      const bool any_grow = __any_sync(0xffffffffu, grow);
-      float alpha = 1.0f;
-      if (grow) {
-        alpha = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_new);
-        m_used = m_new;
-      }
-      if (any_grow && j > 0) {
-        // S_FULL of tile j was committed after P V of tile j-1, so O is quiescent here
-        l *= alpha;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(tmem_o + lane_addr + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st_32x32b_x32(tmem_o + lane_addr + c * 32, r);
-        }
-      }
-      const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
-      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t pk[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float p0 = fast_exp2(fmaf(s[c * 64 + 2 * i], p.scale_log2, neg_m));
-          const float p1 = fast_exp2(fmaf(s[c * 64 + 2 * i + 1], p.scale_log2, neg_m));
-          sum4[i & 3] += p0 + p1;
-          pk[i] = BF16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
-        }
-        tmem_st_32x32b_x32(tmem_s + lane_addr + c * 32, pk);
-      }
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      tmem_st_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(P_FULL));
-    }
-    // epilogue: O / l
-    if (ok && n_kv > 0) {
-      if (!mbar_wait(bar(PV_DONE), (n_kv - 1) & 1, abort_flag)) {
-        report_status(p.status, 32, 0);
-        *abort_flag = 1;
-        ok = false;
-      }
-    }
-    tc_fence_after_sync();
-    const bool row_ok = (q0 + row) < p.sq;
-    uint16_t* o_row = static_cast<uint16_t*>(p.out) + b * p.o_stride_b + h * p.o_stride_h +
-                      static_cast<int64_t>(q0 + row) * p.o_stride_s;
-    const bool vec_ok = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0) && (p.o_stride_b % 8 == 0) &&
-                        (p.o_stride_h % 8 == 0) && (p.o_stride_s % 8 == 0);
-    const float inv_l = (l > 0.0f) ? __fdividef(1.0f, l) : 0.0f;
-#pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
-      uint32_t r[32];
-      if (ok && n_kv > 0) {
-        tmem_ld_32x32b_x32(tmem_o + lane_addr + c * 32, r);
-        tmem_ld_wait();
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) r[i] = 0;
-      }
-      if (row_ok) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float a = __uint_as_float(r[2 * i]) * inv_l;
-          const float c2 = __uint_as_float(r[2 * i + 1]) * inv_l;
-          pk[i] = BF16 ? pack_bf16x2(a, c2) : pack_f16x2(a, c2);
-        }
-        if (vec_ok) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            reinterpret_cast<uint4*>(o_row + c * 32)[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            o_row[c * 32 + 2 * i] = static_cast<uint16_t>(pk[i] & 0xffff);
-            o_row[c * 32 + 2 * i + 1] = static_cast<uint16_t>(pk[i] >> 16);
-          }
-        }
-      }
-    }
+    softmax_tile<D, BF16>(p, warp, lane, b, h, q0, n_kv, tmem_s, tmem_o, bar(S_FULL), bar(P_FULL),
+                          bar(PV_DONE), abort_flag);
   }
 
   tc_fence_before_sync();
@@ -323,6 +338,201 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kFmhaTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Two query tiles per CTA (head dim 128): one CTA per SM owns 256 query rows.  Warp group A
+// (warps 2-5) does the softmax of rows [q0, q0 + 128), warp group B (warps 6-9) of rows
+// [q0 + 128, q0 + 256); the single MMA thread interleaves their matrix products
+//     P V (A, j)   S (A, j + 1)   P V (B, j)   S (B, j + 1)
+// so that while one group is in its softmax the tensor core works for the other.  K and V
+// tiles are double-buffered and shared by both query tiles.
+// TMEM: S_A [0,128)  S_B [128,256)  O_A [256,384)  O_B [384,512); P aliases S.
+// ---------------------------------------------------------------------------
+constexpr int kFmha2Threads = 320;
+
+template <bool BF16>
+__global__ void __launch_bounds__(kFmha2Threads, 1)
+fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, const FmhaParams p) {
+  constexpr int D = 128;
+  constexpr int kTileBytes = 128 * D * 2;
+  constexpr int kBoxBytes = 128 * 128;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_smem = base;                          // Q_A, Q_B
+  const uint32_t k_smem = base + 2 * kTileBytes;         // K[2]
+  const uint32_t v_smem = base + 4 * kTileBytes;         // V[2]
+  uint8_t* tail = smem + 6 * kTileBytes;
+  const uint32_t bar0 = smem_u32(tail);
+  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11,
+         PV_DONE = 13, NUM_BARS = 15 };
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * NUM_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8 * NUM_BARS + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int q_pairs = (p.sq + 255) / 256;
+  const int bh = blockIdx.x / q_pairs;
+  const int qp = q_pairs - 1 - (blockIdx.x - bh * q_pairs);   // heaviest (causal) tiles first
+  const int b = bh / p.heads_q;
+  const int h = bh - b * p.heads_q;
+  const int h_kv = h / p.group;
+  const int q0 = qp * 256;
+
+  // key tiles per query tile
+  const int kv_all = (p.sk + kFmhaBN - 1) / kFmhaBN;
+  int n_x[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    const int qx = q0 + x * 128;
+    int n = kv_all;
+    if (p.causal) n = min(n, (p.input_pos + qx + kFmhaBM - 1) / kFmhaBN + 1);
+    if (qx >= p.sq) n = 0;
+    n_x[x] = n;
+  }
+  const int n_kv = max(n_x[0], n_x[1]);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NUM_BARS; ++i) mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? 4 : 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t kFmt = BF16 ? kFmtBF16 : kFmtF16;
+
+  if (warp == 0) {
+    if (lane == 0 && n_kv > 0) {
+      mbar_arrive_expect_tx(bar(Q_FULL), 2 * kTileBytes);
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+          tma_load_4d(q_smem + x * kTileBytes + i * kBoxBytes, &tmap_q, bar(Q_FULL), i * 64, q0 + x * 128, h, b);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(bar(K_EMPTY + st), ph ^ 1, abort_flag)) {
+          report_status(p.status, 61, j);
+          *abort_flag = 1;
+          break;
+        }
+        mbar_arrive_expect_tx(bar(K_FULL + st), kTileBytes);
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+          tma_load_4d(k_smem + st * kTileBytes + i * kBoxBytes, &tmap_k, bar(K_FULL + st), i * 64,
+                      j * kFmhaBN, h_kv, b);
+        if (!mbar_wait(bar(V_EMPTY + st), ph ^ 1, abort_flag)) {
+          report_status(p.status, 62, j);
+          *abort_flag = 1;
+          break;
+        }
+        mbar_arrive_expect_tx(bar(V_FULL + st), kTileBytes);
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+          tma_load_4d(v_smem + st * kTileBytes + i * kBoxBytes, &tmap_v, bar(V_FULL + st), i * 64,
+                      j * kFmhaBN, h_kv, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && n_kv > 0) {
+      constexpr uint32_t idesc_qk = make_idesc(kFmt, kFmt, false, false, kFmhaBM, kFmhaBN);
+      constexpr uint32_t idesc_pv = make_idesc(kFmt, kFmt, false, true, kFmhaBM, D);
+      // S_x = Q_x K^T for key tile j (stage st): 8 MMAs of K = 16
+      auto issue_s = [&](int x, int st) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kBoxBytes;
+          const uint64_t qd = make_smem_desc(q_smem + x * kTileBytes + off, 16, 1024, kSwizzle128B) + 2 * (kk % 4);
+          const uint64_t kd = make_smem_desc(k_smem + st * kTileBytes + off, 16, 1024, kSwizzle128B) + 2 * (kk % 4);
+          umma<kKindF16>(tmem_base + x * 128, qd, kd, idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(bar(S_FULL + x));
+      };
+      // O_x += P_x V for key tile j: P from TMEM, V MN-major
+      auto issue_pv = [&](int x, int st, bool first) {
+#pragma unroll
+        for (int kk = 0; kk < kFmhaBN / 16; ++kk) {
+          const uint64_t vd = make_smem_desc(v_smem + st * kTileBytes + kk * 2048, kBoxBytes, 1024, kSwizzle128B);
+          umma_f16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + kk * 8, vd, idesc_pv,
+                      (!first || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(bar(PV_DONE + x));
+      };
+      bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag);
+      if (ok) ok = mbar_wait(bar(K_FULL), 0, abort_flag);
+      if (!ok) {
+        report_status(p.status, 70, 0);
+        *abort_flag = 1;
+      } else {
+        tc_fence_after_sync();
+        if (n_x[0] > 0) issue_s(0, 0);
+        if (n_x[1] > 0) issue_s(1, 0);
+        tc_commit(bar(K_EMPTY));
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const bool more = j + 1 < n_kv;
+        const int st1 = (j + 1) & 1;
+        const uint32_t ph1 = ((j + 1) >> 1) & 1;
+        if (!mbar_wait(bar(V_FULL + st), ph, abort_flag)) {
+          report_status(p.status, 71, j);
+          *abort_flag = 1;
+          break;
+        }
+        if (more && !mbar_wait(bar(K_FULL + st1), ph1, abort_flag)) {
+          report_status(p.status, 72, j);
+          *abort_flag = 1;
+          break;
+        }
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (j < n_x[x]) {
+            if (!mbar_wait(bar(P_FULL + x), j & 1, abort_flag)) {
+              report_status(p.status, 73 + x, j);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            issue_pv(x, st, j == 0);
+          }
+          if (more && j + 1 < n_x[x]) issue_s(x, st1);
+        }
+        if (!ok) break;
+        tc_commit(bar(V_EMPTY + st));
+        if (more) tc_commit(bar(K_EMPTY + st1));
+      }
+    }
+    __syncwarp();
+  } else {
+    const int x = (warp - 2) >> 2;           // warp group: query tile A or B
+    softmax_tile<D, BF16>(p, warp, lane, b, h, q0 + x * 128, n_x[x], tmem_base + x * 128,
+                          tmem_base + 256 + x * 128, bar(S_FULL + x), bar(P_FULL + x), bar(PV_DONE + x),
+                          abort_flag);
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -344,6 +554,25 @@ int launch_fmha(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
   }
   kernel<<<grid, kFmhaThreads, kSmem, stream>>>(tq, tk, tv, p);
   B200K_CHECK_LAUNCH("fmha launch");
+  return B200K_OK;
+}
+
+template <bool BF16>
+int launch_fmha_pair(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                     const FmhaParams& p, int grid, cudaStream_t stream) {
+  constexpr int kSmem = 1024 + 6 * 128 * 128 * 2 + 256;
+  auto kernel = fmha_fwd_pair_kernel<BF16>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e != cudaSuccess)
+      return fail(B200K_CUDA_ERROR, "cudaFuncSetAttribute(%d): %s", kSmem, cudaGetErrorString(e));
+    configured[dev] = true;
+  }
+  kernel<<<grid, kFmha2Threads, kSmem, stream>>>(tq, tk, tv, p);
+  B200K_CHECK_LAUNCH("fmha (two-tile) launch");
   return B200K_OK;
 }
 
@@ -410,6 +639,15 @@ extern "C" int b200k_fmha_fwd(const b200k_fmha_args* a, b200k_stream stream_) {
   if (grid64 > INT32_MAX) return fail(B200K_UNSUPPORTED, "too many tiles");
   const int grid = static_cast<int>(grid64);
   const bool bf16 = a->dtype == B200K_BF16;
+  // head dim 128 and more than one query tile: two query tiles per CTA (B200K_FMHA_ONE_TILE=1
+  // forces the one-tile kernel)
+  const char* one_tile = getenv("B200K_FMHA_ONE_TILE");
+  if (d == 128 && a->seq_q > 128 && !(one_tile != nullptr && one_tile[0] == '1')) {
+    const int64_t g2 = ceil_div(a->seq_q, 256) * a->batch * a->heads_q;
+    if (g2 > INT32_MAX) return fail(B200K_UNSUPPORTED, "too many tiles");
+    return bf16 ? launch_fmha_pair<true>(tq, tk, tv, p, static_cast<int>(g2), stream)
+                : launch_fmha_pair<false>(tq, tk, tv, p, static_cast<int>(g2), stream);
+  }
   if (d == 128)
     return bf16 ? launch_fmha<128, true>(tq, tk, tv, p, grid, stream)
                 : launch_fmha<128, false>(tq, tk, tv, p, grid, stream);

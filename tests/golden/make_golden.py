@@ -15,7 +15,7 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("REFERENCE_PATH", "/root/reference")
+REF = os.environ.get("REFERENCE_PATH", os.path.expanduser("~/reference"))
 sys.path.insert(0, os.path.join(REF, "test"))
 sys.path.insert(0, os.path.join(REF, "samples"))
 HERE = os.path.dirname(os.path.abspath(__file__))

@@ -115,7 +115,7 @@ def test_nvfp4_matmul(m, n, k, device_ok):
                                   out_dtype=torch.float32)
     # against the de-quantised operands the kernel is exact up to fp32 summation order
     torch.testing.assert_close(c.cpu(), ref, atol=1e-4 * float(ref.abs().max()), rtol=1e-3)
-    # against the unquantised product: BASELINE's 5e-2 bound is on bf16 outputs of the
+    # against the unquantised product: the 5e-2 Frobenius bound applies to bf16 outputs of the
     # quantised pipeline; fp4 quantisation noise itself is ~13 % per operand pair
     assert oracle.rel_frobenius(c, a @ b.T) < 0.2
 
@@ -136,7 +136,7 @@ def test_nvfp4_end_to_end_bf16(device_ok):
 
 
 def test_mxfp8_sampled_rows_at_full_size(device_ok):
-    # BASELINE config 2 (8192^3, bf16 out): sampled rows against the oracle and a
+    # the headline configuration (8192^3, bf16 out): sampled rows against the oracle and a
     # row-sum identity over the whole output
     n = 8192
     g = torch.Generator(device="cuda").manual_seed(1)

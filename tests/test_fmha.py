@@ -2,7 +2,7 @@
 
 Shapes follow test/test_attention.py:13-64 (batch {1,4}, q heads {8,16} over 8 kv heads,
 ragged q/k lengths, causal with input_pos) scaled to this kernel's head dims, plus
-BASELINE-shaped slices; tolerances are the reference's for 16-bit inputs
+slices of the benchmark-sized problem; tolerances are the reference's for 16-bit inputs
 (atol 1e-2, rtol 5e-2, test/test_attention.py:62-63).
 """
 import math
@@ -100,7 +100,7 @@ def test_fmha_bench_form_and_validation(device_ok):
 
 
 def test_fmha_baseline_shape_slice(device_ok):
-    # BASELINE config 4 is (4, 32, 8192, 128) causal; one batch and 2 heads of it at full
+    # the benchmark-sized problem is (4, 32, 8192, 128) causal; one batch and 2 heads of it at full
     # sequence length against the oracle on sampled query rows, plus the row-sum property
     # that attention over a constant V returns that constant
     g = torch.Generator().manual_seed(3)
