@@ -1,7 +1,7 @@
 """Benchmark of the hot path on B200: TFLOPS of the block-scaled / dense contraction kernels.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload mxfp8_gemm|nvfp4_gemm|dense_f16|ag_nvfp4_gemm]
+                    [--workload mxfp8_gemm|nvfp4_gemm|dense_f16|ag_nvfp4_gemm|moe_ep_bf16]
 
 One step = one pass of the workload's kernel over one batch of seeded synthetic input.
 The default workload is the headline configuration: MXFP8 GEMM, M = N = K = 8192, e4m3 operands
@@ -264,6 +264,84 @@ class AgNvfp4Gemm(Nvfp4Gemm):
         return c
 
 
+class MoeEpBf16(Workload):
+    """The MoE FFN configuration (16384 tokens, hidden 4096, 64 experts, intermediate 1536,
+    top-8) with experts and tokens sharded over the ranks and an NVLink all-to-all for
+    dispatch and combine.  The whole problem is fixed, so this scales strongly."""
+    name = "moe_ffn_ep_16384tok_h4096_e64_i1536_top8_bf16"
+    dtype = "bf16 x bf16 -> fp32 accumulate -> bf16"
+    tensor_rate_vs_bf16 = 1.0
+    distributed = True
+    scaling = "strong"
+    T, H, E, I, K = 16384, 4096, 64, 1536, 8
+    seed = 4
+    launches_per_step = 8
+
+    def flops(self):
+        return 6.0 * self.T * self.K * self.H * self.I / self.world   # per rank
+
+    def algorithmic_bytes(self):
+        return 2 * (self.E * 3 * self.I * self.H + 2 * self.T * self.H) // self.world
+
+    def setup(self, device):
+        import torch.distributed as dist
+        import b200k
+        self.world, rank = dist.get_world_size(), dist.get_rank()
+        tl, el = self.T // self.world, self.E // self.world
+        g = torch.Generator(device=device).manual_seed(self.seed + 1000 * rank)
+        self.x = torch.randn(tl, self.H, device=device, generator=g).bfloat16()
+        w1 = (0.02 * torch.randn(el, 2 * self.I, self.H, device=device, generator=g)).bfloat16()
+        w2 = (0.02 * torch.randn(el, self.H, self.I, device=device, generator=g)).bfloat16()
+        logits = torch.randn(tl, self.E, device=device, generator=g)
+        vals, self.ids = torch.topk(logits, self.K, dim=-1)
+        self.tw = torch.softmax(vals, dim=-1).bfloat16()
+        self.ep = b200k.ExpertParallelMoE(w1, w2, self.E)
+        self.b200k = b200k
+
+    def step(self):
+        return self.ep.forward(self.x, self.tw, self.ids)
+
+    def setup_e2e(self, device):
+        self.host_in = [t.cpu().pin_memory() for t in (self.x, self.tw, self.ids)]
+        self.dev_in = [torch.empty_like(t) for t in (self.x, self.tw, self.ids)]
+        self.host_out = torch.empty_like(self.x, device="cpu").pin_memory()
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host_in)
+        self.d2h = self.host_out.numel() * self.host_out.element_size()
+
+    def step_e2e(self):
+        for d, h in zip(self.dev_in, self.host_in):
+            d.copy_(h, non_blocking=True)
+        out = self.ep.forward(*self.dev_in)
+        self.host_out.copy_(out, non_blocking=True)
+
+    def cpu_setup(self):
+        import oracle
+        g = torch.Generator().manual_seed(self.seed)
+        t, e = 512, 8
+        self.cpu_ops = ((0.5 * torch.randn(t, self.H, generator=g)),
+                        0.02 * torch.randn(e, 2 * self.I, self.H, generator=g),
+                        0.02 * torch.randn(e, self.H, self.I, generator=g))
+        self.cpu_route = oracle.moe_route_ref(torch.randn(t, e, generator=g), 2)
+        self.oracle = oracle
+
+    def cpu_step(self, s):
+        x, w1, w2 = self.cpu_ops
+        tw, ids = self.cpu_route
+        return self.oracle.moe_ref(x[:s], w1, w2, tw[:s], ids[:s])
+
+    def cpu_flops(self, s):
+        return 6.0 * s * 2 * self.H * self.I
+
+    def cpu_sample_desc(self, s):
+        return f"{s} tokens, 8 experts, top-2 of the same FFN in fp32 (torch CPU)"
+
+    def config(self):
+        return {"workload": self.name, "tokens": self.T, "hidden": self.H, "experts": self.E,
+                "intermediate": self.I, "topk": self.K, "seed": self.seed,
+                "sharding": "experts E/world and tokens T/world per rank; all_to_all dispatch + combine",
+                "l2": "expert weights alone are 2.4 GB / world per rank (> 126 MiB L2)"}
+
+
 class DenseF16(Mxfp8Gemm):
     """The sample-sized dense fp16 matmul (2048 cubed)."""
     name = "dense_f16_gemm_2048x2048x2048"
@@ -329,7 +407,7 @@ class DenseF16(Mxfp8Gemm):
 
 
 WORKLOADS = {"mxfp8_gemm": Mxfp8Gemm, "nvfp4_gemm": Nvfp4Gemm, "dense_f16": DenseF16,
-             "ag_nvfp4_gemm": AgNvfp4Gemm}
+             "ag_nvfp4_gemm": AgNvfp4Gemm, "moe_ep_bf16": MoeEpBf16}
 
 
 # --------------------------------------------------------------------------------------
@@ -510,7 +588,7 @@ def run_ours(args, w):
         line = {
             "metric": "tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "higher_is_better": True, "scaling": getattr(w, "scaling", "weak"), "vs_baseline": None,
             "dtype": w.dtype, "data": "synthetic", "config": w.config(),
             "e2e": {"value": world * flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h,
