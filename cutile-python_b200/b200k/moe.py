@@ -144,10 +144,11 @@ def invoke_silu_and_mul_kernel(AB: torch.Tensor, C: torch.Tensor) -> None:
                                                  _lib.stream_ptr(AB.device)))
 
 
-def _topk_sum(x: torch.Tensor, tokens: int, topk: int, hidden: int) -> torch.Tensor:
+def _topk_sum(x: torch.Tensor, tokens: int, topk: int, hidden: int,
+              index: torch.Tensor | None = None) -> torch.Tensor:
     out = torch.empty((tokens, hidden), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
-        _lib.check(_lib.lib().b200k_topk_sum(x.data_ptr(), tokens, topk, hidden, out.data_ptr(),
+        _lib.check(_lib.lib().b200k_topk_sum(x.data_ptr(), _lib.ptr(index), tokens, topk, hidden, out.data_ptr(),
                                              _lib.dtype_enum(x.dtype), _lib.stream_ptr(x.device)))
     return out
 

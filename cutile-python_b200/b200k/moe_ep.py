@@ -103,28 +103,35 @@ class ExpertParallelMoE:
                 topk_ids: torch.Tensor, expert_fn=None) -> torch.Tensor:
         tokens, hidden = hidden_states.shape
         topk = topk_ids.shape[1]
-        if hidden_states.is_cuda:
+        cuda = hidden_states.is_cuda
+        flat_ids = topk_ids.reshape(-1)
+        if cuda:
             from . import moe
-            order, _, _ = moe.moe_align_device(topk_ids, 1, self.num_experts)
-            order = order.long()
-            counts = torch.bincount(topk_ids.reshape(-1), minlength=self.num_experts)
+            order32, _, _ = moe.moe_align_device(topk_ids, 1, self.num_experts)
+            order = order32.long()
+            counts = torch.bincount(flat_ids, minlength=self.num_experts)
+            x = hidden_states if hidden_states.stride(1) == 1 else hidden_states.contiguous()
+            rows = moe._gather_rows(x, order32, topk, tokens * topk, None)
         else:
             order, counts = route(topk_ids, self.num_experts)
+            rows = hidden_states[order // topk]
         send_counts = expert_owner_counts(counts, self.world)
-        flat_ids = topk_ids.reshape(-1)
-        rows = hidden_states[order // topk]
-        ids = (flat_ids[order] % self.local_experts_n).to(torch.int32)
-        wts = topk_weights.reshape(-1)[order].float()
-        (rows_in, ids_in, wts_in), recv_counts = exchange([rows, ids, wts], send_counts, self.group)
+        # local expert id and routing weight travel together as one (R, 2) fp32 tensor
+        meta = torch.stack([(flat_ids[order] % self.local_experts_n).float(),
+                            topk_weights.reshape(-1)[order].float()], dim=1)
+        (rows_in, meta_in), recv_counts = exchange([rows, meta], send_counts, self.group)
+        ids_in = meta_in[:, 0].to(torch.int32)
+        wts_in = meta_in[:, 1].contiguous()
         fn = expert_fn if expert_fn is not None else self.local_experts
         y_in = fn(rows_in, ids_in, wts_in)
         (y_back,), _ = exchange_back(y_in, recv_counts, send_counts, self.group)
-        per_replica = torch.empty((tokens * topk, hidden), dtype=hidden_states.dtype, device=hidden_states.device)
-        per_replica.index_copy_(0, order, y_back)
-        if hidden_states.is_cuda and hidden % 8 == 0:
+        # y_back is in dispatch order: replica order[i] sits in row i
+        inverse = torch.empty_like(order)
+        inverse[order] = torch.arange(order.numel(), device=order.device)
+        if cuda and hidden % 8 == 0:
             from . import moe
-            return moe._topk_sum(per_replica, tokens, topk, hidden)
-        return per_replica.reshape(tokens, topk, hidden).float().sum(dim=1).to(hidden_states.dtype)
+            return moe._topk_sum(y_back, tokens, topk, hidden, index=inverse.to(torch.int32))
+        return y_back[inverse].reshape(tokens, topk, hidden).float().sum(dim=1).to(hidden_states.dtype)
 
 
 def exchange_back(t: torch.Tensor, send_counts: list[int], recv_counts: list[int], group=None):

@@ -72,31 +72,24 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
         break;
       }
       tc_fence_after_sync();
-      float s[128];
+      // Pass 1: row maximum, streaming S out of tensor memory 32 columns at a time.
+      const int key0 = j * kFmhaBN;
+      const bool need_mask = (key0 + kFmhaBN > p.sk) || (p.causal && key0 + kFmhaBN - 1 > p.input_pos + q0);
+      const int limit = p.causal ? min(p.sk - 1, q_pos) : p.sk - 1;  // last visible key
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_s + lane_addr + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]);
+        for (int i = 0; i < 32; ++i) {
+          float v = __uint_as_float(r[i]);
+          if (need_mask && key0 + c * 32 + i > limit) v = -INFINITY;
+          mx4[i & 3] = fmaxf(mx4[i & 3], v);
+        }
       }
-      const int key0 = j * kFmhaBN;
-      const bool need_mask = (key0 + kFmhaBN > p.sk) || (p.causal && key0 + kFmhaBN - 1 > p.input_pos + q0);
-      if (need_mask) {
-        const int limit = p.causal ? min(p.sk - 1, q_pos) : p.sk - 1;  // last visible key
-#pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (key0 + i > limit) s[i] = -INFINITY;
-      }
-      // eight independent chains keep the max / sum reductions off the critical path
-      float mx8[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) mx8[i] = s[i];
-#pragma unroll
-      for (int i = 8; i < 128; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], s[i]);
-      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       // Deferred rescale: keep the stale maximum while the true one is less than 2^8
       // above it.  A row whose maximum is still -inf has seen no key yet.
@@ -120,17 +113,35 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
           tmem_st_32x32b_x32(tmem_o + lane_addr + c * 32, r);
         }
       }
+      // Pass 2: P = exp2(S * scale - m), 64 scores -> 32 packed columns per step.  The packed
+      // columns [32 c, 32 c + 32) overwrite scores that this thread has already consumed.
       const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
       float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32b_x32(tmem_s + lane_addr + c * 64, r0);
+        tmem_ld_32x32b_x32(tmem_s + lane_addr + c * 64 + 32, r1);
+        tmem_ld_wait();
         uint32_t pk[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float p0 = fast_exp2(fmaf(s[c * 64 + 2 * i], p.scale_log2, neg_m));
-          const float p1 = fast_exp2(fmaf(s[c * 64 + 2 * i + 1], p.scale_log2, neg_m));
-          sum4[i & 3] += p0 + p1;
+        for (int i = 0; i < 16; ++i) {
+          float a0 = __uint_as_float(r0[2 * i]), a1 = __uint_as_float(r0[2 * i + 1]);
+          float b0 = __uint_as_float(r1[2 * i]), b1 = __uint_as_float(r1[2 * i + 1]);
+          if (need_mask) {
+            if (key0 + c * 64 + 2 * i > limit) a0 = -INFINITY;
+            if (key0 + c * 64 + 2 * i + 1 > limit) a1 = -INFINITY;
+            if (key0 + c * 64 + 32 + 2 * i > limit) b0 = -INFINITY;
+            if (key0 + c * 64 + 32 + 2 * i + 1 > limit) b1 = -INFINITY;
+          }
+          const float p0 = fast_exp2(fmaf(a0, p.scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(a1, p.scale_log2, neg_m));
+          const float p2 = fast_exp2(fmaf(b0, p.scale_log2, neg_m));
+          const float p3 = fast_exp2(fmaf(b1, p.scale_log2, neg_m));
+          sum4[i & 1] += p0 + p1;
+          sum4[2 + (i & 1)] += p2 + p3;
           pk[i] = BF16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
+          pk[16 + i] = BF16 ? pack_bf16x2(p2, p3) : pack_f16x2(p2, p3);
         }
         tmem_st_32x32b_x32(tmem_s + lane_addr + c * 32, pk);
       }

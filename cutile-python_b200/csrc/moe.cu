@@ -203,8 +203,8 @@ silu_and_mul_kernel(const uint16_t* __restrict__ ab, int64_t rows, int64_t n, in
 // out[t, :] = sum_j x[t, j, :], fp32 accumulation, 8 columns per thread.
 template <bool BF16>
 __global__ void __launch_bounds__(256)
-topk_sum_kernel(const uint16_t* __restrict__ x, int64_t tokens, int topk, int64_t h,
-                uint16_t* __restrict__ out) {
+topk_sum_kernel(const uint16_t* __restrict__ x, const int* __restrict__ index, int64_t tokens,
+                int topk, int64_t h, uint16_t* __restrict__ out) {
   const int64_t vecs = h / 8;
   const int64_t total = tokens * vecs;
   for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
@@ -213,7 +213,8 @@ topk_sum_kernel(const uint16_t* __restrict__ x, int64_t tokens, int topk, int64_
     const int64_t v = idx - t * vecs;
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int j = 0; j < topk; ++j) {
-      const uint4 q = *reinterpret_cast<const uint4*>(x + (t * topk + j) * h + v * 8);
+      const int64_t src = index != nullptr ? index[t * topk + j] : t * topk + j;
+      const uint4 q = *reinterpret_cast<const uint4*>(x + src * h + v * 8);
       const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -343,8 +344,8 @@ extern "C" int b200k_silu_and_mul(const void* ab, int64_t rows, int64_t n, int64
   return B200K_OK;
 }
 
-extern "C" int b200k_topk_sum(const void* x, int64_t tokens, int32_t topk, int64_t hidden, void* out,
-                              int32_t dtype, b200k_stream stream_) {
+extern "C" int b200k_topk_sum(const void* x, const int32_t* index, int64_t tokens, int32_t topk,
+                              int64_t hidden, void* out, int32_t dtype, b200k_stream stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (tokens < 0 || topk <= 0 || hidden < 0) return fail(B200K_INVALID_ARG, "bad sizes");
   if (tokens == 0 || hidden == 0) return B200K_OK;
@@ -353,10 +354,10 @@ extern "C" int b200k_topk_sum(const void* x, int64_t tokens, int32_t topk, int64
     return fail(B200K_UNSUPPORTED, "hidden must be a multiple of 8 and buffers 16-byte aligned");
   const int grid = blocks_for(tokens * hidden / 8, 256);
   if (dtype == B200K_BF16)
-    topk_sum_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), tokens, topk, hidden,
+    topk_sum_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), index, tokens, topk, hidden,
                                                     static_cast<uint16_t*>(out));
   else if (dtype == B200K_F16)
-    topk_sum_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), tokens, topk, hidden,
+    topk_sum_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), index, tokens, topk, hidden,
                                                      static_cast<uint16_t*>(out));
   else
     return fail(B200K_INVALID_ARG, "dtype must be f16 or bf16");

@@ -238,10 +238,11 @@ int b200k_gather_rows(const void* src, int64_t src_rows, int64_t row_bytes,
 int b200k_silu_and_mul(const void* ab, int64_t rows, int64_t n, int64_t ld_ab, void* c,
                        int64_t ld_c, int32_t dtype, b200k_stream stream);
 
-/* out[t, :] = sum over slot of x[t, slot, :] with fp32 accumulation; replaces
+/* out[t, :] = sum over slot of x[row(t, slot), :] with fp32 accumulation, where
+ * row(t, slot) = index[t * topk + slot], or t * topk + slot when index is NULL; replaces
  * torch.sum(intermediate_cache3, dim=1) (reference: samples/MoE.py:288). */
-int b200k_topk_sum(const void* x, int64_t tokens, int32_t topk, int64_t hidden, void* out,
-                   int32_t dtype, b200k_stream stream);
+int b200k_topk_sum(const void* x, const int32_t* index, int64_t tokens, int32_t topk,
+                   int64_t hidden, void* out, int32_t dtype, b200k_stream stream);
 
 /* ---- peer-memory gather (AllGather GEMM) -------------------------------
  * dst rows [p * rows, (p + 1) * rows) = shard p, read through `shards[p]`, a pointer this
