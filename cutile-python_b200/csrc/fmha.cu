@@ -41,6 +41,12 @@ struct FmhaParams {
   int* status;
 };
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -72,22 +78,28 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
         break;
       }
       tc_fence_after_sync();
-      // Pass 1: row maximum, streaming S out of tensor memory 32 columns at a time.
-      const int key0 = j * kFmhaBN;
-      const bool need_mask = (key0 + kFmhaBN > p.sk) || (p.causal && key0 + kFmhaBN - 1 > p.input_pos + q0);
-      const int limit = p.causal ? min(p.sk - 1, q_pos) : p.sk - 1;  // last visible key
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_s + lane_addr + c * 32, r);
+      float s[128];
+      {
+        uint32_t r[128];
+        tmem_ld_32x32b_x128(tmem_s + lane_addr, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(r[i]);
-          if (need_mask && key0 + c * 32 + i > limit) v = -INFINITY;
-          mx4[i & 3] = fmaxf(mx4[i & 3], v);
-        }
+        for (int i = 0; i < 128; ++i) s[i] = __uint_as_float(r[i]);
+      }
+      const int key0 = j * kFmhaBN;
+      const bool need_mask = (key0 + kFmhaBN > p.sk) || (p.causal && key0 + kFmhaBN - 1 > p.input_pos + q0);
+      if (need_mask) {
+        const int limit = p.causal ? min(p.sk - 1, q_pos) : p.sk - 1;  // last visible key
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (key0 + i > limit) s[i] = -INFINITY;
+      }
+      // three-input max in four independent chains
+      float mx4[4] = {s[0], s[1], s[2], s[3]};
+#pragma unroll
+      for (int i = 4; i < 128; i += 8) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) mx4[c] = fmax3(mx4[c], s[i + 2 * c], s[i + 2 * c + 1]);
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
@@ -113,39 +125,27 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
           tmem_st_32x32b_x32(tmem_o + lane_addr + c * 32, r);
         }
       }
-      // Pass 2: P = exp2(S * scale - m), 64 scores -> 32 packed columns per step.  The packed
-      // columns [32 c, 32 c + 32) overwrite scores that this thread has already consumed.
       const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
-      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      // packed fp32 pairs: one FFMA2 scales and shifts two scores, one FADD2 adds two
+      // probabilities into the running sums
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2 negm2 = make_float2(neg_m, neg_m);
+      float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f),
+                        make_float2(0.f, 0.f)};
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32b_x32(tmem_s + lane_addr + c * 64, r0);
-        tmem_ld_32x32b_x32(tmem_s + lane_addr + c * 64 + 32, r1);
-        tmem_ld_wait();
         uint32_t pk[32];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float a0 = __uint_as_float(r0[2 * i]), a1 = __uint_as_float(r0[2 * i + 1]);
-          float b0 = __uint_as_float(r1[2 * i]), b1 = __uint_as_float(r1[2 * i + 1]);
-          if (need_mask) {
-            if (key0 + c * 64 + 2 * i > limit) a0 = -INFINITY;
-            if (key0 + c * 64 + 2 * i + 1 > limit) a1 = -INFINITY;
-            if (key0 + c * 64 + 32 + 2 * i > limit) b0 = -INFINITY;
-            if (key0 + c * 64 + 32 + 2 * i + 1 > limit) b1 = -INFINITY;
-          }
-          const float p0 = fast_exp2(fmaf(a0, p.scale_log2, neg_m));
-          const float p1 = fast_exp2(fmaf(a1, p.scale_log2, neg_m));
-          const float p2 = fast_exp2(fmaf(b0, p.scale_log2, neg_m));
-          const float p3 = fast_exp2(fmaf(b1, p.scale_log2, neg_m));
-          sum4[i & 1] += p0 + p1;
-          sum4[2 + (i & 1)] += p2 + p3;
-          pk[i] = BF16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
-          pk[16 + i] = BF16 ? pack_bf16x2(p2, p3) : pack_f16x2(p2, p3);
+        for (int i = 0; i < 32; ++i) {
+          const float2 x = __ffma2_rn(make_float2(s[c * 64 + 2 * i], s[c * 64 + 2 * i + 1]), scale2, negm2);
+          const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          sum2[i & 3] = __fadd2_rn(sum2[i & 3], e);
+          pk[i] = BF16 ? pack_bf16x2(e.x, e.y) : pack_f16x2(e.x, e.y);
         }
         tmem_st_32x32b_x32(tmem_s + lane_addr + c * 32, pk);
       }
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      l += ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y)) +
+           ((sum2[2].x + sum2[2].y) + (sum2[3].x + sum2[3].y));
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
