@@ -41,9 +41,47 @@ struct FmhaParams {
   int* status;
 };
 
+#ifdef B200K_TRACE
+// Debug build only: cycles per softmax thread summed over threads of lane 0, quarter 0.
+// 0 wait S_FULL, 1 TMEM load, 2 max + bookkeeping, 3 exp / pack / store, 4 tiles
+__device__ unsigned long long g_fmha_trace[8];
+#define FT0(v) long long v = clock64()
+#define FTADD(i, v) do { if (trace_me) atomicAdd(&g_fmha_trace[i], static_cast<unsigned long long>(clock64() - (v))); } while (0)
+#else
+#define FT0(v)
+#define FTADD(i, v)
+#endif
+
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// Every kFmhaPolyEvery-th pair of scores takes its exp2 on the FMA pipe (a degree-3
+// polynomial after splitting off the integer part) instead of the special-function unit,
+// which is the busiest pipe of the softmax.  Relative error 7.5e-5, far below the rounding
+// of P to 16 bits.  0 disables the polynomial path.
+#ifndef B200K_FMHA_POLY
+#define B200K_FMHA_POLY 4
+#endif
+constexpr int kFmhaPolyEvery = B200K_FMHA_POLY;
+
+__device__ __forceinline__ float2 exp2_poly_pair(float2 x) {
+  const float2 magic = make_float2(12582912.0f, 12582912.0f);       // 1.5 * 2^23
+  const float2 neg_magic = make_float2(-12582912.0f, -12582912.0f);
+  x.x = fmaxf(x.x, -125.0f);
+  x.y = fmaxf(x.y, -125.0f);
+  const float2 t = __fadd2_rn(x, magic);            // integer part lands in the low mantissa bits
+  const float2 i = __fadd2_rn(t, neg_magic);
+  const float2 f = __fadd2_rn(x, make_float2(-i.x, -i.y));   // in [-0.5, 0.5]
+  float2 p = __ffma2_rn(make_float2(0.05517164617776871f, 0.05517164617776871f), f,
+                        make_float2(0.2426111251115799f, 0.2426111251115799f));
+  p = __ffma2_rn(p, f, make_float2(0.6932609677314758f, 0.6932609677314758f));
+  p = __ffma2_rn(p, f, make_float2(0.9999280571937561f, 0.9999280571937561f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
   return r;
 }
 
@@ -69,8 +107,12 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
     float m_used = -INFINITY;
     float l = 0.0f;
     bool ok = true;
+#ifdef B200K_TRACE
+    const bool trace_me = (lane == 0) && (quarter == 0);
+#endif
     for (int j = 0; j < n_kv; ++j) {
       const uint32_t ph = j & 1;
+      FT0(t_w);
       if (!mbar_wait(s_full, ph, abort_flag)) {
         report_status(p.status, 31, j);
         *abort_flag = 1;
@@ -78,6 +120,8 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
         break;
       }
       tc_fence_after_sync();
+      FTADD(0, t_w);
+      FT0(t_l);
       float s[128];
       {
         uint32_t r[128];
@@ -86,6 +130,8 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
 #pragma unroll
         for (int i = 0; i < 128; ++i) s[i] = __uint_as_float(r[i]);
       }
+      FTADD(1, t_l);
+      FT0(t_m);
       const int key0 = j * kFmhaBN;
       const bool need_mask = (key0 + kFmhaBN > p.sk) || (p.causal && key0 + kFmhaBN - 1 > p.input_pos + q0);
       if (need_mask) {
@@ -94,14 +140,17 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
         for (int i = 0; i < 128; ++i)
           if (key0 + i > limit) s[i] = -INFINITY;
       }
-      // three-input max in four independent chains
-      float mx4[4] = {s[0], s[1], s[2], s[3]};
+      // three-input max, eight independent chains of 16 scores
+      float mx8[8];
 #pragma unroll
-      for (int i = 4; i < 128; i += 8) {
+      for (int c = 0; c < 8; ++c) {
+        float m = fmax3(s[16 * c], s[16 * c + 1], s[16 * c + 2]);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) mx4[c] = fmax3(mx4[c], s[i + 2 * c], s[i + 2 * c + 1]);
+        for (int i = 3; i < 15; i += 2) m = fmax3(m, s[16 * c + i], s[16 * c + i + 1]);
+        mx8[c] = fmaxf(m, s[16 * c + 15]);
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      const float mx = fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]),
+                             fmaxf(mx8[6], mx8[7]));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       // Deferred rescale: keep the stale maximum while the true one is less than 2^8
       // above it.  A row whose maximum is still -inf has seen no key yet.
@@ -126,6 +175,8 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
         }
       }
       const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
+      FTADD(2, t_m);
+      FT0(t_e);
       // packed fp32 pairs: one FFMA2 scales and shifts two scores, one FADD2 adds two
       // probabilities into the running sums
       const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
@@ -138,7 +189,8 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const float2 x = __ffma2_rn(make_float2(s[c * 64 + 2 * i], s[c * 64 + 2 * i + 1]), scale2, negm2);
-          const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          const bool poly = kFmhaPolyEvery > 0 && (i % (kFmhaPolyEvery > 0 ? kFmhaPolyEvery : 1)) == kFmhaPolyEvery - 1;
+          const float2 e = poly ? exp2_poly_pair(x) : make_float2(fast_exp2(x.x), fast_exp2(x.y));
           sum2[i & 3] = __fadd2_rn(sum2[i & 3], e);
           pk[i] = BF16 ? pack_bf16x2(e.x, e.y) : pack_f16x2(e.x, e.y);
         }
@@ -150,6 +202,10 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
+      FTADD(3, t_e);
+#ifdef B200K_TRACE
+      if (trace_me) atomicAdd(&g_fmha_trace[4], 1ull);
+#endif
     }
     // epilogue: O / l
     if (ok && n_kv > 0) {
@@ -260,11 +316,16 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   constexpr uint32_t kFmt = BF16 ? kFmtBF16 : kFmtF16;
 
   if (warp == 0) {
-    if (lane == 0 && n_kv > 0) {
-      mbar_arrive_expect_tx(bar(Q_FULL), kTileBytes);
+    // warp-uniform loop (addresses and coordinates stay in uniform registers), one elected
+    // lane issues
+    if (n_kv > 0) {
+      const bool elected = elect_one();
+      if (elected) {
+        mbar_arrive_expect_tx(bar(Q_FULL), kTileBytes);
 #pragma unroll
-      for (int i = 0; i < kBoxes; ++i)
-        tma_load_4d(q_smem + i * kBoxBytes, &tmap_q, bar(Q_FULL), i * 64, q0, h, b);
+        for (int i = 0; i < kBoxes; ++i)
+          tma_load_4d(q_smem + i * kBoxBytes, &tmap_q, bar(Q_FULL), i * 64, q0, h, b);
+      }
       for (int j = 0; j < n_kv; ++j) {
         const uint32_t ph = j & 1;
         if (!mbar_wait(bar(K_EMPTY), ph ^ 1, abort_flag)) {
@@ -272,24 +333,29 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           *abort_flag = 1;
           break;
         }
-        mbar_arrive_expect_tx(bar(K_FULL), kTileBytes);
+        if (elected) {
+          mbar_arrive_expect_tx(bar(K_FULL), kTileBytes);
 #pragma unroll
-        for (int i = 0; i < kBoxes; ++i)
-          tma_load_4d(k_smem + i * kBoxBytes, &tmap_k, bar(K_FULL), i * 64, j * kFmhaBN, h_kv, b);
+          for (int i = 0; i < kBoxes; ++i)
+            tma_load_4d(k_smem + i * kBoxBytes, &tmap_k, bar(K_FULL), i * 64, j * kFmhaBN, h_kv, b);
+        }
         if (!mbar_wait(bar(V_EMPTY), ph ^ 1, abort_flag)) {
           report_status(p.status, 12, j);
           *abort_flag = 1;
           break;
         }
-        mbar_arrive_expect_tx(bar(V_FULL), kTileBytes);
+        if (elected) {
+          mbar_arrive_expect_tx(bar(V_FULL), kTileBytes);
 #pragma unroll
-        for (int i = 0; i < kBoxes; ++i)
-          tma_load_4d(v_smem + i * kBoxBytes, &tmap_v, bar(V_FULL), i * 64, j * kFmhaBN, h_kv, b);
+          for (int i = 0; i < kBoxes; ++i)
+            tma_load_4d(v_smem + i * kBoxBytes, &tmap_v, bar(V_FULL), i * 64, j * kFmhaBN, h_kv, b);
+        }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0 && n_kv > 0) {
+    if (n_kv > 0) {
+      const bool elected = elect_one();
       constexpr uint32_t idesc_qk = make_idesc(kFmt, kFmt, false, false, kFmhaBM, kFmhaBN);
       constexpr uint32_t idesc_pv = make_idesc(kFmt, kFmt, false, true, kFmhaBM, D);
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag);
@@ -311,10 +377,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           const uint32_t off = (kk / 4) * kBoxBytes;
           const uint64_t qd = make_smem_desc(q_smem + off, 16, 1024, kSwizzle128B) + 2 * (kk % 4);
           const uint64_t kd = make_smem_desc(k_smem + off, 16, 1024, kSwizzle128B) + 2 * (kk % 4);
-          umma<kKindF16>(tmem_s, qd, kd, idesc_qk, kk > 0 ? 1u : 0u);
+          if (elected) umma<kKindF16>(tmem_s, qd, kd, idesc_qk, kk > 0 ? 1u : 0u);
         }
-        tc_commit(bar(K_EMPTY));
-        tc_commit(bar(S_FULL));
+        if (elected) {
+          tc_commit(bar(K_EMPTY));
+          tc_commit(bar(S_FULL));
+        }
         if (!mbar_wait(bar(P_FULL), ph, abort_flag)) {
           report_status(p.status, 22, j);
           *abort_flag = 1;
@@ -332,10 +400,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
         for (int kk = 0; kk < kFmhaBN / 16; ++kk) {
           const uint64_t vd = make_smem_desc(v_smem + kk * 2048, kBoxBytes, 1024, kSwizzle128B);
-          umma_f16_ts(tmem_o, tmem_s + kk * 8, vd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          if (elected) umma_f16_ts(tmem_o, tmem_s + kk * 8, vd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        tc_commit(bar(V_EMPTY));
-        tc_commit(bar(PV_DONE));
+        if (elected) {
+          tc_commit(bar(V_EMPTY));
+          tc_commit(bar(PV_DONE));
+        }
       }
     }
     __syncwarp();
@@ -352,6 +422,164 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   }
 }
 
+// The softmax of one 128-row query tile spread over EIGHT warps: two threads share a row,
+// thread `half` 0 owns score columns [0, 64) and output columns [0, 64), thread 1 the rest.
+// Twice the warps per scheduler hide the TMEM, special-function and dependency latencies
+// that a single warp per scheduler leaves exposed.  The two threads of a row agree on the
+// row maximum through shared memory once per key tile (named barrier of their two warps)
+// and add their partial sums once at the end.
+template <bool BF16>
+__device__ __forceinline__ void softmax_half_tile(const FmhaParams& p, int quarter, int half, int lane,
+                                                  int b, int h, int q0, int n_kv, uint32_t tmem_s,
+                                                  uint32_t tmem_o, uint32_t s_full, uint32_t p_full,
+                                                  uint32_t pv_done, volatile int* abort_flag,
+                                                  float* xchg /* [2 slots][2 halves][128] */,
+                                                  int pair_barrier) {
+  const int row = quarter * 32 + lane;
+  const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
+  const int q_pos = p.input_pos + q0 + row;
+  const int col0 = half * 64;
+  float m_used = -INFINITY;
+  float l = 0.0f;
+  bool ok = true;
+  auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory"); };
+  for (int j = 0; j < n_kv; ++j) {
+    if (!mbar_wait(s_full, j & 1, abort_flag)) {
+      report_status(p.status, 31, j);
+      *abort_flag = 1;
+      ok = false;
+      break;
+    }
+    tc_fence_after_sync();
+    float s[64];
+    {
+      uint32_t r[64];
+      tmem_ld_32x32b_x64(tmem_s + lane_addr + col0, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 64; ++i) s[i] = __uint_as_float(r[i]);
+    }
+    const int key0 = j * kFmhaBN + col0;
+    const bool need_mask = (j * kFmhaBN + kFmhaBN > p.sk) ||
+                           (p.causal && j * kFmhaBN + kFmhaBN - 1 > p.input_pos + q0);
+    if (need_mask) {
+      const int limit = p.causal ? min(p.sk - 1, q_pos) : p.sk - 1;  // last visible key
+#pragma unroll
+      for (int i = 0; i < 64; ++i)
+        if (key0 + i > limit) s[i] = -INFINITY;
+    }
+    float mx4[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      float m = fmax3(s[16 * c], s[16 * c + 1], s[16 * c + 2]);
+#pragma unroll
+      for (int i = 3; i < 15; i += 2) m = fmax3(m, s[16 * c + i], s[16 * c + i + 1]);
+      mx4[c] = fmaxf(m, s[16 * c + 15]);
+    }
+    float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+    // agree on the row maximum with the thread that owns the other 64 columns; both have
+    // their scores in registers once they pass the barrier, so P may overwrite S after it
+    float* slot = xchg + (j & 1) * 256;
+    slot[half * 128 + row] = mx;
+    pair_sync();
+    mx = fmaxf(mx, slot[(half ^ 1) * 128 + row]);
+    const float m_new = fmaxf(m_used, mx * p.scale_log2);
+    bool grow = (m_new - m_used > kRescaleThreshold) || (m_used == -INFINITY && m_new > -INFINITY);
+    const bool any_grow = __any_sync(0xffffffffu, grow);
+    float alpha = 1.0f;
+    if (grow) {
+      alpha = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_new);
+      m_used = m_new;
+    }
+    if (any_grow && j > 0) {
+      l *= alpha;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_o + lane_addr + col0 + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+        tmem_st_32x32b_x32(tmem_o + lane_addr + col0 + c * 32, r);
+      }
+    }
+    const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
+    const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+    const float2 negm2 = make_float2(neg_m, neg_m);
+    float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f),
+                      make_float2(0.f, 0.f)};
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float2 x = __ffma2_rn(make_float2(s[32 * c + 2 * i], s[32 * c + 2 * i + 1]), scale2, negm2);
+        const bool poly = kFmhaPolyEvery > 0 && (i % (kFmhaPolyEvery > 0 ? kFmhaPolyEvery : 1)) == kFmhaPolyEvery - 1;
+        const float2 e = poly ? exp2_poly_pair(x) : make_float2(fast_exp2(x.x), fast_exp2(x.y));
+        sum2[i & 3] = __fadd2_rn(sum2[i & 3], e);
+        pk[i] = BF16 ? pack_bf16x2(e.x, e.y) : pack_f16x2(e.x, e.y);
+      }
+      tmem_st_32x32b_x16(tmem_s + lane_addr + half * 32 + c * 16, pk);
+    }
+    l += ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y)) +
+         ((sum2[2].x + sum2[2].y) + (sum2[3].x + sum2[3].y));
+    tmem_st_wait();
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(p_full);
+  }
+  // O / l: the row sum is the sum of the two threads' partial sums
+  if (ok && n_kv > 0) {
+    if (!mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag)) {
+      report_status(p.status, 32, 0);
+      *abort_flag = 1;
+      ok = false;
+    }
+  }
+  tc_fence_after_sync();
+  float* lslot = xchg + 512;
+  lslot[half * 128 + row] = l;
+  pair_sync();
+  l += lslot[(half ^ 1) * 128 + row];
+  const bool row_ok = (q0 + row) < p.sq;
+  uint16_t* o_row = static_cast<uint16_t*>(p.out) + b * p.o_stride_b + h * p.o_stride_h +
+                    static_cast<int64_t>(q0 + row) * p.o_stride_s + col0;
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0) && (p.o_stride_b % 8 == 0) &&
+                      (p.o_stride_h % 8 == 0) && (p.o_stride_s % 8 == 0);
+  const float inv_l = (l > 0.0f) ? __fdividef(1.0f, l) : 0.0f;
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    uint32_t r[32];
+    if (ok && n_kv > 0) {
+      tmem_ld_32x32b_x32(tmem_o + lane_addr + col0 + c * 32, r);
+      tmem_ld_wait();
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) r[i] = 0;
+    }
+    if (row_ok) {
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float a = __uint_as_float(r[2 * i]) * inv_l;
+        const float c2 = __uint_as_float(r[2 * i + 1]) * inv_l;
+        pk[i] = BF16 ? pack_bf16x2(a, c2) : pack_f16x2(a, c2);
+      }
+      if (vec_ok) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          reinterpret_cast<uint4*>(o_row + c * 32)[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          o_row[c * 32 + 2 * i] = static_cast<uint16_t>(pk[i] & 0xffff);
+          o_row[c * 32 + 2 * i + 1] = static_cast<uint16_t>(pk[i] >> 16);
+        }
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Two query tiles per CTA (head dim 128): one CTA per SM owns 256 query rows.  Warp group A
 // (warps 2-5) does the softmax of rows [q0, q0 + 128), warp group B (warps 6-9) of rows
@@ -361,10 +589,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 // tiles are double-buffered and shared by both query tiles.
 // TMEM: S_A [0,128)  S_B [128,256)  O_A [256,384)  O_B [384,512); P aliases S.
 // ---------------------------------------------------------------------------
-constexpr int kFmha2Threads = 320;
-
-template <bool BF16>
-__global__ void __launch_bounds__(kFmha2Threads, 1)
+// SPLIT: each query row is shared by two softmax threads (2 x 8 softmax warps, 576 threads)
+// instead of one (2 x 4 softmax warps, 320 threads).
+template <bool BF16, bool SPLIT>
+__global__ void __launch_bounds__(SPLIT ? 576 : 320, 1)
 fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, const FmhaParams p) {
   constexpr int D = 128;
@@ -383,6 +611,7 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   auto bar = [&](int i) { return bar0 + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8 * NUM_BARS + 8);
+  float* xchg = reinterpret_cast<float*>(tail + 256);   // per warp group: 768 floats
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -409,7 +638,7 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const int n_kv = max(n_x[0], n_x[1]);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NUM_BARS; ++i) mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? 4 : 1);
+    for (int i = 0; i < NUM_BARS; ++i) mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? (SPLIT ? 8 : 4) : 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_q);
@@ -427,13 +656,16 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   constexpr uint32_t kFmt = BF16 ? kFmtBF16 : kFmtF16;
 
   if (warp == 0) {
-    if (lane == 0 && n_kv > 0) {
-      mbar_arrive_expect_tx(bar(Q_FULL), 2 * kTileBytes);
+    if (n_kv > 0) {
+      const bool elected = elect_one();
+      if (elected) {
+        mbar_arrive_expect_tx(bar(Q_FULL), 2 * kTileBytes);
 #pragma unroll
-      for (int x = 0; x < 2; ++x)
+        for (int x = 0; x < 2; ++x)
 #pragma unroll
-        for (int i = 0; i < 2; ++i)
-          tma_load_4d(q_smem + x * kTileBytes + i * kBoxBytes, &tmap_q, bar(Q_FULL), i * 64, q0 + x * 128, h, b);
+          for (int i = 0; i < 2; ++i)
+            tma_load_4d(q_smem + x * kTileBytes + i * kBoxBytes, &tmap_q, bar(Q_FULL), i * 64, q0 + x * 128, h, b);
+      }
       for (int j = 0; j < n_kv; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
@@ -442,26 +674,31 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           *abort_flag = 1;
           break;
         }
-        mbar_arrive_expect_tx(bar(K_FULL + st), kTileBytes);
+        if (elected) {
+          mbar_arrive_expect_tx(bar(K_FULL + st), kTileBytes);
 #pragma unroll
-        for (int i = 0; i < 2; ++i)
-          tma_load_4d(k_smem + st * kTileBytes + i * kBoxBytes, &tmap_k, bar(K_FULL + st), i * 64,
-                      j * kFmhaBN, h_kv, b);
+          for (int i = 0; i < 2; ++i)
+            tma_load_4d(k_smem + st * kTileBytes + i * kBoxBytes, &tmap_k, bar(K_FULL + st), i * 64,
+                        j * kFmhaBN, h_kv, b);
+        }
         if (!mbar_wait(bar(V_EMPTY + st), ph ^ 1, abort_flag)) {
           report_status(p.status, 62, j);
           *abort_flag = 1;
           break;
         }
-        mbar_arrive_expect_tx(bar(V_FULL + st), kTileBytes);
+        if (elected) {
+          mbar_arrive_expect_tx(bar(V_FULL + st), kTileBytes);
 #pragma unroll
-        for (int i = 0; i < 2; ++i)
-          tma_load_4d(v_smem + st * kTileBytes + i * kBoxBytes, &tmap_v, bar(V_FULL + st), i * 64,
-                      j * kFmhaBN, h_kv, b);
+          for (int i = 0; i < 2; ++i)
+            tma_load_4d(v_smem + st * kTileBytes + i * kBoxBytes, &tmap_v, bar(V_FULL + st), i * 64,
+                        j * kFmhaBN, h_kv, b);
+        }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0 && n_kv > 0) {
+    if (n_kv > 0) {
+      const bool elected = elect_one();
       constexpr uint32_t idesc_qk = make_idesc(kFmt, kFmt, false, false, kFmhaBM, kFmhaBN);
       constexpr uint32_t idesc_pv = make_idesc(kFmt, kFmt, false, true, kFmhaBM, D);
       // S_x = Q_x K^T for key tile j (stage st): 8 MMAs of K = 16
@@ -471,19 +708,20 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           const uint32_t off = (kk / 4) * kBoxBytes;
           const uint64_t qd = make_smem_desc(q_smem + x * kTileBytes + off, 16, 1024, kSwizzle128B) + 2 * (kk % 4);
           const uint64_t kd = make_smem_desc(k_smem + st * kTileBytes + off, 16, 1024, kSwizzle128B) + 2 * (kk % 4);
-          umma<kKindF16>(tmem_base + x * 128, qd, kd, idesc_qk, kk > 0 ? 1u : 0u);
+          if (elected) umma<kKindF16>(tmem_base + x * 128, qd, kd, idesc_qk, kk > 0 ? 1u : 0u);
         }
-        tc_commit(bar(S_FULL + x));
+        if (elected) tc_commit(bar(S_FULL + x));
       };
       // O_x += P_x V for key tile j: P from TMEM, V MN-major
       auto issue_pv = [&](int x, int st, bool first) {
 #pragma unroll
         for (int kk = 0; kk < kFmhaBN / 16; ++kk) {
           const uint64_t vd = make_smem_desc(v_smem + st * kTileBytes + kk * 2048, kBoxBytes, 1024, kSwizzle128B);
-          umma_f16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + kk * 8, vd, idesc_pv,
-                      (!first || kk > 0) ? 1u : 0u);
+          if (elected)
+            umma_f16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + kk * 8, vd, idesc_pv,
+                        (!first || kk > 0) ? 1u : 0u);
         }
-        tc_commit(bar(PV_DONE + x));
+        if (elected) tc_commit(bar(PV_DONE + x));
       };
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag);
       if (ok) ok = mbar_wait(bar(K_FULL), 0, abort_flag);
@@ -494,7 +732,7 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         tc_fence_after_sync();
         if (n_x[0] > 0) issue_s(0, 0);
         if (n_x[1] > 0) issue_s(1, 0);
-        tc_commit(bar(K_EMPTY));
+        if (elected) tc_commit(bar(K_EMPTY));
       }
       for (int j = 0; j < n_kv && ok; ++j) {
         const int st = j & 1;
@@ -527,16 +765,27 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           if (more && j + 1 < n_x[x]) issue_s(x, st1);
         }
         if (!ok) break;
-        tc_commit(bar(V_EMPTY + st));
-        if (more) tc_commit(bar(K_EMPTY + st1));
+        if (elected) {
+          tc_commit(bar(V_EMPTY + st));
+          if (more) tc_commit(bar(K_EMPTY + st1));
+        }
       }
     }
     __syncwarp();
   } else {
-    const int x = (warp - 2) >> 2;           // warp group: query tile A or B
-    softmax_tile<D, BF16>(p, warp, lane, b, h, q0 + x * 128, n_x[x], tmem_base + x * 128,
-                          tmem_base + 256 + x * 128, bar(S_FULL + x), bar(P_FULL + x), bar(PV_DONE + x),
-                          abort_flag);
+    if constexpr (SPLIT) {
+      const int x = (warp - 2) >> 3;           // warp group: query tile A (warps 2-9) or B (10-17)
+      const int half = ((warp - 2) >> 2) & 1;  // which 64 columns of the row
+      const int quarter = warp & 3;            // TMEM lanes this warp may touch
+      softmax_half_tile<BF16>(p, quarter, half, lane, b, h, q0 + x * 128, n_x[x], tmem_base + x * 128,
+                              tmem_base + 256 + x * 128, bar(S_FULL + x), bar(P_FULL + x),
+                              bar(PV_DONE + x), abort_flag, xchg + x * 768, 1 + x * 4 + quarter);
+    } else {
+      const int x = (warp - 2) >> 2;           // warp group: query tile A (warps 2-5) or B (6-9)
+      softmax_tile<D, BF16>(p, warp, lane, b, h, q0 + x * 128, n_x[x], tmem_base + x * 128,
+                            tmem_base + 256 + x * 128, bar(S_FULL + x), bar(P_FULL + x),
+                            bar(PV_DONE + x), abort_flag);
+    }
   }
 
   tc_fence_before_sync();
@@ -568,11 +817,11 @@ int launch_fmha(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
   return B200K_OK;
 }
 
-template <bool BF16>
+template <bool BF16, bool SPLIT>
 int launch_fmha_pair(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                      const FmhaParams& p, int grid, cudaStream_t stream) {
-  constexpr int kSmem = 1024 + 6 * 128 * 128 * 2 + 256;
-  auto kernel = fmha_fwd_pair_kernel<BF16>;
+  constexpr int kSmem = 1024 + 6 * 128 * 128 * 2 + 256 + 2 * 768 * 4;
+  auto kernel = fmha_fwd_pair_kernel<BF16, SPLIT>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -582,7 +831,7 @@ int launch_fmha_pair(const CUtensorMap& tq, const CUtensorMap& tk, const CUtenso
       return fail(B200K_CUDA_ERROR, "cudaFuncSetAttribute(%d): %s", kSmem, cudaGetErrorString(e));
     configured[dev] = true;
   }
-  kernel<<<grid, kFmha2Threads, kSmem, stream>>>(tq, tk, tv, p);
+  kernel<<<grid, SPLIT ? 576 : 320, kSmem, stream>>>(tq, tk, tv, p);
   B200K_CHECK_LAUNCH("fmha (two-tile) launch");
   return B200K_OK;
 }
@@ -656,8 +905,13 @@ extern "C" int b200k_fmha_fwd(const b200k_fmha_args* a, b200k_stream stream_) {
   if (d == 128 && a->seq_q > 128 && !(one_tile != nullptr && one_tile[0] == '1')) {
     const int64_t g2 = ceil_div(a->seq_q, 256) * a->batch * a->heads_q;
     if (g2 > INT32_MAX) return fail(B200K_UNSUPPORTED, "too many tiles");
-    return bf16 ? launch_fmha_pair<true>(tq, tk, tv, p, static_cast<int>(g2), stream)
-                : launch_fmha_pair<false>(tq, tk, tv, p, static_cast<int>(g2), stream);
+    const char* split_env = getenv("B200K_FMHA_SPLIT_ROWS");
+    const bool split = split_env != nullptr && split_env[0] == '1';
+    if (split)
+      return bf16 ? launch_fmha_pair<true, true>(tq, tk, tv, p, static_cast<int>(g2), stream)
+                  : launch_fmha_pair<false, true>(tq, tk, tv, p, static_cast<int>(g2), stream);
+    return bf16 ? launch_fmha_pair<true, false>(tq, tk, tv, p, static_cast<int>(g2), stream)
+                : launch_fmha_pair<false, false>(tq, tk, tv, p, static_cast<int>(g2), stream);
   }
   if (d == 128)
     return bf16 ? launch_fmha<128, true>(tq, tk, tv, p, grid, stream)
@@ -665,3 +919,13 @@ extern "C" int b200k_fmha_fwd(const b200k_fmha_args* a, b200k_stream stream_) {
   return bf16 ? launch_fmha<64, true>(tq, tk, tv, p, grid, stream)
               : launch_fmha<64, false>(tq, tk, tv, p, grid, stream);
 }
+
+#ifdef B200K_TRACE
+extern "C" int b200k_debug_fmha_trace(unsigned long long* out8) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out8, b200k::g_fmha_trace, sizeof(unsigned long long) * 8);
+  unsigned long long zero[8] = {};
+  cudaMemcpyToSymbol(b200k::g_fmha_trace, zero, sizeof(zero));
+  return 0;
+}
+#endif

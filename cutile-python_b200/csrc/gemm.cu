@@ -77,7 +77,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
-    if (lane == 0) {
+    // The whole warp walks the loop so that addresses and coordinates stay warp-uniform
+    // (they feed the TMA unit from uniform registers); one elected lane issues.
+    {
+      const bool elected = elect_one();
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -104,11 +107,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             sfa_atoms = min(Cfg::kSfaAtoms, p.sf_k_atoms - kb * Cfg::kSfaAtoms);
             tx += sfa_atoms * 512 * (1 + BN / 128);
           }
-          mbar_arrive_expect_tx(full_bar(s), tx);
           const uint32_t a_dst = tiles_base + s * Cfg::kStageBytes;
           const uint32_t b_dst = a_dst + Cfg::kABytes;
           // TMA x coordinate in tensor-map elements (fp4 maps are byte typed)
           const int kx = kb * (KIND == kKindNVF4 ? 128 : Cfg::kBKElems);
+          if (elected) {
+          mbar_arrive_expect_tx(full_bar(s), tx);
           tma_load_3d(a_dst, &tmap_a, full_bar(s), kx, m0, p.tile_group ? 0 : tc.batch);
           if constexpr (B_MN) {
 #pragma unroll
@@ -142,13 +146,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               bulk_load(sfb_dst + j * Cfg::kSfaAtoms * 512, sfb_src, sfa_atoms * 512, full_bar(s));
             }
           }
+          }
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    {
+      const bool elected = elect_one();
       uint32_t it = 0;
       uint32_t local_tile = 0;
       bool ok = true;
@@ -190,16 +196,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             const uint32_t sfb_addr = sfa_addr + Cfg::kSfaAtoms * 512;
             const int atoms = min(Cfg::kSfaAtoms, p.sf_k_atoms - kb * Cfg::kSfaAtoms);
             for (int ka = 0; ka < atoms; ++ka) {
-              tmem_cp_sf_atom(tsfa + ka * 4, make_smem_desc(sfa_addr + ka * 512, 128, 128, kSwizzleNone));
+              const uint64_t da = make_smem_desc(sfa_addr + ka * 512, 128, 128, kSwizzleNone);
+              if (elected) tmem_cp_sf_atom(tsfa + ka * 4, da);
 #pragma unroll
-              for (int j = 0; j < BN / 128; ++j)
-                tmem_cp_sf_atom(tsfb + ka * (BN / 128) * 4 + j * 4,
-                                make_smem_desc(sfb_addr + (j * Cfg::kSfaAtoms + ka) * 512, 128, 128, kSwizzleNone));
+              for (int j = 0; j < BN / 128; ++j) {
+                const uint64_t db = make_smem_desc(sfb_addr + (j * Cfg::kSfaAtoms + ka) * 512, 128, 128, kSwizzleNone);
+                if (elected) tmem_cp_sf_atom(tsfb + ka * (BN / 128) * 4 + j * 4, db);
+              }
             }
           }
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            if (kk < n_mma) {
+            if (kk < n_mma && elected) {
               const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
               // K-major: 32 bytes of K per MMA inside the 128-byte swizzle atom.
               // MN-major B: kMmaK rows of 128 bytes per MMA.
@@ -218,9 +226,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               }
             }
           }
-          tc_commit(empty_bar(s));
+          if (elected) tc_commit(empty_bar(s));
         }
-        if (ok) tc_commit(acc_full_bar(as));
+        if (ok && elected) tc_commit(acc_full_bar(as));
         ++local_tile;
       }
     }

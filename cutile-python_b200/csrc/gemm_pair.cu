@@ -116,7 +116,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
-    if (lane == 0) {
+    // warp-uniform loop, one elected lane issues (see the MMA warp)
+    {
+      const bool elected = elect_one();
       uint32_t it = 0;
       bool ok = true;
       TRACE_T0(t_total);
@@ -140,31 +142,38 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           TRACE_ACC(w_empty, t_w);
           // the leader's barrier collects the bytes of both CTAs
           const uint32_t lead_full = map_to_cta(full_bar(s), 0);
-          if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * (Cfg::kStageBytes + Cfg::kSfBytes));
           const uint32_t a_dst = tiles_base + s * Cfg::kStageBytes;
           const uint32_t b_dst = a_dst + Cfg::kABytes;
           const int kx = kb * (KIND == kKindNVF4 ? 128 : Cfg::kBKElems);
-          tma_load_3d_pair(a_dst, &tmap_a, lead_full, kx, m0, tc.batch);
-          tma_load_3d_pair(b_dst, &tmap_b, lead_full, kx, nb, tc.batch);
-          if constexpr (Cfg::kScaled) {
-            const uint32_t sfa_dst = sf_base + s * Cfg::kSfBytes;
-            const uint32_t sfb_dst = sfa_dst + Cfg::kSfAtoms * 512;
-            tma_load_4d_pair(sfa_dst, &tmap_sfa, lead_full, 0, 0, kb * Cfg::kSfAtoms, tc.pid_m * 2 + rank);
-            tma_load_4d_pair(sfb_dst, &tmap_sfb, lead_full, 0, 0, kb * Cfg::kSfAtoms, tc.pid_n * 2);
-            tma_load_4d_pair(sfb_dst + Cfg::kSfAtoms * 512, &tmap_sfb, lead_full, 0, 0,
-                             kb * Cfg::kSfAtoms, tc.pid_n * 2 + 1);
+          if (elected) {
+            if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * (Cfg::kStageBytes + Cfg::kSfBytes));
+            tma_load_3d_pair(a_dst, &tmap_a, lead_full, kx, m0, tc.batch);
+            tma_load_3d_pair(b_dst, &tmap_b, lead_full, kx, nb, tc.batch);
+            if constexpr (Cfg::kScaled) {
+              const uint32_t sfa_dst = sf_base + s * Cfg::kSfBytes;
+              const uint32_t sfb_dst = sfa_dst + Cfg::kSfAtoms * 512;
+              tma_load_4d_pair(sfa_dst, &tmap_sfa, lead_full, 0, 0, kb * Cfg::kSfAtoms, tc.pid_m * 2 + rank);
+              tma_load_4d_pair(sfb_dst, &tmap_sfb, lead_full, 0, 0, kb * Cfg::kSfAtoms, tc.pid_n * 2);
+              tma_load_4d_pair(sfb_dst + Cfg::kSfAtoms * 512, &tmap_sfb, lead_full, 0, 0,
+                               kb * Cfg::kSfAtoms, tc.pid_n * 2 + 1);
+            }
           }
         }
       }
 #ifdef B200K_TRACE
-      atomicAdd(&g_trace[0], static_cast<unsigned long long>(w_empty));
-      TRACE_ADD(1, t_total);
+      if (elected) {
+        atomicAdd(&g_trace[0], static_cast<unsigned long long>(w_empty));
+        TRACE_ADD(1, t_total);
+      }
 #endif
     }
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer (leader only) ----------------
-    if (lane == 0 && leader) {
+    // The whole warp walks the loop so that descriptors and addresses stay warp-uniform
+    // (uniform registers feed the MMA directly); one elected lane issues the tcgen05 work.
+    if (leader) {
+      const bool elected = elect_one();
       uint32_t it = 0;
       uint32_t lt = 0;
       bool ok = true;
@@ -217,16 +226,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const uint32_t sfb_addr = sfa_addr + Cfg::kSfAtoms * 512;
 #pragma unroll
             for (int ka = 0; ka < Cfg::kSfAtoms; ++ka) {
-              tmem_cp_sf_atom_pair(tsfa + ka * 4, make_smem_desc(sfa_addr + ka * 512, 128, 128, kSwizzleNone));
+              const uint64_t da = make_smem_desc(sfa_addr + ka * 512, 128, 128, kSwizzleNone);
+              if (elected) tmem_cp_sf_atom_pair(tsfa + ka * 4, da);
 #pragma unroll
-              for (int j = 0; j < 2; ++j)
-                tmem_cp_sf_atom_pair(tsfb + ka * 8 + j * 4,
-                                     make_smem_desc(sfb_addr + (j * Cfg::kSfAtoms + ka) * 512, 128, 128, kSwizzleNone));
+              for (int j = 0; j < 2; ++j) {
+                const uint64_t db = make_smem_desc(sfb_addr + (j * Cfg::kSfAtoms + ka) * 512, 128, 128, kSwizzleNone);
+                if (elected) tmem_cp_sf_atom_pair(tsfb + ka * 8 + j * 4, db);
+              }
             }
           }
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            if (kk < n_mma) {
+            if (kk < n_mma && elected) {
               const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
               const uint64_t a_d = a_desc + static_cast<uint64_t>(kk * 2);
               const uint64_t b_d = b_desc + static_cast<uint64_t>(kk * 2);
@@ -241,20 +252,28 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
           // release the stage in both CTAs
-          tc_commit_pair(map_to_cta(empty_bar(s), 0));
-          tc_commit_pair(map_to_cta(empty_bar(s), 1));
+          const uint32_t e0 = map_to_cta(empty_bar(s), 0), e1 = map_to_cta(empty_bar(s), 1);
+          if (elected) {
+            tc_commit_pair(e0);
+            tc_commit_pair(e1);
+          }
           TRACE_ACC(t_issue, t_i);
         }
         if (ok) {
-          tc_commit_pair(map_to_cta(acc_full_bar(w), 0));
-          tc_commit_pair(map_to_cta(acc_full_bar(w), 1));
+          const uint32_t f0 = map_to_cta(acc_full_bar(w), 0), f1 = map_to_cta(acc_full_bar(w), 1);
+          if (elected) {
+            tc_commit_pair(f0);
+            tc_commit_pair(f1);
+          }
         }
       }
 #ifdef B200K_TRACE
-      atomicAdd(&g_trace[2], static_cast<unsigned long long>(w_full));
-      atomicAdd(&g_trace[3], static_cast<unsigned long long>(w_acc));
-      atomicAdd(&g_trace[7], static_cast<unsigned long long>(t_issue));
-      TRACE_ADD(4, t_total);
+      if (elected) {
+        atomicAdd(&g_trace[2], static_cast<unsigned long long>(w_full));
+        atomicAdd(&g_trace[3], static_cast<unsigned long long>(w_acc));
+        atomicAdd(&g_trace[7], static_cast<unsigned long long>(t_issue));
+        TRACE_ADD(4, t_total);
+      }
 #endif
     }
     __syncwarp();
