@@ -618,7 +618,7 @@ def run_ours(args, w):
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
 # ncu captures summarised under profiles/ (None until captured)
 TRAFFIC_BYTES: dict[str, float | None] = {
-    "mxfp8_gemm_8192x8192x8192_bf16out": 567.0e6,   # profiles/gemm_mxfp8_8192_1cta.md
+    "mxfp8_gemm_8192x8192x8192_bf16out": 466.0e6,   # profiles/gemm_pair_mxfp8_8192.md
 }
 
 
