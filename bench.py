@@ -1,7 +1,8 @@
 """Benchmark of the hot path on B200: TFLOPS of the block-scaled / dense contraction kernels.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload mxfp8_gemm|nvfp4_gemm|dense_f16|ag_nvfp4_gemm|moe_ep_bf16]
+                    [--workload mxfp8_gemm|nvfp4_gemm|dense_f16|ag_nvfp4_gemm|moe_ep_bf16|
+                                fmha_causal|moe_bf16|moe_mxfp8|mxfp8_quantize]
 
 One step = one pass of the workload's kernel over one batch of seeded synthetic input.
 The default workload is the headline configuration: MXFP8 GEMM, M = N = K = 8192, e4m3 operands
@@ -342,6 +343,198 @@ class MoeEpBf16(Workload):
                 "l2": "expert weights alone are 2.4 GB / world per rank (> 126 MiB L2)"}
 
 
+class FmhaCausal(Workload):
+    """Causal attention forward, bf16, batch 4, 32 heads, sequence 8192, head dim 128."""
+    name = "fmha_causal_bf16_b4_h32_s8192_d128"
+    dtype = "bf16 x bf16 -> fp32 softmax / accumulate -> bf16"
+    tensor_rate_vs_bf16 = 1.0
+    B, H, S, D = 4, 32, 8192, 128
+    seed = 3
+    sets = 1
+    cpu_limit = 4096
+    launches_per_step = 1
+
+    def flops(self):
+        return 4.0 * self.B * self.H * self.S * self.S * self.D * 0.5
+
+    def algorithmic_bytes(self):
+        return 4 * self.B * self.H * self.S * self.D * 2
+
+    def setup(self, device):
+        import b200k
+        g = torch.Generator(device=device).manual_seed(self.seed)
+        shape = (self.B, self.H, self.S, self.D)
+        self.q, self.k, self.v = (torch.randn(shape, device=device, generator=g).bfloat16() for _ in range(3))
+        self.o = torch.empty_like(self.q)
+        self.b200k = b200k
+
+    def step(self):
+        return self.b200k.cutile_fmha(self.q, self.k, self.v, causal=True, Out=self.o)
+
+    def setup_e2e(self, device):
+        self.host_in = [t.cpu().pin_memory() for t in (self.q, self.k, self.v)]
+        self.host_out = torch.empty_like(self.o, device="cpu").pin_memory()
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host_in)
+        self.d2h = self.host_out.numel() * self.host_out.element_size()
+
+    def step_e2e(self):
+        for d, h in zip((self.q, self.k, self.v), self.host_in):
+            d.copy_(h, non_blocking=True)
+        self.step()
+        self.host_out.copy_(self.o, non_blocking=True)
+
+    def cpu_setup(self):
+        import oracle
+        g = torch.Generator().manual_seed(self.seed)
+        self.cpu_ops = tuple(torch.randn(1, 1, 4096, self.D, generator=g).bfloat16() for _ in range(3))
+        self.oracle = oracle
+
+    def cpu_step(self, s):
+        q, k, v = self.cpu_ops
+        return self.oracle.fmha_ref(q[:, :, :s], k[:, :, :s], v[:, :, :s], causal=True)
+
+    def cpu_flops(self, s):
+        return 4.0 * s * s * self.D * 0.5
+
+    def cpu_sample_desc(self, s):
+        return f"one head, sequence {s}: fp32 softmax(QK^T + causal mask)V (torch CPU)"
+
+    def config(self):
+        return {"workload": self.name, "batch": self.B, "heads": self.H, "seq": self.S,
+                "head_dim": self.D, "causal": True, "seed": self.seed,
+                "l2": "Q, K, V and O are 268 MB each (> 126 MiB L2)"}
+
+
+class MoeBf16(Workload):
+    """The MoE FFN (16384 tokens, hidden 4096, 64 experts, intermediate 1536, top-8) on one GPU,
+    bf16 weights: align -> gather -> grouped GEMM + SwiGLU -> grouped GEMM + scatter -> sum."""
+    name = "moe_ffn_16384tok_h4096_e64_i1536_top8_bf16"
+    dtype = "bf16 x bf16 -> fp32 accumulate -> bf16"
+    tensor_rate_vs_bf16 = 1.0
+    T, H, E, I, K = 16384, 4096, 64, 1536, 8
+    seed = 4
+    mxfp8 = False
+    launches_per_step = 8
+
+    def flops(self):
+        return 6.0 * self.T * self.K * self.H * self.I
+
+    def algorithmic_bytes(self):
+        return 2 * (self.E * 3 * self.I * self.H + 2 * self.T * self.H)
+
+    def setup(self, device):
+        import b200k
+        g = torch.Generator(device=device).manual_seed(self.seed)
+        self.x = torch.randn(self.T, self.H, device=device, generator=g).bfloat16()
+        w1 = (0.02 * torch.randn(self.E, 2 * self.I, self.H, device=device, generator=g)).bfloat16()
+        w2 = (0.02 * torch.randn(self.E, self.H, self.I, device=device, generator=g)).bfloat16()
+        vals, self.ids = torch.topk(torch.randn(self.T, self.E, device=device, generator=g), self.K, dim=-1)
+        self.tw = torch.softmax(vals, dim=-1).bfloat16()
+        if self.mxfp8:
+            self.w = b200k.quantize_expert_weights(w1) + b200k.quantize_expert_weights(w2)
+        else:
+            self.w = (w1, w2)
+        self.b200k = b200k
+
+    def step(self):
+        if self.mxfp8:
+            return self.b200k.cutile_moe_mxfp8(self.x, *self.w, self.tw, self.ids)
+        return self.b200k.cutile_moe(self.x, *self.w, self.tw, self.ids)
+
+    def setup_e2e(self, device):
+        self.host_in = [t.cpu().pin_memory() for t in (self.x, self.tw, self.ids)]
+        self.dev_in = [self.x, self.tw, self.ids]
+        self.host_out = torch.empty_like(self.x, device="cpu").pin_memory()
+        self.h2d = sum(t.numel() * t.element_size() for t in self.host_in)
+        self.d2h = self.host_out.numel() * self.host_out.element_size()
+
+    def step_e2e(self):
+        for d, h in zip(self.dev_in, self.host_in):
+            d.copy_(h, non_blocking=True)
+        self.host_out.copy_(self.step(), non_blocking=True)
+
+    cpu_setup = MoeEpBf16.cpu_setup
+    cpu_step = MoeEpBf16.cpu_step
+    cpu_flops = MoeEpBf16.cpu_flops
+    cpu_sample_desc = MoeEpBf16.cpu_sample_desc
+
+    def config(self):
+        return {"workload": self.name, "tokens": self.T, "hidden": self.H, "experts": self.E,
+                "intermediate": self.I, "topk": self.K, "seed": self.seed,
+                "l2": "expert weights alone are 2.4 GB (> 126 MiB L2)"}
+
+
+class MoeMxfp8(MoeBf16):
+    name = "moe_ffn_16384tok_h4096_e64_i1536_top8_mxfp8"
+    dtype = "e4m3 x e4m3 (ue8m0 scale / 32) -> fp32 accumulate -> bf16"
+    tensor_rate_vs_bf16 = 2.0
+    mxfp8 = True
+    launches_per_step = 9
+
+
+class Mxfp8Quantize(Workload):
+    """The quantiser that feeds the headline GEMM: bf16 8192 x 8192 -> e4m3 + swizzled ue8m0
+    scales.  One pass over the data: HBM-bound."""
+    name = "mxfp8_quantize_bf16_8192x8192"
+    dtype = "bf16 -> e4m3 + ue8m0 / 32"
+    bound = "hbm"
+    M = K = 8192
+    seed = 1
+    sets = 3
+    launches_per_step = 1
+
+    def flops(self):
+        return float(self.algorithmic_bytes())   # "work" of an HBM-bound kernel = its bytes
+
+    def algorithmic_bytes(self):
+        return self.M * self.K * 2 + self.M * self.K + self.M * self.K // 32
+
+    def setup(self, device):
+        import b200k
+        g = torch.Generator(device=device).manual_seed(self.seed)
+        self.xs = [torch.randn(self.M, self.K, device=device, generator=g).bfloat16() for _ in range(self.sets)]
+        self.b200k = b200k
+        self.i = 0
+
+    def step(self):
+        x = self.xs[self.i % self.sets]
+        self.i += 1
+        return self.b200k.block_quantize(x, 32, swizzled_scale=True)
+
+    def setup_e2e(self, device):
+        self.host_in = [self.xs[0].cpu().pin_memory()]
+        q, s = self.step()
+        self.host_out = [torch.empty_like(q.view(torch.uint8), device="cpu").pin_memory(),
+                         torch.empty_like(s.view(torch.uint8), device="cpu").pin_memory()]
+        self.h2d = self.host_in[0].numel() * 2
+        self.d2h = sum(t.numel() for t in self.host_out)
+
+    def step_e2e(self):
+        self.xs[0].copy_(self.host_in[0], non_blocking=True)
+        q, s = self.b200k.block_quantize(self.xs[0], 32, swizzled_scale=True)
+        self.host_out[0].copy_(q.view(torch.uint8), non_blocking=True)
+        self.host_out[1].copy_(s.view(torch.uint8), non_blocking=True)
+
+    def cpu_setup(self):
+        import oracle
+        g = torch.Generator().manual_seed(self.seed)
+        self.cpu_ops = (torch.randn(4096, self.K, generator=g).bfloat16(),)
+        self.oracle = oracle
+
+    def cpu_step(self, s):
+        return self.oracle.block_quantize_ref(self.cpu_ops[0][:s])
+
+    def cpu_flops(self, s):
+        return float(s * self.K * 3 + s * self.K // 32)
+
+    def cpu_sample_desc(self, s):
+        return f"{s} rows of {self.K} bf16 values through block_quantize's restatement (torch CPU)"
+
+    def config(self):
+        return {"workload": self.name, "rows": self.M, "K": self.K, "seed": self.seed,
+                "l2": f"{self.sets} rotating inputs of 128 MiB each (> 126 MiB L2)"}
+
+
 class DenseF16(Mxfp8Gemm):
     """The sample-sized dense fp16 matmul (2048 cubed)."""
     name = "dense_f16_gemm_2048x2048x2048"
@@ -407,7 +600,8 @@ class DenseF16(Mxfp8Gemm):
 
 
 WORKLOADS = {"mxfp8_gemm": Mxfp8Gemm, "nvfp4_gemm": Nvfp4Gemm, "dense_f16": DenseF16,
-             "ag_nvfp4_gemm": AgNvfp4Gemm, "moe_ep_bf16": MoeEpBf16}
+             "ag_nvfp4_gemm": AgNvfp4Gemm, "moe_ep_bf16": MoeEpBf16, "fmha_causal": FmhaCausal,
+             "moe_bf16": MoeBf16, "moe_mxfp8": MoeMxfp8, "mxfp8_quantize": Mxfp8Quantize}
 
 
 # --------------------------------------------------------------------------------------
@@ -485,7 +679,9 @@ def time_cpu(w, steps, warmup, budget_s=120.0):
     t0 = time.perf_counter()
     w.cpu_step(probe)
     t_probe = min(t_probe, time.perf_counter() - t0)
-    limit = len(w.cpu_ops[0][0]) if isinstance(w.cpu_ops[0], tuple) else w.cpu_ops[0].shape[0]
+    limit = getattr(w, "cpu_limit", None)
+    if limit is None:
+        limit = len(w.cpu_ops[0][0]) if isinstance(w.cpu_ops[0], tuple) else w.cpu_ops[0].shape[0]
     per_step = budget_s / max(1, steps + warmup)
     # cost grows about quadratically with the block edge
     s = int(probe * max(1.0, (per_step / max(t_probe, 1e-4)) ** 0.5))
@@ -504,17 +700,18 @@ def run_reference(args, w):
     if rank != 0:
         return
     dt, s = time_cpu(w, args.steps, args.warmup)
-    tflops = w.cpu_flops(s) / dt / 1e12
+    hbm = getattr(w, "bound", "tensor") == "hbm"
+    unit = "GB/s" if hbm else "TFLOP/s"
+    rate = w.cpu_flops(s) / dt / (1e9 if hbm else 1e12)
     line = {
-        "impl": "reference", "metric": "tflops", "value": tflops, "unit": "TFLOP/s",
+        "impl": "reference", "metric": "hbm_gbs" if hbm else "tflops", "value": rate, "unit": unit,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32 (de-quantised operands)", "data": "synthetic",
+        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": getattr(w, "scaling", "weak"),
+        "vs_baseline": None, "dtype": "f32 (torch CPU)", "data": "synthetic",
         "config": w.config(),
-        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+        "cpu_baseline": {"value": rate, "unit": unit, "cores": torch.get_num_threads(),
                          "kind": "port", "sample": w.cpu_sample_desc(s)},
-        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
-                "d2h_bytes_per_step": 0},
+        "e2e": {"value": rate, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
@@ -582,24 +779,30 @@ def run_ours(args, w):
     if rank == 0:
         peaks = load_peaks()
         flops = w.flops()
-        value = world * flops / (ms * 1e-3) / 1e12
-        per_gpu = flops / (ms * 1e-3) / 1e12
-        peak = peaks["bf16_tflops"] * w.tensor_rate_vs_bf16
+        hbm = getattr(w, "bound", "tensor") == "hbm"
+        unit = "GB/s" if hbm else "TFLOP/s"
+        scale = 1e9 if hbm else 1e12
+        value = world * flops / (ms * 1e-3) / scale
+        per_gpu = flops / (ms * 1e-3) / scale
+        if hbm:
+            peak = peaks["hbm_gbs"]
+            peak_source = f"{peaks['source']} copy bandwidth"
+        else:
+            peak = peaks["bf16_tflops"] * w.tensor_rate_vs_bf16
+            peak_source = (f"{peaks['source']} cuBLAS bf16 burst x {w.tensor_rate_vs_bf16:g} "
+                           f"(tensor-core rate of the operand format relative to bf16)")
         line = {
-            "metric": "tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "metric": "hbm_gbs" if hbm else "tflops", "value": value, "unit": unit, "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
             "higher_is_better": True, "scaling": getattr(w, "scaling", "weak"), "vs_baseline": None,
             "dtype": w.dtype, "data": "synthetic", "config": w.config(),
-            "e2e": {"value": world * flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "e2e": {"value": world * flops / (ms_e2e * 1e-3) / scale, "unit": unit,
                     "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h,
                     "ms_per_step": ms_e2e, "steps": e2e_steps},
             "gpu_launches": args.steps * w.launches_per_step,
             "clocks": sampler.summary(),
-            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
-                         "frac": per_gpu / peak,
-                         "peak_source": f"{peaks['source']} cuBLAS bf16 burst x "
-                                        f"{w.tensor_rate_vs_bf16:g} (tensor-core rate of the "
-                                        f"operand format relative to bf16)",
+            "roofline": {"bound": "hbm" if hbm else "tensor", "achieved": per_gpu, "peak": peak,
+                         "unit": unit, "frac": per_gpu / peak, "peak_source": peak_source,
                          "traffic": TRAFFIC_BYTES.get(w.name),
                          "algorithmic_bytes": w.algorithmic_bytes()},
         }
@@ -607,7 +810,7 @@ def run_ours(args, w):
             line["e2e"] = None
         if world == 1 and not args.no_cpu_baseline and not args.kernel_only:
             dt, s = time_cpu(w, 1, 1, budget_s=30.0)
-            line["cpu_baseline"] = {"value": w.cpu_flops(s) / dt / 1e12, "unit": "TFLOP/s",
+            line["cpu_baseline"] = {"value": w.cpu_flops(s) / dt / scale, "unit": unit,
                                     "cores": torch.get_num_threads(), "kind": "port",
                                     "sample": w.cpu_sample_desc(s)}
         print(json.dumps(line), flush=True)

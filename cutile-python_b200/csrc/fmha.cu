@@ -422,164 +422,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   }
 }
 
-// The softmax of one 128-row query tile spread over EIGHT warps: two threads share a row,
-// thread `half` 0 owns score columns [0, 64) and output columns [0, 64), thread 1 the rest.
-// Twice the warps per scheduler hide the TMEM, special-function and dependency latencies
-// that a single warp per scheduler leaves exposed.  The two threads of a row agree on the
-// row maximum through shared memory once per key tile (named barrier of their two warps)
-// and add their partial sums once at the end.
-template <bool BF16>
-__device__ __forceinline__ void softmax_half_tile(const FmhaParams& p, int quarter, int half, int lane,
-                                                  int b, int h, int q0, int n_kv, uint32_t tmem_s,
-                                                  uint32_t tmem_o, uint32_t s_full, uint32_t p_full,
-                                                  uint32_t pv_done, volatile int* abort_flag,
-                                                  float* xchg /* [2 slots][2 halves][128] */,
-                                                  int pair_barrier) {
-  const int row = quarter * 32 + lane;
-  const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
-  const int q_pos = p.input_pos + q0 + row;
-  const int col0 = half * 64;
-  float m_used = -INFINITY;
-  float l = 0.0f;
-  bool ok = true;
-  auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory"); };
-  for (int j = 0; j < n_kv; ++j) {
-    if (!mbar_wait(s_full, j & 1, abort_flag)) {
-      report_status(p.status, 31, j);
-      *abort_flag = 1;
-      ok = false;
-      break;
-    }
-    tc_fence_after_sync();
-    float s[64];
-    {
-      uint32_t r[64];
-      tmem_ld_32x32b_x64(tmem_s + lane_addr + col0, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 64; ++i) s[i] = __uint_as_float(r[i]);
-    }
-    const int key0 = j * kFmhaBN + col0;
-    const bool need_mask = (j * kFmhaBN + kFmhaBN > p.sk) ||
-                           (p.causal && j * kFmhaBN + kFmhaBN - 1 > p.input_pos + q0);
-    if (need_mask) {
-      const int limit = p.causal ? min(p.sk - 1, q_pos) : p.sk - 1;  // last visible key
-#pragma unroll
-      for (int i = 0; i < 64; ++i)
-        if (key0 + i > limit) s[i] = -INFINITY;
-    }
-    float mx4[4];
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      float m = fmax3(s[16 * c], s[16 * c + 1], s[16 * c + 2]);
-#pragma unroll
-      for (int i = 3; i < 15; i += 2) m = fmax3(m, s[16 * c + i], s[16 * c + i + 1]);
-      mx4[c] = fmaxf(m, s[16 * c + 15]);
-    }
-    float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-    // agree on the row maximum with the thread that owns the other 64 columns; both have
-    // their scores in registers once they pass the barrier, so P may overwrite S after it
-    float* slot = xchg + (j & 1) * 256;
-    slot[half * 128 + row] = mx;
-    pair_sync();
-    mx = fmaxf(mx, slot[(half ^ 1) * 128 + row]);
-    const float m_new = fmaxf(m_used, mx * p.scale_log2);
-    bool grow = (m_new - m_used > kRescaleThreshold) || (m_used == -INFINITY && m_new > -INFINITY);
-    const bool any_grow = __any_sync(0xffffffffu, grow);
-    float alpha = 1.0f;
-    if (grow) {
-      alpha = (m_used == -INFINITY) ? 0.0f : fast_exp2(m_used - m_new);
-      m_used = m_new;
-    }
-    if (any_grow && j > 0) {
-      l *= alpha;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_o + lane_addr + col0 + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-        tmem_st_32x32b_x32(tmem_o + lane_addr + col0 + c * 32, r);
-      }
-    }
-    const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
-    const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
-    const float2 negm2 = make_float2(neg_m, neg_m);
-    float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f),
-                      make_float2(0.f, 0.f)};
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      uint32_t pk[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float2 x = __ffma2_rn(make_float2(s[32 * c + 2 * i], s[32 * c + 2 * i + 1]), scale2, negm2);
-        const bool poly = kFmhaPolyEvery > 0 && (i % (kFmhaPolyEvery > 0 ? kFmhaPolyEvery : 1)) == kFmhaPolyEvery - 1;
-        const float2 e = poly ? exp2_poly_pair(x) : make_float2(fast_exp2(x.x), fast_exp2(x.y));
-        sum2[i & 3] = __fadd2_rn(sum2[i & 3], e);
-        pk[i] = BF16 ? pack_bf16x2(e.x, e.y) : pack_f16x2(e.x, e.y);
-      }
-      tmem_st_32x32b_x16(tmem_s + lane_addr + half * 32 + c * 16, pk);
-    }
-    l += ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y)) +
-         ((sum2[2].x + sum2[2].y) + (sum2[3].x + sum2[3].y));
-    tmem_st_wait();
-    tc_fence_before_sync();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(p_full);
-  }
-  // O / l: the row sum is the sum of the two threads' partial sums
-  if (ok && n_kv > 0) {
-    if (!mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag)) {
-      report_status(p.status, 32, 0);
-      *abort_flag = 1;
-      ok = false;
-    }
-  }
-  tc_fence_after_sync();
-  float* lslot = xchg + 512;
-  lslot[half * 128 + row] = l;
-  pair_sync();
-  l += lslot[(half ^ 1) * 128 + row];
-  const bool row_ok = (q0 + row) < p.sq;
-  uint16_t* o_row = static_cast<uint16_t*>(p.out) + b * p.o_stride_b + h * p.o_stride_h +
-                    static_cast<int64_t>(q0 + row) * p.o_stride_s + col0;
-  const bool vec_ok = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0) && (p.o_stride_b % 8 == 0) &&
-                      (p.o_stride_h % 8 == 0) && (p.o_stride_s % 8 == 0);
-  const float inv_l = (l > 0.0f) ? __fdividef(1.0f, l) : 0.0f;
-#pragma unroll
-  for (int c = 0; c < 2; ++c) {
-    uint32_t r[32];
-    if (ok && n_kv > 0) {
-      tmem_ld_32x32b_x32(tmem_o + lane_addr + col0 + c * 32, r);
-      tmem_ld_wait();
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) r[i] = 0;
-    }
-    if (row_ok) {
-      uint32_t pk[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float a = __uint_as_float(r[2 * i]) * inv_l;
-        const float c2 = __uint_as_float(r[2 * i + 1]) * inv_l;
-        pk[i] = BF16 ? pack_bf16x2(a, c2) : pack_f16x2(a, c2);
-      }
-      if (vec_ok) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          reinterpret_cast<uint4*>(o_row + c * 32)[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          o_row[c * 32 + 2 * i] = static_cast<uint16_t>(pk[i] & 0xffff);
-          o_row[c * 32 + 2 * i + 1] = static_cast<uint16_t>(pk[i] >> 16);
-        }
-      }
-    }
-  }
-}
-
 // ---------------------------------------------------------------------------
 // Two query tiles per CTA (head dim 128): one CTA per SM owns 256 query rows.  Warp group A
 // (warps 2-5) does the softmax of rows [q0, q0 + 128), warp group B (warps 6-9) of rows
@@ -589,10 +431,10 @@ __device__ __forceinline__ void softmax_half_tile(const FmhaParams& p, int quart
 // tiles are double-buffered and shared by both query tiles.
 // TMEM: S_A [0,128)  S_B [128,256)  O_A [256,384)  O_B [384,512); P aliases S.
 // ---------------------------------------------------------------------------
-// SPLIT: each query row is shared by two softmax threads (2 x 8 softmax warps, 576 threads)
-// instead of one (2 x 4 softmax warps, 320 threads).
-template <bool BF16, bool SPLIT>
-__global__ void __launch_bounds__(SPLIT ? 576 : 320, 1)
+constexpr int kFmha2Threads = 320;   // TMA warp, MMA warp, 2 x 4 softmax warps
+
+template <bool BF16>
+__global__ void __launch_bounds__(kFmha2Threads, 1)
 fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, const FmhaParams p) {
   constexpr int D = 128;
@@ -611,7 +453,6 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   auto bar = [&](int i) { return bar0 + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8 * NUM_BARS + 8);
-  float* xchg = reinterpret_cast<float*>(tail + 256);   // per warp group: 768 floats
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -638,7 +479,7 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const int n_kv = max(n_x[0], n_x[1]);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NUM_BARS; ++i) mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? (SPLIT ? 8 : 4) : 1);
+    for (int i = 0; i < NUM_BARS; ++i) mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? 4 : 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_q);
@@ -773,19 +614,10 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     }
     __syncwarp();
   } else {
-    if constexpr (SPLIT) {
-      const int x = (warp - 2) >> 3;           // warp group: query tile A (warps 2-9) or B (10-17)
-      const int half = ((warp - 2) >> 2) & 1;  // which 64 columns of the row
-      const int quarter = warp & 3;            // TMEM lanes this warp may touch
-      softmax_half_tile<BF16>(p, quarter, half, lane, b, h, q0 + x * 128, n_x[x], tmem_base + x * 128,
-                              tmem_base + 256 + x * 128, bar(S_FULL + x), bar(P_FULL + x),
-                              bar(PV_DONE + x), abort_flag, xchg + x * 768, 1 + x * 4 + quarter);
-    } else {
-      const int x = (warp - 2) >> 2;           // warp group: query tile A (warps 2-5) or B (6-9)
-      softmax_tile<D, BF16>(p, warp, lane, b, h, q0 + x * 128, n_x[x], tmem_base + x * 128,
-                            tmem_base + 256 + x * 128, bar(S_FULL + x), bar(P_FULL + x),
-                            bar(PV_DONE + x), abort_flag);
-    }
+    const int x = (warp - 2) >> 2;           // warp group: query tile A (warps 2-5) or B (6-9)
+    softmax_tile<D, BF16>(p, warp, lane, b, h, q0 + x * 128, n_x[x], tmem_base + x * 128,
+                          tmem_base + 256 + x * 128, bar(S_FULL + x), bar(P_FULL + x),
+                          bar(PV_DONE + x), abort_flag);
   }
 
   tc_fence_before_sync();
@@ -817,11 +649,11 @@ int launch_fmha(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
   return B200K_OK;
 }
 
-template <bool BF16, bool SPLIT>
+template <bool BF16>
 int launch_fmha_pair(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                      const FmhaParams& p, int grid, cudaStream_t stream) {
-  constexpr int kSmem = 1024 + 6 * 128 * 128 * 2 + 256 + 2 * 768 * 4;
-  auto kernel = fmha_fwd_pair_kernel<BF16, SPLIT>;
+  constexpr int kSmem = 1024 + 6 * 128 * 128 * 2 + 256;
+  auto kernel = fmha_fwd_pair_kernel<BF16>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -831,7 +663,7 @@ int launch_fmha_pair(const CUtensorMap& tq, const CUtensorMap& tk, const CUtenso
       return fail(B200K_CUDA_ERROR, "cudaFuncSetAttribute(%d): %s", kSmem, cudaGetErrorString(e));
     configured[dev] = true;
   }
-  kernel<<<grid, SPLIT ? 576 : 320, kSmem, stream>>>(tq, tk, tv, p);
+  kernel<<<grid, kFmha2Threads, kSmem, stream>>>(tq, tk, tv, p);
   B200K_CHECK_LAUNCH("fmha (two-tile) launch");
   return B200K_OK;
 }
@@ -905,13 +737,8 @@ extern "C" int b200k_fmha_fwd(const b200k_fmha_args* a, b200k_stream stream_) {
   if (d == 128 && a->seq_q > 128 && !(one_tile != nullptr && one_tile[0] == '1')) {
     const int64_t g2 = ceil_div(a->seq_q, 256) * a->batch * a->heads_q;
     if (g2 > INT32_MAX) return fail(B200K_UNSUPPORTED, "too many tiles");
-    const char* split_env = getenv("B200K_FMHA_SPLIT_ROWS");
-    const bool split = split_env != nullptr && split_env[0] == '1';
-    if (split)
-      return bf16 ? launch_fmha_pair<true, true>(tq, tk, tv, p, static_cast<int>(g2), stream)
-                  : launch_fmha_pair<false, true>(tq, tk, tv, p, static_cast<int>(g2), stream);
-    return bf16 ? launch_fmha_pair<true, false>(tq, tk, tv, p, static_cast<int>(g2), stream)
-                : launch_fmha_pair<false, false>(tq, tk, tv, p, static_cast<int>(g2), stream);
+    return bf16 ? launch_fmha_pair<true>(tq, tk, tv, p, static_cast<int>(g2), stream)
+                : launch_fmha_pair<false>(tq, tk, tv, p, static_cast<int>(g2), stream);
   }
   if (d == 128)
     return bf16 ? launch_fmha<128, true>(tq, tk, tv, p, grid, stream)
