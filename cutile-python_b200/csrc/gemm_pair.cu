@@ -311,30 +311,41 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                        (static_cast<int64_t>(tc.batch) * p.stride_c + static_cast<int64_t>(row) * p.ldc) * elem_bytes;
       const uint32_t taddr = tmem_base + w * Cfg::kAccStride + (uint32_t(quarter * 32) << 16);
       const int n0 = tc.pid_n * 256;
-      // columns shared with the other window first: the last chunks of window 0, the first
-      // chunks of window 1
+      // Columns shared with the other window first (the last chunks of window 0, the first
+      // chunks of window 1): they are pulled into registers back to back and released
+      // before anything is converted or stored, so the next tile's first MMA waits only
+      // for these loads.
       const int first = (w == 0) ? (8 - Cfg::kOverlapChunks) & 7 : 0;
-      if (Cfg::kOverlapChunks == 0) {
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(lead_ovl);
-      }
-#pragma unroll 1
-      for (int ci = 0; ci < 8; ++ci) {
-        const int c = (first + ci) & 7;
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, r);
+      constexpr int kOvl = Cfg::kOverlapChunks > 0 ? Cfg::kOverlapChunks : 1;
+      uint32_t held[kOvl][32];
+      if constexpr (Cfg::kOverlapChunks > 0) {
+#pragma unroll
+        for (int ci = 0; ci < Cfg::kOverlapChunks; ++ci)
+          tmem_ld_32x32b_x32(taddr + ((first + ci) & 7) * 32, held[ci]);
         tmem_ld_wait();
-        if (Cfg::kOverlapChunks > 0 && ci == Cfg::kOverlapChunks - 1) {
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(lead_ovl);
-        }
+        tc_fence_before_sync();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(lead_ovl);
+      auto emit = [&](int c, const uint32_t (&r)[32]) {
         if (row_ok && n0 + c * 32 < p.n) {
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * scale;
           store_row_chunk<OUT>(c_row, n0 + c * 32, p.n, v, vec_ok);
         }
+      };
+      if constexpr (Cfg::kOverlapChunks > 0) {
+#pragma unroll
+        for (int ci = 0; ci < Cfg::kOverlapChunks; ++ci) emit((first + ci) & 7, held[ci]);
+      }
+#pragma unroll 1
+      for (int ci = Cfg::kOverlapChunks; ci < 8; ++ci) {
+        const int c = (first + ci) & 7;
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        emit(c, r);
       }
       tc_fence_before_sync();
       __syncwarp();

@@ -65,12 +65,26 @@ moe_offsets_kernel(int* __restrict__ counts, int num_chunks, int num_experts, in
   extern __shared__ int sm[];
   int* totals = sm;                      // [E] replicas per expert
   int* starts = sm + num_experts;        // [E] first slot of the expert's padded run
+  int* partial = sm + 2 * num_experts;   // [groups][E] replicas per expert in a group of chunks
   __shared__ int total_blocks;
+  // two-level prefix over the chunks of every expert: thread (group, expert) first sums its
+  // group's chunks, a short scan over the groups follows, then each thread rewrites its
+  // chunks' histogram entries as write offsets
+  const int groups = max(1, static_cast<int>(blockDim.x) / num_experts);
+  const int per_group = (num_chunks + groups - 1) / groups;
+  for (int t = threadIdx.x; t < groups * num_experts; t += blockDim.x) {
+    const int e = t % num_experts, g = t / num_experts;
+    const int c0 = g * per_group, c1 = min(num_chunks, c0 + per_group);
+    int sum = 0;
+    for (int c = c0; c < c1; ++c) sum += counts[c * num_experts + e];
+    partial[g * num_experts + e] = sum;
+  }
+  __syncthreads();
   for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
     int run = 0;
-    for (int c = 0; c < num_chunks; ++c) {
-      const int v = counts[c * num_experts + e];
-      counts[c * num_experts + e] = run;   // exclusive prefix inside the expert
+    for (int g = 0; g < groups; ++g) {
+      const int v = partial[g * num_experts + e];
+      partial[g * num_experts + e] = run;
       run += v;
     }
     totals[e] = run;
@@ -87,8 +101,15 @@ moe_offsets_kernel(int* __restrict__ counts, int num_chunks, int num_experts, in
   }
   __syncthreads();
   const int sentinel = static_cast<int>(total);
-  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
-    for (int c = 0; c < num_chunks; ++c) counts[c * num_experts + e] += starts[e];
+  for (int t = threadIdx.x; t < groups * num_experts; t += blockDim.x) {
+    const int e = t % num_experts, g = t / num_experts;
+    const int c0 = g * per_group, c1 = min(num_chunks, c0 + per_group);
+    int run = starts[e] + partial[g * num_experts + e];
+    for (int c = c0; c < c1; ++c) {
+      const int v = counts[c * num_experts + e];
+      counts[c * num_experts + e] = run;
+      run += v;
+    }
   }
   // expert id of every tile_m block, -1 beyond the blocks in use
   for (int64_t b = threadIdx.x; b < block_capacity; b += blockDim.x) {
@@ -286,7 +307,7 @@ extern "C" int b200k_moe_align(const b200k_moe_align_args* a, b200k_stream strea
       moe_count_kernel<int><<<grid, kAlignWarps * 32, smem, stream>>>(
           static_cast<const int*>(a->topk_ids), a->num_replicas, a->num_experts, counts, status);
   }
-  moe_offsets_kernel<<<1, 1024, 2 * a->num_experts * sizeof(int), stream>>>(
+  moe_offsets_kernel<<<1, 1024, (2 + (1024 / a->num_experts > 1 ? 1024 / a->num_experts : 1)) * a->num_experts * sizeof(int), stream>>>(
       counts, chunks, a->num_experts, a->tile_m, a->num_replicas, a->sorted_token_ids, a->capacity,
       a->sorted_expert_ids, a->block_capacity, a->num_blocks);
   if (a->num_replicas > 0) {
