@@ -26,6 +26,8 @@ __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+__device__ __forceinline__ float2 to_f32x2(__nv_bfloat162 v) { return __bfloat1622float2(v); }
+__device__ __forceinline__ float2 to_f32x2(__half2 v) { return __half22float2(v); }
 
 // Loads N consecutive elements (N * sizeof(T) a multiple of 16, address 16-byte aligned
 // when `vec` is true) and widens them to fp32.
@@ -70,6 +72,59 @@ __device__ __forceinline__ int ceil_log2_f32(float q) {
   return static_cast<int>(ceilf(static_cast<float>(log2(static_cast<double>(q)))));
 }
 
+// The scale byte (ue8m0) and the exact reciprocal 2^-e of one block with maximum `amax`;
+// NaN or infinity anywhere in the block gives the byte 0xff and a NaN reciprocal, as the
+// reference's float arithmetic does.
+__device__ __forceinline__ uint8_t block_scale(float amax, bool has_nan, float* inv_scale) {
+  if (has_nan || amax == __int_as_float(0x7f800000)) {
+    *inv_scale = __int_as_float(0x7fc00000);
+    return 0xff;
+  }
+  float s = __fdiv_rn(amax, 448.0f);
+  s = fmaxf(s, 1e-12f);
+  const int e = ceil_log2_f32(s);
+  // 2^-e, exact: e is in [-39, 120]
+  *inv_scale = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+  if (127 - e <= 0) *inv_scale = ldexpf(1.0f, -e);
+  return static_cast<uint8_t>(e + 127);
+}
+
+template <typename T> struct Packed2;
+template <> struct Packed2<__nv_bfloat16> { using type = __nv_bfloat162; };
+template <> struct Packed2<__half> { using type = __half2; };
+
+// One full, 16-byte-aligned block of 16-bit elements: the maximum is taken on packed pairs
+// (NaN-propagating), the products are formed in fp32 and converted two at a time.  Returns
+// the scale byte; writes the 32 quantised bytes.
+template <typename T>
+__device__ __forceinline__ uint8_t quantize_block_packed(const T* src, uint8_t* dst, int fmt_e5m2) {
+  using P = typename Packed2<T>::type;
+  uint4 raw[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) raw[i] = reinterpret_cast<const uint4*>(src)[i];
+  const P* pairs = reinterpret_cast<const P*>(raw);
+  P m = __habs2(pairs[0]);
+#pragma unroll
+  for (int i = 1; i < 16; ++i) m = __hmax2_nan(m, __habs2(pairs[i]));
+  const float2 mf = to_f32x2(m);
+  const bool has_nan = (mf.x != mf.x) || (mf.y != mf.y);
+  float inv_scale;
+  const uint8_t sf_byte = block_scale(fmaxf(mf.x, mf.y), has_nan, &inv_scale);
+  uint32_t out[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float2 lo = to_f32x2(pairs[2 * i]), hi = to_f32x2(pairs[2 * i + 1]);
+    lo.x *= inv_scale; lo.y *= inv_scale; hi.x *= inv_scale; hi.y *= inv_scale;
+    const __nv_fp8_interpretation_t fmt = fmt_e5m2 ? __NV_E5M2 : __NV_E4M3;
+    const uint32_t a = __nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, fmt);
+    const uint32_t b = __nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, fmt);
+    out[i] = a | (b << 16);
+  }
+  reinterpret_cast<uint4*>(dst)[0] = make_uint4(out[0], out[1], out[2], out[3]);
+  reinterpret_cast<uint4*>(dst)[1] = make_uint4(out[4], out[5], out[6], out[7]);
+  return sf_byte;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 mxfp8_quantize_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t ldx,
@@ -87,14 +142,30 @@ mxfp8_quantize_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t 
   const bool vec_out = (reinterpret_cast<uintptr_t>(q) % 16 == 0) && (ldq % 16 == 0);
   for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
        idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t row = idx / kblocks;
-    const int64_t kb = idx - row * kblocks;
+    int64_t row, kb;
+    if (total < (1ll << 31)) {   // 32-bit division is several times cheaper than the 64-bit one
+      const uint32_t r32 = static_cast<uint32_t>(idx) / static_cast<uint32_t>(kblocks);
+      row = r32;
+      kb = static_cast<uint32_t>(idx) - r32 * static_cast<uint32_t>(kblocks);
+    } else {
+      row = idx / kblocks;
+      kb = idx - row * kblocks;
+    }
     const int valid = static_cast<int>(k - kb * 32 < 32 ? k - kb * 32 : 32);
     float v[32];
     int64_t src_row = row;
     if (gather_index != nullptr) {
       const int g = gather_index[row];
       src_row = (g >= 0 && g / gather_div < src_rows) ? g / gather_div : -1;
+    }
+    if constexpr (sizeof(T) == 2) {
+      if (vec_in && vec_out && valid == 32 && src_row >= 0) {
+        const uint8_t sf_byte = quantize_block_packed<T>(x + src_row * ldx + kb * 32,
+                                                         q + row * ldq + kb * 32, fmt_e5m2);
+        if (sf_logical != nullptr) sf_logical[row * kblocks + kb] = sf_byte;
+        if (sf_swizzled != nullptr) sf_swizzled[swizzled_sf_offset(row, kb, k_atoms)] = sf_byte;
+        continue;
+      }
     }
     if (src_row >= 0) {
       load_block<T, 32>(x + src_row * ldx + kb * 32, v, vec_in, valid);
@@ -109,20 +180,8 @@ mxfp8_quantize_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t 
       amax = fmaxf(amax, fabsf(v[i]));
       has_nan |= (v[i] != v[i]);
     }
-    uint8_t sf_byte;
     float inv_scale;
-    if (has_nan || amax == __int_as_float(0x7f800000)) {
-      sf_byte = 0xff;  // the reference propagates NaN / inf into the scale
-      inv_scale = __int_as_float(0x7fc00000);
-    } else {
-      float s = __fdiv_rn(amax, 448.0f);
-      s = fmaxf(s, 1e-12f);
-      const int e = ceil_log2_f32(s);
-      sf_byte = static_cast<uint8_t>(e + 127);
-      // 2^-e, exact: e is in [-39, 120]
-      inv_scale = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
-      if (127 - e <= 0) inv_scale = ldexpf(1.0f, -e);
-    }
+    const uint8_t sf_byte = block_scale(amax, has_nan, &inv_scale);
     uint32_t packed[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -145,96 +204,6 @@ mxfp8_quantize_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t 
     }
     if (sf_logical != nullptr) sf_logical[row * kblocks + kb] = sf_byte;
     if (sf_swizzled != nullptr) sf_swizzled[swizzled_sf_offset(row, kb, k_atoms)] = sf_byte;
-  }
-}
-
-// Coalesced variant for K % 32 == 0 and 16-byte-aligned rows: four consecutive lanes share one
-// 32-element block, each loading 8 consecutive elements, so a warp reads and writes
-// contiguous memory (512 B of bf16 in, 256 B of fp8 out per instruction); the block maximum
-// is two shuffles away.
-template <typename T>
-__global__ void __launch_bounds__(256)
-mxfp8_quantize_vec_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t ldx,
-                          uint8_t* __restrict__ q, int64_t ldq, uint8_t* __restrict__ sf_logical,
-                          uint8_t* __restrict__ sf_swizzled, int64_t k_atoms, int fmt_e5m2,
-                          const int* __restrict__ gather_index, int gather_div, int64_t src_rows,
-                          const int* __restrict__ live_blocks, int tile_m) {
-  if (live_blocks != nullptr) {
-    const int64_t live = static_cast<int64_t>(*live_blocks) * tile_m;
-    rows = live < rows ? live : rows;
-  }
-  const int64_t vec_per_row = k >> 3;
-  const int64_t kblocks = k >> 5;
-  const int64_t total = rows * vec_per_row;   // a multiple of 4: whole blocks per warp quad
-  const bool small = total < (1ll << 31);
-  // whole warps stay in the loop (the shuffles below need every lane); lanes past the end
-  // just do not touch memory
-  for (int64_t warp_base = blockIdx.x * static_cast<int64_t>(blockDim.x) + (threadIdx.x & ~31);
-       warp_base < total; warp_base += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t idx = warp_base + (threadIdx.x & 31);
-    const bool active = idx < total;
-    int64_t row = 0, c = 0;
-    if (active) {
-      if (small) {   // 32-bit division: the 64-bit one costs more than the rest of the loop
-        const uint32_t r32 = static_cast<uint32_t>(idx) / static_cast<uint32_t>(vec_per_row);
-        row = r32;
-        c = static_cast<uint32_t>(idx) - r32 * static_cast<uint32_t>(vec_per_row);
-      } else {
-        row = idx / vec_per_row;
-        c = idx - row * vec_per_row;
-      }
-    }
-    int64_t src_row = active ? row : -1;
-    if (active && gather_index != nullptr) {
-      const int g = gather_index[row];
-      src_row = (g >= 0 && g / gather_div < src_rows) ? g / gather_div : -1;
-    }
-    float v[8];
-    if (src_row >= 0) {
-      load_block<T, 8>(x + src_row * ldx + c * 8, v, true, 8);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = 0.0f;
-    }
-    float amax = 0.0f;
-    bool has_nan = false;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      amax = fmaxf(amax, fabsf(v[i]));
-      has_nan |= (v[i] != v[i]);
-    }
-    // the four lanes of a block are aligned to a multiple of 4 within the warp
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    const unsigned nan_lanes = __ballot_sync(0xffffffffu, has_nan);
-    has_nan = ((nan_lanes >> (threadIdx.x & 28)) & 0xf) != 0;
-    uint8_t sf_byte;
-    float inv_scale;
-    if (has_nan || amax == __int_as_float(0x7f800000)) {
-      sf_byte = 0xff;
-      inv_scale = __int_as_float(0x7fc00000);
-    } else {
-      float sc = __fdiv_rn(amax, 448.0f);
-      sc = fmaxf(sc, 1e-12f);
-      const int e = ceil_log2_f32(sc);
-      sf_byte = static_cast<uint8_t>(e + 127);
-      inv_scale = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
-    }
-    uint32_t w[2] = {0, 0};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float y = v[i] * inv_scale;
-      const uint8_t b = fmt_e5m2 ? __nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E5M2)
-                                 : __nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3);
-      w[i >> 2] |= static_cast<uint32_t>(b) << (8 * (i & 3));
-    }
-    if (!active) continue;
-    *reinterpret_cast<uint2*>(q + row * ldq + c * 8) = make_uint2(w[0], w[1]);
-    if ((c & 3) == 0) {
-      const int64_t kb = c >> 2;
-      if (sf_logical != nullptr) sf_logical[row * kblocks + kb] = sf_byte;
-      if (sf_swizzled != nullptr) sf_swizzled[swizzled_sf_offset(row, kb, k_atoms)] = sf_byte;
-    }
   }
 }
 
@@ -453,20 +422,11 @@ extern "C" int b200k_mxfp8_quantize(const b200k_quantize_args* a, b200k_stream s
   uint8_t* sl = static_cast<uint8_t*>(a->sf_logical);
   uint8_t* ss = static_cast<uint8_t*>(a->sf_swizzled);
   const int gdiv = a->gather_divisor > 0 ? a->gather_divisor : 1;
-  const int elem = a->x_dtype == B200K_F32 ? 4 : 2;
-  const bool vec = (a->k % 32 == 0) && (reinterpret_cast<uintptr_t>(a->x) % 16 == 0) &&
-                   ((a->ldx * elem) % 16 == 0) && (reinterpret_cast<uintptr_t>(a->q) % 8 == 0) &&
-                   (a->ldq % 8 == 0);
-  const int grid = grid_for(vec ? a->rows * (a->k / 8) : a->rows * kblocks, 256);
-#define B200K_MXFP8_CASE(T)                                                                         \
-  if (vec)                                                                                          \
-    mxfp8_quantize_vec_kernel<T><<<grid, 256, 0, stream>>>(                                         \
-        static_cast<const T*>(a->x), a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, e5m2, \
-        a->gather_index, gdiv, a->src_rows, a->live_blocks, a->tile_m);                             \
-  else                                                                                              \
-    mxfp8_quantize_kernel<T><<<grid, 256, 0, stream>>>(                                             \
-        static_cast<const T*>(a->x), a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, e5m2, \
-        a->gather_index, gdiv, a->src_rows, a->live_blocks, a->tile_m)
+  const int grid = grid_for(a->rows * kblocks, 256);
+#define B200K_MXFP8_CASE(T)                                                                       \
+  mxfp8_quantize_kernel<T><<<grid, 256, 0, stream>>>(                                             \
+      static_cast<const T*>(a->x), a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, e5m2, \
+      a->gather_index, gdiv, a->src_rows, a->live_blocks, a->tile_m)
   switch (a->x_dtype) {
     case B200K_F32: B200K_MXFP8_CASE(float); break;
     case B200K_BF16: B200K_MXFP8_CASE(__nv_bfloat16); break;
