@@ -564,11 +564,13 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
     CUtensorMap tsa, tsb;
     const uint32_t atoms = fp4 ? 4 : 1;
     const uint64_t ka = static_cast<uint64_t>(a->sf_k_atoms);
-    if (!encode_tmap_4d(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->sfa, 16, 32, ka, ceil_div(a->m, 128), 16,
-                        512, ka * 512, 16, 32, atoms, 1, CU_TENSOR_MAP_SWIZZLE_NONE))
+    // one 512-byte atom per innermost row (128 32-bit words), so every request of the copy
+    // engine is a whole run of cache lines rather than a 16-byte row of the atom
+    if (!encode_tmap_3d(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT32, a->sfa, 128, ka, ceil_div(a->m, 128), 512,
+                        ka * 512, 128, atoms, 1, CU_TENSOR_MAP_SWIZZLE_NONE))
       return B200K_INVALID_ARG;
-    if (!encode_tmap_4d(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->sfb, 16, 32, ka, ceil_div(a->n, 128), 16,
-                        512, ka * 512, 16, 32, atoms, 1, CU_TENSOR_MAP_SWIZZLE_NONE))
+    if (!encode_tmap_3d(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT32, a->sfb, 128, ka, ceil_div(a->n, 128), 512,
+                        ka * 512, 128, atoms, 2, CU_TENSOR_MAP_SWIZZLE_NONE))
       return B200K_INVALID_ARG;
     const CUtensorMap maps[4] = {ta, tb, tsa, tsb};
     return launch_gemm_pair(fp4 ? kKindNVF4 : kKindMXF8, a->c_dtype, maps, pp, sms, stream);

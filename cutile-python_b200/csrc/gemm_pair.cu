@@ -152,10 +152,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if constexpr (Cfg::kScaled) {
               const uint32_t sfa_dst = sf_base + s * Cfg::kSfBytes;
               const uint32_t sfb_dst = sfa_dst + Cfg::kSfAtoms * 512;
-              tma_load_4d_pair(sfa_dst, &tmap_sfa, lead_full, 0, 0, kb * Cfg::kSfAtoms, tc.pid_m * 2 + rank);
-              tma_load_4d_pair(sfb_dst, &tmap_sfb, lead_full, 0, 0, kb * Cfg::kSfAtoms, tc.pid_n * 2);
-              tma_load_4d_pair(sfb_dst + Cfg::kSfAtoms * 512, &tmap_sfb, lead_full, 0, 0,
-                               kb * Cfg::kSfAtoms, tc.pid_n * 2 + 1);
+              tma_load_3d_pair(sfa_dst, &tmap_sfa, lead_full, 0, kb * Cfg::kSfAtoms, tc.pid_m * 2 + rank);
+              // both 128-row tiles of SFB in one box: [row tile][atom][512 B] in shared memory
+              tma_load_3d_pair(sfb_dst, &tmap_sfb, lead_full, 0, kb * Cfg::kSfAtoms, tc.pid_n * 2);
             }
           }
         }
