@@ -8,13 +8,23 @@
 // atoms of B are simply fetched by both) and reports the bytes to the leader's mbarrier.
 //
 //   warp 0      TMA producer, one lane, in both CTAs
-//   warp 1      MMA issuer, one lane, leader CTA only (allocates TMEM in both)
+//   warp 1      MMA issuer of the even k-steps, one lane, leader CTA only (allocates TMEM)
 //   warps 2..5  epilogue, both CTAs
+//   warp 6      MMA issuer of the odd k-steps, one lane, leader CTA only
+//
+// Two issuers because one thread cannot feed the tensor pipe of a block-scaled kind: a
+// tcgen05 instruction costs its issuing thread 25 to 30 cycles, and an NVFP4 k-step is
+// twelve scale-factor copies (tcgen05.cp), four MMAs of 132 cycles and two commits, 430
+// cycles of issue against 529 of MMA time before any barrier wait.  The k-steps of a tile
+// alternate between the issuers, each with its own scale-factor slot in tensor memory, so
+// copies and MMAs of one k-step stay in one thread's program order.  Only the first k-step
+// of a tile (the one that overwrites the accumulator) has to be complete before the other
+// issuer may add to it; after that the order of the additions does not matter.
 //
 // Two accumulator windows let a tile's epilogue overlap the next tile's mainloop.  The
-// block-scaled kinds also need TMEM columns for scale factors, so their windows overlap
-// by 32 (MXFP8) or 64 (NVFP4) columns: the epilogue drains the shared columns first and
-// releases them early; the next tile's first MMA waits only for that.
+// block-scaled kinds also need TMEM columns for the two scale-factor slots, so their
+// windows overlap by 32 (MXFP8) or 96 (NVFP4) columns: the epilogue drains the shared
+// columns first and releases them early; the next tile's first MMA waits only for that.
 #include "gemm_common.cuh"
 #include "gemm_pair.h"
 
@@ -23,7 +33,8 @@ namespace b200k {
 #ifdef B200K_TRACE
 // Debug build only: cycle counters summed over all CTAs.
 // 0 producer wait(empty), 1 producer total, 2 mma wait(full), 3 mma wait(acc), 4 mma total,
-// 5 epilogue wait(acc_full), 6 epilogue total, 7 mma issue (descs + cp + mma + commit)
+// 5 epilogue wait(acc_full), 6 epilogue total, 7 mma issue (descs + cp + mma + commit);
+// 2, 3, 4 and 7 are those of the first issuer
 __device__ unsigned long long g_trace[16];
 #define TRACE_T0(var) long long var = clock64()
 #define TRACE_ADD(idx, var) atomicAdd(&g_trace[idx], static_cast<unsigned long long>(clock64() - (var)))
@@ -45,19 +56,20 @@ struct PairCfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kSfAtoms = kScaled ? (KIND == kKindNVF4 ? 4 : 1) : 0;  // along K, per stage
   static constexpr int kSfBytes = kSfAtoms * 512 * 3;                       // SFA + both SFB row tiles
-  static constexpr int kAccStride = !kScaled ? 256 : (KIND == kKindNVF4 ? 192 : 224);
+  static constexpr int kAccStride = !kScaled ? 256 : (KIND == kKindNVF4 ? 160 : 224);
   static constexpr int kOverlapChunks = (256 - kAccStride) / 32;
-  static constexpr int kSfBase = 2 * kAccStride + 32 * kOverlapChunks;     // 480 / 448
-  static constexpr int kSfSlots = (KIND == kKindMXF8) ? 2 : 1;
+  static constexpr int kSfBase = 2 * kAccStride + 32 * kOverlapChunks;     // 480 / 416
+  static constexpr int kSfSlots = 2;
   static constexpr int kSfaCols = kSfAtoms * 4;
   static constexpr int kSfSlotCols = kSfAtoms * 12;
+  static constexpr int kThreads = 224;
   static constexpr int kSmemBytes = 1024 + kStages * (kStageBytes + kSfBytes) + 256;
   static_assert(!kScaled || kSfBase + kSfSlots * kSfSlotCols <= 512, "TMEM budget");
   static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
 template <int KIND, int OUT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<KIND>::kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_sfa,
                  const __grid_constant__ CUtensorMap tmap_sfb, const GemmParams p) {
@@ -70,14 +82,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const uint32_t sf_base = tiles_base + S * Cfg::kStageBytes;
   uint8_t* tail = smem + S * (Cfg::kStageBytes + Cfg::kSfBytes);
   const uint32_t bar_base = smem_u32(tail);
-  // full[S], empty[S], acc_full[2], acc_empty[2], ovl_free
+  // full[S], empty[S], acc_full[2], acc_empty[2], ovl_free, tile_open[2]
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
   auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * S + a); };
   auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * S + 2 + a); };
   const uint32_t ovl_free_bar = bar_base + 8u * (2 * S + 4);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * S + 5));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8 * (2 * S + 5) + 8);
+  auto tile_open_bar = [&](int a) { return bar_base + 8u * (2 * S + 5 + a); };   // leader's
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * S + 7));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8 * (2 * S + 7) + 8);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -90,8 +103,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_full_bar(a), p.k_iters > 1 ? 2 : 1);   // one commit per issuer with work
       mbar_init(acc_empty_bar(a), 8);   // 4 epilogue warps in each CTA of the pair
+      mbar_init(tile_open_bar(a), 1);
     }
     mbar_init(ovl_free_bar, 8);
     *abort_flag = 0;
@@ -167,21 +181,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #endif
     }
     __syncwarp();
-  } else if (warp == 1) {
-    // ---------------- MMA issuer (leader only) ----------------
+  } else if (warp == 1 || warp == 6) {
+    // ---------------- MMA issuers (leader only) ----------------
     // The whole warp walks the loop so that descriptors and addresses stay warp-uniform
     // (uniform registers feed the MMA directly); one elected lane issues the tcgen05 work.
+    // Issuer q takes the k-steps kb = q, q + 2, ... of every tile.
     if (leader) {
+      const int q = warp == 1 ? 0 : 1;
       const bool elected = elect_one();
-      uint32_t it = 0;
+      uint32_t it_base = 0;
       uint32_t lt = 0;
       bool ok = true;
       TRACE_T0(t_total);
 #ifdef B200K_TRACE
       long long w_full = 0, w_acc = 0, t_issue = 0;
 #endif
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++lt) {
+      uint32_t tsfa = 0, tsfb = 0;
+      if constexpr (Cfg::kScaled) {
+        tsfa = tmem_base + Cfg::kSfBase + q * Cfg::kSfSlotCols;
+        tsfb = tsfa + Cfg::kSfaCols;
+      }
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++lt, it_base += p.k_iters) {
         const int w = lt & 1;
+        if (q >= p.k_iters) continue;   // a single k-step: nothing for the second issuer
         TRACE_T0(t_a);
         if (!mbar_wait(acc_empty_bar(w), ((lt >> 1) & 1) ^ 1, abort_flag)) {
           report_status(p.status, 52, 100 + w);
@@ -195,10 +217,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             break;
           }
         }
+        if (q == 1) {
+          // the k-step that overwrites the accumulator must be complete before this
+          // issuer adds to it
+          if (!mbar_wait(tile_open_bar(w), (lt >> 1) & 1, abort_flag)) {
+            report_status(p.status, 52, 300 + w);
+            *abort_flag = 1;
+            break;
+          }
+        }
         tc_fence_after_sync();
         TRACE_ACC(w_acc, t_a);
         const uint32_t tmem_acc = tmem_base + w * Cfg::kAccStride;
-        for (int kb = 0; kb < p.k_iters; ++kb, ++it) {
+        for (int kb = q; kb < p.k_iters; kb += 2) {
+          const uint32_t it = it_base + kb;
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
           TRACE_T0(t_f);
@@ -216,11 +248,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024, kSwizzle128B);
           const uint64_t b_desc = make_smem_desc(b_addr, 16, 1024, kSwizzle128B);
           const int n_mma = (kb == p.k_iters - 1) ? p.k_tail_mmas : 4;
-          uint32_t tsfa = 0, tsfb = 0;
           if constexpr (Cfg::kScaled) {
-            const int slot = (Cfg::kSfSlots == 2) ? (it & 1) : 0;
-            tsfa = tmem_base + Cfg::kSfBase + slot * Cfg::kSfSlotCols;
-            tsfb = tsfa + Cfg::kSfaCols;
+            // this issuer's slot: its previous MMAs precede these copies in program order
             const uint32_t sfa_addr = sf_base + s * Cfg::kSfBytes;
             const uint32_t sfb_addr = sfa_addr + Cfg::kSfAtoms * 512;
 #pragma unroll
@@ -255,6 +284,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (elected) {
             tc_commit_pair(e0);
             tc_commit_pair(e1);
+            if (kb == 0 && p.k_iters > 1) tc_commit_pair(map_to_cta(tile_open_bar(w), 0));
           }
           TRACE_ACC(t_issue, t_i);
         }
@@ -267,7 +297,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
 #ifdef B200K_TRACE
-      if (elected) {
+      if (elected && q == 0) {
         atomicAdd(&g_trace[2], static_cast<unsigned long long>(w_full));
         atomicAdd(&g_trace[3], static_cast<unsigned long long>(w_acc));
         atomicAdd(&g_trace[7], static_cast<unsigned long long>(t_issue));
@@ -276,7 +306,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #endif
     }
     __syncwarp();
-  } else {
+  } else if (warp < 6) {
     // ---------------- epilogue (both CTAs) ----------------
     const int quarter = warp & 3;
     float alpha = p.alpha;
@@ -295,7 +325,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
       const int w = lt & 1;
       TRACE_T0(t_e);
-      if (!mbar_wait_relaxed(acc_full_bar(w), (lt >> 1) & 1, abort_flag, 256)) {
+      if (!mbar_wait_relaxed(acc_full_bar(w), (lt >> 1) & 1, abort_flag, 64)) {
         report_status(p.status, 53, w);
         *abort_flag = 1;
         break;
@@ -325,7 +355,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tc_fence_before_sync();
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(lead_ovl);
+      if (lane == 0) mbar_arrive_cluster_relaxed(lead_ovl);
       auto emit = [&](int c, const uint32_t (&r)[32]) {
         if (row_ok && n0 + c * 32 < p.n) {
           float v[32];
@@ -348,7 +378,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(w), 0));
+      if (lane == 0) mbar_arrive_cluster_relaxed(map_to_cta(acc_empty_bar(w), 0));
     }
 #ifdef B200K_TRACE
     if (threadIdx.x == 64) {
@@ -382,7 +412,7 @@ int launch_pair(const CUtensorMap* maps, const GemmParams& p, int grid, cudaStre
       return fail(B200K_CUDA_ERROR, "cudaFuncSetAttribute(%d bytes): %s", Cfg::kSmemBytes, cudaGetErrorString(e));
     configured[dev] = true;
   }
-  kernel<<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(maps[0], maps[1], maps[2], maps[3], p);
   B200K_CHECK_LAUNCH("gemm (CTA pair) launch");
   return B200K_OK;
 }
