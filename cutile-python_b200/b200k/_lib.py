@@ -43,6 +43,7 @@ class GemmArgs(Structure):
         ("alpha", c_float), ("max_ctas", c_int32),
         ("tile_group", c_void_p), ("num_row_tiles", c_void_p),
         ("row_map", c_void_p), ("row_scale", c_void_p), ("c_rows", c_int64),
+        ("tile_rows", c_int32),
     ]
 
 
@@ -58,6 +59,7 @@ class BlockScaledGemmArgs(Structure):
         ("max_ctas", c_int32),
         ("tile_group", c_void_p), ("num_row_tiles", c_void_p),
         ("row_map", c_void_p), ("row_scale", c_void_p), ("c_rows", c_int64),
+        ("tile_rows", c_int32),
     ]
 
 

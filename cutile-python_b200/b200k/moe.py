@@ -10,19 +10,29 @@ cutile_moe_mxfp8             the same FFN with MXFP8 expert weights and activati
 Pipeline of cutile_moe (no host synchronisation anywhere): device-side alignment ->
 row gather of the hidden states into expert order -> grouped GEMM with fused SiLU-and-
 multiply epilogue -> grouped GEMM with routed-weight scaling and row scatter -> top-k sum.
-The grouped GEMM's row tile is 128, so the alignment always uses tile_m = 128 internally;
+The grouped GEMM runs on CTA pairs over 256-row tiles (each tile one expert), so the
+alignment uses tile_m = 256 internally (128 with the one-CTA kernels, B200K_MOE_TILE=128);
 `tile_m/tile_n/tile_k` are accepted for signature compatibility.
 """
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
 from . import _lib
 from .block_scaled import _as_u8, swizzled_shape
 
-ROW_TILE = 128
+ROW_TILE = 128          # row tile of the one-CTA grouped GEMM
+ROW_TILES = (128, 256)  # 256: the CTA-pair grouped GEMM
+
+
+def _moe_tile() -> int:
+    """Row tile the FFN entry points align with."""
+    if os.environ.get("B200K_SINGLE_CTA") == "1" or os.environ.get("B200K_MOE_TILE") == "128":
+        return 128
+    return 256
 
 
 def _cdiv(a: int, b: int) -> int:
@@ -69,7 +79,7 @@ def moe_align_tile_size_torch(topk_ids: torch.Tensor, tile_m: int, num_experts: 
 
 
 def _gather_rows(src: torch.Tensor, index: torch.Tensor, divisor: int, rows: int,
-                 num_blocks: torch.Tensor | None) -> torch.Tensor:
+                 num_blocks: torch.Tensor | None, tile: int = ROW_TILE) -> torch.Tensor:
     if src.stride(1) != 1 or (src.stride(0) * src.element_size()) % 16 or src.data_ptr() % 16 \
             or (src.shape[1] * src.element_size()) % 16:
         raise ValueError("gather source rows must be contiguous multiples of 16 bytes")
@@ -78,14 +88,14 @@ def _gather_rows(src: torch.Tensor, index: torch.Tensor, divisor: int, rows: int
         _lib.check(_lib.lib().b200k_gather_rows(
             src.data_ptr(), src.shape[0], src.shape[1] * src.element_size(),
             src.stride(0) * src.element_size(), index.data_ptr(), divisor,
-            _lib.ptr(num_blocks), ROW_TILE, rows, dst.data_ptr(),
+            _lib.ptr(num_blocks), tile, rows, dst.data_ptr(),
             dst.stride(0) * dst.element_size(), _lib.stream_ptr(src.device)))
     return dst
 
 
 def _grouped_gemm(a_sorted, w, c, expert_ids, *, num_blocks=None, row_map=None, row_scale=None,
-                  c_rows=0, swiglu=False):
-    """a_sorted (Mp, K) x w (E, N, K)^T with the expert of each 128-row tile in expert_ids."""
+                  c_rows=0, swiglu=False, tile=ROW_TILE):
+    """a_sorted (Mp, K) x w (E, N, K)^T with the expert of each `tile`-row tile in expert_ids."""
     mp, k = a_sorted.shape
     e, n, _ = w.shape
     args = _lib.GemmArgs()
@@ -103,6 +113,7 @@ def _grouped_gemm(a_sorted, w, c, expert_ids, *, num_blocks=None, row_map=None, 
     args.row_map = _lib.ptr(row_map)
     args.row_scale = _lib.ptr(row_scale)
     args.c_rows = c_rows
+    args.tile_rows = tile
     with torch.cuda.device(c.device):
         _lib.check(_lib.lib().b200k_gemm(ctypes.byref(args), _lib.stream_ptr(c.device)))
     return c
@@ -121,18 +132,18 @@ def invoke_fused_moe_kernel(A, B, C, topk_weights, sorted_token_ids, sorted_expe
                             tile_m: int = ROW_TILE, tile_n: int = 128, tile_k: int = 64) -> None:
     """C.view(-1, N)[r] = (A[r // num_token_replicas] @ B[expert(r)].T) [* topk_weights[r]] for
     every replica id r in sorted_token_ids; sentinel ids are skipped."""
-    if tile_m != ROW_TILE:
-        raise ValueError(f"this kernel's row tile is {ROW_TILE}: align with tile_m={ROW_TILE}")
+    if tile_m not in ROW_TILES:
+        raise ValueError(f"this kernel's row tiles are {ROW_TILES}: align with one of them")
     if sorted_token_ids.numel() != sorted_expert_ids.numel() * tile_m:
         raise ValueError("sorted_token_ids / sorted_expert_ids lengths disagree")
     c2 = C.view(-1, C.shape[-1])
     rows = sorted_token_ids.numel()
     if rows == 0:
         return
-    a_sorted = _gather_rows(A, sorted_token_ids, num_token_replicas, rows, None)
+    a_sorted = _gather_rows(A, sorted_token_ids, num_token_replicas, rows, None, tile_m)
     scale = topk_weights.reshape(-1).float().contiguous() if mul_routed_weight else None
     _grouped_gemm(a_sorted, _check_weight(B), c2, sorted_expert_ids, row_map=sorted_token_ids,
-                  row_scale=scale, c_rows=c2.shape[0])
+                  row_scale=scale, c_rows=c2.shape[0], tile=tile_m)
 
 
 def invoke_silu_and_mul_kernel(AB: torch.Tensor, C: torch.Tensor) -> None:
@@ -179,19 +190,21 @@ def cutile_moe(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
     x = hidden_states if hidden_states.stride(1) == 1 else hidden_states.contiguous()
     w1c, w2c = _check_weight(w1), _check_weight(w2)
 
-    sorted_ids, expert_ids, num_blocks = moe_align_device(topk_ids, ROW_TILE, experts)
+    tile = _moe_tile()
+    sorted_ids, expert_ids, num_blocks = moe_align_device(topk_ids, tile, experts)
     cap = sorted_ids.numel()
-    a_sorted = _gather_rows(x, sorted_ids, topk, cap, num_blocks)
+    a_sorted = _gather_rows(x, sorted_ids, topk, cap, num_blocks, tile)
     act = torch.empty((cap, inter), dtype=dtype, device=dev)
     if inter % 128 == 0:
-        _grouped_gemm(a_sorted, w1c, act, expert_ids, num_blocks=num_blocks, swiglu=True)
+        _grouped_gemm(a_sorted, w1c, act, expert_ids, num_blocks=num_blocks, swiglu=True, tile=tile)
     else:
         gate_up = torch.empty((cap, 2 * inter), dtype=dtype, device=dev)
-        _grouped_gemm(a_sorted, w1c, gate_up, expert_ids, num_blocks=num_blocks)
+        _grouped_gemm(a_sorted, w1c, gate_up, expert_ids, num_blocks=num_blocks, tile=tile)
         invoke_silu_and_mul_kernel(gate_up, act)
     per_replica = torch.empty((tokens * topk, hidden), dtype=dtype, device=dev)
     _grouped_gemm(act, w2c, per_replica, expert_ids, num_blocks=num_blocks, row_map=sorted_ids,
-                  row_scale=topk_weights.reshape(-1).float().contiguous(), c_rows=tokens * topk)
+                  row_scale=topk_weights.reshape(-1).float().contiguous(), c_rows=tokens * topk,
+                  tile=tile)
     return _topk_sum(per_replica, tokens, topk, hidden)
 
 
@@ -207,7 +220,7 @@ def quantize_expert_weights(w: torch.Tensor):
     return q.reshape(e, n, k), sf.reshape(e, n // 128, k // 128, 32, 16)
 
 
-def _quantize_rows(x, *, rows, gather=None, divisor=1, num_blocks=None):
+def _quantize_rows(x, *, rows, gather=None, divisor=1, num_blocks=None, tile=ROW_TILE):
     """MXFP8 quantisation of (optionally gathered) rows with swizzled scales."""
     k = x.shape[1]
     q = torch.empty((rows, k), dtype=torch.uint8, device=x.device)
@@ -218,7 +231,7 @@ def _quantize_rows(x, *, rows, gather=None, divisor=1, num_blocks=None):
     a.rows, a.k, a.ldx, a.ldq, a.sf_k_atoms = rows, k, x.stride(0), k, shape[1]
     a.x_dtype, a.q_dtype = _lib.dtype_enum(x.dtype), _lib.E4M3
     a.gather_index = _lib.ptr(gather)
-    a.gather_divisor, a.tile_m, a.src_rows = divisor, ROW_TILE, x.shape[0]
+    a.gather_divisor, a.tile_m, a.src_rows = divisor, tile, x.shape[0]
     a.live_blocks = _lib.ptr(num_blocks)
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().b200k_mxfp8_quantize(ctypes.byref(a), _lib.stream_ptr(x.device)))
@@ -226,7 +239,7 @@ def _quantize_rows(x, *, rows, gather=None, divisor=1, num_blocks=None):
 
 
 def _grouped_scaled_gemm(a_q, a_sf, w_q, w_sf, c, expert_ids, *, num_blocks, row_map=None,
-                         row_scale=None, c_rows=0, swiglu=False):
+                         row_scale=None, c_rows=0, swiglu=False, tile=ROW_TILE):
     mp, k = a_q.shape
     e, n, _ = w_q.shape
     args = _lib.BlockScaledGemmArgs()
@@ -245,6 +258,7 @@ def _grouped_scaled_gemm(a_q, a_sf, w_q, w_sf, c, expert_ids, *, num_blocks, row
     args.row_map = _lib.ptr(row_map)
     args.row_scale = _lib.ptr(row_scale)
     args.c_rows = c_rows
+    args.tile_rows = tile
     with torch.cuda.device(c.device):
         _lib.check(_lib.lib().b200k_block_scaled_gemm(ctypes.byref(args), _lib.stream_ptr(c.device)))
     return c
@@ -266,16 +280,18 @@ def cutile_moe_mxfp8(hidden_states: torch.Tensor, w1_q: torch.Tensor, w1_sf: tor
     if tokens == 0:
         return torch.empty_like(hidden_states)
     x = hidden_states if hidden_states.stride(1) == 1 else hidden_states.contiguous()
-    sorted_ids, expert_ids, num_blocks = moe_align_device(topk_ids, ROW_TILE, experts)
+    tile = _moe_tile()
+    sorted_ids, expert_ids, num_blocks = moe_align_device(topk_ids, tile, experts)
     cap = sorted_ids.numel()
-    a_q, a_sf = _quantize_rows(x, rows=cap, gather=sorted_ids, divisor=topk, num_blocks=num_blocks)
+    a_q, a_sf = _quantize_rows(x, rows=cap, gather=sorted_ids, divisor=topk, num_blocks=num_blocks,
+                               tile=tile)
     act = torch.empty((cap, inter), dtype=dtype, device=dev)
     _grouped_scaled_gemm(a_q, a_sf, w1_q, _as_u8(w1_sf), act, expert_ids, num_blocks=num_blocks,
-                         swiglu=True)
-    act_q, act_sf = _quantize_rows(act, rows=cap, num_blocks=num_blocks)
+                         swiglu=True, tile=tile)
+    act_q, act_sf = _quantize_rows(act, rows=cap, num_blocks=num_blocks, tile=tile)
     per_replica = torch.empty((tokens * topk, hidden), dtype=dtype, device=dev)
     _grouped_scaled_gemm(act_q, act_sf, w2_q, _as_u8(w2_sf), per_replica, expert_ids,
                          num_blocks=num_blocks, row_map=sorted_ids,
                          row_scale=topk_weights.reshape(-1).float().contiguous(),
-                         c_rows=tokens * topk)
+                         c_rows=tokens * topk, tile=tile)
     return _topk_sum(per_replica, tokens, topk, hidden)

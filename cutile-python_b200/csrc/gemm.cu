@@ -20,7 +20,6 @@
 
 namespace b200k {
 
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 
 template <int KIND, int BN, bool B_MN, int OUT>
 __global__ void __launch_bounds__(kNumThreads, 1)
@@ -456,13 +455,17 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
   if (a->max_ctas > 0 && grid > a->max_ctas) grid = a->max_ctas;
 
   const int out = a->c_dtype;
-  if (!grouped && !b_mn && a->epilogue == B200K_EPI_STORE && a->row_map == nullptr &&
-      pair_kernels_enabled()) {
+  const bool pair_plain = !grouped && a->epilogue == B200K_EPI_STORE && a->row_map == nullptr;
+  const bool pair_grouped = grouped && a->tile_rows == 256;
+  if (!b_mn && (pair_plain || pair_grouped) && pair_kernels_enabled()) {
     GemmParams pp = p;
     pp.idesc = make_idesc(fmt, fmt, false, false, 256, BN);
     const CUtensorMap maps[4] = {ta, tb, ta, ta};
     return launch_gemm_pair(kind, out, maps, pp, sms, stream);
   }
+  if (grouped && a->tile_rows != 0 && a->tile_rows != 128)
+    return fail(B200K_UNSUPPORTED, "tile_rows %d: 256-row tiles need B stored (N, K) and the CTA-pair "
+                "kernels, otherwise tile_group entries are per 128 rows", a->tile_rows);
   if (kind == kKindF16)
     return b_mn ? launch_out<kKindF16, BN, true>(out, ta, tb, p, grid, stream)
                 : launch_out<kKindF16, BN, false>(out, ta, tb, p, grid, stream);
@@ -557,24 +560,36 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
   int grid = static_cast<int>(total_tiles < sms ? total_tiles : sms);
   if (a->max_ctas > 0 && grid > a->max_ctas) grid = a->max_ctas;
 
-  if (!grouped && a->batch == 1 && a->epilogue == B200K_EPI_STORE && a->row_map == nullptr &&
-      pair_kernels_enabled()) {
+  const bool pair_plain = !grouped && a->batch == 1 && a->epilogue == B200K_EPI_STORE && a->row_map == nullptr;
+  // grouped: scale tensors of B packed per expert in whole row tiles; SwiGLU only where one
+  // chunk of accumulator columns is shared between the windows (MXFP8)
+  const bool swiglu = a->epilogue == B200K_EPI_SWIGLU;
+  const int64_t sfb_tile_bytes = a->sf_k_atoms * 512;
+  const bool pair_grouped = grouped && a->tile_rows == 256 && !(swiglu && fp4) &&
+                            a->stride_sfb % sfb_tile_bytes == 0;
+  if ((pair_plain || pair_grouped) && pair_kernels_enabled()) {
     GemmParams pp = p;
     pp.idesc = make_idesc_block_scaled(fmt, fmt, 256, BN, /*ue8m0=*/!fp4, 0, 0);
+    pp.sfb_group_tiles = grouped ? static_cast<int>(a->stride_sfb / sfb_tile_bytes) : 0;
     CUtensorMap tsa, tsb;
     const uint32_t atoms = fp4 ? 4 : 1;
     const uint64_t ka = static_cast<uint64_t>(a->sf_k_atoms);
+    const uint64_t sfb_tiles = grouped ? static_cast<uint64_t>(pp.sfb_group_tiles) * a->batch
+                                       : static_cast<uint64_t>(ceil_div(a->n, 128));
     // one 512-byte atom per innermost row (128 32-bit words), so every request of the copy
     // engine is a whole run of cache lines rather than a 16-byte row of the atom
     if (!encode_tmap_3d(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT32, a->sfa, 128, ka, ceil_div(a->m, 128), 512,
                         ka * 512, 128, atoms, 1, CU_TENSOR_MAP_SWIZZLE_NONE))
       return B200K_INVALID_ARG;
-    if (!encode_tmap_3d(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT32, a->sfb, 128, ka, ceil_div(a->n, 128), 512,
-                        ka * 512, 128, atoms, 2, CU_TENSOR_MAP_SWIZZLE_NONE))
+    if (!encode_tmap_3d(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT32, a->sfb, 128, ka, sfb_tiles, 512,
+                        ka * 512, 128, atoms, swiglu ? 1 : 2, CU_TENSOR_MAP_SWIZZLE_NONE))
       return B200K_INVALID_ARG;
     const CUtensorMap maps[4] = {ta, tb, tsa, tsb};
     return launch_gemm_pair(fp4 ? kKindNVF4 : kKindMXF8, a->c_dtype, maps, pp, sms, stream);
   }
+  if (grouped && a->tile_rows != 0 && a->tile_rows != 128)
+    return fail(B200K_UNSUPPORTED, "tile_rows %d is not available for this grouped problem: "
+                "tile_group entries are per 128 rows on the one-CTA kernel", a->tile_rows);
   if (fp4) return launch_out<kKindNVF4, BN, false>(a->c_dtype, ta, tb, p, grid, stream);
   return launch_out<kKindMXF8, BN, false>(a->c_dtype, ta, tb, p, grid, stream);
 }

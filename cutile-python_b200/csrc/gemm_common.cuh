@@ -32,6 +32,7 @@ struct GemmParams {
   const uint8_t* sfb;
   int sf_k_atoms;
   int sfb_row_tiles;    // 128-row tiles present in sfb (reads are clamped to it)
+  int sfb_group_tiles;  // 128-row tiles of sfb per group (grouped CTA-pair kernel)
   int64_t stride_sfa, stride_sfb;
   // grouped mode
   const int* tile_group;
@@ -80,6 +81,8 @@ struct GemmCfg {
                 "scale factors do not fit in tensor memory");
   static_assert(!(B_MN && KIND == kKindNVF4), "fp4 operands are K-major only");
 };
+
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 
 struct TileCoord {
   int batch, pid_m, pid_n;

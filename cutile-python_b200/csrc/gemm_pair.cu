@@ -123,8 +123,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int tiles_m = (p.m + 255) / 256;
+  // grouped mode: 256-row tiles, the live count comes from the device
+  int tiles_m = (p.m + 255) / 256;
+  if (p.num_row_tiles != nullptr) tiles_m = min(tiles_m, *p.num_row_tiles);
   const int num_tiles = tiles_m * p.tiles_n * p.batch;
+  const bool swiglu = p.epilogue == B200K_EPI_SWIGLU;
   const int cluster_id = blockIdx.x >> 1;
   const int num_clusters = gridDim.x >> 1;
 
@@ -141,8 +144,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #endif
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
+        int group = tc.batch, a_batch = tc.batch;
+        if (p.tile_group != nullptr) {
+          group = p.tile_group[tc.pid_m];
+          a_batch = 0;
+          if (group < 0) continue;
+        }
         const int m0 = tc.pid_m * 256 + rank * 128;
-        const int nb = tc.pid_n * 256 + rank * 128;
+        // SwiGLU: the leader stages 128 gate rows of B, its peer the matching up rows
+        const int nb = swiglu ? tc.pid_n * 128 + static_cast<int>(rank) * (p.n / 2)
+                              : tc.pid_n * 256 + static_cast<int>(rank) * 128;
+        const int sfb_tile0 = group * p.sfb_group_tiles + (swiglu ? tc.pid_n : tc.pid_n * 2);
         for (int kb = 0; kb < p.k_iters; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
@@ -161,14 +173,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const int kx = kb * (KIND == kKindNVF4 ? 128 : Cfg::kBKElems);
           if (elected) {
             if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * (Cfg::kStageBytes + Cfg::kSfBytes));
-            tma_load_3d_pair(a_dst, &tmap_a, lead_full, kx, m0, tc.batch);
-            tma_load_3d_pair(b_dst, &tmap_b, lead_full, kx, nb, tc.batch);
+            tma_load_3d_pair(a_dst, &tmap_a, lead_full, kx, m0, a_batch);
+            tma_load_3d_pair(b_dst, &tmap_b, lead_full, kx, nb, group);
             if constexpr (Cfg::kScaled) {
               const uint32_t sfa_dst = sf_base + s * Cfg::kSfBytes;
               const uint32_t sfb_dst = sfa_dst + Cfg::kSfAtoms * 512;
               tma_load_3d_pair(sfa_dst, &tmap_sfa, lead_full, 0, kb * Cfg::kSfAtoms, tc.pid_m * 2 + rank);
-              // both 128-row tiles of SFB in one box: [row tile][atom][512 B] in shared memory
-              tma_load_3d_pair(sfb_dst, &tmap_sfb, lead_full, 0, kb * Cfg::kSfAtoms, tc.pid_n * 2);
+              if (!swiglu) {
+                // both 128-row tiles of SFB in one box: [row tile][atom][512 B] in shared memory
+                tma_load_3d_pair(sfb_dst, &tmap_sfb, lead_full, 0, kb * Cfg::kSfAtoms, sfb_tile0);
+              } else {
+                // gate and up tiles are N / 256 row tiles apart: one-tile boxes
+                tma_load_3d_pair(sfb_dst, &tmap_sfb, lead_full, 0, kb * Cfg::kSfAtoms, sfb_tile0);
+                tma_load_3d_pair(sfb_dst + Cfg::kSfAtoms * 512, &tmap_sfb, lead_full, 0, kb * Cfg::kSfAtoms,
+                                 sfb_tile0 + p.n / 256);
+              }
             }
           }
         }
@@ -201,9 +220,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tsfa = tmem_base + Cfg::kSfBase + q * Cfg::kSfSlotCols;
         tsfb = tsfa + Cfg::kSfaCols;
       }
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++lt, it_base += p.k_iters) {
+      if (q >= p.k_iters) ok = false;   // a single k-step: nothing for the second issuer
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        if (p.tile_group != nullptr && p.tile_group[tile_coord(tile, tiles_m, p.tiles_n).pid_m] < 0) continue;
         const int w = lt & 1;
-        if (q >= p.k_iters) continue;   // a single k-step: nothing for the second issuer
         TRACE_T0(t_a);
         if (!mbar_wait(acc_empty_bar(w), ((lt >> 1) & 1) ^ 1, abort_flag)) {
           report_status(p.status, 52, 100 + w);
@@ -295,6 +315,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tc_commit_pair(f1);
           }
         }
+        ++lt;
+        it_base += p.k_iters;
       }
 #ifdef B200K_TRACE
       if (elected && q == 0) {
@@ -321,8 +343,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #ifdef B200K_TRACE
     long long w_accf = 0;
 #endif
-    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++lt) {
+    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
       const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
+      if (p.tile_group != nullptr && p.tile_group[tc.pid_m] < 0) continue;
       const int w = lt & 1;
       TRACE_T0(t_e);
       if (!mbar_wait_relaxed(acc_full_bar(w), (lt >> 1) & 1, abort_flag, 64)) {
@@ -333,13 +356,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       TRACE_ACC(w_accf, t_e);
       tc_fence_after_sync();
       const int row = tc.pid_m * 256 + rank * 128 + quarter * 32 + lane;
-      const bool row_ok = row < p.m;
+      int64_t out_row = row;
+      bool row_ok = row < p.m;
+      if (p.row_map != nullptr && row_ok) {
+        out_row = p.row_map[row];
+        row_ok = out_row >= 0 && out_row < p.c_rows;
+      }
       float scale = alpha;
-      if (p.row_scale != nullptr && row_ok) scale *= p.row_scale[row];
+      if (p.row_scale != nullptr && row_ok) scale *= p.row_scale[out_row];
       uint8_t* c_row = static_cast<uint8_t*>(p.c) +
-                       (static_cast<int64_t>(tc.batch) * p.stride_c + static_cast<int64_t>(row) * p.ldc) * elem_bytes;
+                       (static_cast<int64_t>(p.tile_group ? 0 : tc.batch) * p.stride_c + out_row * p.ldc) * elem_bytes;
       const uint32_t taddr = tmem_base + w * Cfg::kAccStride + (uint32_t(quarter * 32) << 16);
-      const int n0 = tc.pid_n * 256;
       // Columns shared with the other window first (the last chunks of window 0, the first
       // chunks of window 1): they are pulled into registers back to back and released
       // before anything is converted or stored, so the next tile's first MMA waits only
@@ -356,29 +383,59 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster_relaxed(lead_ovl);
-      auto emit = [&](int c, const uint32_t (&r)[32]) {
-        if (row_ok && n0 + c * 32 < p.n) {
-          float v[32];
+      if (!swiglu) {
+        const int n0 = tc.pid_n * 256;
+        auto emit = [&](int c, const uint32_t (&r)[32]) {
+          if (row_ok && n0 + c * 32 < p.n) {
+            float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * scale;
-          store_row_chunk<OUT>(c_row, n0 + c * 32, p.n, v, vec_ok);
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * scale;
+            store_row_chunk<OUT>(c_row, n0 + c * 32, p.n, v, vec_ok);
+          }
+        };
+        if constexpr (Cfg::kOverlapChunks > 0) {
+#pragma unroll
+          for (int ci = 0; ci < Cfg::kOverlapChunks; ++ci) emit((first + ci) & 7, held[ci]);
         }
-      };
-      if constexpr (Cfg::kOverlapChunks > 0) {
-#pragma unroll
-        for (int ci = 0; ci < Cfg::kOverlapChunks; ++ci) emit((first + ci) & 7, held[ci]);
-      }
 #pragma unroll 1
-      for (int ci = Cfg::kOverlapChunks; ci < 8; ++ci) {
-        const int c = (first + ci) & 7;
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        emit(c, r);
+        for (int ci = Cfg::kOverlapChunks; ci < 8; ++ci) {
+          const int c = (first + ci) & 7;
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          emit(c, r);
+        }
+      } else if constexpr (Cfg::kOverlapChunks <= 1) {
+        // columns [0, 128) of the tile are gate, [128, 256) the matching up projections
+        const int n_out = p.n / 2;
+        const int n0 = tc.pid_n * 128;
+        auto fetch = [&](int c, uint32_t (&r)[32]) {
+          if (Cfg::kOverlapChunks == 1 && c == first) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = held[0][i];
+          } else {
+            tmem_ld_32x32b_x32(taddr + c * 32, r);
+          }
+        };
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t g[32], u[32];
+          fetch(c, g);
+          fetch(c + 4, u);
+          tmem_ld_wait();
+          if (row_ok && n0 + c * 32 < n_out) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              v[i] = silu(__uint_as_float(g[i]) * scale) * (__uint_as_float(u[i]) * scale);
+            store_row_chunk<OUT>(c_row, n0 + c * 32, n_out, v, vec_ok);
+          }
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster_relaxed(map_to_cta(acc_empty_bar(w), 0));
+      ++lt;
     }
 #ifdef B200K_TRACE
     if (threadIdx.x == 64) {

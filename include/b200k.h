@@ -81,7 +81,7 @@ typedef struct {
   float alpha;        /* scalar applied to the accumulator */
   int32_t max_ctas;   /* 0 = one CTA per SM (persistent) */
   /* Grouped mode (all optional, NULL = off).  `tile_group[i]` is the B batch index
-   * (expert) of the i-th 128-row tile of A, or a negative value for a tile to skip;
+   * (expert) of the i-th `tile_rows`-row tile of A, or a negative value for a tile to skip;
    * `num_row_tiles` points at the device-side count of row tiles in use. */
   const int32_t* tile_group;
   const int32_t* num_row_tiles;
@@ -91,6 +91,10 @@ typedef struct {
   const int32_t* row_map;
   const float* row_scale;
   int64_t c_rows;
+  /* Rows of A per `tile_group` entry: 128 (also when 0) or 256.  With 256 (and B stored
+   * (N, K)) the grouped GEMM runs on the CTA-pair kernel; `num_row_tiles` then counts
+   * 256-row tiles. */
+  int32_t tile_rows;
 } b200k_gemm_args;
 
 int b200k_gemm(const b200k_gemm_args* args, b200k_stream stream);
@@ -129,6 +133,7 @@ typedef struct {
   const int32_t* row_map;
   const float* row_scale;
   int64_t c_rows;
+  int32_t tile_rows;                     /* as in b200k_gemm_args */
 } b200k_block_scaled_gemm_args;
 
 int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* args, b200k_stream stream);

@@ -77,8 +77,11 @@ def _problem(tokens, hidden, experts, inter, topk, seed, dtype=torch.bfloat16):
 @pytest.mark.parametrize("tokens,hidden,experts,inter,topk", [
     (48, 512, 64, 1024, 8),      # the sample's problem
     (24, 64, 4, 32, 2),          # intermediate not a multiple of 128: unfused SiLU path
-    (300, 256, 8, 128, 2), (1, 128, 4, 128, 1)])
-def test_cutile_moe_bf16(tokens, hidden, experts, inter, topk, device_ok):
+    (300, 256, 8, 128, 2), (1, 128, 4, 128, 1),
+    (1500, 512, 6, 384, 3)])     # several row tiles per expert, three column tiles
+@pytest.mark.parametrize("row_tile", ["128", "256"])   # one-CTA and CTA-pair grouped GEMM
+def test_cutile_moe_bf16(tokens, hidden, experts, inter, topk, row_tile, device_ok, monkeypatch):
+    monkeypatch.setenv("B200K_MOE_TILE", row_tile)
     x, w1, w2, tw, ids = _problem(tokens, hidden, experts, inter, topk, tokens)
     out = b200k.cutile_moe(x.cuda(), w1.cuda(), w2.cuda(), tw.cuda(), ids.cuda(), 128, 128, 64)
     assert out.shape == x.shape and out.dtype == x.dtype
@@ -87,17 +90,18 @@ def test_cutile_moe_bf16(tokens, hidden, experts, inter, topk, device_ok):
     assert oracle.rel_frobenius(out, ref) < 2e-2
 
 
-def test_invoke_fused_moe_kernel_matches_manual_pipeline(device_ok):
+@pytest.mark.parametrize("tile_m", [128, 256])
+def test_invoke_fused_moe_kernel_matches_manual_pipeline(tile_m, device_ok):
     # the sample's three-launch pipeline driven through the reference-named helpers
     x, w1, w2, tw, ids = _problem(40, 256, 8, 128, 2, 7)
     xc, w1c, w2c, twc, idc = (t.cuda() for t in (x, w1, w2, tw, ids))
-    st, se = b200k.moe_align_tile_size_torch(idc, 128, 8)
+    st, se = b200k.moe_align_tile_size_torch(idc, tile_m, 8)
     c1 = torch.zeros(40, 2, 256, dtype=torch.bfloat16, device="cuda")
-    b200k.invoke_fused_moe_kernel(xc, w1c, c1, twc, st, se, False, 2, 128, 128, 64)
+    b200k.invoke_fused_moe_kernel(xc, w1c, c1, twc, st, se, False, 2, tile_m, 128, 64)
     c2 = torch.zeros(80, 128, dtype=torch.bfloat16, device="cuda")
     b200k.invoke_silu_and_mul_kernel(c1.view(-1, 256), c2)
     c3 = torch.zeros(40, 2, 256, dtype=torch.bfloat16, device="cuda")
-    b200k.invoke_fused_moe_kernel(c2, w2c, c3, twc, st, se, True, 1, 128, 128, 64)
+    b200k.invoke_fused_moe_kernel(c2, w2c, c3, twc, st, se, True, 1, tile_m, 128, 64)
     out = torch.sum(c3, dim=1)
     torch.testing.assert_close(out.float().cpu(), oracle.moe_ref(x, w1, w2, tw, ids), rtol=1e-1, atol=1e-1)
     with pytest.raises(ValueError, match="row tile"):
@@ -112,8 +116,11 @@ def test_torch_moe_golden_problem(golden_dir, device_ok):
     torch.testing.assert_close(out.float().cpu(), torch.from_numpy(g["out"]), rtol=1e-1, atol=1e-1)
 
 
-@pytest.mark.parametrize("tokens,hidden,experts,inter,topk", [(64, 256, 8, 128, 2), (500, 512, 16, 256, 4)])
-def test_cutile_moe_mxfp8(tokens, hidden, experts, inter, topk, device_ok):
+@pytest.mark.parametrize("tokens,hidden,experts,inter,topk", [(64, 256, 8, 128, 2), (500, 512, 16, 256, 4),
+                                                             (1500, 512, 6, 384, 3)])
+@pytest.mark.parametrize("row_tile", ["128", "256"])
+def test_cutile_moe_mxfp8(tokens, hidden, experts, inter, topk, row_tile, device_ok, monkeypatch):
+    monkeypatch.setenv("B200K_MOE_TILE", row_tile)
     x, w1, w2, tw, ids = _problem(tokens, hidden, experts, inter, topk, 11)
     w1q, w1s = b200k.quantize_expert_weights(w1.cuda())
     w2q, w2s = b200k.quantize_expert_weights(w2.cuda())
