@@ -44,6 +44,7 @@ class GemmArgs(Structure):
         ("tile_group", c_void_p), ("num_row_tiles", c_void_p),
         ("row_map", c_void_p), ("row_scale", c_void_p), ("c_rows", c_int64),
         ("tile_rows", c_int32),
+        ("workspace", c_void_p), ("workspace_bytes", c_int64),
     ]
 
 
@@ -115,6 +116,7 @@ SIGNATURES = {
     "b200k_sm_count": (c_int, []),
     "b200k_device_status": (c_int, [POINTER(c_int), POINTER(c_int)]),
     "b200k_gemm": (c_int, [POINTER(GemmArgs), c_void_p]),
+    "b200k_gemm_workspace_bytes": (c_int64, [POINTER(GemmArgs)]),
     "b200k_block_scaled_gemm": (c_int, [POINTER(BlockScaledGemmArgs), c_void_p]),
     "b200k_mxfp8_quantize": (c_int, [POINTER(QuantizeArgs), c_void_p]),
     "b200k_nvfp4_quantize": (c_int, [POINTER(QuantizeArgs), c_void_p]),

@@ -83,6 +83,13 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, alpha: float = 1
     args.alpha = alpha
     args.max_ctas = max_ctas
     with torch.cuda.device(a.device):
+        # a few output tiles with a long K: split-K over the idle SMs needs fp32 scratch
+        workspace = None
+        if -(-m // 128) * -(-n // 256) * nb * 4 <= 256 and k * a3.element_size() >= 1024:
+            ws_bytes = _lib.lib().b200k_gemm_workspace_bytes(ctypes.byref(args))
+            if ws_bytes > 0:
+                workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
+                args.workspace, args.workspace_bytes = workspace.data_ptr(), ws_bytes
         _lib.check(_lib.lib().b200k_gemm(ctypes.byref(args), _lib.stream_ptr(a.device)))
     return c
 

@@ -84,14 +84,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
-        int group = tc.batch;
+        // split-K: the batch index of the raster carries (batch, split)
+        const int batch = p.split_k > 1 ? tc.batch / p.split_k : tc.batch;
+        const int kb0 = p.split_k > 1 ? (tc.batch % p.split_k) * p.k_per_split : 0;
+        const int kb1 = p.split_k > 1 ? min(p.k_iters, kb0 + p.k_per_split) : p.k_iters;
+        int group = batch;
         if (p.tile_group != nullptr) {
           group = p.tile_group[tc.pid_m];
           if (group < 0) continue;
         }
         const int m0 = tc.pid_m * kBM;
         const int n0 = tc.pid_n * BN;
-        for (int kb = 0; kb < p.k_iters; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) {
@@ -112,7 +116,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const int kx = kb * (KIND == kKindNVF4 ? 128 : Cfg::kBKElems);
           if (elected) {
           mbar_arrive_expect_tx(full_bar(s), tx);
-          tma_load_3d(a_dst, &tmap_a, full_bar(s), kx, m0, p.tile_group ? 0 : tc.batch);
+          tma_load_3d(a_dst, &tmap_a, full_bar(s), kx, m0, p.tile_group ? 0 : batch);
           if constexpr (B_MN) {
 #pragma unroll
             for (int j = 0; j < Cfg::kBBoxes; ++j)
@@ -131,7 +135,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if constexpr (Cfg::kScaled) {
             const uint32_t sfa_dst = sf_base + s * Cfg::kSfBytes;
             const uint32_t sfb_dst = sfa_dst + Cfg::kSfaAtoms * 512;
-            const uint8_t* sfa_src = p.sfa + (p.tile_group ? 0 : tc.batch) * p.stride_sfa +
+            const uint8_t* sfa_src = p.sfa + (p.tile_group ? 0 : batch) * p.stride_sfa +
                                      (static_cast<int64_t>(tc.pid_m) * p.sf_k_atoms + kb * Cfg::kSfaAtoms) * 512;
             bulk_load(sfa_dst, sfa_src, sfa_atoms * 512, full_bar(s));
 #pragma unroll
@@ -158,9 +162,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t local_tile = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        if (p.tile_group != nullptr) {
+        int kb0 = 0, kb1 = p.k_iters;
+        if (p.tile_group != nullptr || p.split_k > 1) {
           TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
-          if (p.tile_group[tc.pid_m] < 0) continue;
+          if (p.tile_group != nullptr && p.tile_group[tc.pid_m] < 0) continue;
+          if (p.split_k > 1) {
+            kb0 = (tc.batch % p.split_k) * p.k_per_split;
+            kb1 = min(p.k_iters, kb0 + p.k_per_split);
+          }
         }
         const int as = local_tile % Cfg::kNumAcc;
         const uint32_t aph = (local_tile / Cfg::kNumAcc) & 1;
@@ -171,7 +180,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + as * Cfg::kAccStride;
-        for (int kb = 0; kb < p.k_iters; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(full_bar(s), ph, abort_flag)) {
@@ -207,7 +216,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             if (kk < n_mma && elected) {
-              const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
+              const uint32_t acc = (kb > kb0 || kk > 0) ? 1u : 0u;
               // K-major: 32 bytes of K per MMA inside the 128-byte swizzle atom.
               // MN-major B: kMmaK rows of 128 bytes per MMA.
               const uint64_t a_d = a_desc + static_cast<uint64_t>(kk * 2);
@@ -350,6 +359,78 @@ int launch_out(int out, const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
   }
 }
 
+// Split-K plan for problems with far fewer output tiles than SMs: `split` CTAs share one
+// tile, each reducing k_per_split k-steps into an fp32 partial; a second kernel sums the
+// partials.  Returns 1 when splitting does not pay.
+struct SplitPlan {
+  int split = 1;
+  int k_per_split = 0;
+  int64_t workspace_bytes = 0;
+};
+
+SplitPlan plan_split_k(int64_t m, int64_t n, int64_t batch, int k_iters, int sms) {
+  SplitPlan plan;
+  const int64_t tiles = ceil_div(m, kBM) * ceil_div(n, 256) * batch;
+  if (tiles * 4 > sms || k_iters < 8) return plan;
+  const int max_split = static_cast<int>(sms / tiles);
+  int k_per = static_cast<int>(ceil_div(k_iters, max_split));
+  if (k_per < 4) k_per = 4;
+  const int split = static_cast<int>(ceil_div(k_iters, k_per));
+  if (split <= 1) return plan;
+  plan.split = split;
+  plan.k_per_split = k_per;
+  plan.workspace_bytes = static_cast<int64_t>(split) * batch * m * n * 4;
+  return plan;
+}
+
+// out[b][r][c] = sum over s of partial[b * split + s][r][c], rounded to the output type.
+template <int OUT>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ ws, int split, int64_t m, int64_t n, int64_t batch,
+                     void* __restrict__ c, int64_t ldc, int64_t stride_c) {
+  const int64_t quads = (n + 3) / 4;
+  const int64_t total = batch * m * quads;
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t qd = idx % quads;
+    const int64_t row = (idx / quads) % m;
+    const int64_t b = idx / (quads * m);
+    const int64_t col = qd * 4;
+    const int valid = static_cast<int>(n - col < 4 ? n - col : 4);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* src = ws + ((b * split) * m + row) * n + col;
+    const bool vec = (n % 4 == 0);
+    for (int s = 0; s < split; ++s, src += m * n) {
+      if (vec) {
+        const float4 v = *reinterpret_cast<const float4*>(src);
+        acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+      } else {
+        for (int i = 0; i < valid; ++i) acc[i] += src[i];
+      }
+    }
+    const int64_t off = b * stride_c + row * ldc + col;
+    for (int i = 0; i < valid; ++i) {
+      if constexpr (OUT == kOutF32) static_cast<float*>(c)[off + i] = acc[i];
+      else if constexpr (OUT == kOutF16) static_cast<__half*>(c)[off + i] = __float2half_rn(acc[i]);
+      else static_cast<__nv_bfloat16*>(c)[off + i] = __float2bfloat16_rn(acc[i]);
+    }
+  }
+}
+
+int launch_splitk_reduce(int out, const float* ws, int split, int64_t m, int64_t n, int64_t batch, void* c,
+                         int64_t ldc, int64_t stride_c, cudaStream_t stream) {
+  const int64_t total = batch * m * ((n + 3) / 4);
+  const int grid = static_cast<int>(total / 256 + 1 < 4096 ? total / 256 + 1 : 4096);
+  switch (out) {
+    case B200K_F16: splitk_reduce_kernel<kOutF16><<<grid, 256, 0, stream>>>(ws, split, m, n, batch, c, ldc, stride_c); break;
+    case B200K_BF16: splitk_reduce_kernel<kOutBF16><<<grid, 256, 0, stream>>>(ws, split, m, n, batch, c, ldc, stride_c); break;
+    case B200K_F32: splitk_reduce_kernel<kOutF32><<<grid, 256, 0, stream>>>(ws, split, m, n, batch, c, ldc, stride_c); break;
+    default: return fail(B200K_INVALID_ARG, "unsupported output dtype %d", out);
+  }
+  B200K_CHECK_LAUNCH("split-K reduce launch");
+  return B200K_OK;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // The CTA-pair kernels are the default; B200K_SINGLE_CTA=1 forces the one-CTA kernels.
@@ -455,6 +536,32 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
   if (a->max_ctas > 0 && grid > a->max_ctas) grid = a->max_ctas;
 
   const int out = a->c_dtype;
+  if (!grouped && a->epilogue == B200K_EPI_STORE && a->row_map == nullptr && a->workspace != nullptr) {
+    const SplitPlan plan = plan_split_k(a->m, a->n, a->batch, p.k_iters, sms);
+    if (plan.split > 1 && a->workspace_bytes >= plan.workspace_bytes && aligned16(a->workspace)) {
+      GemmParams ps = p;
+      ps.c = a->workspace;
+      ps.ldc = a->n;
+      ps.stride_c = a->m * a->n;
+      ps.batch = p.batch * plan.split;
+      ps.split_k = plan.split;
+      ps.k_per_split = plan.k_per_split;
+      const int64_t split_tiles = total_tiles * plan.split;
+      const int sgrid = static_cast<int>(split_tiles < sms ? split_tiles : sms);
+      int rc;
+      if (kind == kKindF16)
+        rc = b_mn ? launch<kKindF16, BN, true, kOutF32>(ta, tb, ps, sgrid, stream)
+                  : launch<kKindF16, BN, false, kOutF32>(ta, tb, ps, sgrid, stream);
+      else if (kind == kKindTF32)
+        rc = launch<kKindTF32, BN, false, kOutF32>(ta, tb, ps, sgrid, stream);
+      else
+        rc = b_mn ? launch<kKindF8, BN, true, kOutF32>(ta, tb, ps, sgrid, stream)
+                  : launch<kKindF8, BN, false, kOutF32>(ta, tb, ps, sgrid, stream);
+      if (rc != B200K_OK) return rc;
+      return launch_splitk_reduce(out, static_cast<const float*>(a->workspace), plan.split, a->m, a->n,
+                                  a->batch, a->c, a->ldc, a->stride_c, stream);
+    }
+  }
   const bool pair_plain = !grouped && a->epilogue == B200K_EPI_STORE && a->row_map == nullptr;
   const bool pair_grouped = grouped && a->tile_rows == 256;
   if (!b_mn && (pair_plain || pair_grouped) && pair_kernels_enabled()) {
@@ -592,4 +699,20 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
                 "tile_group entries are per 128 rows on the one-CTA kernel", a->tile_rows);
   if (fp4) return launch_out<kKindNVF4, BN, false>(a->c_dtype, ta, tb, p, grid, stream);
   return launch_out<kKindMXF8, BN, false>(a->c_dtype, ta, tb, p, grid, stream);
+}
+
+extern "C" int64_t b200k_gemm_workspace_bytes(const b200k_gemm_args* a) {
+  if (a == nullptr || a->m <= 0 || a->n <= 0 || a->k <= 0 || a->batch <= 0) return 0;
+  if (a->tile_group != nullptr || a->epilogue != B200K_EPI_STORE || a->row_map != nullptr) return 0;
+  int elem_bytes;
+  switch (a->ab_dtype) {
+    case B200K_F16: case B200K_BF16: elem_bytes = 2; break;
+    case B200K_F32: elem_bytes = 4; break;
+    case B200K_E4M3: case B200K_E5M2: elem_bytes = 1; break;
+    default: return 0;
+  }
+  const int sms = current_sm_count();
+  if (sms <= 0) return 0;
+  const int k_iters = static_cast<int>(ceil_div(a->k, 128 / elem_bytes));
+  return plan_split_k(a->m, a->n, a->batch, k_iters, sms).workspace_bytes;
 }

@@ -23,6 +23,8 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int k_iters;
   int k_tail_mmas;      // MMAs of the last k iteration (1..4)
+  int split_k;          // > 1: `batch` counts (batch, split) pairs, each split owns k_per_split k-steps
+  int k_per_split;
   uint32_t idesc;
   float alpha;
   const float* alpha_a;

@@ -95,9 +95,20 @@ typedef struct {
    * (N, K)) the grouped GEMM runs on the CTA-pair kernel; `num_row_tiles` then counts
    * 256-row tiles. */
   int32_t tile_rows;
+  /* Optional scratch for split-K (see b200k_gemm_workspace_bytes): 16-byte aligned device
+   * memory, contents irrelevant before and after the call.  NULL = never split. */
+  void* workspace;
+  int64_t workspace_bytes;
 } b200k_gemm_args;
 
 int b200k_gemm(const b200k_gemm_args* args, b200k_stream stream);
+
+/* Bytes of `workspace` with which b200k_gemm would split K for this problem on the current
+ * device, 0 when it would not (enough output tiles to fill the GPU, grouped mode, ...).
+ * Split-K is the reference's matmul_split_k_kernel (test/kernels/matmul.py:103-139): a few
+ * output tiles with a long K are spread over many CTAs, fp32 partial tiles are summed by a
+ * second kernel. */
+int64_t b200k_gemm_workspace_bytes(const b200k_gemm_args* args);
 
 /* ---- block-scaled GEMM ------------------------------------------------
  * C = alpha * (A (.) sA) . (B (.) sB), fp32 accumulation.  Replaces

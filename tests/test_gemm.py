@@ -49,6 +49,50 @@ def test_cutile_matmul_transposed_b_view(dtype, device_ok):
     torch.testing.assert_close(c.float().cpu(), oracle.matmul_ref(a, b_nk.T), **TOL[dtype])
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("m,n,k,b_nk", [(256, 256, 4096, False),    # the reference's split-K bench shape
+                                        (256, 256, 4096, True), (100, 300, 4104, False),
+                                        (128, 512, 8192, True), (8, 8, 1024, False)])
+def test_split_k_shapes(dtype, m, n, k, b_nk, device_ok):
+    # few output tiles, long K: the library spreads K over the idle SMs (fp32 partials + a
+    # reduction kernel); the result must not depend on that choice
+    a = (_rand((m, k), dtype, 5) * 0.25).to(dtype)
+    b = _rand((n, k), dtype, 6) if b_nk else _rand((k, n), dtype, 6)
+    bd = b.cuda().T if b_nk else b.cuda()
+    ref = oracle.matmul_ref(a, b.T if b_nk else b)
+    c = b200k.cutile_matmul(a.cuda(), bd)
+    tol = dict(TOL[dtype])
+    tol["atol"] = max(tol["atol"], (2e-3 if dtype != torch.bfloat16 else 8e-3) * 0.25 * k ** 0.5)
+    torch.testing.assert_close(c.float().cpu(), ref, **tol)
+    import ctypes
+    from b200k import _lib
+    probe = _lib.GemmArgs()
+    probe.m, probe.n, probe.k, probe.batch = m, n, k, 1
+    probe.ab_dtype = _lib.dtype_enum(dtype)
+    assert _lib.lib().b200k_gemm_workspace_bytes(ctypes.byref(probe)) > 0   # the split path ran
+    # the same product on one CTA per tile, no workspace: same result within rounding
+    c1 = torch.empty_like(c)
+    args = _lib.GemmArgs()
+    a_d = a.cuda()
+    b_k = (b.cuda() if b_nk else b.cuda().T.contiguous())
+    args.a, args.b, args.c = a_d.data_ptr(), b_k.data_ptr(), c1.data_ptr()
+    args.m, args.n, args.k, args.batch = m, n, k, 1
+    args.lda, args.ldb, args.ldc = k, k, n
+    args.ab_dtype = args.c_dtype = _lib.dtype_enum(dtype)
+    args.b_layout, args.epilogue, args.alpha = _lib.B_NK, _lib.EPI_STORE, 1.0
+    if (k * a.element_size()) % 16 == 0:
+        _lib.check(_lib.lib().b200k_gemm(ctypes.byref(args), _lib.stream_ptr(c.device)))
+        torch.testing.assert_close(c1.float(), c.float(), **tol)
+
+
+def test_split_k_batched(device_ok):
+    a = _rand((3, 128, 2048), torch.float16, 8) * 0.25
+    b = _rand((3, 2048, 256), torch.float16, 9)
+    c = b200k.bmm(a.cuda(), b.cuda(), torch.float16)
+    ref = torch.bmm(a.float(), b.float())
+    torch.testing.assert_close(c.float().cpu(), ref, atol=5e-2, rtol=2e-2)
+
+
 def test_all_ones_known_answer(device_ok):
     # mma of all-ones tiles: every output equals K
     a = torch.ones(128, 448, dtype=torch.float16, device="cuda")
