@@ -97,6 +97,7 @@ class FmhaArgs(Structure):
         ("input_pos", c_int64),
         ("head_dim", c_int32), ("dtype", c_int32), ("query_group_size", c_int32),
         ("causal", c_int32), ("qk_scale", c_float),
+        ("workspace", c_void_p), ("workspace_bytes", c_int64),
     ]
 
 
@@ -130,6 +131,7 @@ SIGNATURES = {
     "b200k_topk_sum": (c_int, [c_void_p, c_void_p, c_int64, c_int32, c_int64, c_void_p, c_int32, c_void_p]),
     "b200k_peer_gather": (c_int, [POINTER(PeerGatherArgs), c_void_p]),
     "b200k_fmha_fwd": (c_int, [POINTER(FmhaArgs), c_void_p]),
+    "b200k_fmha_workspace_bytes": (c_int64, [POINTER(FmhaArgs)]),
     "b200k_sf_swizzle": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int32,
                                  c_void_p]),
 }

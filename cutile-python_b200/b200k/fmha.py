@@ -6,6 +6,7 @@ cutile_fmha_into   test/bench_attention.py:96-113 (bench form: output passed in)
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 
 import torch
@@ -94,6 +95,14 @@ def cutile_fmha(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor,
     a.causal = 1 if causal else 0
     a.qk_scale = float(qk_scale)
     with torch.cuda.device(Q.device):
+        # a few query rows per KV head (decode): the split-KV kernels need scratch for the
+        # partial softmax states (B200K_FMHA_NO_DECODE=1 keeps the tensor-core kernels)
+        workspace = None
+        if seq_q * query_group_size <= 8 and os.environ.get("B200K_FMHA_NO_DECODE") != "1":
+            ws_bytes = _lib.lib().b200k_fmha_workspace_bytes(ctypes.byref(a))
+            if ws_bytes > 0:
+                workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=Q.device)
+                a.workspace, a.workspace_bytes = workspace.data_ptr(), ws_bytes
         _lib.check(_lib.lib().b200k_fmha_fwd(ctypes.byref(a), _lib.stream_ptr(Q.device)))
     if not direct:
         Out.copy_(o[..., :d_v])

@@ -19,6 +19,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "fmha_decode.h"
 #include "host.h"
 
 namespace b200k {
@@ -697,6 +698,16 @@ extern "C" int b200k_fmha_fwd(const b200k_fmha_args* a, b200k_stream stream_) {
        reinterpret_cast<uintptr_t>(a->v)) & 15)
     return fail(B200K_UNSUPPORTED, "Q/K/V must be 16-byte aligned");
 
+  // a few query rows per KV head: stream K / V once over many CTAs instead of padding a
+  // 128-row tensor-core tile
+  if (a->workspace != nullptr && fmha_decode_applies(a) &&
+      (reinterpret_cast<uintptr_t>(a->workspace) & 15) == 0) {
+    const int sms = current_sm_count();
+    if (sms > 0 && a->workspace_bytes >= fmha_decode_workspace_bytes(a, sms) &&
+        (a->o_stride_b | a->o_stride_h | a->o_stride_s) >= 0)
+      return launch_fmha_decode(a, sms, stream);
+  }
+
   const CUtensorMapDataType dt =
       a->dtype == B200K_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUtensorMap tq, tk, tv;
@@ -745,6 +756,15 @@ extern "C" int b200k_fmha_fwd(const b200k_fmha_args* a, b200k_stream stream_) {
                 : launch_fmha<128, false>(tq, tk, tv, p, grid, stream);
   return bf16 ? launch_fmha<64, true>(tq, tk, tv, p, grid, stream)
               : launch_fmha<64, false>(tq, tk, tv, p, grid, stream);
+}
+
+extern "C" int64_t b200k_fmha_workspace_bytes(const b200k_fmha_args* a) {
+  if (a == nullptr || a->batch <= 0 || a->heads_kv <= 0 || a->seq_q <= 0 || a->seq_kv <= 0 ||
+      a->query_group_size <= 0 || (a->head_dim != 64 && a->head_dim != 128))
+    return 0;
+  const int sms = current_sm_count();
+  if (sms <= 0) return 0;
+  return fmha_decode_workspace_bytes(a, sms);
 }
 
 #ifdef B200K_TRACE

@@ -400,13 +400,17 @@ splitk_reduce_kernel(const float* __restrict__ ws, int split, int64_t m, int64_t
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const float* src = ws + ((b * split) * m + row) * n + col;
     const bool vec = (n % 4 == 0);
-    for (int s = 0; s < split; ++s, src += m * n) {
-      if (vec) {
-        const float4 v = *reinterpret_cast<const float4*>(src);
+    if (vec) {
+      // independent loads, issued eight at a time: the partials are a few megabytes in L2
+      // and the sum of one output quad is latency-bound otherwise
+#pragma unroll 8
+      for (int s = 0; s < split; ++s) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(src + static_cast<int64_t>(s) * m * n));
         acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
-      } else {
-        for (int i = 0; i < valid; ++i) acc[i] += src[i];
       }
+    } else {
+      for (int s = 0; s < split; ++s, src += m * n)
+        for (int i = 0; i < valid; ++i) acc[i] += src[i];
     }
     const int64_t off = b * stride_c + row * ldc + col;
     for (int i = 0; i < valid; ++i) {

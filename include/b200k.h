@@ -301,9 +301,21 @@ typedef struct {
   int32_t query_group_size;
   int32_t causal;
   float qk_scale;
+  /* Optional scratch for the split-KV path (see b200k_fmha_workspace_bytes): 16-byte aligned
+   * device memory, contents irrelevant before and after the call.  NULL = tensor-core
+   * kernels only. */
+  void* workspace;
+  int64_t workspace_bytes;
 } b200k_fmha_args;
 
 int b200k_fmha_fwd(const b200k_fmha_args* args, b200k_stream stream);
+
+/* Bytes of `workspace` with which b200k_fmha_fwd takes the split-KV path on the current
+ * device: seq_q * query_group_size <= 8 query rows per key/value head (decode steps; the
+ * reference benches q (1, 32, 1, 128) against 1024 keys, test/bench_attention.py:33-44).
+ * The keys are split over CTAs that stream K and V once on the CUDA cores; a second kernel
+ * merges the partial softmax states.  0 = the path does not apply. */
+int64_t b200k_fmha_workspace_bytes(const b200k_fmha_args* args);
 
 #ifdef __cplusplus
 }

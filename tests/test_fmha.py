@@ -54,6 +54,40 @@ def test_fmha_reference_test_shapes_gqa(batch, q_heads, q_len, k_len, causal, de
     torch.testing.assert_close(out.float().cpu(), ref, **TOL)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("b,hq,hkv,sq,sk,causal", [
+    (1, 32, 32, 1, 1024, True),     # the reference's decode bench shape
+    (2, 32, 8, 1, 1000, True),      # grouped-query decode: 4 rows share a KV head, ragged keys
+    (1, 16, 4, 2, 4100, True),      # two new tokens, 8 rows per KV head, many splits
+    (2, 8, 8, 3, 70, True),         # keys shorter than one chunk
+    (1, 8, 2, 1, 300, False),
+    (3, 4, 4, 5, 129, False),
+    (5, 32, 8, 2, 600, True),       # enough KV heads for the one-kernel (cluster) path, 8 rows each
+    (20, 8, 8, 3, 200, False),      # cluster path, 3 rows
+    (4, 8, 8, 1, 20, True)])        # cluster path with most CTAs of a cluster idle
+def test_fmha_decode_split_kv(dtype, d, b, hq, hkv, sq, sk, causal, device_ok, monkeypatch):
+    q, k, v = _qkv(b, hq, hkv, sq, sk, d, dtype, b + hq + sk)
+    group = hq // hkv
+    input_pos = sk - sq if causal else 0
+    args = dict(query_group_size=group, causal=causal, input_pos=input_pos)
+    out = b200k.cutile_fmha(q.cuda(), k.cuda(), v.cuda(), **args)
+    ref = oracle.fmha_ref(q, k, v, **args)
+    torch.testing.assert_close(out.float().cpu(), ref, **TOL)
+    # the tensor-core kernels on the same inputs agree with the split-KV path
+    monkeypatch.setenv("B200K_FMHA_NO_DECODE", "1")
+    out_tc = b200k.cutile_fmha(q.cuda(), k.cuda(), v.cuda(), **args)
+    torch.testing.assert_close(out.float(), out_tc.float(), **TOL)
+
+
+def test_fmha_decode_mid_sequence_position(device_ok):
+    # input_pos in the middle of a longer cache: keys beyond the position are never read
+    q, k, v = _qkv(1, 8, 8, 1, 2048, 128, torch.bfloat16, 77)
+    out = b200k.cutile_fmha(q.cuda(), k.cuda(), v.cuda(), causal=True, input_pos=700)
+    ref = oracle.fmha_ref(q, k[:, :, :701], v[:, :, :701], causal=False)
+    torch.testing.assert_close(out.float().cpu(), ref, **TOL)
+
+
 def test_fmha_bshd_storage_and_scale(device_ok):
     # (B, S, H, D) storage viewed as (B, H, S, D), explicit scale
     g = torch.Generator().manual_seed(5)
