@@ -567,11 +567,31 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
     }
   }
   const bool pair_plain = !grouped && a->epilogue == B200K_EPI_STORE && a->row_map == nullptr;
-  const bool pair_grouped = grouped && a->tile_rows == 256;
-  if (!b_mn && (pair_plain || pair_grouped) && pair_kernels_enabled()) {
+  const bool pair_grouped = grouped && a->tile_rows == 256 && !b_mn;
+  // N-contiguous B on the pair kernel: 16-bit operands, plain problems (for fp8 the one-CTA
+  // kernel is the faster one with this layout: 612 against 641 us on 4 x 8192 x 8192 x 2000)
+  const bool pair_b_ok = !b_mn || (pair_plain && kind == kKindF16);
+  if (pair_b_ok && (pair_plain || pair_grouped) && pair_kernels_enabled()) {
     GemmParams pp = p;
-    pp.idesc = make_idesc(fmt, fmt, false, false, 256, BN);
-    const CUtensorMap maps[4] = {ta, tb, ta, ta};
+    // Tile width: 256 x 256.  256 x 128 tiles (B200K_PAIR_BN=128) halve the cost of a
+    // partly filled last wave on paper (4096 cubed: 256 tiles on 74 clusters are 4 rounds,
+    // 512 narrow tiles 7 half rounds), but a narrow tile re-reads A twice as often and
+    // pays the per-tile hand-offs twice: measured 113 against 96 us there.
+    int bn = 256;
+    const char* force_bn = getenv("B200K_PAIR_BN");
+    if (force_bn != nullptr && pair_plain) bn = force_bn[0] == '1' ? 128 : 256;
+    pp.pair_bn = bn;
+    pp.b_mn = b_mn ? 1 : 0;
+    pp.tiles_n = static_cast<int>(ceil_div(a->n, bn));
+    pp.idesc = make_idesc(fmt, fmt, false, b_mn, 256, bn);
+    CUtensorMap tbp = tb;
+    if (!b_mn && bn == 128) {
+      const uint64_t sb = (b_batches > 1 ? a->stride_b : a->n * a->ldb) * elem_bytes;
+      if (!encode_tmap_3d(&tbp, tdt, a->b, a->k, a->n, b_batches, a->ldb * elem_bytes, sb, bk, 64, 1,
+                          CU_TENSOR_MAP_SWIZZLE_128B))
+        return B200K_INVALID_ARG;
+    }
+    const CUtensorMap maps[4] = {ta, tbp, ta, ta};
     return launch_gemm_pair(kind, out, maps, pp, sms, stream);
   }
   if (grouped && a->tile_rows != 0 && a->tile_rows != 128)

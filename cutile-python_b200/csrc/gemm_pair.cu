@@ -34,7 +34,7 @@ namespace b200k {
 // Debug build only: cycle counters summed over all CTAs.
 // 0 producer wait(empty), 1 producer total, 2 mma wait(full), 3 mma wait(acc), 4 mma total,
 // 5 epilogue wait(acc_full), 6 epilogue total, 7 mma issue (descs + cp + mma + commit);
-// 2, 3, 4 and 7 are those of the first issuer
+// 2, 3, 4 and 7 are those of the first issuer; 12 / 13 cycles and nanoseconds of CTA 0's producer
 __device__ unsigned long long g_trace[16];
 #define TRACE_T0(var) long long var = clock64()
 #define TRACE_ADD(idx, var) atomicAdd(&g_trace[idx], static_cast<unsigned long long>(clock64() - (var)))
@@ -54,6 +54,10 @@ struct PairCfg {
   static constexpr int kABytes = 128 * 128;
   static constexpr int kBBytes = 128 * 128;          // this CTA's half of the 256 B rows
   static constexpr int kStageBytes = kABytes + kBBytes;
+  // N-contiguous ("MN-major") B: boxes of 128 bytes of N by kBKElems rows of K
+  static constexpr int kBBoxN = 128 * 8 / T::kElemBits;
+  static constexpr int kBBoxBytes = kBKElems * 128;
+  static constexpr int kMmaK = kBKElems / 4;
   static constexpr int kSfAtoms = kScaled ? (KIND == kKindNVF4 ? 4 : 1) : 0;  // along K, per stage
   static constexpr int kSfBytes = kSfAtoms * 512 * 3;                       // SFA + both SFB row tiles
   static constexpr int kAccStride = !kScaled ? 256 : (KIND == kKindNVF4 ? 160 : 224);
@@ -128,6 +132,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (p.num_row_tiles != nullptr) tiles_m = min(tiles_m, *p.num_row_tiles);
   const int num_tiles = tiles_m * p.tiles_n * p.batch;
   const bool swiglu = p.epilogue == B200K_EPI_SWIGLU;
+  const int bn = p.pair_bn;         // tile width: 256, or 128 when that wastes less of the last wave
+  const int b_rows = bn / 2;        // rows (columns of C) of B this CTA stages
   const int cluster_id = blockIdx.x >> 1;
   const int num_clusters = gridDim.x >> 1;
 
@@ -141,6 +147,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       TRACE_T0(t_total);
 #ifdef B200K_TRACE
       long long w_empty = 0;
+      const unsigned long long ns0 = global_timer_ns();
 #endif
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
@@ -153,7 +160,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int m0 = tc.pid_m * 256 + rank * 128;
         // SwiGLU: the leader stages 128 gate rows of B, its peer the matching up rows
         const int nb = swiglu ? tc.pid_n * 128 + static_cast<int>(rank) * (p.n / 2)
-                              : tc.pid_n * 256 + static_cast<int>(rank) * 128;
+                              : tc.pid_n * bn + static_cast<int>(rank) * b_rows;
         const int sfb_tile0 = group * p.sfb_group_tiles + (swiglu ? tc.pid_n : tc.pid_n * 2);
         for (int kb = 0; kb < p.k_iters; ++kb, ++it) {
           const int s = it % S;
@@ -172,9 +179,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t b_dst = a_dst + Cfg::kABytes;
           const int kx = kb * (KIND == kKindNVF4 ? 128 : Cfg::kBKElems);
           if (elected) {
-            if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * (Cfg::kStageBytes + Cfg::kSfBytes));
+            if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * (Cfg::kABytes + b_rows * 128 + Cfg::kSfBytes));
             tma_load_3d_pair(a_dst, &tmap_a, lead_full, kx, m0, a_batch);
-            tma_load_3d_pair(b_dst, &tmap_b, lead_full, kx, nb, group);
+            if (!p.b_mn) {
+              tma_load_3d_pair(b_dst, &tmap_b, lead_full, kx, nb, group);   // box of b_rows rows
+            } else {
+              // N-contiguous B: boxes of 128 bytes of N by one k-step of K rows
+              for (int j = 0; j < b_rows / Cfg::kBBoxN; ++j)
+                tma_load_3d_pair(b_dst + j * Cfg::kBBoxBytes, &tmap_b, lead_full, nb + j * Cfg::kBBoxN,
+                                 kb * Cfg::kBKElems, group);
+            }
             if constexpr (Cfg::kScaled) {
               const uint32_t sfa_dst = sf_base + s * Cfg::kSfBytes;
               const uint32_t sfb_dst = sfa_dst + Cfg::kSfAtoms * 512;
@@ -196,6 +210,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (elected) {
         atomicAdd(&g_trace[0], static_cast<unsigned long long>(w_empty));
         TRACE_ADD(1, t_total);
+        if (blockIdx.x == 0) {   // SM clock seen by this kernel: cycles / nanoseconds of one producer
+          g_trace[12] = static_cast<unsigned long long>(clock64() - t_total);
+          g_trace[13] = global_timer_ns() - ns0;
+        }
       }
 #endif
     }
@@ -266,7 +284,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t a_addr = tiles_base + s * Cfg::kStageBytes;
           const uint32_t b_addr = a_addr + Cfg::kABytes;
           const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024, kSwizzle128B);
-          const uint64_t b_desc = make_smem_desc(b_addr, 16, 1024, kSwizzle128B);
+          const uint64_t b_desc = p.b_mn ? make_smem_desc(b_addr, Cfg::kBBoxBytes, 1024, kSwizzle128B)
+                                         : make_smem_desc(b_addr, 16, 1024, kSwizzle128B);
+          const uint32_t b_step = p.b_mn ? Cfg::kMmaK * 128 / 16 : 2;   // descriptor advance per MMA
           const int n_mma = (kb == p.k_iters - 1) ? p.k_tail_mmas : 4;
           if constexpr (Cfg::kScaled) {
             // this issuer's slot: its previous MMAs precede these copies in program order
@@ -288,7 +308,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (kk < n_mma && elected) {
               const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
               const uint64_t a_d = a_desc + static_cast<uint64_t>(kk * 2);
-              const uint64_t b_d = b_desc + static_cast<uint64_t>(kk * 2);
+              const uint64_t b_d = b_desc + static_cast<uint64_t>(kk * b_step);
               if constexpr (KIND == kKindMXF8) {
                 umma_block_scaled_pair<KIND>(tmem_acc, a_d, b_d,
                                              p.idesc | (uint32_t(kk) << 29) | (uint32_t(kk) << 4), acc, tsfa, tsfb);
@@ -384,7 +404,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster_relaxed(lead_ovl);
       if (!swiglu) {
-        const int n0 = tc.pid_n * 256;
+        const int n0 = tc.pid_n * bn;
+        const int chunks = bn / 32;
         auto emit = [&](int c, const uint32_t (&r)[32]) {
           if (row_ok && n0 + c * 32 < p.n) {
             float v[32];
@@ -398,7 +419,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           for (int ci = 0; ci < Cfg::kOverlapChunks; ++ci) emit((first + ci) & 7, held[ci]);
         }
 #pragma unroll 1
-        for (int ci = Cfg::kOverlapChunks; ci < 8; ++ci) {
+        for (int ci = Cfg::kOverlapChunks; ci < chunks; ++ci) {
           const int c = (first + ci) & 7;
           uint32_t r[32];
           tmem_ld_32x32b_x32(taddr + c * 32, r);
@@ -486,8 +507,10 @@ int launch_pair_out(int out, const CUtensorMap* maps, const GemmParams& p, int g
 
 }  // namespace
 
-int launch_gemm_pair(int kind, int out_dtype, const CUtensorMap* maps, const GemmParams& p, int sms,
+int launch_gemm_pair(int kind, int out_dtype, const CUtensorMap* maps, const GemmParams& p_in, int sms,
                      cudaStream_t stream) {
+  GemmParams p = p_in;
+  if (p.pair_bn != 128) p.pair_bn = 256;
   const int64_t tiles = static_cast<int64_t>((p.m + 255) / 256) * p.tiles_n * p.batch;
   int clusters = static_cast<int>(tiles < sms / 2 ? tiles : sms / 2);
   if (clusters < 1) clusters = 1;

@@ -93,6 +93,30 @@ def test_split_k_batched(device_ok):
     torch.testing.assert_close(c.float().cpu(), ref, atol=5e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("bn", ["128", "256"])
+@pytest.mark.parametrize("b_nk", [False, True])
+@pytest.mark.parametrize("m,n,k", [(512, 640, 256), (1000, 500, 700), (2304, 1152, 192)])
+def test_pair_kernel_tile_widths_and_b_layouts(dtype, bn, b_nk, m, n, k, device_ok, monkeypatch):
+    # the CTA-pair kernel with 256 x 128 and 256 x 256 tiles, B stored (K, N) and (N, K)
+    monkeypatch.setenv("B200K_PAIR_BN", bn)
+    a = _rand((m, k), dtype, 11)
+    b = _rand((n, k), dtype, 12) if b_nk else _rand((k, n), dtype, 12)
+    c = b200k.cutile_matmul(a.cuda(), b.cuda().T if b_nk else b.cuda())
+    tol = dict(TOL[dtype])
+    if dtype == torch.float32:
+        tol["atol"] = max(tol["atol"], 6e-3 * k ** 0.5)
+    torch.testing.assert_close(c.float().cpu(), oracle.matmul_ref(a, b.T if b_nk else b), **tol)
+
+
+def test_pair_kernel_fp8_row_major_b(device_ok):
+    g = torch.Generator().manual_seed(3)
+    a = torch.randn(2, 384, 256, generator=g).to(torch.float8_e4m3fn)
+    b = torch.randn(2, 256, 512, generator=g).to(torch.float8_e4m3fn)
+    c = b200k.bmm(a.cuda(), b.cuda(), torch.float32)
+    torch.testing.assert_close(c.cpu(), torch.bmm(a.float(), b.float()), atol=1e-3, rtol=1e-3)
+
+
 def test_all_ones_known_answer(device_ok):
     # mma of all-ones tiles: every output equals K
     a = torch.ones(128, 448, dtype=torch.float16, device="cuda")
