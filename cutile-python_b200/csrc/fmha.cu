@@ -99,8 +99,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
 template <int D, bool BF16>
 __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int lane, int b, int h,
                                              int q0, int n_kv, uint32_t tmem_s, uint32_t tmem_o,
-                                             uint32_t s_full, uint32_t p_full, uint32_t pv_done,
-                                             volatile int* abort_flag) {
+                                             uint32_t s_full, uint32_t p_half, uint32_t p_full,
+                                             uint32_t pv_done, volatile int* abort_flag) {
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
@@ -196,6 +196,13 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
           pk[i] = BF16 ? pack_bf16x2(e.x, e.y) : pack_f16x2(e.x, e.y);
         }
         tmem_st_32x32b_x32(tmem_s + lane_addr + c * 32, pk);
+        if (c == 0 && p_half != 0) {
+          // the first 64 keys of P are enough for the first half of P V
+          tmem_st_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(p_half);
+        }
       }
       l += ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y)) +
            ((sum2[2].x + sum2[2].y) + (sum2[3].x + sum2[3].y));
@@ -411,7 +418,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
     __syncwarp();
   } else {
-    softmax_tile<D, BF16>(p, warp, lane, b, h, q0, n_kv, tmem_s, tmem_o, bar(S_FULL), bar(P_FULL),
+    softmax_tile<D, BF16>(p, warp, lane, b, h, q0, n_kv, tmem_s, tmem_o, bar(S_FULL), 0u, bar(P_FULL),
                           bar(PV_DONE), abort_flag);
   }
 
@@ -450,7 +457,7 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   uint8_t* tail = smem + 6 * kTileBytes;
   const uint32_t bar0 = smem_u32(tail);
   enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11,
-         PV_DONE = 13, NUM_BARS = 15 };
+         PV_DONE = 13, P_HALF = 15, NUM_BARS = 17 };
   auto bar = [&](int i) { return bar0 + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8 * NUM_BARS + 8);
@@ -480,7 +487,8 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const int n_kv = max(n_x[0], n_x[1]);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NUM_BARS; ++i) mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? 4 : 1);
+    for (int i = 0; i < NUM_BARS; ++i)
+      mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1 || i == P_HALF || i == P_HALF + 1) ? 4 : 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_q);
@@ -555,15 +563,17 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         if (elected) tc_commit(bar(S_FULL + x));
       };
       // O_x += P_x V for key tile j: P from TMEM, V MN-major
-      auto issue_pv = [&](int x, int st, bool first) {
+      // `half` 0: keys 0..63 of the tile, 1: keys 64..127 (and the completion signal)
+      auto issue_pv = [&](int x, int st, bool first, int half) {
 #pragma unroll
-        for (int kk = 0; kk < kFmhaBN / 16; ++kk) {
+        for (int k4 = 0; k4 < kFmhaBN / 32; ++k4) {
+          const int kk = half * (kFmhaBN / 32) + k4;
           const uint64_t vd = make_smem_desc(v_smem + st * kTileBytes + kk * 2048, kBoxBytes, 1024, kSwizzle128B);
           if (elected)
             umma_f16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + kk * 8, vd, idesc_pv,
                         (!first || kk > 0) ? 1u : 0u);
         }
-        if (elected) tc_commit(bar(PV_DONE + x));
+        if (half == 1 && elected) tc_commit(bar(PV_DONE + x));
       };
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag);
       if (ok) ok = mbar_wait(bar(K_FULL), 0, abort_flag);
@@ -595,6 +605,14 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if (j < n_x[x]) {
+            if (!mbar_wait(bar(P_HALF + x), j & 1, abort_flag)) {
+              report_status(p.status, 75 + x, j);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            issue_pv(x, st, j == 0, 0);
             if (!mbar_wait(bar(P_FULL + x), j & 1, abort_flag)) {
               report_status(p.status, 73 + x, j);
               *abort_flag = 1;
@@ -602,7 +620,7 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
               break;
             }
             tc_fence_after_sync();
-            issue_pv(x, st, j == 0);
+            issue_pv(x, st, j == 0, 1);
           }
           if (more && j + 1 < n_x[x]) issue_s(x, st1);
         }
@@ -617,7 +635,7 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   } else {
     const int x = (warp - 2) >> 2;           // warp group: query tile A (warps 2-5) or B (6-9)
     softmax_tile<D, BF16>(p, warp, lane, b, h, q0 + x * 128, n_x[x], tmem_base + x * 128,
-                          tmem_base + 256 + x * 128, bar(S_FULL + x), bar(P_FULL + x),
+                          tmem_base + 256 + x * 128, bar(S_FULL + x), bar(P_HALF + x), bar(P_FULL + x),
                           bar(PV_DONE + x), abort_flag);
   }
 
