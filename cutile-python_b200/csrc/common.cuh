@@ -104,8 +104,15 @@ constexpr uint64_t kWaitBudgetNs = 2000000000ull;
 
 // Bounded wait on an mbarrier phase.  `abort_flag` is a CTA-shared word that any
 // role raises after it gave up; it shortens the other roles' waits.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile int* abort_flag) {
+//
+// Warp-collective: every lane of a converged warp calls it together.  The lanes poll on
+// their own, but nobody leaves before the slowest lane has seen the phase (__syncwarp): a
+// parity wait only tells "this phase" from "the previous one", so a lane that fell two
+// phases behind its warp's issuing lane would wait for a flip that never comes.  The answer
+// is per lane; after a failure the lanes may leave a loop a few polls apart, which the
+// __syncwarp() that closes every role tolerates.
+__device__ __forceinline__ bool mbar_wait_lane(uint32_t bar, uint32_t parity,
+                                               volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
@@ -119,23 +126,34 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   }
 }
 
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
+                                          volatile int* abort_flag) {
+  const bool ok = mbar_wait_lane(bar, parity, abort_flag);
+  __syncwarp();
+  return ok;
+}
+
 // Same contract, for roles whose wake-up latency does not matter (epilogue warps waiting
 // for a whole tile, producers waiting for a free stage): the thread sleeps between polls,
 // so a waiting warp costs no issue slots and little power.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
                                                   volatile int* abort_flag, uint32_t sleep_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = 0;
-  for (uint32_t it = 1;; ++it) {
-    __nanosleep(sleep_ns);
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 0xff) == 0) {
-      if (*abort_flag) return false;
-      uint64_t now = global_timer_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitBudgetNs) return false;
+  bool ok = mbar_try_wait(bar, parity);
+  if (!ok) {
+    uint64_t t0 = 0;
+    for (uint32_t it = 1;; ++it) {
+      __nanosleep(sleep_ns);
+      if (mbar_try_wait(bar, parity)) { ok = true; break; }
+      if ((it & 0xff) == 0) {
+        if (*abort_flag) break;
+        uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > kWaitBudgetNs) break;
+      }
     }
   }
+  __syncwarp();
+  return ok;
 }
 
 // ---------------------------------------------------------------------------
