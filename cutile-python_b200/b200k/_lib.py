@@ -130,6 +130,7 @@ SIGNATURES = {
                                    c_void_p]),
     "b200k_topk_sum": (c_int, [c_void_p, c_void_p, c_int64, c_int32, c_int64, c_void_p, c_int32, c_void_p]),
     "b200k_peer_gather": (c_int, [POINTER(PeerGatherArgs), c_void_p]),
+    "b200k_peer_scalar_expand": (c_int, [POINTER(c_void_p), c_int32, c_int64, c_void_p, c_void_p]),
     "b200k_fmha_fwd": (c_int, [POINTER(FmhaArgs), c_void_p]),
     "b200k_fmha_workspace_bytes": (c_int64, [POINTER(FmhaArgs)]),
     "b200k_sf_swizzle": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int32,

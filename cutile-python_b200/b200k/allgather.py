@@ -5,7 +5,8 @@ cutile_gather_matmul   samples/AllGatherMatmul.py:85-120
 
 Each rank pulls the other ranks' shards out of their symmetric-memory buffers into a local
 staging buffer with one kernel (plain peer loads over NVLink, all peers at once) and runs
-the tcgen05 GEMM on the staged A.  As in the sample, the caller makes the peers' inputs
+the tcgen05 GEMM on the staged A; the NVFP4 form multiplies its own rows while the gather
+is in flight.  As in the sample, the caller makes the peers' inputs
 visible first (a barrier) and keeps them unchanged until every rank has finished.
 """
 from __future__ import annotations
@@ -132,24 +133,49 @@ class Nvfp4GatherMatmul:
                               dtype=torch.uint8, device=dev)
         self.ts = torch.empty((self.world, 1), dtype=torch.float32, device=dev)
         self.row_scale = torch.empty(self.world * self.m, dtype=torch.float32, device=dev)
+        self.sf_own = _as_u8(a_sf)
+        self.side = torch.cuda.Stream(dev)
+        self.gathered = torch.cuda.Event()
 
     def gather(self):
         peer_gather(self.q_peers, self.rank, out=self.q)
         peer_gather(self.sf_peers, self.rank, out=self.sf)
-        # one float per rank: a 16-byte-row gather does not apply, torch copies do
-        for r, t in enumerate(self.ts_peers):
-            self.ts[r].copy_(t[0])
-        self.row_scale.copy_(self.ts.expand(self.world, self.m).reshape(-1))
+        ptrs = (ctypes.c_void_p * self.world)(*[t.data_ptr() for t in self.ts_peers])
+        dev = self.q.device
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().b200k_peer_scalar_expand(
+                ctypes.cast(ptrs, ctypes.POINTER(ctypes.c_void_p)), self.world, self.m,
+                self.row_scale.data_ptr(), _lib.stream_ptr(dev)))
 
     def run(self, w_q, w_sf, w_ts, out: torch.Tensor | None = None,
             out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-        self.gather()
+        """The gather runs on a side stream while the rows this rank owns are multiplied
+        straight out of its own buffers; the remote rows follow once the gather has landed
+        (an event, no kernel waits on another)."""
         n = w_q.shape[0]
+        dev = self.q.device
+        m, world, rank = self.m, self.world, self.rank
         if out is None:
-            out = torch.empty((self.world * self.m, n), dtype=out_dtype, device=self.q.device)
-        sf = self.sf.reshape(self.world * self.sf_shape[0], *self.sf_shape[1:])
-        return _scaled_gemm(self.q, sf, _as_u8(w_q), _as_u8(w_sf), out, fp4=True, alpha_b=w_ts,
-                            row_scale=self.row_scale)
+            out = torch.empty((world * m, n), dtype=out_dtype, device=dev)
+        wq, wsf = _as_u8(w_q), _as_u8(w_sf)
+        main = torch.cuda.current_stream(dev)
+        if world > 1:
+            self.side.wait_stream(main)    # the previous call's GEMMs are done with the staging
+            with torch.cuda.stream(self.side):
+                self.gather()
+                self.gathered.record(self.side)
+        _scaled_gemm(self.q_peers[rank], self.sf_own, wq, wsf, out[rank * m:(rank + 1) * m], fp4=True,
+                     alpha_a=self.ts_peers[rank], alpha_b=w_ts)
+        if world > 1:
+            main.wait_event(self.gathered)
+            tiles = self.sf_shape[0]       # 128-row scale tiles per rank
+            sf = self.sf.reshape(world * tiles, *self.sf_shape[1:])
+            for lo, hi in ((0, rank), (rank + 1, world)):
+                if hi > lo:
+                    _scaled_gemm(self.q[lo * m:hi * m], sf[lo * tiles:hi * tiles], wq, wsf,
+                                 out[lo * m:hi * m], fp4=True, alpha_b=w_ts,
+                                 row_scale=self.row_scale[lo * m:hi * m])
+        return out
 
 
 def cutile_gather_matmul_nvfp4(a_q: torch.Tensor, a_sf: torch.Tensor, a_ts: torch.Tensor,

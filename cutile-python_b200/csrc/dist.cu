@@ -57,6 +57,16 @@ peer_gather_kernel(PeerPtrs peers, int world, int rank, int64_t rows, int64_t ro
   }
 }
 
+// out[p * rows + i] = the fp32 scalar rank p holds, for every rank: per-row scales of a
+// gathered operand whose shards carry one tensor scale each.
+__global__ void __launch_bounds__(256)
+peer_scalar_expand_kernel(PeerPtrs peers, int64_t rows, float* __restrict__ out) {
+  const float v = *reinterpret_cast<const float*>(peers.p[blockIdx.y]);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < rows;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    out[static_cast<int64_t>(blockIdx.y) * rows + i] = v;
+}
+
 }  // namespace
 }  // namespace b200k
 
@@ -88,5 +98,24 @@ extern "C" int b200k_peer_gather(const b200k_peer_gather_args* a, b200k_stream s
       peers, a->world, a->rank, a->rows, a->row_bytes / 16, a->src_stride_bytes,
       static_cast<uint8_t*>(a->dst), a->dst_stride_bytes, a->round_tf32);
   B200K_CHECK_LAUNCH("peer_gather launch");
+  return B200K_OK;
+}
+
+extern "C" int b200k_peer_scalar_expand(const void* const* shards, int32_t world, int64_t rows,
+                                        float* out, b200k_stream stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (world <= 0 || world > kMaxPeers) return fail(B200K_INVALID_ARG, "world must be in [1, %d]", kMaxPeers);
+  if (rows < 0) return fail(B200K_INVALID_ARG, "negative size");
+  if (rows == 0) return B200K_OK;
+  if (!shards || !out) return fail(B200K_INVALID_ARG, "null pointer");
+  PeerPtrs peers = {};
+  for (int i = 0; i < world; ++i) {
+    if (shards[i] == nullptr || reinterpret_cast<uintptr_t>(shards[i]) % 4)
+      return fail(B200K_INVALID_ARG, "shard %d pointer is null or not 4-byte aligned", i);
+    peers.p[i] = static_cast<const uint8_t*>(shards[i]);
+  }
+  const dim3 grid(static_cast<unsigned>(rows / 256 + 1 < 64 ? rows / 256 + 1 : 64), static_cast<unsigned>(world));
+  peer_scalar_expand_kernel<<<grid, 256, 0, stream>>>(peers, rows, out);
+  B200K_CHECK_LAUNCH("peer_scalar_expand launch");
   return B200K_OK;
 }

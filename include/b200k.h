@@ -277,6 +277,12 @@ typedef struct {
 
 int b200k_peer_gather(const b200k_peer_gather_args* args, b200k_stream stream);
 
+/* out[p * rows + i] = *(const float*)shards[p] for p < world, i < rows: the per-row scale
+ * vector of a gathered operand whose shards carry one fp32 tensor scale each (NVFP4 form
+ * of the gather GEMM).  `shards` as in b200k_peer_gather_args. */
+int b200k_peer_scalar_expand(const void* const* shards, int32_t world, int64_t rows, float* out,
+                             b200k_stream stream);
+
 /* ---- attention forward ------------------------------------------------
  * Out = softmax(qk_scale * Q K^T + mask) V per (batch, head); replaces fmha_kernel
  * (reference: test/kernels/attention.py:20-128) behind cutile_fmha
