@@ -83,20 +83,22 @@ class ExpertParallelMoE:
         y = torch.zeros((n, hidden), dtype=rows.dtype, device=rows.device)
         if n == 0:
             return y
-        sorted_ids, expert_ids, num_blocks = moe.moe_align_device(local_ids.reshape(n, 1), moe.ROW_TILE,
+        tile = moe._moe_tile()
+        sorted_ids, expert_ids, num_blocks = moe.moe_align_device(local_ids.reshape(n, 1), tile,
                                                                   self.local_experts_n)
         cap = sorted_ids.numel()
-        a_sorted = moe._gather_rows(rows, sorted_ids, 1, cap, num_blocks)
+        a_sorted = moe._gather_rows(rows, sorted_ids, 1, cap, num_blocks, tile)
         act = torch.empty((cap, inter), dtype=rows.dtype, device=rows.device)
         if inter % 128 == 0:
             moe._grouped_gemm(a_sorted, moe._check_weight(self.w1), act, expert_ids,
-                              num_blocks=num_blocks, swiglu=True)
+                              num_blocks=num_blocks, swiglu=True, tile=tile)
         else:
             gate_up = torch.empty((cap, 2 * inter), dtype=rows.dtype, device=rows.device)
-            moe._grouped_gemm(a_sorted, moe._check_weight(self.w1), gate_up, expert_ids, num_blocks=num_blocks)
+            moe._grouped_gemm(a_sorted, moe._check_weight(self.w1), gate_up, expert_ids,
+                              num_blocks=num_blocks, tile=tile)
             moe.invoke_silu_and_mul_kernel(gate_up, act)
         moe._grouped_gemm(act, moe._check_weight(self.w2), y, expert_ids, num_blocks=num_blocks,
-                          row_map=sorted_ids, row_scale=weights.float().contiguous(), c_rows=n)
+                          row_map=sorted_ids, row_scale=weights.float().contiguous(), c_rows=n, tile=tile)
         return y
 
     def forward(self, hidden_states: torch.Tensor, topk_weights: torch.Tensor,

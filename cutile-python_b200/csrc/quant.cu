@@ -28,6 +28,9 @@ template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
 __device__ __forceinline__ float2 to_f32x2(__nv_bfloat162 v) { return __bfloat1622float2(v); }
 __device__ __forceinline__ float2 to_f32x2(__half2 v) { return __half22float2(v); }
+template <typename P> __device__ __forceinline__ P to_packed2(float v);
+template <> __device__ __forceinline__ __nv_bfloat162 to_packed2<__nv_bfloat162>(float v) { return __float2bfloat162_rn(v); }
+template <> __device__ __forceinline__ __half2 to_packed2<__half2>(float v) { return __float2half2_rn(v); }
 
 // Loads N consecutive elements (N * sizeof(T) a multiple of 16, address 16-byte aligned
 // when `vec` is true) and widens them to fp32.
@@ -92,6 +95,67 @@ __device__ __forceinline__ uint8_t block_scale(float amax, bool has_nan, float* 
 template <typename T> struct Packed2;
 template <> struct Packed2<__nv_bfloat16> { using type = __nv_bfloat162; };
 template <> struct Packed2<__half> { using type = __half2; };
+
+// max |x| over the elements [begin, end) of the row-major index space of an (rows, k) tensor
+// with leading dimension ldx, strided over the block's threads.  NaNs are ignored, as fmaxf
+// does.  Rows of whole 16-byte vectors on 16-byte boundaries take a vector path: 16-bit
+// types stay packed (|x| and max on pairs), one 16-byte load per 8 elements.
+template <typename T>
+__device__ __forceinline__ float block_strided_absmax(const T* __restrict__ x, int64_t k, int64_t ldx,
+                                                      int64_t begin, int64_t end, int64_t first,
+                                                      int64_t stride) {
+  constexpr int VE = 16 / sizeof(T);
+  const bool vec = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && ((ldx * sizeof(T)) % 16 == 0) &&
+                   (k % VE == 0) && (begin % VE == 0);
+  float m = 0.0f;
+  if (vec) {
+    const int64_t kv = k / VE;
+    const int64_t v_end = end / VE;
+    if constexpr (sizeof(T) == 2) {
+      using P = typename Packed2<T>::type;
+      P pm[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pm[i] = to_packed2<P>(0.0f);
+      int64_t v = begin / VE + first;
+      if (ldx == k) {
+        // contiguous tensor: a flat array, four independent 16-byte loads per trip
+        const uint4* flat = reinterpret_cast<const uint4*>(x);
+        for (; v + 3 * stride < v_end; v += 4 * stride) {
+          uint4 raw[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) raw[u] = flat[v + u * stride];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const P* pr = reinterpret_cast<const P*>(&raw[u]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pm[i] = __hmax2(pm[i], __habs2(pr[i]));
+          }
+        }
+      }
+      for (; v < v_end; v += stride) {
+        const int64_t row = v / kv;
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + row * ldx + (v - row * kv) * VE);
+        const P* pr = reinterpret_cast<const P*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pm[i] = __hmax2(pm[i], __habs2(pr[i]));
+      }
+      const float2 a = to_f32x2(__hmax2(__hmax2(pm[0], pm[1]), __hmax2(pm[2], pm[3])));
+      m = fmaxf(a.x, a.y);
+    } else {
+      for (int64_t v = begin / VE + first; v < v_end; v += stride) {
+        const int64_t row = v / kv;
+        const float4 f = *reinterpret_cast<const float4*>(x + row * ldx + (v - row * kv) * VE);
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
+      }
+    }
+    begin = v_end * VE;   // scalar tail of a range that does not end on a vector
+  }
+  for (int64_t idx = begin + first; idx < end; idx += stride) {
+    const int64_t row = idx / k;
+    m = fmaxf(m, fabsf(to_f32<T>(x[row * ldx + (idx - row * k)])));
+  }
+  return m;
+}
 
 // One full, 16-byte-aligned block of 16-bit elements: the maximum is taken on packed pairs
 // (NaN-propagating), the products are formed in fp32 and converted two at a time.  Returns
@@ -240,14 +304,9 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 absmax_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t ldx,
               uint32_t* __restrict__ amax_bits) {
-  float m = 0.0f;
-  const int64_t total = rows * k;
-  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
-       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t row = idx / k;
-    const int64_t col = idx - row * k;
-    m = fmaxf(m, fabsf(to_f32<T>(x[row * ldx + col])));
-  }
+  float m = block_strided_absmax<T>(x, k, ldx, 0, rows * k,
+                                    blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x,
+                                    static_cast<int64_t>(gridDim.x) * blockDim.x);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   __shared__ float part[8];
@@ -265,7 +324,47 @@ __device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
   return __half2float(*reinterpret_cast<__half*>(&h));
 }
 
-template <typename T>
+// One 16-element block: returns the ue4m3 scale byte, packs the sixteen e2m1 codes into
+// lo (elements 0..7) and hi (8..15), low nibble = even element.
+__device__ __forceinline__ uint8_t nvfp4_block(const float (&v)[16], float six_st, float s_t,
+                                               uint32_t* lo_out, uint32_t* hi_out) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  uint8_t sf_byte = 0;
+  float denom = 0.0f;
+  if (amax > 0.0f && six_st > 0.0f) {
+    const float r = __fdiv_rn(amax, six_st);
+    sf_byte = __nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
+    denom = __fmul_rn(e4m3_to_f32(sf_byte), s_t);
+  }
+  // x / denom as x * (1 / denom), both correctly rounded: one reciprocal per block instead
+  // of sixteen divisions.  A subnormal denom (reciprocal not finite) keeps the division.
+  const float inv = (denom >= 1.17549435e-38f) ? __frcp_rn(denom) : 0.0f;
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float a = 0.0f, b = 0.0f;
+    if (inv > 0.0f) {
+      a = __fmul_rn(v[2 * i], inv);
+      b = __fmul_rn(v[2 * i + 1], inv);
+    } else if (denom > 0.0f) {
+      a = __fdiv_rn(v[2 * i], denom);
+      b = __fdiv_rn(v[2 * i + 1], denom);
+    }
+    const uint32_t byte = __nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest);
+    if (i < 4) lo |= (byte & 0xff) << (8 * i);
+    else hi |= (byte & 0xff) << (8 * (i - 4));
+  }
+  *lo_out = lo;
+  *hi_out = hi;
+  return sf_byte;
+}
+
+// BPT = blocks per thread.  2 (K a multiple of 32, 16-byte-aligned rows in and out): 64 or
+// 128 bytes in flight per thread, one 16-byte store of codes and one 2-byte store of
+// scales.  1: any shape.
+template <typename T, int BPT>
 __global__ void __launch_bounds__(256)
 nvfp4_quantize_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t ldx,
                       uint8_t* __restrict__ q, int64_t ldq_bytes, uint8_t* __restrict__ sf_logical,
@@ -276,47 +375,50 @@ nvfp4_quantize_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t 
   if (blockIdx.x == 0 && threadIdx.x == 0 && tensor_scale != nullptr) *tensor_scale = s_t;
   const float six_st = __fmul_rn(6.0f, s_t);
   const int64_t kblocks = (k + 15) >> 4;
-  const int64_t total = rows * kblocks;
+  const int64_t per_row = kblocks / BPT;          // BPT == 2 only with an even block count
+  const int64_t total = rows * per_row;
   const bool vec_in = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && ((ldx * sizeof(T)) % 16 == 0);
   for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
        idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t row = idx / kblocks;
-    const int64_t kb = idx - row * kblocks;
-    const int valid = static_cast<int>(k - kb * 16 < 16 ? k - kb * 16 : 16);
-    float v[16];
-    load_block<T, 16>(x + row * ldx + kb * 16, v, vec_in, valid);
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    uint8_t sf_byte = 0;
-    float denom = 0.0f;
-    if (amax > 0.0f && six_st > 0.0f) {
-      const float r = __fdiv_rn(amax, six_st);
-      sf_byte = __nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
-      denom = __fmul_rn(e4m3_to_f32(sf_byte), s_t);
-    }
-    uint32_t lo = 0, hi = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float a = 0.0f, b = 0.0f;
-      if (denom > 0.0f) {
-        a = __fdiv_rn(v[2 * i], denom);
-        b = __fdiv_rn(v[2 * i + 1], denom);
-      }
-      // low nibble = even element
-      const uint32_t byte = __nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest);
-      if (i < 4) lo |= (byte & 0xff) << (8 * i);
-      else hi |= (byte & 0xff) << (8 * (i - 4));
-    }
-    uint8_t* dst = q + row * ldq_bytes + kb * 8;
-    if (valid == 16 && (reinterpret_cast<uintptr_t>(dst) % 8 == 0)) {
-      *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+    int64_t row, item;
+    if (total < (1ll << 31)) {
+      const uint32_t r32 = static_cast<uint32_t>(idx) / static_cast<uint32_t>(per_row);
+      row = r32;
+      item = static_cast<uint32_t>(idx) - r32 * static_cast<uint32_t>(per_row);
     } else {
-      for (int i = 0; i < (valid + 1) / 2; ++i)
-        dst[i] = ((i < 4 ? lo >> (8 * i) : hi >> (8 * (i - 4))) & 0xff);
+      row = idx / per_row;
+      item = idx - row * per_row;
     }
-    if (sf_logical != nullptr) sf_logical[row * kblocks + kb] = sf_byte;
-    if (sf_swizzled != nullptr) sf_swizzled[swizzled_sf_offset(row, kb, k_atoms)] = sf_byte;
+    const int64_t kb = item * BPT;
+    if constexpr (BPT == 2) {
+      float v[2][16];
+      load_block<T, 16>(x + row * ldx + kb * 16, v[0], true, 16);
+      load_block<T, 16>(x + row * ldx + kb * 16 + 16, v[1], true, 16);
+      uint32_t w[4];
+      const uint8_t s0 = nvfp4_block(v[0], six_st, s_t, &w[0], &w[1]);
+      const uint8_t s1 = nvfp4_block(v[1], six_st, s_t, &w[2], &w[3]);
+      *reinterpret_cast<uint4*>(q + row * ldq_bytes + kb * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+      const uint16_t pair = static_cast<uint16_t>(s0) | (static_cast<uint16_t>(s1) << 8);
+      // kb is even: the two scale bytes are neighbours in both layouts
+      if (sf_logical != nullptr) *reinterpret_cast<uint16_t*>(sf_logical + row * kblocks + kb) = pair;
+      if (sf_swizzled != nullptr)
+        *reinterpret_cast<uint16_t*>(sf_swizzled + swizzled_sf_offset(row, kb, k_atoms)) = pair;
+    } else {
+      const int valid = static_cast<int>(k - kb * 16 < 16 ? k - kb * 16 : 16);
+      float v[16];
+      load_block<T, 16>(x + row * ldx + kb * 16, v, vec_in, valid);
+      uint32_t lo, hi;
+      const uint8_t sf_byte = nvfp4_block(v, six_st, s_t, &lo, &hi);
+      uint8_t* dst = q + row * ldq_bytes + kb * 8;
+      if (valid == 16 && (reinterpret_cast<uintptr_t>(dst) % 8 == 0)) {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+      } else {
+        for (int i = 0; i < (valid + 1) / 2; ++i)
+          dst[i] = ((i < 4 ? lo >> (8 * i) : hi >> (8 * (i - 4))) & 0xff);
+      }
+      if (sf_logical != nullptr) sf_logical[row * kblocks + kb] = sf_byte;
+      if (sf_swizzled != nullptr) sf_swizzled[swizzled_sf_offset(row, kb, k_atoms)] = sf_byte;
+    }
   }
 }
 
@@ -336,11 +438,7 @@ absmax_slab_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t ldx
   const int64_t total = rows * k;
   const int64_t begin = static_cast<int64_t>(blockIdx.x) * kNoAllocSlabElems;
   const int64_t end = begin + kNoAllocSlabElems < total ? begin + kNoAllocSlabElems : total;
-  float m = 0.0f;
-  for (int64_t idx = begin + threadIdx.x; idx < end; idx += blockDim.x) {
-    const int64_t row = idx / k;
-    m = fmaxf(m, fabsf(to_f32<T>(x[row * ldx + (idx - row * k)])));
-  }
+  float m = block_strided_absmax<T>(x, k, ldx, begin, end, threadIdx.x, blockDim.x);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   __shared__ float part[8];
@@ -455,6 +553,27 @@ extern "C" int b200k_sf_swizzle(const void* sf, int64_t rows, int64_t kblocks, i
   return B200K_OK;
 }
 
+// Two blocks per thread when every access of the fast path is aligned.
+template <typename T>
+void launch_nvfp4_quantize(const b200k_quantize_args* a, const uint32_t* amax, cudaStream_t stream) {
+  uint8_t* q = static_cast<uint8_t*>(a->q);
+  uint8_t* sl = static_cast<uint8_t*>(a->sf_logical);
+  uint8_t* ss = static_cast<uint8_t*>(a->sf_swizzled);
+  const T* x = static_cast<const T*>(a->x);
+  const int64_t kblocks = ceil_div(a->k, 16);
+  const bool pairs = (a->k % 32 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
+                     ((a->ldx * sizeof(T)) % 16 == 0) && (reinterpret_cast<uintptr_t>(q) % 16 == 0) &&
+                     (a->ldq % 16 == 0) && (reinterpret_cast<uintptr_t>(sl) % 2 == 0) &&
+                     (reinterpret_cast<uintptr_t>(ss) % 2 == 0);
+  if (pairs) {
+    nvfp4_quantize_kernel<T, 2><<<grid_for(a->rows * kblocks / 2, 256), 256, 0, stream>>>(
+        x, a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, amax, a->tensor_scale);
+  } else {
+    nvfp4_quantize_kernel<T, 1><<<grid_for(a->rows * kblocks, 256), 256, 0, stream>>>(
+        x, a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, amax, a->tensor_scale);
+  }
+}
+
 extern "C" int b200k_nvfp4_quantize(const b200k_quantize_args* a, b200k_stream stream_) {
   if (a == nullptr) return fail(B200K_INVALID_ARG, "null args");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -468,7 +587,7 @@ extern "C" int b200k_nvfp4_quantize(const b200k_quantize_args* a, b200k_stream s
   uint32_t* amax = static_cast<uint32_t*>(a->scratch);
   cudaError_t e = cudaMemsetAsync(amax, 0, sizeof(uint32_t), stream);
   if (e != cudaSuccess) return fail(B200K_CUDA_ERROR, "memset: %s", cudaGetErrorString(e));
-  const int grid_r = grid_for(a->rows * a->k / 4, 256);
+  const int grid_r = grid_for(a->rows * a->k / 16, 256);
   const int grid_q = grid_for(a->rows * kblocks, 256);
   uint8_t* q = static_cast<uint8_t*>(a->q);
   uint8_t* sl = static_cast<uint8_t*>(a->sf_logical);
@@ -476,9 +595,7 @@ extern "C" int b200k_nvfp4_quantize(const b200k_quantize_args* a, b200k_stream s
 #define B200K_NVFP4_CASE(T)                                                                       \
   absmax_kernel<T><<<grid_r, 256, 0, stream>>>(static_cast<const T*>(a->x), a->rows, a->k, a->ldx, \
                                                amax);                                             \
-  nvfp4_quantize_kernel<T><<<grid_q, 256, 0, stream>>>(static_cast<const T*>(a->x), a->rows, a->k, \
-                                                       a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms,  \
-                                                       amax, a->tensor_scale)
+  launch_nvfp4_quantize<T>(a, amax, stream)
   switch (a->x_dtype) {
     case B200K_F32: B200K_NVFP4_CASE(float); break;
     case B200K_BF16: B200K_NVFP4_CASE(__nv_bfloat16); break;
@@ -516,9 +633,7 @@ extern "C" int b200k_nvfp4_quantize_noalloc(const b200k_quantize_args* a, b200k_
   absmax_slab_kernel<T><<<static_cast<int>(slabs), 256, 0, stream>>>(                             \
       static_cast<const T*>(a->x), a->rows, a->k, a->ldx, slots);                                 \
   fold_slots_kernel<<<1, 256, 0, stream>>>(slots, static_cast<int>(slabs));                       \
-  nvfp4_quantize_kernel<T><<<grid_q, 256, 0, stream>>>(static_cast<const T*>(a->x), a->rows, a->k, \
-                                                       a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms,  \
-                                                       slots, a->tensor_scale)
+  launch_nvfp4_quantize<T>(a, slots, stream)
   switch (a->x_dtype) {
     case B200K_F32: B200K_NVFP4_NOALLOC_CASE(float); break;
     case B200K_BF16: B200K_NVFP4_NOALLOC_CASE(__nv_bfloat16); break;

@@ -187,7 +187,8 @@ int b200k_mxfp8_quantize(const b200k_quantize_args* args, b200k_stream stream);
  * round-to-nearest operations:
  *   s_t   = amax(x) / 2688                      (448 * 6)
  *   s_blk = rn_e4m3(amax_blk / (6 * s_t))       one per 16 elements, 0 for a zero block
- *   q     = rn_e2m1(x / (f32(s_blk) * s_t))     ties to even, saturating at +-6
+ *   q     = rn_e2m1(x * rn(1 / d)), d = f32(s_blk) * s_t   ties to even, saturating at +-6
+ *           (product and reciprocal each rounded to fp32; x / d when d is subnormal)
  * x ~= q * s_blk * s_t.  Byte i of a row holds elements 2i (low nibble) and 2i+1. */
 int b200k_nvfp4_quantize(const b200k_quantize_args* args, b200k_stream stream);
 

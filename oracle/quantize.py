@@ -86,8 +86,13 @@ def nvfp4_quantize_ref(x: torch.Tensor):
         r = np.where((amax_b > 0) & (six_st > 0), (amax_b / six_st).astype(f32), f32(0))
     sf = formats.e4m3_encode_rne(np.minimum(r, f32(448.0)))
     denom = (formats.e4m3_decode(sf).astype(f32) * s_t).astype(f32)
-    with np.errstate(divide="ignore", invalid="ignore"):
-        y = np.where(denom[..., None] > 0, (blocks / denom[..., None]).astype(f32), f32(0))
+    # x / denom evaluated as x * (1 / denom), each step rounded to fp32 (one reciprocal per
+    # block); a subnormal denom, whose reciprocal overflows, keeps the division
+    normal = denom >= np.finfo(f32).tiny
+    with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
+        inv = np.where(normal, (f32(1.0) / denom).astype(f32), f32(0))
+        y = np.where(normal[..., None], (blocks * inv[..., None]).astype(f32),
+                     np.where(denom[..., None] > 0, (blocks / denom[..., None]).astype(f32), f32(0)))
     codes = formats.e2m1_encode_rne(y).reshape(rows, -1)[:, :k]
     return formats.e2m1_pack(codes), sf, s_t
 
