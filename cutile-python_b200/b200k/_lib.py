@@ -61,6 +61,7 @@ class BlockScaledGemmArgs(Structure):
         ("tile_group", c_void_p), ("num_row_tiles", c_void_p),
         ("row_map", c_void_p), ("row_scale", c_void_p), ("c_rows", c_int64),
         ("tile_rows", c_int32),
+        ("c_sf", c_void_p), ("c_sf_k_atoms", c_int64),
     ]
 
 

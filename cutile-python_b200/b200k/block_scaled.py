@@ -159,7 +159,7 @@ def nvfp4_quantize(x: torch.Tensor, *, swizzled_scale: bool = True):
 
 
 def _scaled_gemm(a_km, sfa, b_nk, sfb, c, *, fp4: bool, alpha: float = 1.0, alpha_a=None,
-                 alpha_b=None, max_ctas: int = 0, row_scale=None):
+                 alpha_b=None, max_ctas: int = 0, row_scale=None, c_sf=None):
     """a_km (M, Kp), b_nk (N, Kp) K-contiguous byte tensors (Kp = K or K/2 bytes);
     sfa/sfb swizzled 4-D byte tensors."""
     m, kp = a_km.shape
@@ -182,6 +182,8 @@ def _scaled_gemm(a_km, sfa, b_nk, sfb, c, *, fp4: bool, alpha: float = 1.0, alph
     args.alpha_b = _lib.ptr(alpha_b)
     args.max_ctas = max_ctas
     args.row_scale = _lib.ptr(row_scale)
+    if c_sf is not None:
+        args.c_sf, args.c_sf_k_atoms = c_sf.data_ptr(), c_sf.shape[1]
     with torch.cuda.device(c.device):
         _lib.check(_lib.lib().b200k_block_scaled_gemm(ctypes.byref(args), _lib.stream_ptr(c.device)))
     return c
@@ -205,7 +207,9 @@ def cutile_block_scaled_matmul(A: torch.Tensor, A_scale: torch.Tensor, B: torch.
     elements of K.  A is (M, K); B is (K, N) (normally the transposed view of an (N, K)
     tensor); scales are 2-D logical ((M, K/32) and (K/32, N)) or 4-D swizzle_32_4_4
     tensors (B's swizzled over (N, K/32)).  The reference returns fp32; ``out_dtype``
-    selects bf16/fp16 instead.
+    selects bf16/fp16 instead, and ``torch.float8_e4m3fn`` returns the pair (C quantised to
+    MXFP8 in the epilogue, its swizzled scales): bit for bit
+    ``block_quantize(C_bf16, 32, swizzled_scale=True)`` of the bf16 result.
     """
     if A.shape[1] != B.shape[0]:
         raise ValueError(f"Incompatible matrices: K dimension of A ({A.shape[1]}) "
@@ -231,14 +235,26 @@ def cutile_block_scaled_matmul(A: torch.Tensor, A_scale: torch.Tensor, B: torch.
         raise ValueError(f"swizzled A_scale must be {swizzled_shape(m, kblocks)}")
     if tuple(B_scale.shape) != swizzled_shape(n, kblocks):
         raise ValueError(f"swizzled B_scale must be {swizzled_shape(n, kblocks)}")
+    a_km = _k_major(A)
+    b_nk = _k_major(B.T)
+    if out_dtype == torch.float8_e4m3fn and C is None:
+        # quantise in the epilogue: the product comes back as an MXFP8 operand
+        # (e4m3 (M, N), swizzled ue8m0 scales over (M, N / 32)) for a GEMM chained on N
+        if n % 32 or m == 0 or n == 0 or k == 0:
+            raise ValueError("quantised output needs non-empty operands and N a multiple of 32")
+        C = torch.empty((m, n), device=A.device, dtype=torch.float8_e4m3fn)
+        shape = swizzled_shape(m, n // 32)
+        C_sf = (torch.zeros if (m % 128 or (n // 32) % 4) else torch.empty)(shape, dtype=torch.uint8,
+                                                                           device=A.device)
+        _scaled_gemm(a_km, _as_u8(A_scale).contiguous(), b_nk, _as_u8(B_scale).contiguous(), C,
+                     fp4=False, c_sf=C_sf)
+        return C, C_sf.view(torch.float8_e8m0fnu)
     if C is None:
         C = torch.empty((m, n), device=A.device, dtype=out_dtype)
     if m == 0 or n == 0:
         return C
     if k == 0:
         return C.zero_()
-    a_km = _k_major(A)
-    b_nk = _k_major(B.T)
     return _scaled_gemm(a_km, _as_u8(A_scale).contiguous(), b_nk, _as_u8(B_scale).contiguous(), C,
                         fp4=False)
 

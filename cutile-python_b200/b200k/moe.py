@@ -239,7 +239,9 @@ def _quantize_rows(x, *, rows, gather=None, divisor=1, num_blocks=None, tile=ROW
 
 
 def _grouped_scaled_gemm(a_q, a_sf, w_q, w_sf, c, expert_ids, *, num_blocks, row_map=None,
-                         row_scale=None, c_rows=0, swiglu=False, tile=ROW_TILE):
+                         row_scale=None, c_rows=0, swiglu=False, tile=ROW_TILE, c_sf=None):
+    """`c` of dtype float8_e4m3fn together with `c_sf` (swizzled scale bytes) asks for the
+    quantise-in-epilogue form: the result leaves the GEMM as an MXFP8 operand."""
     mp, k = a_q.shape
     e, n, _ = w_q.shape
     args = _lib.BlockScaledGemmArgs()
@@ -259,6 +261,8 @@ def _grouped_scaled_gemm(a_q, a_sf, w_q, w_sf, c, expert_ids, *, num_blocks, row
     args.row_scale = _lib.ptr(row_scale)
     args.c_rows = c_rows
     args.tile_rows = tile
+    if c_sf is not None:
+        args.c_sf, args.c_sf_k_atoms = c_sf.data_ptr(), c_sf.shape[1]
     with torch.cuda.device(c.device):
         _lib.check(_lib.lib().b200k_block_scaled_gemm(ctypes.byref(args), _lib.stream_ptr(c.device)))
     return c
@@ -285,10 +289,18 @@ def cutile_moe_mxfp8(hidden_states: torch.Tensor, w1_q: torch.Tensor, w1_sf: tor
     cap = sorted_ids.numel()
     a_q, a_sf = _quantize_rows(x, rows=cap, gather=sorted_ids, divisor=topk, num_blocks=num_blocks,
                                tile=tile)
-    act = torch.empty((cap, inter), dtype=dtype, device=dev)
-    _grouped_scaled_gemm(a_q, a_sf, w1_q, _as_u8(w1_sf), act, expert_ids, num_blocks=num_blocks,
-                         swiglu=True, tile=tile)
-    act_q, act_sf = _quantize_rows(act, rows=cap, num_blocks=num_blocks, tile=tile)
+    if tile == 256 and dtype == torch.bfloat16 and os.environ.get("B200K_MOE_FUSED_QUANT") != "0":
+        # the gate/up GEMM quantises its SiLU-and-multiply output in the epilogue: the
+        # activation never exists as a 16-bit tensor in memory (same bytes as the two-step form)
+        act_q = torch.empty((cap, inter), dtype=torch.float8_e4m3fn, device=dev)
+        act_sf = torch.empty(swizzled_shape(cap, inter // 32), dtype=torch.uint8, device=dev)
+        _grouped_scaled_gemm(a_q, a_sf, w1_q, _as_u8(w1_sf), act_q, expert_ids, num_blocks=num_blocks,
+                             swiglu=True, tile=tile, c_sf=act_sf)
+    else:
+        act = torch.empty((cap, inter), dtype=dtype, device=dev)
+        _grouped_scaled_gemm(a_q, a_sf, w1_q, _as_u8(w1_sf), act, expert_ids, num_blocks=num_blocks,
+                             swiglu=True, tile=tile)
+        act_q, act_sf = _quantize_rows(act, rows=cap, num_blocks=num_blocks, tile=tile)
     per_replica = torch.empty((tokens * topk, hidden), dtype=dtype, device=dev)
     _grouped_scaled_gemm(act_q, act_sf, w2_q, _as_u8(w2_sf), per_replica, expert_ids,
                          num_blocks=num_blocks, row_map=sorted_ids,

@@ -673,6 +673,16 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
   p.status = device_status_word();
   const bool grouped = a->tile_group != nullptr;
   if (grouped) p.batch = 1;
+  const bool mx_out = a->c_dtype == B200K_E4M3;
+  if (mx_out) {
+    const int64_t n_out = a->epilogue == B200K_EPI_SWIGLU ? a->n / 2 : a->n;
+    if (fp4 || a->c_sf == nullptr || a->row_map != nullptr || n_out % 32 != 0 ||
+        a->c_sf_k_atoms < ceil_div(n_out, 128))
+      return fail(B200K_UNSUPPORTED, "quantised (e4m3 + ue8m0) output needs MXFP8 operands, c_sf with "
+                  "c_sf_k_atoms >= ceil(N_out / 128), N_out a multiple of 32 and no row_map");
+    p.c_sf = static_cast<uint8_t*>(a->c_sf);
+    p.c_sf_k_atoms = static_cast<int>(a->c_sf_k_atoms);
+  }
 
   CUtensorMap ta, tb;
   const uint64_t a_batches = grouped ? 1 : a->batch;
@@ -718,6 +728,9 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
     const CUtensorMap maps[4] = {ta, tb, tsa, tsb};
     return launch_gemm_pair(fp4 ? kKindNVF4 : kKindMXF8, a->c_dtype, maps, pp, sms, stream);
   }
+  if (mx_out)
+    return fail(B200K_UNSUPPORTED, "quantised output is produced by the CTA-pair kernel only (plain "
+                "problems, or grouped ones with tile_rows = 256)");
   if (grouped && a->tile_rows != 0 && a->tile_rows != 128)
     return fail(B200K_UNSUPPORTED, "tile_rows %d is not available for this grouped problem: "
                 "tile_group entries are per 128 rows on the one-CTA kernel", a->tile_rows);

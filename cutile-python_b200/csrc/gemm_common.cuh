@@ -12,7 +12,8 @@ constexpr int kGroupM = 8;
 constexpr int kNumThreads = 192;
 constexpr int kTmemCols = 512;
 
-enum OutType : int { kOutF16 = 0, kOutBF16 = 1, kOutF32 = 2 };
+enum OutType : int { kOutF16 = 0, kOutBF16 = 1, kOutF32 = 2,
+                     kOutMX8 = 3 /* e4m3 + swizzled ue8m0 scale per 32 columns (CTA-pair kernel) */ };
 
 struct GemmParams {
   void* c;
@@ -45,6 +46,8 @@ struct GemmParams {
   const float* row_scale;
   int64_t c_rows;
   int epilogue;
+  uint8_t* c_sf;        // kOutMX8: swizzled scales of the output
+  int c_sf_k_atoms;
   int* status;
 };
 

@@ -27,6 +27,7 @@
 // columns first and releases them early; the next tile's first MMA waits only for that.
 #include "gemm_common.cuh"
 #include "gemm_pair.h"
+#include "mx_quant.cuh"
 
 namespace b200k {
 
@@ -354,7 +355,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     float alpha = p.alpha;
     if (p.alpha_a != nullptr) alpha *= *p.alpha_a;
     if (p.alpha_b != nullptr) alpha *= *p.alpha_b;
-    const int elem_bytes = (OUT == kOutF32) ? 4 : 2;
+    const int elem_bytes = (OUT == kOutF32) ? 4 : (OUT == kOutMX8 ? 1 : 2);
     const bool vec_ok = ((p.ldc * elem_bytes) % 16 == 0) && ((p.stride_c * elem_bytes) % 16 == 0) &&
                         (reinterpret_cast<uintptr_t>(p.c) % 16 == 0);
     const uint32_t lead_ovl = map_to_cta(ovl_free_bar, 0);
@@ -403,6 +404,26 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster_relaxed(lead_ovl);
+      // kOutMX8: the 32 columns of a chunk are one MX block of the row.  The values are
+      // first rounded to bf16, so the bytes equal those of writing a bf16 tensor and
+      // running the MXFP8 quantiser over it.
+      auto store_mx = [&](int col, float (&v)[32]) {
+        if constexpr (OUT == kOutMX8) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __bfloat162float(__float2bfloat16_rn(v[i]));
+          uint32_t pk[8];
+          const uint8_t sf = mx_quantize_block32(v, pk);
+          uint8_t* dst = c_row + col;
+          if (vec_ok) {
+            reinterpret_cast<uint4*>(dst)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            reinterpret_cast<uint4*>(dst)[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) dst[i] = (pk[i >> 2] >> (8 * (i & 3))) & 0xff;
+          }
+          p.c_sf[swizzled_sf_offset(out_row, col >> 5, p.c_sf_k_atoms)] = sf;
+        }
+      };
       if (!swiglu) {
         const int n0 = tc.pid_n * bn;
         const int chunks = bn / 32;
@@ -411,7 +432,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             float v[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * scale;
-            store_row_chunk<OUT>(c_row, n0 + c * 32, p.n, v, vec_ok);
+            if constexpr (OUT == kOutMX8) store_mx(n0 + c * 32, v);
+            else store_row_chunk<OUT>(c_row, n0 + c * 32, p.n, v, vec_ok);
           }
         };
         if constexpr (Cfg::kOverlapChunks > 0) {
@@ -449,7 +471,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               v[i] = silu(__uint_as_float(g[i]) * scale) * (__uint_as_float(u[i]) * scale);
-            store_row_chunk<OUT>(c_row, n0 + c * 32, n_out, v, vec_ok);
+            if constexpr (OUT == kOutMX8) store_mx(n0 + c * 32, v);
+            else store_row_chunk<OUT>(c_row, n0 + c * 32, n_out, v, vec_ok);
           }
         }
       }
@@ -501,6 +524,9 @@ int launch_pair_out(int out, const CUtensorMap* maps, const GemmParams& p, int g
     case B200K_F16: return launch_pair<KIND, kOutF16>(maps, p, grid, stream);
     case B200K_BF16: return launch_pair<KIND, kOutBF16>(maps, p, grid, stream);
     case B200K_F32: return launch_pair<KIND, kOutF32>(maps, p, grid, stream);
+    case B200K_E4M3:
+      if constexpr (KIND == kKindMXF8) return launch_pair<KIND, kOutMX8>(maps, p, grid, stream);
+      return fail(B200K_UNSUPPORTED, "quantised output is available for MXFP8 operands only");
     default: return fail(B200K_INVALID_ARG, "unsupported output dtype %d", out);
   }
 }

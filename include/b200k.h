@@ -145,6 +145,14 @@ typedef struct {
   const float* row_scale;
   int64_t c_rows;
   int32_t tile_rows;                     /* as in b200k_gemm_args */
+  /* c_dtype B200K_E4M3 (MXFP8 operands, CTA-pair kernel): the result is rounded to bf16 and
+   * quantised in the epilogue exactly as b200k_mxfp8_quantize would quantise that bf16
+   * tensor: e4m3 bytes to `c` (ldc in bytes), one ue8m0 scale per 32 output columns to
+   * `c_sf` in the swizzle_32_4_4 layout with `c_sf_k_atoms` atoms along N.  This is the
+   * quantise-in-epilogue step between chained block-scaled GEMMs (reference pattern:
+   * experimental/cuda-lang/tutorial/nvfp4_gemm_2_quantize_fp4.py:136-192). */
+  void* c_sf;
+  int64_t c_sf_k_atoms;
 } b200k_block_scaled_gemm_args;
 
 int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* args, b200k_stream stream);

@@ -154,3 +154,21 @@ def test_mxfp8_sampled_rows_at_full_size(device_ok):
     want = adeq @ bsum
     got = c.float().sum(1)
     torch.testing.assert_close(got, want, atol=0.02 * float(want.abs().max()), rtol=2e-2)
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (384, 640, 512), (1000, 96, 160)])
+def test_quantise_in_epilogue_equals_two_steps(m, n, k, device_ok):
+    # e4m3 output + swizzled scales straight from the GEMM epilogue == quantising the bf16 result
+    g = torch.Generator().manual_seed(m + n)
+    a = torch.randn(m, k, generator=g).bfloat16().cuda()
+    b = torch.randn(n, k, generator=g).bfloat16().cuda()
+    aq, sa = b200k.block_quantize(a, 32, swizzled_scale=True)
+    bq, sb = b200k.block_quantize(b, 32, swizzled_scale=True)
+    c_bf16 = b200k.cutile_block_scaled_matmul(aq, sa, bq.T, sb, out_dtype=torch.bfloat16)
+    q_ref, s_ref = b200k.block_quantize(c_bf16, 32, swizzled_scale=True)
+    q, s = b200k.cutile_block_scaled_matmul(aq, sa, bq.T, sb, out_dtype=torch.float8_e4m3fn)
+    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+    # scale atoms: compare the bytes that belong to real rows / blocks
+    lo = oracle.unswizzle_32_4_4_ref(s.cpu().view(torch.uint8))[:m, : n // 32]
+    lo_ref = oracle.unswizzle_32_4_4_ref(s_ref.cpu().view(torch.uint8))[:m, : n // 32]
+    assert torch.equal(lo, lo_ref)
