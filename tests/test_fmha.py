@@ -88,6 +88,19 @@ def test_fmha_decode_mid_sequence_position(device_ok):
     torch.testing.assert_close(out.float().cpu(), ref, **TOL)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("sq,sk", [(257, 257), (640, 640), (300, 1000), (1024, 2048 + 17), (384, 64)])
+def test_fmha_long_rows_head_dim_128(dtype, causal, sq, sk, device_ok):
+    # several key steps per query tile, ragged tails in both directions, grouped-query heads
+    q, k, v = _qkv(2, 4, 2, sq, sk, 128, dtype, sq * 3 + sk)
+    input_pos = sk - sq if (causal and sk > sq) else 0
+    out = b200k.cutile_fmha(q.cuda(), k.cuda(), v.cuda(), causal=causal, input_pos=input_pos,
+                            query_group_size=2)
+    ref = oracle.fmha_ref(q, k, v, causal=causal, input_pos=input_pos, query_group_size=2)
+    torch.testing.assert_close(out.float().cpu(), ref, **TOL)
+
+
 def test_fmha_bshd_storage_and_scale(device_ok):
     # (B, S, H, D) storage viewed as (B, H, S, D), explicit scale
     g = torch.Generator().manual_seed(5)
