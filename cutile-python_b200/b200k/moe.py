@@ -39,9 +39,11 @@ def _cdiv(a: int, b: int) -> int:
     return (a + b - 1) // b
 
 
-def moe_align_device(topk_ids: torch.Tensor, tile_m: int, num_experts: int):
+def moe_align_device(topk_ids: torch.Tensor, tile_m: int, num_experts: int, *,
+                     want_expert_ids: bool = True):
     """Device-side alignment.  Returns (sorted_token_ids [capacity] int32,
-    sorted_expert_ids [capacity / tile_m] int32, num_blocks int32 device scalar)."""
+    sorted_expert_ids [capacity / tile_m] int32 (None when not wanted), num_blocks int32
+    device scalar)."""
     if topk_ids.dim() != 2:
         raise ValueError("topk_ids must be (num_tokens, topk)")
     if not topk_ids.is_cuda:
@@ -53,13 +55,13 @@ def moe_align_device(topk_ids: torch.Tensor, tile_m: int, num_experts: int):
     blocks = _cdiv(total + num_experts * (tile_m - 1), tile_m)
     dev = ids.device
     sorted_ids = torch.empty(blocks * tile_m, dtype=torch.int32, device=dev)
-    expert_ids = torch.empty(blocks, dtype=torch.int32, device=dev)
+    expert_ids = torch.empty(blocks, dtype=torch.int32, device=dev) if want_expert_ids else None
     num_blocks = torch.empty(1, dtype=torch.int32, device=dev)
     ws_bytes = _lib.lib().b200k_moe_align_workspace_bytes(total, num_experts)
     ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
     a = _lib.MoeAlignArgs()
     a.topk_ids = ids.data_ptr()
-    a.sorted_token_ids, a.sorted_expert_ids = sorted_ids.data_ptr(), expert_ids.data_ptr()
+    a.sorted_token_ids, a.sorted_expert_ids = sorted_ids.data_ptr(), _lib.ptr(expert_ids)
     a.num_blocks, a.workspace, a.workspace_bytes = num_blocks.data_ptr(), ws.data_ptr(), ws.numel()
     a.num_replicas, a.capacity, a.block_capacity = total, sorted_ids.numel(), blocks
     a.num_experts, a.tile_m = num_experts, tile_m

@@ -33,6 +33,8 @@ def exchange(tensors, send_counts: list[int], group=None):
     """all_to_all_single of several row-aligned tensors with the same split sizes.
     Returns (received tensors, recv_counts)."""
     world = dist.get_world_size(group)
+    if world == 1:   # everything stays here: no copy, no collective, no host round trip
+        return list(tensors), list(send_counts)
     dev = tensors[0].device
     sc = torch.tensor(send_counts, dtype=torch.int64, device=dev)
     rc = torch.empty(world, dtype=torch.int64, device=dev)
@@ -80,7 +82,9 @@ class ExpertParallelMoE:
         n = rows.shape[0]
         hidden = rows.shape[1]
         inter = self.w2.shape[2]
-        y = torch.zeros((n, hidden), dtype=rows.dtype, device=rows.device)
+        # every received row is routed to exactly one local expert, so the scatter of the
+        # down projection writes every row of y
+        y = torch.empty((n, hidden), dtype=rows.dtype, device=rows.device)
         if n == 0:
             return y
         tile = moe._moe_tile()
@@ -109,7 +113,7 @@ class ExpertParallelMoE:
         flat_ids = topk_ids.reshape(-1)
         if cuda:
             from . import moe
-            order32, _, _ = moe.moe_align_device(topk_ids, 1, self.num_experts)
+            order32, _, _ = moe.moe_align_device(topk_ids, 1, self.num_experts, want_expert_ids=False)
             order = order32.long()
             counts = torch.bincount(flat_ids, minlength=self.num_experts)
             x = hidden_states if hidden_states.stride(1) == 1 else hidden_states.contiguous()
@@ -138,6 +142,8 @@ class ExpertParallelMoE:
 
 def exchange_back(t: torch.Tensor, send_counts: list[int], recv_counts: list[int], group=None):
     """The reverse all-to-all of `exchange` (split sizes already known on both sides)."""
+    if dist.get_world_size(group) == 1:
+        return (t,), recv_counts
     r = torch.empty((sum(recv_counts),) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
     dist.all_to_all_single(r, t.contiguous(), output_split_sizes=recv_counts,
                            input_split_sizes=send_counts, group=group)

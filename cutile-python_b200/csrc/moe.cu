@@ -111,18 +111,25 @@ moe_offsets_kernel(int* __restrict__ counts, int num_chunks, int num_experts, in
       run += v;
     }
   }
-  // expert id of every tile_m block, -1 beyond the blocks in use
-  for (int64_t b = threadIdx.x; b < block_capacity; b += blockDim.x) {
-    int owner = -1;
-    if (b < total_blocks) {
-      // experts are few: linear search of the run that holds block b
-      const int slot = static_cast<int>(b) * tile_m;
-      for (int e = 0; e < num_experts; ++e) {
-        const int padded = (totals[e] + tile_m - 1) / tile_m * tile_m;
-        if (slot >= starts[e] && slot < starts[e] + padded) { owner = e; break; }
+  // expert id of every tile_m block, -1 beyond the blocks in use (skipped when the caller
+  // only wants the sorted order): binary search of the padded run that holds the block
+  if (sorted_expert_ids != nullptr) {
+    for (int64_t b = threadIdx.x; b < block_capacity; b += blockDim.x) {
+      int owner = -1;
+      if (b < total_blocks) {
+        const int slot = static_cast<int>(b) * tile_m;
+        int lo = 0, hi = num_experts - 1;   // last expert whose run starts at or before slot
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (starts[mid] <= slot) lo = mid; else hi = mid - 1;
+        }
+        // runs of experts without replicas are empty and share their start with the next
+        // run: the owner is the last expert among them that has rows
+        while (lo > 0 && totals[lo] == 0) --lo;
+        owner = lo;
       }
+      sorted_expert_ids[b] = owner;
     }
-    sorted_expert_ids[b] = owner;
   }
   // sentinels: the padding tail of every run and everything beyond the last block
   for (int e = 0; e < num_experts; ++e) {
@@ -280,7 +287,7 @@ extern "C" int b200k_moe_align(const b200k_moe_align_args* a, b200k_stream strea
     return fail(B200K_INVALID_ARG, "bad sizes");
   if (a->num_experts > 2048) return fail(B200K_UNSUPPORTED, "at most 2048 experts");
   if (a->num_replicas >= INT32_MAX) return fail(B200K_UNSUPPORTED, "too many token replicas");
-  if (!a->sorted_token_ids || !a->sorted_expert_ids || !a->num_blocks || !a->workspace)
+  if (!a->sorted_token_ids || !a->num_blocks || !a->workspace)
     return fail(B200K_INVALID_ARG, "null pointer");
   if (a->num_replicas > 0 && !a->topk_ids) return fail(B200K_INVALID_ARG, "null topk_ids");
   // worst case: every expert wastes tile_m - 1 slots

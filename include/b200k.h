@@ -236,7 +236,7 @@ int b200k_sf_swizzle(const void* sf, int64_t rows, int64_t kblocks, int64_t ld, 
 typedef struct {
   const void* topk_ids;        /* (num_replicas) int32 or int64 expert ids */
   int32_t* sorted_token_ids;   /* [capacity] */
-  int32_t* sorted_expert_ids;  /* [block_capacity] */
+  int32_t* sorted_expert_ids;  /* [block_capacity]; NULL when only the sorted order is wanted */
   int32_t* num_blocks;         /* device scalar */
   void* workspace;             /* b200k_moe_align_workspace_bytes() bytes of device memory */
   int64_t workspace_bytes;
