@@ -4,7 +4,7 @@ Importing this package needs only torch; the first operator call loads
 ``libb200k.so`` (built by ``cutile-python_b200/build.py``) and raises if it is missing.
 """
 from ._lib import B200KError, device_status, raise_on_device_error  # noqa: F401
-from .matmul import (bmm, cutile_batch_matmul, cutile_matmul,  # noqa: F401
+from .matmul import (bmm, cutile_batch_matmul, cutile_group_matmul, cutile_matmul,  # noqa: F401
                      cutile_persistent_matmul)
 from .block_scaled import (block_quantize, cutile_block_scaled_matmul,  # noqa: F401
                            cutile_nvfp4_matmul, cutile_swizzled_scaled_matmul, nvfp4_quantize,

@@ -4,6 +4,7 @@ cutile_matmul            samples/MatMul.py:179-251
 bmm                      samples/BatchMatMul.py:53-92
 cutile_persistent_matmul test/bench_matmul.py:396-410 (bench form, output passed in)
 cutile_batch_matmul      test/bench_matmul.py:323-329 (bench form)
+cutile_group_matmul      the list-of-problems form of test/kernels/group_gemm.py:10-38
 
 All of them run the tcgen05 GEMM behind ``b200k_gemm``; tile sizes are fixed by the
 kernel (128 x 256 x one 128-byte K atom), so the reference's tile-size choice by dtype
@@ -160,3 +161,52 @@ def cutile_batch_matmul(bs: int, A: torch.Tensor, B: torch.Tensor, C: torch.Tens
         raise ValueError("batch size does not match A")
     _validate(A, B)
     return _gemm(A, B, C)
+
+
+def cutile_group_matmul(As, Bs, Cs=None):
+    """Cs[g] = As[g] @ Bs[g] for a list of independent problems of any shapes
+    (grouped_matmul_kernel, test/kernels/group_gemm.py:10-38, which walks the tiles of all
+    problems with one persistent grid).  Here every problem is one launch of the GEMM;
+    problems too small to fill the GPU are spread over a few side streams so that they
+    overlap, and the caller's stream waits for all of them."""
+    if len(As) != len(Bs) or (Cs is not None and len(Cs) != len(As)):
+        raise ValueError("As, Bs and Cs must list the same number of problems")
+    if Cs is None:
+        Cs = [torch.empty((a.shape[0], b.shape[1]), device=a.device, dtype=a.dtype) for a, b in zip(As, Bs)]
+    if not As:
+        return Cs
+    for a, b, c in zip(As, Bs, Cs):
+        _validate(a, b)
+        if c.shape != (a.shape[0], b.shape[1]):
+            raise ValueError("output shape does not match its problem")
+    dev = As[0].device
+    main = torch.cuda.current_stream(dev)
+    small = [g for g, (a, b) in enumerate(zip(As, Bs))
+             if -(-a.shape[0] // 256) * -(-b.shape[1] // 256) < 64 and a.shape[0] and b.shape[1] and a.shape[1]]
+    side = _side_streams(dev, min(4, len(small))) if len(small) > 1 else []
+    for st in side:
+        st.wait_stream(main)
+    for i, (a, b, c) in enumerate(zip(As, Bs, Cs)):
+        if c.numel() == 0:
+            continue
+        if a.shape[1] == 0:
+            c.zero_()
+            continue
+        if side and i in small:
+            with torch.cuda.stream(side[small.index(i) % len(side)]):
+                _gemm(a, b, c)
+        else:
+            _gemm(a, b, c)
+    for st in side:
+        main.wait_stream(st)
+    return Cs
+
+
+_SIDE_STREAMS: dict = {}
+
+
+def _side_streams(dev, n: int):
+    pool = _SIDE_STREAMS.setdefault(dev, [])
+    while len(pool) < n:
+        pool.append(torch.cuda.Stream(dev))
+    return pool[:n]

@@ -117,6 +117,23 @@ def test_pair_kernel_fp8_row_major_b(device_ok):
     torch.testing.assert_close(c.cpu(), torch.bmm(a.float(), b.float()), atol=1e-3, rtol=1e-3)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("mnk", [[(4, 4, 8)], [(2, 4, 8), (8, 6, 8), (12, 16, 8)],
+                                 [(300, 200, 64), (1024, 2048, 512), (8, 8, 4096), (64, 640, 72)]])
+def test_group_matmul_list_of_problems(dtype, mnk, device_ok):
+    # shapes of test/test_group_gemm.py (K raised to the 16-byte row pitch of fp16) and larger ones
+    As = [_rand((m, k), dtype, 20 + i) for i, (m, n, k) in enumerate(mnk)]
+    Bs = [_rand((k, n), dtype, 40 + i) for i, (m, n, k) in enumerate(mnk)]
+    Cs = b200k.cutile_group_matmul([a.cuda() for a in As], [b.cuda() for b in Bs])
+    for a, b, c, (m, n, k) in zip(As, Bs, Cs, mnk):
+        tol = dict(TOL[dtype])
+        if dtype == torch.float32:
+            tol["atol"] = max(tol["atol"], 6e-3 * k ** 0.5)
+        else:
+            tol["atol"] = max(tol["atol"], 2e-3 * k ** 0.5)
+        torch.testing.assert_close(c.float().cpu(), oracle.matmul_ref(a, b), **tol)
+
+
 def test_all_ones_known_answer(device_ok):
     # mma of all-ones tiles: every output equals K
     a = torch.ones(128, 448, dtype=torch.float16, device="cuda")
