@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload mxfp8_gemm|nvfp4_gemm|dense_f16|ag_nvfp4_gemm|moe_ep_bf16|ref_shapes|
-                                fmha_causal|moe_bf16|moe_mxfp8|mxfp8_quantize]
+                                fmha_causal|moe_bf16|moe_mxfp8|mxfp8_quantize|nvfp4_quantize]
 
 One step = one pass of the workload's kernel over one batch of seeded synthetic input.
 The default workload is the headline configuration: MXFP8 GEMM, M = N = K = 8192, e4m3 operands
@@ -566,6 +566,46 @@ class Mxfp8Quantize(Workload):
                 "l2": f"{self.sets} rotating inputs of 128 MiB each (> 126 MiB L2)"}
 
 
+class Nvfp4Quantize(Mxfp8Quantize):
+    """bf16 8192 x 8192 -> packed e2m1 + swizzled ue4m3 scales + fp32 tensor scale.  Two kernels
+    (tensor maximum, then the quantiser), so the input is read twice: HBM-bound."""
+    name = "nvfp4_quantize_bf16_8192x8192"
+    dtype = "bf16 -> e2m1 + ue4m3 / 16 + fp32 tensor scale"
+    launches_per_step = 3   # memset of the maximum, absmax, quantise
+
+    def algorithmic_bytes(self):
+        # the input twice (maximum, then values), codes, scales
+        return 2 * self.M * self.K * 2 + self.M * self.K // 2 + self.M * self.K // 16
+
+    def step(self):
+        x = self.xs[self.i % self.sets]
+        self.i += 1
+        return self.b200k.nvfp4_quantize(x)
+
+    def setup_e2e(self, device):
+        self.host_in = [self.xs[0].cpu().pin_memory()]
+        q, s, t = self.step()
+        self.host_out = [torch.empty_like(q.view(torch.uint8), device="cpu").pin_memory(),
+                         torch.empty_like(s.view(torch.uint8), device="cpu").pin_memory()]
+        self.h2d = self.host_in[0].numel() * 2
+        self.d2h = sum(t.numel() for t in self.host_out)
+
+    def step_e2e(self):
+        self.xs[0].copy_(self.host_in[0], non_blocking=True)
+        q, s, _ = self.b200k.nvfp4_quantize(self.xs[0])
+        self.host_out[0].copy_(q.view(torch.uint8), non_blocking=True)
+        self.host_out[1].copy_(s.view(torch.uint8), non_blocking=True)
+
+    def cpu_step(self, s):
+        return self.oracle.nvfp4_quantize_ref(self.cpu_ops[0][:s])
+
+    def cpu_flops(self, s):
+        return float(s * self.K * 4 + s * self.K // 2 + s * self.K // 16)
+
+    def cpu_sample_desc(self, s):
+        return f"{s} rows of {self.K} bf16 values through the NVFP4 quantiser's restatement (numpy CPU)"
+
+
 class DenseF16(Mxfp8Gemm):
     """The sample-sized dense fp16 matmul (2048 cubed)."""
     name = "dense_f16_gemm_2048x2048x2048"
@@ -625,7 +665,8 @@ class DenseF16(Mxfp8Gemm):
 
 WORKLOADS = {"mxfp8_gemm": Mxfp8Gemm, "nvfp4_gemm": Nvfp4Gemm, "dense_f16": DenseF16,
              "ag_nvfp4_gemm": AgNvfp4Gemm, "moe_ep_bf16": MoeEpBf16, "fmha_causal": FmhaCausal,
-             "moe_bf16": MoeBf16, "moe_mxfp8": MoeMxfp8, "mxfp8_quantize": Mxfp8Quantize}
+             "moe_bf16": MoeBf16, "moe_mxfp8": MoeMxfp8, "mxfp8_quantize": Mxfp8Quantize,
+             "nvfp4_quantize": Nvfp4Quantize}
 
 
 # --------------------------------------------------------------------------------------
@@ -956,10 +997,11 @@ def run_ref_shapes(args):
 # ncu captures summarised under profiles/ (None until captured)
 TRAFFIC_BYTES: dict[str, float | None] = {
     "mxfp8_gemm_8192x8192x8192_bf16out": 466.0e6,          # profiles/gemm_pair_mxfp8_8192.md
-    "nvfp4_gemm_8192x28672x8192_bf16out": 1006.0e6,        # profiles/gemm_pair_nvfp4_8192x28672x8192.md
-    "fmha_causal_bf16_b4_h32_s8192_d128": 1067.0e6,        # profiles/fmha_fwd_pair_causal_b4_h32_s8192_d128.md
+    "nvfp4_gemm_8192x28672x8192_bf16out": 1005.0e6,        # profiles/gemm_pair_nvfp4_8192x28672x8192.md
+    "fmha_causal_bf16_b4_h32_s8192_d128": 1066.0e6,        # profiles/fmha_fwd_pair_causal_b4_h32_s8192_d128.md
     "mxfp8_quantize_bf16_8192x8192": 173.0e6,              # profiles/mxfp8_quantize_bf16_8192x8192.md
     "dense_f16_gemm_2048x2048x2048": 16.8e6,               # profiles/gemm_dense_f16_2048.md
+    "nvfp4_quantize_bf16_8192x8192": 293.0e6,              # profiles/nvfp4_quantize_bf16_8192x8192.md (both kernels)
 }
 
 
