@@ -329,6 +329,11 @@ __device__ __forceinline__ void tmem_st_32x32b_x8(uint32_t taddr, const uint32_t
                : "memory");
 }
 
+// 16 bytes to shared memory (address in the shared window, 16-byte aligned).
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 // 16 bytes from shared memory (address in the shared window, 16-byte aligned).
 __device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t (&r)[4]) {
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"

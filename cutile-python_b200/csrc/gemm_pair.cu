@@ -25,6 +25,8 @@
 // block-scaled kinds also need TMEM columns for the two scale-factor slots, so their
 // windows overlap by 32 (MXFP8) or 96 (NVFP4) columns: the epilogue drains the shared
 // columns first and releases them early; the next tile's first MMA waits only for that.
+#include <stdlib.h>
+
 #include "gemm_common.cuh"
 #include "gemm_pair.h"
 #include "mx_quant.cuh"
@@ -68,7 +70,8 @@ struct PairCfg {
   static constexpr int kSfaCols = kSfAtoms * 4;
   static constexpr int kSfSlotCols = kSfAtoms * 12;
   static constexpr int kThreads = 224;
-  static constexpr int kSmemBytes = 1024 + kStages * (kStageBytes + kSfBytes) + 256;
+  static constexpr int kStagingBytes = 4 * 4096;   // epilogue: 32 rows x 128 bytes per warp
+  static constexpr int kSmemBytes = 1024 + kStages * (kStageBytes + kSfBytes) + 256 + kStagingBytes;
   static_assert(!kScaled || kSfBase + kSfSlots * kSfSlotCols <= 512, "TMEM budget");
   static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
@@ -86,6 +89,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const uint32_t tiles_base = smem_base;
   const uint32_t sf_base = tiles_base + S * Cfg::kStageBytes;
   uint8_t* tail = smem + S * (Cfg::kStageBytes + Cfg::kSfBytes);
+  const uint32_t staging_base = smem_u32(tail) + 256;   // behind the barriers
   const uint32_t bar_base = smem_u32(tail);
   // full[S], empty[S], acc_full[2], acc_empty[2], ovl_free, tile_open[2]
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -424,7 +428,87 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           p.c_sf[swizzled_sf_offset(out_row, col >> 5, p.c_sf_k_atoms)] = sf;
         }
       };
-      if (!swiglu) {
+      // Coalesced store path (plain STORE epilogue, 16-byte-aligned rows): a lane holds 128
+      // bytes of ONE row per group of columns, so storing from registers makes every warp
+      // store touch 32 different cache lines - 4096 store wavefronts per tile and CTA, more
+      // LSU time than a tile of 12 - 16 k-steps has MMA time.  Each warp therefore turns its
+      // 32 x 128-byte block through shared memory (XOR-swizzled 16-byte pieces, conflict
+      // free both ways) and writes it back with eight lanes per row: four full lines per
+      // instruction.  The staging traffic competes with the MMAs for shared-memory
+      // bandwidth (-4 % on 8192 cubed), so the host turns this on only where the epilogue
+      // is the longer leg: tiles of few k-steps.
+      constexpr int kGroupCols = (OUT == kOutF32) ? 32 : 64;     // 128 bytes of a row
+      const bool coalesced = (OUT != kOutMX8) && p.coalesce_store && !swiglu && vec_ok &&
+                             ((p.n * elem_bytes) % 16 == 0);
+      if (coalesced) {
+        const int n0 = tc.pid_n * bn;
+        const uint32_t stg = staging_base + (warp - 2) * 4096;
+        const int piece = lane & 7;
+        // the eight rows this lane stores (row i * 4 + lane / 8 of the warp's 32): their
+        // output pointers and validity come from the lanes that own those rows
+        const uint64_t my_ptr = reinterpret_cast<uint64_t>(c_row);
+        uint64_t row_ptr[8];
+        uint32_t row_valid = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int src = i * 4 + (lane >> 3);
+          row_ptr[i] = __shfl_sync(0xffffffffu, my_ptr, src);
+          row_valid |= (__shfl_sync(0xffffffffu, row_ok ? 1u : 0u, src) & 1u) << i;
+        }
+        const int64_t n_bytes = static_cast<int64_t>(p.n) * elem_bytes;
+        auto fetch = [&](int c, uint32_t (&r)[32]) {
+          bool from_held = false;
+          if constexpr (Cfg::kOverlapChunks > 0) {
+#pragma unroll
+            for (int ci = 0; ci < Cfg::kOverlapChunks; ++ci) {
+              if (c == ((first + ci) & 7)) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = held[ci][i];
+                from_held = true;
+              }
+            }
+          }
+          if (!from_held) tmem_ld_32x32b_x32(taddr + c * 32, r);
+        };
+#pragma unroll 1
+        for (int g = 0; g < bn / kGroupCols; ++g) {
+          uint32_t out[32];   // this lane's 128 bytes of the group
+          if constexpr (OUT == kOutF32) {
+            uint32_t r[32];
+            fetch(g, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) out[i] = __float_as_uint(__uint_as_float(r[i]) * scale);
+          } else {
+            uint32_t ra[32], rb[32];
+            fetch(2 * g, ra);
+            fetch(2 * g + 1, rb);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float a0 = __uint_as_float(ra[2 * i]) * scale, a1 = __uint_as_float(ra[2 * i + 1]) * scale;
+              const float b0 = __uint_as_float(rb[2 * i]) * scale, b1 = __uint_as_float(rb[2 * i + 1]) * scale;
+              out[i] = (OUT == kOutBF16) ? pack_bf16x2(a0, a1) : pack_f16x2(a0, a1);
+              out[16 + i] = (OUT == kOutBF16) ? pack_bf16x2(b0, b1) : pack_f16x2(b0, b1);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            st_shared_v4(stg + lane * 128 + ((j ^ (lane & 7)) << 4), out[4 * j], out[4 * j + 1], out[4 * j + 2],
+                         out[4 * j + 3]);
+          __syncwarp();
+          const int64_t col_byte = static_cast<int64_t>(n0 + g * kGroupCols) * elem_bytes + piece * 16;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int row_in_warp = i * 4 + (lane >> 3);
+            uint32_t q[4];
+            ld_shared_v4(stg + row_in_warp * 128 + ((piece ^ (row_in_warp & 7)) << 4), q);
+            if (((row_valid >> i) & 1u) && col_byte + 16 <= n_bytes)
+              *reinterpret_cast<uint4*>(row_ptr[i] + col_byte) = make_uint4(q[0], q[1], q[2], q[3]);
+          }
+          __syncwarp();
+        }
+      } else if (!swiglu) {
         const int n0 = tc.pid_n * bn;
         const int chunks = bn / 32;
         auto emit = [&](int c, const uint32_t (&r)[32]) {
@@ -537,6 +621,10 @@ int launch_gemm_pair(int kind, int out_dtype, const CUtensorMap* maps, const Gem
                      cudaStream_t stream) {
   GemmParams p = p_in;
   if (p.pair_bn != 128) p.pair_bn = 256;
+  // direct stores take about 8000 cycles per tile (16-bit output; twice the store
+  // instructions for fp32), a k-step about 530
+  p.coalesce_store = p.k_iters <= (out_dtype == B200K_F32 ? 40 : 20);
+  if (const char* e = getenv("B200K_EPILOGUE")) p.coalesce_store = (e[0] == 'c');
   const int64_t tiles = static_cast<int64_t>((p.m + 255) / 256) * p.tiles_n * p.batch;
   int clusters = static_cast<int>(tiles < sms / 2 ? tiles : sms / 2);
   if (clusters < 1) clusters = 1;

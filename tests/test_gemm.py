@@ -97,9 +97,12 @@ def test_split_k_batched(device_ok):
 @pytest.mark.parametrize("bn", ["128", "256"])
 @pytest.mark.parametrize("b_nk", [False, True])
 @pytest.mark.parametrize("m,n,k", [(512, 640, 256), (1000, 500, 700), (2304, 1152, 192)])
-def test_pair_kernel_tile_widths_and_b_layouts(dtype, bn, b_nk, m, n, k, device_ok, monkeypatch):
-    # the CTA-pair kernel with 256 x 128 and 256 x 256 tiles, B stored (K, N) and (N, K)
+@pytest.mark.parametrize("epilogue", ["coalesced", "direct"])
+def test_pair_kernel_tile_widths_and_b_layouts(dtype, bn, b_nk, m, n, k, epilogue, device_ok, monkeypatch):
+    # the CTA-pair kernel with 256 x 128 and 256 x 256 tiles, B stored (K, N) and (N, K), both
+    # epilogue forms (stores straight from registers / through shared memory)
     monkeypatch.setenv("B200K_PAIR_BN", bn)
+    monkeypatch.setenv("B200K_EPILOGUE", epilogue)
     a = _rand((m, k), dtype, 11)
     b = _rand((n, k), dtype, 12) if b_nk else _rand((k, n), dtype, 12)
     c = b200k.cutile_matmul(a.cuda(), b.cuda().T if b_nk else b.cuda())
