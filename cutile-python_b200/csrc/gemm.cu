@@ -568,9 +568,8 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
   }
   const bool pair_plain = !grouped && a->epilogue == B200K_EPI_STORE && a->row_map == nullptr;
   const bool pair_grouped = grouped && a->tile_rows == 256 && !b_mn;
-  // N-contiguous B on the pair kernel: 16-bit operands, plain problems (for fp8 the one-CTA
-  // kernel is the faster one with this layout: 612 against 641 us on 4 x 8192 x 8192 x 2000)
-  const bool pair_b_ok = !b_mn || (pair_plain && kind == kKindF16);
+  // N-contiguous B on the pair kernel: 8- and 16-bit operands, plain problems
+  const bool pair_b_ok = !b_mn || (pair_plain && kind != kKindTF32);
   if (pair_b_ok && (pair_plain || pair_grouped) && pair_kernels_enabled()) {
     GemmParams pp = p;
     // Tile width: 256 x 256.  256 x 128 tiles (B200K_PAIR_BN=128) halve the cost of a
