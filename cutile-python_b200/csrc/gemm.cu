@@ -37,6 +37,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
   const uint32_t bar_base = smem_u32(bars);
   // full[kStages], empty[kStages], acc_full[2], acc_empty[2]
+  const uint32_t staging_base = bar_base + 256;   // behind the barriers
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
@@ -276,7 +277,66 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint8_t* c_row = static_cast<uint8_t*>(p.c) +
                        (static_cast<int64_t>(p.tile_group ? 0 : tc.batch) * p.stride_c + out_row * p.ldc) * elem_bytes;
       const uint32_t taddr = tmem_base + as * Cfg::kAccStride + (uint32_t(quarter * 32) << 16);
-      if (!swiglu) {
+      // Short-K tiles (split-K partials above all) are bound by their stores: a lane owns one
+      // row, so a store from registers touches 32 cache lines.  Same remedy as in the
+      // CTA-pair kernel: the warp turns its 32 x 128-byte block through an XOR-swizzled
+      // staging buffer and stores with eight lanes per row.
+      constexpr int kGroupCols = (OUT == kOutF32) ? 32 : 64;     // 128 bytes of a row
+      const bool coalesced = Cfg::kStagingBytes > 0 && p.coalesce_store && !swiglu && vec_ok &&
+                             ((p.n * elem_bytes) % 16 == 0);
+      if (coalesced) {
+        const int n0 = tc.pid_n * BN;
+        const uint32_t stg = staging_base + (warp - 2) * 4096;
+        const int piece = lane & 7;
+        const uint64_t my_ptr = reinterpret_cast<uint64_t>(c_row);
+        uint64_t row_ptr[8];
+        uint32_t row_valid = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int src = i * 4 + (lane >> 3);
+          row_ptr[i] = __shfl_sync(0xffffffffu, my_ptr, src);
+          row_valid |= (__shfl_sync(0xffffffffu, row_ok ? 1u : 0u, src) & 1u) << i;
+        }
+        const int64_t n_bytes = static_cast<int64_t>(p.n) * elem_bytes;
+#pragma unroll 1
+        for (int g = 0; g < BN / kGroupCols; ++g) {
+          uint32_t out[32];   // this lane's 128 bytes of the group
+          if constexpr (OUT == kOutF32) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(taddr + g * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) out[i] = __float_as_uint(__uint_as_float(r[i]) * scale);
+          } else {
+            uint32_t ra[32], rb[32];
+            tmem_ld_32x32b_x32(taddr + g * 64, ra);
+            tmem_ld_32x32b_x32(taddr + g * 64 + 32, rb);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float a0 = __uint_as_float(ra[2 * i]) * scale, a1 = __uint_as_float(ra[2 * i + 1]) * scale;
+              const float b0 = __uint_as_float(rb[2 * i]) * scale, b1 = __uint_as_float(rb[2 * i + 1]) * scale;
+              out[i] = (OUT == kOutBF16) ? pack_bf16x2(a0, a1) : pack_f16x2(a0, a1);
+              out[16 + i] = (OUT == kOutBF16) ? pack_bf16x2(b0, b1) : pack_f16x2(b0, b1);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            st_shared_v4(stg + lane * 128 + ((j ^ (lane & 7)) << 4), out[4 * j], out[4 * j + 1], out[4 * j + 2],
+                         out[4 * j + 3]);
+          __syncwarp();
+          const int64_t col_byte = static_cast<int64_t>(n0 + g * kGroupCols) * elem_bytes + piece * 16;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int row_in_warp = i * 4 + (lane >> 3);
+            uint32_t q[4];
+            ld_shared_v4(stg + row_in_warp * 128 + ((piece ^ (row_in_warp & 7)) << 4), q);
+            if (((row_valid >> i) & 1u) && col_byte + 16 <= n_bytes)
+              *reinterpret_cast<uint4*>(row_ptr[i] + col_byte) = make_uint4(q[0], q[1], q[2], q[3]);
+          }
+          __syncwarp();
+        }
+      } else if (!swiglu) {
         const int n0 = tc.pid_n * BN;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
@@ -343,7 +403,11 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, in
                   cudaGetErrorString(e));
     configured[dev] = true;
   }
-  kernel<<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  GemmParams pl = p;
+  const int steps = p.split_k > 1 ? p.k_per_split : p.k_iters;   // k-steps per tile (128 x 256 here)
+  pl.coalesce_store = steps <= (OUT == kOutF32 ? 40 : 20);
+  if (const char* e = getenv("B200K_EPILOGUE")) pl.coalesce_store = (e[0] == 'c');
+  kernel<<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(ta, tb, pl);
   B200K_CHECK_LAUNCH("gemm launch");
   return B200K_OK;
 }

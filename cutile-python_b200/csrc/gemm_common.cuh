@@ -83,8 +83,10 @@ struct GemmCfg {
   static constexpr int kSfTmemBase = 256;
   static constexpr int kSfaCols = kSfaAtoms * 4;
   static constexpr int kSfbCols = kSfbAtoms * 4;
+  // epilogue staging (32 rows x 128 bytes per warp) where shared memory has room for it
+  static constexpr int kStagingBytes = (KIND == kKindNVF4) ? 0 : 4 * 4096;
   static constexpr int kSmemBytes =
-      1024 /*alignment slack*/ + kStages * (kStageBytes + kSfBytes) + 256 /*barriers*/;
+      1024 /*alignment slack*/ + kStages * (kStageBytes + kSfBytes) + 256 /*barriers*/ + kStagingBytes;
   static_assert(!kScaled || kSfTmemBase + kStages * (kSfaCols + kSfbCols) <= kTmemCols,
                 "scale factors do not fit in tensor memory");
   static_assert(!(B_MN && KIND == kKindNVF4), "fp4 operands are K-major only");
