@@ -92,7 +92,10 @@ struct GemmCfg {
   static_assert(!(B_MN && KIND == kKindNVF4), "fp4 operands are K-major only");
 };
 
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+// x * sigmoid(x) with the fast exponential and reciprocal (two special-function ops): the
+// result is rounded to 16 bits or quantised right after, and an IEEE division per element
+// made the SwiGLU epilogue longer than the mainloop of a 32-k-step tile.
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 struct TileCoord {
   int batch, pid_m, pid_n;
