@@ -62,3 +62,38 @@ def test_wrappers_validate_like_the_samples():
         b200k.cutile_matmul(a, torch.zeros(8, 4))
     with pytest.raises(ValueError, match="larger than the inner most"):
         b200k.block_quantize(torch.zeros(4, 16), 32)
+
+
+def test_ctypes_mirrors_match_the_header_layout(tmp_path):
+    """Every ctypes.Structure in b200k/_lib.py has the size and field offsets a C compiler
+    gives the struct of the same role in include/b200k.h."""
+    import shutil
+    import subprocess
+    from b200k import _lib
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    pairs = {"b200k_gemm_args": _lib.GemmArgs, "b200k_block_scaled_gemm_args": _lib.BlockScaledGemmArgs,
+             "b200k_quantize_args": _lib.QuantizeArgs, "b200k_moe_align_args": _lib.MoeAlignArgs,
+             "b200k_fmha_args": _lib.FmhaArgs, "b200k_peer_gather_args": _lib.PeerGatherArgs}
+    lines = ["#include <stdio.h>", "#include <stddef.h>", '#include "b200k.h"', "int main(void) {"]
+    for cname, mirror in pairs.items():
+        lines.append(f'  printf("{cname} size %zu\\n", sizeof({cname}));')
+        for field, _ in mirror._fields_:
+            lines.append(f'  printf("{cname} {field} %zu\\n", offsetof({cname}, {field}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run([cc, "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    seen = 0
+    for line in out.splitlines():
+        cname, what, value = line.split()
+        mirror = pairs[cname]
+        if what == "size":
+            assert ctypes.sizeof(mirror) == int(value), cname
+        else:
+            assert getattr(mirror, what).offset == int(value), f"{cname}.{what}"
+        seen += 1
+    assert seen == sum(len(m._fields_) + 1 for m in pairs.values())
