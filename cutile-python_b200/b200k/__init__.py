@@ -16,3 +16,4 @@ from .moe import (cutile_moe, cutile_moe_mxfp8, invoke_fused_moe_kernel,  # noqa
 from .allgather import (Nvfp4GatherMatmul, cutile_gather_matmul, cutile_gather_matmul_nvfp4, peer_buffers,  # noqa: F401
                         peer_gather, shard_rows)
 from .moe_ep import ExpertParallelMoE  # noqa: F401
+from . import tune  # noqa: F401

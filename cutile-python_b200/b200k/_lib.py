@@ -33,6 +33,11 @@ class B200KError(RuntimeError):
         self.code = code
 
 
+class GemmConfig(Structure):
+    _fields_ = [("kernel", c_int32), ("tile_n", c_int32), ("epilogue_store", c_int32),
+                ("split_k", c_int32)]
+
+
 class GemmArgs(Structure):
     _fields_ = [
         ("a", c_void_p), ("b", c_void_p), ("c", c_void_p),
@@ -45,6 +50,7 @@ class GemmArgs(Structure):
         ("row_map", c_void_p), ("row_scale", c_void_p), ("c_rows", c_int64),
         ("tile_rows", c_int32),
         ("workspace", c_void_p), ("workspace_bytes", c_int64),
+        ("config", POINTER(GemmConfig)),
     ]
 
 
@@ -62,6 +68,7 @@ class BlockScaledGemmArgs(Structure):
         ("row_map", c_void_p), ("row_scale", c_void_p), ("c_rows", c_int64),
         ("tile_rows", c_int32),
         ("c_sf", c_void_p), ("c_sf_k_atoms", c_int64),
+        ("config", POINTER(GemmConfig)),
     ]
 
 

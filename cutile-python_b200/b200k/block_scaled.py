@@ -14,7 +14,7 @@ import ctypes
 
 import torch
 
-from . import _lib
+from . import _lib, tune
 
 _E8M0 = torch.float8_e8m0fnu
 _E8M0_ONE = 127  # byte of 2^0
@@ -184,6 +184,10 @@ def _scaled_gemm(a_km, sfa, b_nk, sfb, c, *, fp4: bool, alpha: float = 1.0, alph
     args.row_scale = _lib.ptr(row_scale)
     if c_sf is not None:
         args.c_sf, args.c_sf_k_atoms = c_sf.data_ptr(), c_sf.shape[1]
+    cfg = tune.config_for("block_scaled_gemm", args.ab_dtype, args.c_dtype, _lib.B_NK, m, n, k, 1)
+    if cfg is not None:
+        c_cfg = cfg.to_c()                      # kept alive until the call has returned
+        args.config = ctypes.pointer(c_cfg)
     with torch.cuda.device(c.device):
         _lib.check(_lib.lib().b200k_block_scaled_gemm(ctypes.byref(args), _lib.stream_ptr(c.device)))
     return c

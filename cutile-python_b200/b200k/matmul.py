@@ -16,7 +16,7 @@ import ctypes
 
 import torch
 
-from . import _lib
+from . import _lib, tune
 
 
 def _aligned(t: torch.Tensor, ld: int) -> bool:
@@ -83,10 +83,15 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, alpha: float = 1
     args.epilogue = _lib.EPI_STORE
     args.alpha = alpha
     args.max_ctas = max_ctas
+    cfg = tune.config_for("gemm", args.ab_dtype, args.c_dtype, layout, m, n, k, nb)
+    if cfg is not None:
+        c_cfg = cfg.to_c()                      # kept alive until the call has returned
+        args.config = ctypes.pointer(c_cfg)
     with torch.cuda.device(a.device):
         # a few output tiles with a long K: split-K over the idle SMs needs fp32 scratch
         workspace = None
-        if -(-m // 128) * -(-n // 256) * nb * 4 <= 256 and k * a3.element_size() >= 1024:
+        if (cfg is not None and cfg.split_k > 1) or (
+                -(-m // 128) * -(-n // 256) * nb * 4 <= 256 and k * a3.element_size() >= 1024):
             ws_bytes = _lib.lib().b200k_gemm_workspace_bytes(ctypes.byref(args))
             if ws_bytes > 0:
                 workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)

@@ -404,9 +404,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, in
     configured[dev] = true;
   }
   GemmParams pl = p;
-  const int steps = p.split_k > 1 ? p.k_per_split : p.k_iters;   // k-steps per tile (128 x 256 here)
-  pl.coalesce_store = steps <= (OUT == kOutF32 ? 40 : 20);
-  if (const char* e = getenv("B200K_EPILOGUE")) pl.coalesce_store = (e[0] == 'c');
+  pl.coalesce_store = p.store_mode != 1;   // staged stores unless the caller asks for direct ones
   kernel<<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(ta, tb, pl);
   B200K_CHECK_LAUNCH("gemm launch");
   return B200K_OK;
@@ -432,13 +430,23 @@ struct SplitPlan {
   int64_t workspace_bytes = 0;
 };
 
-SplitPlan plan_split_k(int64_t m, int64_t n, int64_t batch, int k_iters, int sms) {
+// `forced`: 0 = decide by shape, 1 = never, n > 1 = up to n slices whatever the shape.
+SplitPlan plan_split_k(int64_t m, int64_t n, int64_t batch, int k_iters, int sms, int forced) {
   SplitPlan plan;
+  if (forced == 1) return plan;
   const int64_t tiles = ceil_div(m, kBM) * ceil_div(n, 256) * batch;
-  if (tiles * 4 > sms || k_iters < 8) return plan;
-  const int max_split = static_cast<int>(sms / tiles);
-  int k_per = static_cast<int>(ceil_div(k_iters, max_split));
-  if (k_per < 4) k_per = 4;
+  int k_per;
+  if (forced > 1) {
+    k_per = static_cast<int>(ceil_div(k_iters, forced));
+    if (k_per < 1) k_per = 1;
+  } else {
+    // The second kernel and the fp32 round trip cost about as much as 16 k-steps: with a
+    // short K (1024 cubed, 16-bit: 16 k-steps, 14 us whole against 19 us split) it loses.
+    if (tiles * 4 > sms || k_iters < 32) return plan;
+    const int max_split = static_cast<int>(sms / tiles);
+    k_per = static_cast<int>(ceil_div(k_iters, max_split));
+    if (k_per < 4) k_per = 4;
+  }
   const int split = static_cast<int>(ceil_div(k_iters, k_per));
   if (split <= 1) return plan;
   plan.split = split;
@@ -501,10 +509,25 @@ int launch_splitk_reduce(int out, const float* ws, int split, int64_t m, int64_t
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-// The CTA-pair kernels are the default; B200K_SINGLE_CTA=1 forces the one-CTA kernels.
-bool pair_kernels_enabled() {
-  const char* v = getenv("B200K_SINGLE_CTA");
-  return !(v != nullptr && v[0] == '1');
+// The caller's b200k_gemm_config, or, where it leaves a choice open, the process-wide
+// diagnostic switches: B200K_SINGLE_CTA=1 (one-CTA kernels), B200K_PAIR_BN=128 (narrow
+// pair tiles), B200K_EPILOGUE=c|d (staged / direct stores).
+b200k_gemm_config effective_config(const b200k_gemm_config* c) {
+  b200k_gemm_config r = {0, 0, 0, 0};
+  if (c != nullptr) r = *c;
+  if (r.kernel == 0) {
+    const char* v = getenv("B200K_SINGLE_CTA");
+    if (v != nullptr && v[0] == '1') r.kernel = 1;
+  }
+  if (r.tile_n == 0) {
+    const char* v = getenv("B200K_PAIR_BN");
+    if (v != nullptr) r.tile_n = v[0] == '1' ? 128 : 256;
+  }
+  if (r.epilogue_store == 0) {
+    const char* v = getenv("B200K_EPILOGUE");
+    if (v != nullptr) r.epilogue_store = v[0] == 'c' ? 2 : 1;
+  }
+  return r;
 }
 
 }  // namespace
@@ -575,6 +598,8 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
   p.c_rows = a->row_map ? a->c_rows : a->m;
   p.epilogue = a->epilogue;
   p.status = device_status_word();
+  const b200k_gemm_config cfg = effective_config(a->config);
+  p.store_mode = cfg.epilogue_store;
   const bool grouped = a->tile_group != nullptr;
   if (grouped) p.batch = 1;
 
@@ -605,7 +630,9 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
 
   const int out = a->c_dtype;
   if (!grouped && a->epilogue == B200K_EPI_STORE && a->row_map == nullptr && a->workspace != nullptr) {
-    const SplitPlan plan = plan_split_k(a->m, a->n, a->batch, p.k_iters, sms);
+    // a caller that asks for the CTA-pair kernel gets no split (the split kernel is one-CTA)
+    const SplitPlan plan = plan_split_k(a->m, a->n, a->batch, p.k_iters, sms,
+                                        cfg.kernel == 2 && cfg.split_k == 0 ? 1 : cfg.split_k);
     if (plan.split > 1 && a->workspace_bytes >= plan.workspace_bytes && aligned16(a->workspace)) {
       GemmParams ps = p;
       ps.c = a->workspace;
@@ -634,15 +661,15 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
   const bool pair_grouped = grouped && a->tile_rows == 256 && !b_mn;
   // N-contiguous B on the pair kernel: 8- and 16-bit operands, plain problems
   const bool pair_b_ok = !b_mn || (pair_plain && kind != kKindTF32);
-  if (pair_b_ok && (pair_plain || pair_grouped) && pair_kernels_enabled()) {
+  if (pair_b_ok && (pair_plain || pair_grouped) && cfg.kernel != 1) {
     GemmParams pp = p;
-    // Tile width: 256 x 256.  256 x 128 tiles (B200K_PAIR_BN=128) halve the cost of a
+    // Tile width: 256 x 256.  256 x 128 tiles (config tile_n = 128) halve the cost of a
     // partly filled last wave on paper (4096 cubed: 256 tiles on 74 clusters are 4 rounds,
     // 512 narrow tiles 7 half rounds), but a narrow tile re-reads A twice as often and
     // pays the per-tile hand-offs twice: measured 113 against 96 us there.
-    int bn = 256;
-    const char* force_bn = getenv("B200K_PAIR_BN");
-    if (force_bn != nullptr && pair_plain) bn = force_bn[0] == '1' ? 128 : 256;
+    // (an N-contiguous B is loaded in boxes of 128 bytes of N: each CTA's half of a narrow
+    // tile, 64 columns, is a whole box only for 16-bit operands)
+    const int bn = (cfg.tile_n == 128 && pair_plain && !(b_mn && elem_bytes != 2)) ? 128 : 256;
     pp.pair_bn = bn;
     pp.b_mn = b_mn ? 1 : 0;
     pp.tiles_n = static_cast<int>(ceil_div(a->n, bn));
@@ -734,6 +761,8 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
   p.c_rows = a->row_map ? a->c_rows : a->m;
   p.epilogue = a->epilogue;
   p.status = device_status_word();
+  const b200k_gemm_config cfg = effective_config(a->config);
+  p.store_mode = cfg.epilogue_store;
   const bool grouped = a->tile_group != nullptr;
   if (grouped) p.batch = 1;
   const bool mx_out = a->c_dtype == B200K_E4M3;
@@ -771,7 +800,7 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
   const int64_t sfb_tile_bytes = a->sf_k_atoms * 512;
   const bool pair_grouped = grouped && a->tile_rows == 256 && !(swiglu && fp4) &&
                             a->stride_sfb % sfb_tile_bytes == 0;
-  if ((pair_plain || pair_grouped) && pair_kernels_enabled()) {
+  if ((pair_plain || pair_grouped) && cfg.kernel != 1) {
     GemmParams pp = p;
     pp.idesc = make_idesc_block_scaled(fmt, fmt, 256, BN, /*ue8m0=*/!fp4, 0, 0);
     pp.sfb_group_tiles = grouped ? static_cast<int>(a->stride_sfb / sfb_tile_bytes) : 0;
@@ -814,5 +843,7 @@ extern "C" int64_t b200k_gemm_workspace_bytes(const b200k_gemm_args* a) {
   const int sms = current_sm_count();
   if (sms <= 0) return 0;
   const int k_iters = static_cast<int>(ceil_div(a->k, 128 / elem_bytes));
-  return plan_split_k(a->m, a->n, a->batch, k_iters, sms).workspace_bytes;
+  const b200k_gemm_config cfg = effective_config(a->config);
+  return plan_split_k(a->m, a->n, a->batch, k_iters, sms,
+                      cfg.kernel == 2 && cfg.split_k == 0 ? 1 : cfg.split_k).workspace_bytes;
 }

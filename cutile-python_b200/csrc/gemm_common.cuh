@@ -26,7 +26,8 @@ struct GemmParams {
   int k_tail_mmas;      // MMAs of the last k iteration (1..4)
   int pair_bn;          // CTA-pair kernel: tile width 256 (also when 0) or 128 (unscaled kinds)
   int b_mn;             // CTA-pair kernel: B stored (K, N), N contiguous
-  int coalesce_store;   // CTA-pair kernel: store the tile through shared memory (short-K problems)
+  int coalesce_store;   // store the tile through shared memory (set by the launchers from store_mode)
+  int store_mode;       // host side only: 1 = direct stores, 0 or 2 = staged
   int split_k;          // > 1: `batch` counts (batch, split) pairs, each split owns k_per_split k-steps
   int k_per_split;
   uint32_t idesc;

@@ -60,6 +60,22 @@ int b200k_sm_count(void);                       /* SMs of the current device, <0
  * *info packs (role << 8 | detail << 16) of the wait that gave up. */
 int b200k_device_status(int* code, int* info);
 
+/* ---- kernel-form selection ------------------------------------------------
+ * Which of the library's kernel forms a GEMM call uses.  Every field is 0 for "choose
+ * automatically" (the library's shape heuristics); a NULL pointer to this struct means all
+ * automatic.  A request the problem cannot honour (split-K for a grouped problem, a tile
+ * width the kernel does not have) is ignored rather than refused, so that one search space
+ * serves every shape; results are the same for every setting up to fp32 summation order.
+ * This is what the reference leaves to its tile-size arguments and tuner
+ * (src/cuda/tile/tune/_tune.py:132-336): the search itself is host code above this ABI. */
+typedef struct {
+  int32_t kernel;          /* 1 = one-CTA kernel (128-row tiles), 2 = CTA-pair kernel (256-row tiles) */
+  int32_t tile_n;          /* 128 or 256 output columns per tile (CTA-pair kernel) */
+  int32_t epilogue_store;  /* 1 = straight from registers, 2 = staged through shared memory */
+  int32_t split_k;         /* 1 = never split K, n > 1 = split K into (up to) n slices; needs the
+                            * workspace b200k_gemm_workspace_bytes reports for the same args */
+} b200k_gemm_config;
+
 /* ---- dense GEMM -------------------------------------------------------
  * C[b] = A[b] . B[b], fp32 accumulation, result rounded to c_dtype.
  * Replaces matmul_kernel / persistent_matmul_kernel / batch_matmul_kernel
@@ -99,6 +115,7 @@ typedef struct {
    * memory, contents irrelevant before and after the call.  NULL = never split. */
   void* workspace;
   int64_t workspace_bytes;
+  const b200k_gemm_config* config;  /* host pointer, read during the call; NULL = automatic */
 } b200k_gemm_args;
 
 int b200k_gemm(const b200k_gemm_args* args, b200k_stream stream);
@@ -153,6 +170,7 @@ typedef struct {
    * experimental/cuda-lang/tutorial/nvfp4_gemm_2_quantize_fp4.py:136-192). */
   void* c_sf;
   int64_t c_sf_k_atoms;
+  const b200k_gemm_config* config;  /* as in b200k_gemm_args (split_k is not used here) */
 } b200k_block_scaled_gemm_args;
 
 int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* args, b200k_stream stream);

@@ -1,0 +1,201 @@
+"""Kernel-form tuning: the measuring search and the database on the host, and on the GPU the
+parity of every kernel form a search may pick.
+
+The search mirrors the surface of the reference's tuner (src/cuda/tile/tune/_tune.py:23-60:
+`Measurement`, `TuningResult.best / successes / failures`; `:132-336`: every config measured,
+failing configs recorded, ValueError when none works or the space is empty).
+"""
+import ctypes
+import random
+
+import pytest
+import torch
+
+import b200k
+import oracle
+from b200k import _lib, tune
+
+
+# ---- host side (no GPU) --------------------------------------------------------------------
+def _fake_timer(times, noise=0.01, seed=0):
+    rng = random.Random(seed)
+    return lambda run_fn, cfg: times[cfg] * (1.0 + rng.gauss(0.0, noise))
+
+
+def test_search_returns_the_fastest_and_records_failures():
+    times = {"a": 100.0, "b": 61.0, "c": 60.0, "d": 300.0, "e": 90.0}
+
+    def run(cfg):
+        if cfg == "d":
+            raise RuntimeError("config not available")
+
+    res = tune.exhaustive_search(list(times), None, run, timer=_fake_timer(times, noise=0.002))
+    assert res.best.config == "c"
+    assert {m.config for m in res.successes} == {"a", "b", "c", "e"}
+    assert [(c, t) for c, t, _ in res.failures] == [("d", RuntimeError)]
+    assert all(m.num_samples >= 5 for m in res.successes)
+    # the two close candidates were sampled until their intervals settled
+    by = {m.config: m for m in res.successes}
+    assert by["b"].error_margin_us <= max(0.01 * by["b"].mean_us, 0.5)
+    assert "best: c" in res.summary()
+
+
+def test_search_stops_sampling_beaten_configs():
+    times = {"fast": 1000.0, "slow": 100000.0}
+    calls = {"fast": 0, "slow": 0}
+
+    def timer(run_fn, cfg):
+        calls[cfg] += 1
+        return times[cfg] * (1.0 + 0.2 * random.Random(calls[cfg]).random())   # noisy: never settles early
+
+    tune.exhaustive_search(["fast", "slow"], None, lambda cfg: None, timer=timer, max_samples=40)
+    assert calls["slow"] == 5            # one batch, then its interval lies above the leader's
+    assert calls["fast"] == 40           # 20 % noise: never within 1 %, runs out of samples
+
+
+def test_search_rejects_empty_and_all_failing_spaces():
+    with pytest.raises(ValueError, match="empty"):
+        tune.exhaustive_search([], None, lambda cfg: None, timer=lambda r, c: 1.0)
+
+    def run(cfg):
+        raise RuntimeError("nope")
+
+    with pytest.raises(ValueError, match="No valid config"):
+        tune.exhaustive_search([1, 2], None, run, timer=lambda r, c: 1.0)
+
+
+def test_config_validation_and_c_mirror():
+    cfg = tune.GemmConfig(kernel=2, tile_n=128, epilogue_store=2, split_k=1)
+    c = cfg.to_c()
+    assert (c.kernel, c.tile_n, c.epilogue_store, c.split_k) == (2, 128, 2, 1)
+    assert ctypes.sizeof(c) == 16
+    assert tune.GemmConfig.from_dict({"kernel": 1}) == tune.GemmConfig(kernel=1)
+    for bad in (dict(kernel=3), dict(tile_n=64), dict(epilogue_store=5), dict(split_k=-1)):
+        with pytest.raises(ValueError):
+            tune.GemmConfig(**bad)
+
+
+def test_database_round_trip_and_lookup_order(tmp_path):
+    db = tune.TuneDB("NVIDIA B200")
+    key = tune.gemm_key("gemm", _lib.F16, _lib.F16, _lib.B_KN, 2048, 2048, 2048, 1)
+    assert key == "gemm:0:0:0:2048x2048x2048x1"
+    won = tune.GemmConfig(kernel=1, epilogue_store=2, split_k=2)
+    db.put(key, won, 17.5)
+    path = tmp_path / "tuned.json"
+    db.save(path)
+    back = tune.TuneDB.load(path)
+    assert len(back) == 1 and back.device == "NVIDIA B200" and back.get(key) == won
+    assert back.get("gemm:0:0:0:1x1x1x1") is None
+
+    parts = ("gemm", _lib.F16, _lib.F16, _lib.B_KN, 2048, 2048, 2048, 1)
+    prev = tune.get_db()
+    try:
+        tune.set_db(None)
+        assert tune.config_for(*parts) is None                       # nothing installed
+        tune.set_db(str(path))
+        assert tune.config_for(*parts) == won                        # database entry
+        assert tune.last_key() == key
+        forced = tune.GemmConfig(kernel=2)
+        with tune.use_config(forced):
+            assert tune.config_for(*parts) == forced                 # the override wins
+            with tune.use_config(None):
+                assert tune.config_for(*parts) is None               # automatic, database ignored
+            assert tune.config_for(*parts) == forced
+        assert tune.config_for(*parts) == won
+    finally:
+        tune.set_db(prev)
+
+
+def test_database_rejects_invalid_entries(tmp_path):
+    path = tmp_path / "bad.json"
+    path.write_text('{"entries": {"gemm:0:0:0:1x1x1x1": {"config": {"kernel": 9}}}}')
+    with pytest.raises(ValueError):
+        tune.TuneDB.load(path)
+
+
+def test_search_space_always_starts_with_automatic():
+    space = tune.gemm_search_space(2048, 2048, 2048)
+    assert space[0] == tune.AUTO and len(set(space)) == len(space)
+    assert any(c.split_k > 1 for c in space)
+    big = tune.gemm_search_space(8192, 8192, 8192)
+    assert not any(c.split_k > 1 for c in big)                       # enough tiles already
+    scaled = tune.gemm_search_space(8192, 8192, 8192, elem_bytes=1, block_scaled=True)
+    assert all(c.tile_n == 0 and c.split_k <= 1 for c in scaled)
+
+
+# ---- GPU: every kernel form a search may pick computes the same product ----------------------
+def _rand(shape, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g).to(dtype)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("m,n,k", [(512, 768, 2048), (300, 520, 1096)])
+def test_every_dense_form_matches_the_oracle(m, n, k, layout, device_ok):
+    a = _rand((m, k), torch.float16, 0)
+    b = _rand((k, n), torch.float16, 1)
+    ref = oracle.matmul_ref(a, b)
+    a_d = a.cuda()
+    b_d = b.cuda() if layout == "kn" else b.t().contiguous().cuda().t()
+    space = tune.gemm_search_space(m, n, k) + [tune.GemmConfig(split_k=5), tune.GemmConfig(kernel=2, split_k=3)]
+    for cfg in space:
+        with tune.use_config(cfg):
+            c = b200k.cutile_matmul(a_d, b_d)
+        torch.testing.assert_close(c.float().cpu(), ref, atol=2e-2, rtol=2e-2, msg=lambda s: f"{cfg}: {s}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+def test_every_fp8_form_matches_the_oracle(layout, device_ok):
+    """8-bit operands, batched, K not a multiple of the k-step (the reference's fp8 batch
+    matmul bench shape in small).  A form the operand layout cannot take (narrow pair tiles
+    with an N-contiguous 8-bit B) falls back to the nearest one instead of failing."""
+    nb, m, n, k = 2, 512, 640, 400
+    a = _rand((nb, m, k), torch.float8_e4m3fn, 6)
+    b = _rand((nb, k, n), torch.float8_e4m3fn, 7)
+    ref = torch.bmm(a.float(), b.float())
+    a_d = a.cuda()
+    b_d = b.cuda() if layout == "kn" else b.transpose(1, 2).contiguous().cuda().transpose(1, 2)
+    for cfg in tune.gemm_search_space(m, n, k, nb, elem_bytes=1):
+        c = torch.empty(nb, m, n, dtype=torch.float32, device="cuda")
+        with tune.use_config(cfg):
+            b200k.cutile_batch_matmul(nb, a_d, b_d, c)
+        torch.testing.assert_close(c.cpu(), ref, atol=1e-3 * float(ref.abs().max()), rtol=1e-3,
+                                   msg=lambda s: f"{cfg}: {s}")
+
+
+@pytest.mark.gpu
+def test_every_block_scaled_form_matches_the_oracle(device_ok):
+    m, n, k = 384, 512, 1024
+    g = torch.Generator().manual_seed(5)
+    aq, sa = oracle.block_quantize_ref(torch.randn(m, k, generator=g))
+    bq, sb = oracle.block_quantize_ref(torch.randn(n, k, generator=g))
+    ref = oracle.block_scaled_matmul_ref(aq, sa, bq, sb)
+    for cfg in tune.gemm_search_space(m, n, k, elem_bytes=1, block_scaled=True):
+        with tune.use_config(cfg):
+            c = b200k.cutile_block_scaled_matmul(aq.cuda(), sa.cuda(), bq.cuda().T, sb.cuda().T)
+        torch.testing.assert_close(c.cpu(), ref, atol=1e-4 * float(ref.abs().max()), rtol=1e-3,
+                                   msg=lambda s: f"{cfg}: {s}")
+
+
+@pytest.mark.gpu
+def test_tune_matmul_records_a_winner_the_wrapper_then_uses(tmp_path, device_ok):
+    m = n = k = 1024
+    a = _rand((m, k), torch.bfloat16, 2).cuda()
+    b = _rand((k, n), torch.bfloat16, 3).cuda()
+    db = tune.TuneDB(torch.cuda.get_device_name())
+    res = tune.tune_matmul(a, b, db=db, max_samples=20)
+    assert len(db) == 1 and res.best.config in tune.gemm_search_space(m, n, k)
+    auto = next(x for x in res.successes if x.config == tune.AUTO)
+    assert res.best.mean_us <= auto.mean_us
+    path = tmp_path / "tuned.json"
+    db.save(path)
+    prev = tune.get_db()
+    try:
+        tune.set_db(str(path))
+        c = b200k.cutile_matmul(a, b)
+        assert tune.get_db().get(tune.last_key()) == res.best.config
+    finally:
+        tune.set_db(prev)
+    torch.testing.assert_close(c.float().cpu(), oracle.matmul_ref(a.cpu(), b.cpu()), atol=2e-2, rtol=2e-2)
