@@ -440,12 +440,14 @@ SplitPlan plan_split_k(int64_t m, int64_t n, int64_t batch, int k_iters, int sms
     k_per = static_cast<int>(ceil_div(k_iters, forced));
     if (k_per < 1) k_per = 1;
   } else {
-    // The second kernel and the fp32 round trip cost about as much as 16 k-steps: with a
-    // short K (1024 cubed, 16-bit: 16 k-steps, 14 us whole against 19 us split) it loses.
-    if (tiles * 4 > sms || k_iters < 32) return plan;
+    if (tiles * 4 > sms) return plan;
     const int max_split = static_cast<int>(sms / tiles);
     k_per = static_cast<int>(ceil_div(k_iters, max_split));
     if (k_per < 4) k_per = 4;
+    // The second kernel and the fp32 round trip cost what some 40 k-steps of a lone tile
+    // take: splitting pays only when it takes more than that off every CTA's K loop
+    // (1024 cubed: 16-bit 14 us whole against 19 us split, tf32 18 against 21).
+    if (k_iters - k_per < 48) return plan;
   }
   const int split = static_cast<int>(ceil_div(k_iters, k_per));
   if (split <= 1) return plan;
@@ -669,7 +671,14 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
     // pays the per-tile hand-offs twice: measured 113 against 96 us there.
     // (an N-contiguous B is loaded in boxes of 128 bytes of N: each CTA's half of a narrow
     // tile, 64 columns, is a whole box only for 16-bit operands)
-    const int bn = (cfg.tile_n == 128 && pair_plain && !(b_mn && elem_bytes != 2)) ? 128 : 256;
+    // Left to the library, narrow tiles are taken when the wide ones would leave more than
+    // half of the CTA pairs without work (1024 cubed, 16-bit: 16.4 -> 14.1 us).
+    int want_bn = cfg.tile_n;
+    if (want_bn == 0) {
+      const int64_t wide_tiles = ceil_div(a->m, 256) * ceil_div(a->n, 256) * a->batch;
+      want_bn = wide_tiles * 2 <= sms / 2 ? 128 : 256;
+    }
+    const int bn = (want_bn == 128 && pair_plain && !(b_mn && elem_bytes != 2)) ? 128 : 256;
     pp.pair_bn = bn;
     pp.b_mn = b_mn ? 1 : 0;
     pp.tiles_n = static_cast<int>(ceil_div(a->n, bn));

@@ -52,7 +52,7 @@ def test_cutile_matmul_transposed_b_view(dtype, device_ok):
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("m,n,k,b_nk", [(256, 256, 4096, False),    # the reference's split-K bench shape
                                         (256, 256, 4096, True), (100, 300, 4104, False),
-                                        (128, 512, 8192, True), (8, 8, 2048, False)])
+                                        (128, 512, 8192, True), (8, 8, 4096, False)])
 def test_split_k_shapes(dtype, m, n, k, b_nk, device_ok):
     # few output tiles, long K: the library spreads K over the idle SMs (fp32 partials + a
     # reduction kernel); the result must not depend on that choice
@@ -86,8 +86,8 @@ def test_split_k_shapes(dtype, m, n, k, b_nk, device_ok):
 
 
 def test_split_k_batched(device_ok):
-    a = _rand((3, 128, 2048), torch.float16, 8) * 0.25
-    b = _rand((3, 2048, 256), torch.float16, 9)
+    a = _rand((3, 128, 4096), torch.float16, 8) * 0.25
+    b = _rand((3, 4096, 256), torch.float16, 9)
     c = b200k.bmm(a.cuda(), b.cuda(), torch.float16)
     ref = torch.bmm(a.float(), b.float())
     torch.testing.assert_close(c.float().cpu(), ref, atol=5e-2, rtol=2e-2)
