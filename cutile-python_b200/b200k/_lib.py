@@ -69,6 +69,7 @@ class BlockScaledGemmArgs(Structure):
         ("tile_rows", c_int32),
         ("c_sf", c_void_p), ("c_sf_k_atoms", c_int64),
         ("config", POINTER(GemmConfig)),
+        ("c_scale", c_void_p),
     ]
 
 

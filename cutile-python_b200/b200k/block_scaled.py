@@ -159,7 +159,7 @@ def nvfp4_quantize(x: torch.Tensor, *, swizzled_scale: bool = True):
 
 
 def _scaled_gemm(a_km, sfa, b_nk, sfb, c, *, fp4: bool, alpha: float = 1.0, alpha_a=None,
-                 alpha_b=None, max_ctas: int = 0, row_scale=None, c_sf=None):
+                 alpha_b=None, max_ctas: int = 0, row_scale=None, c_sf=None, c_scale=None):
     """a_km (M, Kp), b_nk (N, Kp) K-contiguous byte tensors (Kp = K or K/2 bytes);
     sfa/sfb swizzled 4-D byte tensors."""
     m, kp = a_km.shape
@@ -171,11 +171,14 @@ def _scaled_gemm(a_km, sfa, b_nk, sfb, c, *, fp4: bool, alpha: float = 1.0, alph
     args.m, args.n, args.k, args.batch = m, n, k, 1
     mul = 2 if fp4 else 1
     args.lda, args.ldb, args.ldc = a_km.stride(0) * mul, b_nk.stride(0) * mul, c.stride(0)
+    if c_scale is not None:                      # packed e2m1 output: leading dimension in elements
+        args.ldc = c.stride(0) * 2
     args.sf_k_atoms = sfa.shape[1]
     if sfb.shape[1] != sfa.shape[1]:
         raise ValueError("A and B scale tensors disagree on K")
     args.ab_dtype = _lib.E2M1X2 if fp4 else _lib.dtype_enum(a_km.dtype)
-    args.c_dtype = _lib.dtype_enum(c.dtype)
+    args.c_dtype = _lib.E2M1X2 if c_scale is not None else _lib.dtype_enum(c.dtype)
+    args.c_scale = _lib.ptr(c_scale)
     args.epilogue = _lib.EPI_STORE
     args.alpha = alpha
     args.alpha_a = _lib.ptr(alpha_a)
@@ -206,7 +209,8 @@ def _k_major(t: torch.Tensor) -> torch.Tensor:
 
 def cutile_block_scaled_matmul(A: torch.Tensor, A_scale: torch.Tensor, B: torch.Tensor,
                                B_scale: torch.Tensor, *, out_dtype: torch.dtype = torch.float32,
-                               C: torch.Tensor | None = None) -> torch.Tensor:
+                               C: torch.Tensor | None = None,
+                               out_scale: torch.Tensor | None = None) -> torch.Tensor:
     """C = (A (.) A_scale) @ (B (.) B_scale) for fp8 operands with ue8m0 scales per 32
     elements of K.  A is (M, K); B is (K, N) (normally the transposed view of an (N, K)
     tensor); scales are 2-D logical ((M, K/32) and (K/32, N)) or 4-D swizzle_32_4_4
@@ -214,6 +218,8 @@ def cutile_block_scaled_matmul(A: torch.Tensor, A_scale: torch.Tensor, B: torch.
     selects bf16/fp16 instead, and ``torch.float8_e4m3fn`` returns the pair (C quantised to
     MXFP8 in the epilogue, its swizzled scales): bit for bit
     ``block_quantize(C_bf16, 32, swizzled_scale=True)`` of the bf16 result.
+    ``torch.float4_e2m1fn_x2`` with ``out_scale`` (fp32 device scalar, the result's per-tensor
+    scale) returns the NVFP4 pair (packed codes (M, N/2) uint8, swizzled ue4m3 scales).
     """
     if A.shape[1] != B.shape[0]:
         raise ValueError(f"Incompatible matrices: K dimension of A ({A.shape[1]}) "
@@ -253,6 +259,15 @@ def cutile_block_scaled_matmul(A: torch.Tensor, A_scale: torch.Tensor, B: torch.
         _scaled_gemm(a_km, _as_u8(A_scale).contiguous(), b_nk, _as_u8(B_scale).contiguous(), C,
                      fp4=False, c_sf=C_sf)
         return C, C_sf.view(torch.float8_e8m0fnu)
+    if out_dtype == torch.float4_e2m1fn_x2 and C is None:
+        # the same with an NVFP4 result (packed e2m1 (M, N / 2), swizzled ue4m3 scales over
+        # (M, N / 16)) under the per-tensor scale the caller provides
+        if k == 0:
+            raise ValueError("quantised output needs non-empty operands")
+        C, C_sf = _nvfp4_output(m, n, out_scale, A.device)
+        _scaled_gemm(a_km, _as_u8(A_scale).contiguous(), b_nk, _as_u8(B_scale).contiguous(), C,
+                     fp4=False, c_sf=C_sf, c_scale=out_scale)
+        return C, C_sf.view(torch.float8_e4m3fn)
     if C is None:
         C = torch.empty((m, n), device=A.device, dtype=out_dtype)
     if m == 0 or n == 0:
@@ -263,6 +278,19 @@ def cutile_block_scaled_matmul(A: torch.Tensor, A_scale: torch.Tensor, B: torch.
                         fp4=False)
 
 
+def _nvfp4_output(m: int, n: int, out_scale: torch.Tensor, device):
+    """Buffers of an NVFP4 result quantised in the epilogue: packed codes (M, N / 2), swizzled
+    ue4m3 scales over (M, N / 16)."""
+    if n % 32 or m == 0 or n == 0:
+        raise ValueError("NVFP4 output needs non-empty operands and N a multiple of 32")
+    if out_scale is None or out_scale.dtype != torch.float32 or out_scale.numel() != 1 or not out_scale.is_cuda:
+        raise ValueError("NVFP4 output needs out_scale: one fp32 value on the device")
+    c = torch.empty((m, n // 2), device=device, dtype=torch.uint8)
+    shape = swizzled_shape(m, n // 16)
+    c_sf = (torch.zeros if (m % 128 or (n // 16) % 4) else torch.empty)(shape, dtype=torch.uint8, device=device)
+    return c, c_sf
+
+
 def cutile_swizzled_scaled_matmul(A, A_s_swizzled, B, B_s_swizzled, C):
     return cutile_block_scaled_matmul(A, A_s_swizzled, B, B_s_swizzled, C=C)
 
@@ -270,15 +298,25 @@ def cutile_swizzled_scaled_matmul(A, A_s_swizzled, B, B_s_swizzled, C):
 def cutile_nvfp4_matmul(A_q: torch.Tensor, A_sf: torch.Tensor, A_ts: torch.Tensor,
                         B_q: torch.Tensor, B_sf: torch.Tensor, B_ts: torch.Tensor, *,
                         out_dtype: torch.dtype = torch.bfloat16,
-                        C: torch.Tensor | None = None) -> torch.Tensor:
+                        C: torch.Tensor | None = None,
+                        out_scale: torch.Tensor | None = None) -> torch.Tensor:
     """C = (A_ts * B_ts) * (A_q (.) A_sf) @ (B_q (.) B_sf)^T for NVFP4 operands as
     produced by nvfp4_quantize: A_q (M, K/2) and B_q (N, K/2) packed e2m1 bytes, both
-    K-contiguous; *_sf swizzled ue4m3 scales; *_ts fp32 device scalars."""
+    K-contiguous; *_sf swizzled ue4m3 scales; *_ts fp32 device scalars.
+    ``out_dtype=torch.float4_e2m1fn_x2`` with ``out_scale`` (fp32 device scalar) quantises the
+    result in the epilogue and returns (packed codes (M, N/2), swizzled ue4m3 scales): the
+    next NVFP4 GEMM's A operand, bit for bit what quantising the bf16 result with that
+    tensor scale gives."""
     a_km = _k_major(_as_u8(A_q))
     b_nk = _k_major(_as_u8(B_q))
     m, n = a_km.shape[0], b_nk.shape[0]
     if a_km.shape[1] != b_nk.shape[1]:
         raise ValueError("Incompatible matrices: K dimensions differ")
+    if out_dtype == torch.float4_e2m1fn_x2 and C is None:
+        C, C_sf = _nvfp4_output(m, n, out_scale, A_q.device)
+        _scaled_gemm(a_km, _as_u8(A_sf).contiguous(), b_nk, _as_u8(B_sf).contiguous(), C,
+                     fp4=True, alpha_a=A_ts, alpha_b=B_ts, c_sf=C_sf, c_scale=out_scale)
+        return C, C_sf.view(torch.float8_e4m3fn)
     if C is None:
         C = torch.empty((m, n), device=A_q.device, dtype=out_dtype)
     if m == 0 or n == 0:

@@ -784,6 +784,17 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
     p.c_sf = static_cast<uint8_t*>(a->c_sf);
     p.c_sf_k_atoms = static_cast<int>(a->c_sf_k_atoms);
   }
+  const bool nv_out = a->c_dtype == B200K_E2M1X2;
+  if (nv_out) {
+    const int64_t n_out = a->epilogue == B200K_EPI_SWIGLU ? a->n / 2 : a->n;
+    if (a->c_sf == nullptr || a->c_scale == nullptr || a->row_map != nullptr || n_out % 32 != 0 ||
+        a->ldc % 2 != 0 || a->stride_c % 2 != 0 || a->c_sf_k_atoms < ceil_div(n_out, 64))
+      return fail(B200K_UNSUPPORTED, "NVFP4 (e2m1 + ue4m3) output needs c_sf with c_sf_k_atoms >= "
+                  "ceil(N_out / 64), c_scale, N_out a multiple of 32, an even ldc and no row_map");
+    p.c_sf = static_cast<uint8_t*>(a->c_sf);
+    p.c_sf_k_atoms = static_cast<int>(a->c_sf_k_atoms);
+    p.c_scale = a->c_scale;
+  }
 
   CUtensorMap ta, tb;
   const uint64_t a_batches = grouped ? 1 : a->batch;
@@ -829,7 +840,7 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
     const CUtensorMap maps[4] = {ta, tb, tsa, tsb};
     return launch_gemm_pair(fp4 ? kKindNVF4 : kKindMXF8, a->c_dtype, maps, pp, sms, stream);
   }
-  if (mx_out)
+  if (mx_out || nv_out)
     return fail(B200K_UNSUPPORTED, "quantised output is produced by the CTA-pair kernel only (plain "
                 "problems, or grouped ones with tile_rows = 256)");
   if (grouped && a->tile_rows != 0 && a->tile_rows != 128)

@@ -13,7 +13,8 @@ constexpr int kNumThreads = 192;
 constexpr int kTmemCols = 512;
 
 enum OutType : int { kOutF16 = 0, kOutBF16 = 1, kOutF32 = 2,
-                     kOutMX8 = 3 /* e4m3 + swizzled ue8m0 scale per 32 columns (CTA-pair kernel) */ };
+                     kOutMX8 = 3, /* e4m3 + swizzled ue8m0 scale per 32 columns (CTA-pair kernel) */
+                     kOutNVF4 = 4 /* packed e2m1 + swizzled ue4m3 scale per 16 columns (CTA-pair kernel) */ };
 
 struct GemmParams {
   void* c;
@@ -48,8 +49,9 @@ struct GemmParams {
   const float* row_scale;
   int64_t c_rows;
   int epilogue;
-  uint8_t* c_sf;        // kOutMX8: swizzled scales of the output
+  uint8_t* c_sf;        // kOutMX8 / kOutNVF4: swizzled scales of the output
   int c_sf_k_atoms;
+  const float* c_scale; // kOutNVF4: the output's per-tensor scale (device scalar)
   int* status;
 };
 

@@ -359,9 +359,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     float alpha = p.alpha;
     if (p.alpha_a != nullptr) alpha *= *p.alpha_a;
     if (p.alpha_b != nullptr) alpha *= *p.alpha_b;
-    const int elem_bytes = (OUT == kOutF32) ? 4 : (OUT == kOutMX8 ? 1 : 2);
-    const bool vec_ok = ((p.ldc * elem_bytes) % 16 == 0) && ((p.stride_c * elem_bytes) % 16 == 0) &&
+    constexpr bool kQuantOut = (OUT == kOutMX8 || OUT == kOutNVF4);
+    // bytes of `e` output elements (kOutNVF4: two elements per byte, even counts only)
+    constexpr int elem_bytes = (OUT == kOutF32) ? 4 : (kQuantOut ? 1 : 2);
+    auto out_bytes = [](int64_t e) { return OUT == kOutNVF4 ? e / 2 : e * elem_bytes; };
+    const bool vec_ok = (out_bytes(p.ldc) % 16 == 0) && (out_bytes(p.stride_c) % 16 == 0) &&
                         (reinterpret_cast<uintptr_t>(p.c) % 16 == 0);
+    float nv_st = 0.0f, nv_six_st = 0.0f;   // kOutNVF4: tensor scale of the output and 6 x it
+    if constexpr (OUT == kOutNVF4) {
+      nv_st = *p.c_scale;
+      nv_six_st = __fmul_rn(6.0f, nv_st);
+    }
     const uint32_t lead_ovl = map_to_cta(ovl_free_bar, 0);
     uint32_t lt = 0;
     TRACE_T0(t_total);
@@ -390,7 +398,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       float scale = alpha;
       if (p.row_scale != nullptr && row_ok) scale *= p.row_scale[out_row];
       uint8_t* c_row = static_cast<uint8_t*>(p.c) +
-                       (static_cast<int64_t>(p.tile_group ? 0 : tc.batch) * p.stride_c + out_row * p.ldc) * elem_bytes;
+                       out_bytes(static_cast<int64_t>(p.tile_group ? 0 : tc.batch) * p.stride_c + out_row * p.ldc);
       const uint32_t taddr = tmem_base + w * Cfg::kAccStride + (uint32_t(quarter * 32) << 16);
       // Columns shared with the other window first (the last chunks of window 0, the first
       // chunks of window 1): they are pulled into registers back to back and released
@@ -426,6 +434,27 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int i = 0; i < 32; ++i) dst[i] = (pk[i >> 2] >> (8 * (i & 3))) & 0xff;
           }
           p.c_sf[swizzled_sf_offset(out_row, col >> 5, p.c_sf_k_atoms)] = sf;
+        } else if constexpr (OUT == kOutNVF4) {
+          // two NVFP4 blocks of 16 columns: 16 bytes of codes, two neighbouring scale bytes;
+          // again the bytes of quantising the bf16-rounded values with the given tensor scale
+          float lo16[16], hi16[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            lo16[i] = __bfloat162float(__float2bfloat16_rn(v[i]));
+            hi16[i] = __bfloat162float(__float2bfloat16_rn(v[16 + i]));
+          }
+          uint32_t w[4];
+          const uint8_t s0 = nvfp4_block(lo16, nv_six_st, nv_st, &w[0], &w[1]);
+          const uint8_t s1 = nvfp4_block(hi16, nv_six_st, nv_st, &w[2], &w[3]);
+          uint8_t* dst = c_row + (col >> 1);
+          if (vec_ok) {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) dst[i] = (w[i >> 2] >> (8 * (i & 3))) & 0xff;
+          }
+          *reinterpret_cast<uint16_t*>(p.c_sf + swizzled_sf_offset(out_row, col >> 4, p.c_sf_k_atoms)) =
+              static_cast<uint16_t>(s0) | (static_cast<uint16_t>(s1) << 8);
         }
       };
       // Coalesced store path (plain STORE epilogue, 16-byte-aligned rows): a lane holds 128
@@ -434,11 +463,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // LSU time than a tile of 12 - 16 k-steps has MMA time.  Each warp therefore turns its
       // 32 x 128-byte block through shared memory (XOR-swizzled 16-byte pieces, conflict
       // free both ways) and writes it back with eight lanes per row: four full lines per
-      // instruction.  The staging traffic competes with the MMAs for shared-memory
-      // bandwidth (-4 % on 8192 cubed), so the host turns this on only where the epilogue
-      // is the longer leg: tiles of few k-steps.
+      // instruction.  The host selects this form unless the caller asks for direct stores.
       constexpr int kGroupCols = (OUT == kOutF32) ? 32 : 64;     // 128 bytes of a row
-      const bool coalesced = (OUT != kOutMX8) && p.coalesce_store && !swiglu && vec_ok &&
+      const bool coalesced = !kQuantOut && p.coalesce_store && !swiglu && vec_ok &&
                              ((p.n * elem_bytes) % 16 == 0);
       if (coalesced) {
         const int n0 = tc.pid_n * bn;
@@ -516,7 +543,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             float v[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * scale;
-            if constexpr (OUT == kOutMX8) store_mx(n0 + c * 32, v);
+            if constexpr (kQuantOut) store_mx(n0 + c * 32, v);
             else store_row_chunk<OUT>(c_row, n0 + c * 32, p.n, v, vec_ok);
           }
         };
@@ -555,7 +582,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               v[i] = silu(__uint_as_float(g[i]) * scale) * (__uint_as_float(u[i]) * scale);
-            if constexpr (OUT == kOutMX8) store_mx(n0 + c * 32, v);
+            if constexpr (kQuantOut) store_mx(n0 + c * 32, v);
             else store_row_chunk<OUT>(c_row, n0 + c * 32, n_out, v, vec_ok);
           }
         }
@@ -610,7 +637,11 @@ int launch_pair_out(int out, const CUtensorMap* maps, const GemmParams& p, int g
     case B200K_F32: return launch_pair<KIND, kOutF32>(maps, p, grid, stream);
     case B200K_E4M3:
       if constexpr (KIND == kKindMXF8) return launch_pair<KIND, kOutMX8>(maps, p, grid, stream);
-      return fail(B200K_UNSUPPORTED, "quantised output is available for MXFP8 operands only");
+      return fail(B200K_UNSUPPORTED, "MXFP8 output is available for MXFP8 operands only");
+    case B200K_E2M1X2:
+      if constexpr (KIND == kKindMXF8 || KIND == kKindNVF4)
+        return launch_pair<KIND, kOutNVF4>(maps, p, grid, stream);
+      return fail(B200K_UNSUPPORTED, "NVFP4 output is available for block-scaled operands only");
     default: return fail(B200K_INVALID_ARG, "unsupported output dtype %d", out);
   }
 }

@@ -281,48 +281,6 @@ absmax_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t ldx,
   }
 }
 
-__device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
-  __half_raw h = __nv_cvt_fp8_to_halfraw(b, __NV_E4M3);
-  return __half2float(*reinterpret_cast<__half*>(&h));
-}
-
-// One 16-element block: returns the ue4m3 scale byte, packs the sixteen e2m1 codes into
-// lo (elements 0..7) and hi (8..15), low nibble = even element.
-__device__ __forceinline__ uint8_t nvfp4_block(const float (&v)[16], float six_st, float s_t,
-                                               uint32_t* lo_out, uint32_t* hi_out) {
-  float amax = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  uint8_t sf_byte = 0;
-  float denom = 0.0f;
-  if (amax > 0.0f && six_st > 0.0f) {
-    const float r = __fdiv_rn(amax, six_st);
-    sf_byte = __nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
-    denom = __fmul_rn(e4m3_to_f32(sf_byte), s_t);
-  }
-  // x / denom as x * (1 / denom), both correctly rounded: one reciprocal per block instead
-  // of sixteen divisions.  A subnormal denom (reciprocal not finite) keeps the division.
-  const float inv = (denom >= 1.17549435e-38f) ? __frcp_rn(denom) : 0.0f;
-  uint32_t lo = 0, hi = 0;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    float a = 0.0f, b = 0.0f;
-    if (inv > 0.0f) {
-      a = __fmul_rn(v[2 * i], inv);
-      b = __fmul_rn(v[2 * i + 1], inv);
-    } else if (denom > 0.0f) {
-      a = __fdiv_rn(v[2 * i], denom);
-      b = __fdiv_rn(v[2 * i + 1], denom);
-    }
-    const uint32_t byte = __nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest);
-    if (i < 4) lo |= (byte & 0xff) << (8 * i);
-    else hi |= (byte & 0xff) << (8 * (i - 4));
-  }
-  *lo_out = lo;
-  *hi_out = hi;
-  return sf_byte;
-}
-
 // BPT = blocks per thread.  2 (K a multiple of 32, 16-byte-aligned rows in and out): 64 or
 // 128 bytes in flight per thread, one 16-byte store of codes and one 2-byte store of
 // scales.  1: any shape.

@@ -171,6 +171,15 @@ typedef struct {
   void* c_sf;
   int64_t c_sf_k_atoms;
   const b200k_gemm_config* config;  /* as in b200k_gemm_args (split_k is not used here) */
+  /* c_dtype B200K_E2M1X2 (MXFP8 or NVFP4 operands, CTA-pair kernel): the result is rounded to
+   * bf16 and quantised to NVFP4 in the epilogue with the per-tensor scale the caller gives in
+   * `c_scale` (device scalar; e.g. calibrated, or from a b200k_nvfp4_quantize of an earlier
+   * result): packed e2m1 bytes to `c` (ldc in elements, even), one ue4m3 scale per 16 output
+   * columns to `c_sf` (swizzle_32_4_4, `c_sf_k_atoms` >= ceil(N_out / 64) atoms along N), by
+   * the block rule of b200k_nvfp4_quantize with s_t = *c_scale.  Same reference pattern as
+   * above (nvfp4_gemm_2_quantize_fp4.py:136-192,976-991 quantises to fp4 with a given global
+   * scale). */
+  const float* c_scale;
 } b200k_block_scaled_gemm_args;
 
 int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* args, b200k_stream stream);

@@ -135,6 +135,64 @@ def test_nvfp4_end_to_end_bf16(device_ok):
     torch.testing.assert_close(c.float().cpu(), ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2)
 
 
+@pytest.mark.parametrize("operands", ["nvfp4", "mxfp8"])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (384, 640, 512), (1000, 96, 192)])
+def test_nvfp4_quantise_in_epilogue_equals_two_steps(operands, m, n, k, device_ok):
+    # packed e2m1 + swizzled ue4m3 scales straight from the GEMM epilogue == quantising the bf16
+    # result (oracle rule) with the same per-tensor scale
+    g = torch.Generator().manual_seed(m + n + 1)
+    a = torch.randn(m, k, generator=g).bfloat16().cuda()
+    b = (0.05 * torch.randn(n, k, generator=g)).bfloat16().cuda()
+    if operands == "nvfp4":
+        aq, asf, ats = b200k.nvfp4_quantize(a)
+        bq, bsf, bts = b200k.nvfp4_quantize(b)
+        run = lambda **kw: b200k.cutile_nvfp4_matmul(aq, asf, ats, bq, bsf, bts, **kw)
+    else:
+        aq, asf = b200k.block_quantize(a, 32, swizzled_scale=True)
+        bq, bsf = b200k.block_quantize(b, 32, swizzled_scale=True)
+        run = lambda **kw: b200k.cutile_block_scaled_matmul(aq, asf, bq.T, bsf, **kw)
+    c_bf16 = run(out_dtype=torch.bfloat16)
+    q_ref, sf_ref, st_ref = oracle.nvfp4_quantize_ref(c_bf16.cpu())
+    out_scale = torch.tensor([float(st_ref)], device="cuda")
+    q, sf = run(out_dtype=torch.float4_e2m1fn_x2, out_scale=out_scale)
+    assert q.shape == (m, n // 2) and q.dtype == torch.uint8
+    assert np.array_equal(q.cpu().numpy(), q_ref)
+    lo = oracle.unswizzle_32_4_4_ref(sf.cpu().view(torch.uint8))[:m, : n // 16]
+    assert np.array_equal(lo.numpy(), sf_ref)
+    # and the library's own two-step path gives the same bytes
+    q2, sf2, st2 = b200k.nvfp4_quantize(c_bf16)
+    assert float(st2) == float(st_ref) and torch.equal(q2, q)
+
+
+def test_nvfp4_output_chains_into_the_next_gemm(device_ok):
+    # up projection quantised in the epilogue feeds the down projection without a bf16 tensor
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(256, 512, generator=g).bfloat16().cuda()
+    w1 = (0.05 * torch.randn(768, 512, generator=g)).bfloat16().cuda()
+    w2 = (0.05 * torch.randn(384, 768, generator=g)).bfloat16().cuda()
+    xq, xsf, xts = b200k.nvfp4_quantize(x)
+    w1q, w1sf, w1ts = b200k.nvfp4_quantize(w1)
+    w2q, w2sf, w2ts = b200k.nvfp4_quantize(w2)
+    h_bf16 = b200k.cutile_nvfp4_matmul(xq, xsf, xts, w1q, w1sf, w1ts)
+    hq_ref, hsf_ref, hts = b200k.nvfp4_quantize(h_bf16)
+    y_ref = b200k.cutile_nvfp4_matmul(hq_ref, hsf_ref, hts, w2q, w2sf, w2ts, out_dtype=torch.float32)
+    hq, hsf = b200k.cutile_nvfp4_matmul(xq, xsf, xts, w1q, w1sf, w1ts, out_dtype=torch.float4_e2m1fn_x2,
+                                        out_scale=hts)
+    y = b200k.cutile_nvfp4_matmul(hq, hsf, hts, w2q, w2sf, w2ts, out_dtype=torch.float32)
+    torch.testing.assert_close(y, y_ref, atol=1e-5 * float(y_ref.abs().max()), rtol=1e-4)
+
+
+def test_nvfp4_output_validation(device_ok):
+    a = torch.randn(128, 64).bfloat16().cuda()
+    aq, asf, ats = b200k.nvfp4_quantize(a)
+    with pytest.raises(ValueError, match="out_scale"):
+        b200k.cutile_nvfp4_matmul(aq, asf, ats, aq, asf, ats, out_dtype=torch.float4_e2m1fn_x2)
+    aq48, asf48, ats48 = b200k.nvfp4_quantize(a[:48])
+    with pytest.raises(ValueError, match="multiple of 32"):
+        b200k.cutile_nvfp4_matmul(aq, asf, ats, aq48, asf48, ats48, out_dtype=torch.float4_e2m1fn_x2,
+                                  out_scale=ats)
+
+
 def test_mxfp8_sampled_rows_at_full_size(device_ok):
     # the headline configuration (8192^3, bf16 out): sampled rows against the oracle and a
     # row-sum identity over the whole output
