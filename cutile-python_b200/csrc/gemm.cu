@@ -663,7 +663,9 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
   const bool pair_grouped = grouped && a->tile_rows == 256 && !b_mn;
   // N-contiguous B on the pair kernel: 8- and 16-bit operands, plain problems
   const bool pair_b_ok = !b_mn || (pair_plain && kind != kKindTF32);
-  if (pair_b_ok && (pair_plain || pair_grouped) && cfg.kernel != 1) {
+  // (a grouped problem over 256-row tiles exists on the pair kernel only: a request for the
+  // one-CTA kernel is not honoured there)
+  if (pair_b_ok && ((pair_plain && cfg.kernel != 1) || pair_grouped)) {
     GemmParams pp = p;
     // Tile width: 256 x 256.  256 x 128 tiles (config tile_n = 128) halve the cost of a
     // partly filled last wave on paper (4096 cubed: 256 tiles on 74 clusters are 4 rounds,
@@ -820,7 +822,9 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
   const int64_t sfb_tile_bytes = a->sf_k_atoms * 512;
   const bool pair_grouped = grouped && a->tile_rows == 256 && !(swiglu && fp4) &&
                             a->stride_sfb % sfb_tile_bytes == 0;
-  if ((pair_plain || pair_grouped) && cfg.kernel != 1) {
+  // (256-row grouped tiles and quantised outputs exist on the pair kernel only: a request for
+  // the one-CTA kernel is not honoured there)
+  if ((pair_plain && (cfg.kernel != 1 || mx_out || nv_out)) || pair_grouped) {
     GemmParams pp = p;
     pp.idesc = make_idesc_block_scaled(fmt, fmt, 256, BN, /*ue8m0=*/!fp4, 0, 0);
     pp.sfb_group_tiles = grouped ? static_cast<int>(a->stride_sfb / sfb_tile_bytes) : 0;
