@@ -25,6 +25,16 @@ enum : int {
   kTimeout = -4,
 };
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialisation
+// attribute may become resident while its predecessor in the stream still runs (once every
+// CTA of the predecessor has called pdl_launch_dependents() or exited) and blocks in
+// pdl_wait() until the predecessor has completed and its writes are visible.  Both are
+// no-ops for kernels launched the ordinary way.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Device-side status word layout: code in the low 8 bits, role in bits 8..15,
 // detail (stage / tile) above.
 __device__ __forceinline__ void report_status(int* status, int role, int detail) {

@@ -14,6 +14,9 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+#include <type_traits>
+
 namespace b200k {
 namespace {
 
@@ -46,154 +49,229 @@ template <typename T> __device__ __forceinline__ T from_float(float v);
 template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
-// EPL consecutive elements of a row, lane-contiguous (8 or 4 bytes per lane: a warp reads one
-// whole row of 256 or 128 bytes per instruction).  Rows wait in registers as loaded (raw
-// 16-bit pairs) and are widened where they are used: half the registers per row in flight.
-template <int EPL> struct RawRow;
-template <> struct RawRow<4> { uint2 v; };
-template <> struct RawRow<2> { uint32_t v; };
-
-template <typename T, int EPL>
-__device__ __forceinline__ RawRow<EPL> load_raw(const T* row, int lane) {
-  RawRow<EPL> r;
-  if constexpr (EPL == 4) r.v = __ldg(reinterpret_cast<const uint2*>(row + lane * 4));
-  else r.v = __ldg(reinterpret_cast<const uint32_t*>(row + lane * 2));
-  return r;
+__device__ __forceinline__ float decode_exp2(float x) {   // exp2(-inf) = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
-template <typename T, int EPL>
-__device__ __forceinline__ void widen(const RawRow<EPL>& raw, float (&dst)[EPL]) {
-  const T* e = reinterpret_cast<const T*>(&raw.v);
+// Eight 16-bit elements (one 16-byte load) widened to fp32.
+template <typename T>
+__device__ __forceinline__ void widen8(const uint4& raw, float* dst) {
+  const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-  for (int i = 0; i < EPL; ++i) dst[i] = to_float<T>(e[i]);
+  for (int i = 0; i < 8; ++i) dst[i] = to_float<T>(e[i]);
 }
 
-template <typename T, int EPL>
-__device__ __forceinline__ void load_row(const T* row, int lane, float (&dst)[EPL]) {
-  widen<T, EPL>(load_raw<T, EPL>(row, lane), dst);
-}
-
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
+// How a warp is laid over keys and head dimension.  L lanes share one key: lane `sub` of a
+// group holds the elements [v * 8 L + 8 sub, + 8) for v < VEC of that key's row (16-byte
+// loads; the L lanes of a group read whole 128-byte lines).  A warp therefore takes G = 32 / L
+// keys per step, a dot product needs log2(L) shuffle steps - shared by the G keys - instead of
+// five per key, and every group keeps its own online-softmax state (maximum, sum, its slice
+// of the accumulator), merged once at the end: nothing crosses groups in the loop.
+template <int D, int R>
+struct DecodeLayout {
+  static constexpr int L = (D == 128 && R > 4) ? 16 : 8;   // eight rows: halve the accumulator slice
+  static constexpr int G = 32 / L;
+  static constexpr int EPL = D / L;        // 16 or 8 elements per lane
+  static constexpr int VEC = EPL / 8;      // 16-byte loads per row and lane
+  // steps per batch: 16 keys (2 x 4 KB of rows) in flight per warp; 32 keys for one or two
+  // rows, whose accumulators leave the registers for it
+  static constexpr int KS = (R <= 2 ? 32 : 16) / G;
+};
 
 // The CTA-wide partial softmax state of the keys [c0, c1) of one (batch, KV head) for up to R
 // query rows: on return cta_ml[r] = running maximum, cta_ml[R + r] = running sum and
 // cta_acc[r * D + d] = unnormalised output, in shared memory, visible to the whole CTA.
+// q_smem: R * D floats of scratch (the pre-scaled query rows).
 template <typename T, int D, int R, int WARPS>
 __device__ __forceinline__ void decode_cta_partial(const DecodeParams& p, int b, int hkv, int c0, int c1,
-                                                   float* cta_ml, float* cta_acc) {
-  constexpr int EPL = D / 32;
+                                                   float* cta_ml, float* cta_acc, float* q_smem) {
+  using Lay = DecodeLayout<D, R>;
+  constexpr int L = Lay::L, G = Lay::G, EPL = Lay::EPL, VEC = Lay::VEC, KS = Lay::KS;
+  constexpr int KPB = KS * G;   // keys per warp and batch
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int grp = lane / L, sub = lane % L;
   const T* kbase = static_cast<const T*>(p.k) + b * p.k_stride_b + hkv * p.k_stride_h;
   const T* vbase = static_cast<const T*>(p.v) + b * p.v_stride_b + hkv * p.v_stride_h;
 
+  // K / V rows in 16-byte units; this lane's first element of the key `grp` of step 0
+  const int64_t kstep = p.k_stride_s / 8, vstep = p.v_stride_s / 8;
+  const uint4* k16 = reinterpret_cast<const uint4*>(kbase) + sub;
+  const uint4* v16 = reinterpret_cast<const uint4*>(vbase) + sub;
+
+  uint4 kreg[KS][VEC], vreg[KS][VEC];
+  // FULL: the whole batch lies inside [c0, c1) (one multiply per batch, adds per step);
+  // otherwise rows past the end repeat the last key of the chunk and are masked below
+  auto load_rows = [&](const uint4* base16, int64_t step16, int base, bool full, uint4 (&reg)[KS][VEC]) {
+    if (full) {
+      const uint4* row = base16 + static_cast<int64_t>(base + grp) * step16;
+#pragma unroll
+      for (int st = 0; st < KS; ++st) {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) reg[st][v] = __ldg(row + v * L);
+        row += G * step16;
+      }
+    } else {
+#pragma unroll
+      for (int st = 0; st < KS; ++st) {
+        const uint4* row = base16 + static_cast<int64_t>(min(base + st * G + grp, c1 - 1)) * step16;
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) reg[st][v] = __ldg(row + v * L);
+      }
+    }
+  };
+  int base = c0 + warp * KPB;
+  if (base < c1) {   // in flight before anything else is fetched
+    load_rows(k16, kstep, base, base + KPB <= c1, kreg);
+    load_rows(v16, vstep, base, base + KPB <= c1, vreg);
+  }
+
+  // Query rows of this KV head, pre-scaled, to shared memory; row r = g * sq + s (head
+  // hkv * group + g, query s).  Layout [row][v][half][sub][4]: the eight (sixteen) lanes of a
+  // group read consecutive 16-byte pieces, so a 128-bit load has no bank conflicts.
+  for (int idx = threadIdx.x; idx < R * D; idx += WARPS * 32) {
+    const int r = idx / D, d = idx % D;
+    float qf = 0.f;
+    if (r < p.rows) {
+      const int g = r / p.sq, sq_i = r % p.sq;
+      const T* qrow = static_cast<const T*>(p.q) + b * p.q_stride_b +
+                      static_cast<int64_t>(hkv * p.group + g) * p.q_stride_h + sq_i * p.q_stride_s;
+      qf = to_float<T>(qrow[d]) * p.scale_log2;
+    }
+    const int v = d / (8 * L), lane_sub = (d / 8) % L, j = d % 8;
+    q_smem[r * D + ((v * 2 + j / 4) * L + lane_sub) * 4 + (j % 4)] = qf;
+  }
+  __syncthreads();
+
   float m_run[R], l_run[R], acc[R][EPL];
+  int row_pos[R];   // last key a row may see under the causal mask
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     m_run[r] = -INFINITY;
     l_run[r] = 0.f;
+    row_pos[r] = p.input_pos + (r % p.sq);
 #pragma unroll
     for (int e = 0; e < EPL; ++e) acc[r][e] = 0.f;
   }
+  // every key of the chunk visible to every row (always so for a decode step), all R rows real
+  const bool plain = (!p.causal || c1 - 1 <= p.input_pos) && p.rows == R;
 
-  // Keys are taken KB at a time: the K and V rows of a batch are all requested before any
-  // arithmetic, so a warp keeps 2 * KB rows (4 - 8 KB) in flight and four CTAs fit an SM; that is what hides the
-  // HBM latency when the whole problem is a few megabytes.
-  constexpr int KB = (R <= 2) ? 16 : 8;
-  RawRow<EPL> kreg[KB], vreg[KB];
-  auto load_batch = [&](int base) {
-    const int last = min(KB, c1 - base) - 1;   // rows past the end repeat the last one, masked below
+  // One batch: PLAIN = no masks and no row predicates.
+  auto batch = [&](auto plain_tag, bool full) {
+    constexpr bool PLAIN = decltype(plain_tag)::value;
+    // scores of this group's key in every step, for every row (two partial sums per dot
+    // product: half the dependent chain)
+    float sc[R][KS];
 #pragma unroll
-    for (int j = 0; j < KB; ++j)
-      kreg[j] = load_raw<T, EPL>(kbase + static_cast<int64_t>(base + min(j, last)) * p.k_stride_s, lane);
-#pragma unroll
-    for (int j = 0; j < KB; ++j)
-      vreg[j] = load_raw<T, EPL>(vbase + static_cast<int64_t>(base + min(j, last)) * p.v_stride_s, lane);
-  };
-  int base = c0 + warp * KB;
-  if (base < c1) load_batch(base);   // in flight before anything else is fetched
-
-  // query rows of this KV head, pre-scaled; row r = g * sq + s  (head hkv * group + g, query s)
-  float qv[R][EPL];
-#pragma unroll
-  for (int r = 0; r < R; ++r) {
-    if (r < p.rows) {
-      const int g = r / p.sq, s = r % p.sq;
-      const T* qrow = static_cast<const T*>(p.q) + b * p.q_stride_b +
-                      static_cast<int64_t>(hkv * p.group + g) * p.q_stride_h + s * p.q_stride_s;
-      load_row<T, EPL>(qrow, lane, qv[r]);
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) qv[r][e] *= p.scale_log2;
-    } else {
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) qv[r][e] = 0.f;
-    }
-  }
-
-  while (base < c1) {
-    const int nk = min(KB, c1 - base);
-    // scores: lane j ends up with the score of key base + j for every row
-    float s_mine[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) s_mine[r] = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < KB; ++j) {
+    for (int st = 0; st < KS; ++st) {
       float kf[EPL];
-      widen<T, EPL>(kreg[j], kf);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) widen8<T>(kreg[st][v], kf + v * 8);
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        if (r < p.rows) {
-          float part = 0.f;
+        float p0 = 0.f, p1 = 0.f;
+        if (PLAIN || r < p.rows) {
 #pragma unroll
-          for (int e = 0; e < EPL; ++e) part = fmaf(qv[r][e], kf[e], part);
-          part = warp_sum(part);
-          if (lane == j) s_mine[r] = part;
+          for (int v = 0; v < VEC; ++v) {
+            const float4 q0 = *reinterpret_cast<const float4*>(q_smem + r * D + ((v * 2 + 0) * L + sub) * 4);
+            const float4 q1 = *reinterpret_cast<const float4*>(q_smem + r * D + ((v * 2 + 1) * L + sub) * 4);
+            p0 = fmaf(q0.x, kf[v * 8 + 0], p0);
+            p1 = fmaf(q1.x, kf[v * 8 + 4], p1);
+            p0 = fmaf(q0.y, kf[v * 8 + 1], p0);
+            p1 = fmaf(q1.y, kf[v * 8 + 5], p1);
+            p0 = fmaf(q0.z, kf[v * 8 + 2], p0);
+            p1 = fmaf(q1.z, kf[v * 8 + 6], p1);
+            p0 = fmaf(q0.w, kf[v * 8 + 3], p0);
+            p1 = fmaf(q1.w, kf[v * 8 + 7], p1);
+          }
         }
+        sc[r][st] = p0 + p1;
       }
     }
-    float pr[R];
+    const int next = base + WARPS * KPB;
+    // the K registers are free: next batch's keys are fetched behind the P V below
+    if (next < c1) load_rows(k16, kstep, next, next + KPB <= c1, kreg);
+#pragma unroll
+    for (int o = L / 2; o > 0; o >>= 1) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+#pragma unroll
+        for (int st = 0; st < KS; ++st) sc[r][st] += __shfl_xor_sync(0xffffffffu, sc[r][st], o);
+      }
+    }
+    // online softmax of this group's KS keys, per row
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      pr[r] = 0.f;
-      if (r < p.rows) {
-        const int kp = base + lane;
-        bool valid = lane < nk;
-        if (p.causal) valid = valid && (kp <= p.input_pos + (r % p.sq));
-        const float s = valid ? s_mine[r] : -INFINITY;
-        const float m_new = fmaxf(m_run[r], warp_max(s));
-        if (m_new != -INFINITY) {   // otherwise every key so far is masked for this row
-          const float corr = exp2f(m_run[r] - m_new);   // exp2(-inf) = 0 on the first block
-          pr[r] = valid ? exp2f(s - m_new) : 0.f;
-          l_run[r] = l_run[r] * corr + warp_sum(pr[r]);
+      if (PLAIN || r < p.rows) {
+        float m_new = m_run[r];
+#pragma unroll
+        for (int st = 0; st < KS; ++st) {
+          if (!PLAIN || !full) {
+            const int key = base + st * G + grp;
+            if (key >= c1 || (!PLAIN && p.causal && key > row_pos[r])) sc[r][st] = -INFINITY;
+          }
+          m_new = fmaxf(m_new, sc[r][st]);
+        }
+        if (m_new > m_run[r]) {   // also the first block: exp2(-inf) = 0
+          const float corr = decode_exp2(m_run[r] - m_new);
+          l_run[r] *= corr;
 #pragma unroll
           for (int e = 0; e < EPL; ++e) acc[r][e] *= corr;
           m_run[r] = m_new;
         }
-      }
-    }
 #pragma unroll
-    for (int j = 0; j < KB; ++j) {
-      float vf[EPL];
-      widen<T, EPL>(vreg[j], vf);
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        if (r < p.rows) {
-          const float pj = __shfl_sync(0xffffffffu, pr[r], j);   // 0 for masked / repeated rows
-#pragma unroll
-          for (int e = 0; e < EPL; ++e) acc[r][e] = fmaf(pj, vf[e], acc[r][e]);
+        for (int st = 0; st < KS; ++st) {
+          // a masked key (or every key so far masked, m_new = -inf) weighs 0, not exp2(nan)
+          float w = decode_exp2(sc[r][st] - m_new);
+          if ((!PLAIN || !full) && sc[r][st] == -INFINITY) w = 0.f;
+          sc[r][st] = w;
+          l_run[r] += w;
         }
       }
     }
-    base += WARPS * KB;
-    if (base < c1) load_batch(base);
+#pragma unroll
+    for (int st = 0; st < KS; ++st) {
+      float vf[EPL];
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) widen8<T>(vreg[st][v], vf + v * 8);
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        if (PLAIN || r < p.rows) {
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) acc[r][e] = fmaf(sc[r][st], vf[e], acc[r][e]);
+        }
+      }
+    }
+    base = next;
+    if (base < c1) load_rows(v16, vstep, base, base + KPB <= c1, vreg);
+  };
+
+  while (base < c1) {
+    const bool full = base + KPB <= c1;
+    if (plain) batch(std::true_type{}, full);
+    else batch(std::false_type{}, full);
+  }
+
+  // merge the G groups of the warp (same rule as between warps and between CTAs)
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float m_all = m_run[r];
+#pragma unroll
+    for (int o = L; o < 32; o <<= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, o));
+    const float f = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - m_all);
+    float l = l_run[r] * f;
+#pragma unroll
+    for (int o = L; o < 32; o <<= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      float a = acc[r][e] * f;
+#pragma unroll
+      for (int o = L; o < 32; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+      acc[r][e] = a;
+    }
+    m_run[r] = m_all;
+    l_run[r] = l;
   }
 
   // merge the warps
@@ -205,8 +283,10 @@ __device__ __forceinline__ void decode_cta_partial(const DecodeParams& p, int b,
       sm_m[warp][r] = m_run[r];
       sm_l[warp][r] = l_run[r];
     }
+    if (grp == 0) {
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) sm_acc[warp][r][lane * EPL + e] = acc[r][e];
+      for (int e = 0; e < EPL; ++e) sm_acc[warp][r][(e / 8) * 8 * L + sub * 8 + (e % 8)] = acc[r][e];
+    }
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < p.rows * D; idx += WARPS * 32) {
@@ -233,14 +313,16 @@ __device__ __forceinline__ void decode_cta_partial(const DecodeParams& p, int b,
 // Split-KV, two kernels: grid (splits, batch * heads_kv); every CTA writes its partial
 // [max, sum, acc[D]] per row to scratch memory.  R = compile-time bound on the query rows.
 template <typename T, int D, int R>
-__global__ void __launch_bounds__(kDecThreads, 4)
+__global__ void __launch_bounds__(kDecThreads, 2)
 fmha_decode_kernel(const DecodeParams p) {
   __shared__ float cta_ml[2 * R];
   __shared__ float cta_acc[R * D];
+  __shared__ __align__(16) float q_smem[R * D];
+  pdl_launch_dependents();   // the merge kernel may be set up now; it waits for this grid
   const int split = blockIdx.x;
   const int b = blockIdx.y / p.heads_kv, hkv = blockIdx.y % p.heads_kv;
   const int c0 = split * p.chunk;
-  decode_cta_partial<T, D, R, kDecWarps>(p, b, hkv, c0, min(p.sk, c0 + p.chunk), cta_ml, cta_acc);
+  decode_cta_partial<T, D, R, kDecWarps>(p, b, hkv, c0, min(p.sk, c0 + p.chunk), cta_ml, cta_acc, q_smem);
   for (int idx = threadIdx.x; idx < p.rows * D; idx += kDecThreads) {
     const int r = idx / D, d = idx % D;
     float* dst = p.ws + ((static_cast<int64_t>(blockIdx.y) * p.rows + r) * p.splits + split) * (D + 2);
@@ -252,39 +334,48 @@ fmha_decode_kernel(const DecodeParams p) {
   }
 }
 
-// Split-KV, one kernel: the eight CTAs of a cluster share one (batch, KV head); after its
-// chunk every CTA leaves its partial in shared memory, and each CTA merges D / 8 output
-// columns of all rows by reading the eight partials over distributed shared memory.
-constexpr int kClusterSplits = 8;
-constexpr int kClusterThreads = 256;
+// Split-KV, one kernel: the CTAs of a cluster (1, 2, 4 or 8, chosen at launch) share one
+// (batch, KV head); after its chunk every CTA leaves its partial in shared memory, and each
+// CTA merges D / cluster-size output columns of all rows by reading the partials over
+// distributed shared memory.
+constexpr int kMaxClusterSplits = 8;
+constexpr int kClusterThreads = 128;
 
 template <typename T, int D, int R>
-__global__ void __cluster_dims__(kClusterSplits, 1, 1) __launch_bounds__(kClusterThreads, 2)
+__global__ void __launch_bounds__(kClusterThreads, 2)
 fmha_decode_cluster_kernel(const DecodeParams p) {
   __shared__ float cta_ml[2 * R];
   __shared__ float cta_acc[R * D];
+  __shared__ __align__(16) float q_smem[R * D];
   const int split = static_cast<int>(cluster_ctarank());
+  const int cs = p.splits;   // == the cluster size of this launch
   const int b = blockIdx.y / p.heads_kv, hkv = blockIdx.y % p.heads_kv;
   const int c0 = split * p.chunk;
-  decode_cta_partial<T, D, R, kClusterThreads / 32>(p, b, hkv, c0, min(p.sk, c0 + p.chunk), cta_ml, cta_acc);
+  decode_cta_partial<T, D, R, kClusterThreads / 32>(p, b, hkv, c0, min(p.sk, c0 + p.chunk), cta_ml, cta_acc,
+                                                    q_smem);
   cluster_sync_all();   // every partial of the cluster is in place
-  constexpr int kCols = D / kClusterSplits;
+  const int cols = D / cs;
   const uint32_t ml_addr = smem_u32(cta_ml), acc_addr = smem_u32(cta_acc);
-  for (int idx = threadIdx.x; idx < p.rows * kCols; idx += kClusterThreads) {
-    const int r = idx / kCols, d = split * kCols + idx % kCols;
-    float ms[kClusterSplits];
+  for (int idx = threadIdx.x; idx < p.rows * cols; idx += kClusterThreads) {
+    const int r = idx / cols, d = split * cols + idx % cols;
+    float ms[kMaxClusterSplits];
     float m = -INFINITY;
 #pragma unroll
-    for (int c = 0; c < kClusterSplits; ++c) {
-      ms[c] = ld_shared_cluster_f32(map_to_cta(ml_addr + 4u * r, c));
-      m = fmaxf(m, ms[c]);
+    for (int c = 0; c < kMaxClusterSplits; ++c) {
+      ms[c] = -INFINITY;
+      if (c < cs) {
+        ms[c] = ld_shared_cluster_f32(map_to_cta(ml_addr + 4u * r, c));
+        m = fmaxf(m, ms[c]);
+      }
     }
     float l = 0.f, o = 0.f;
 #pragma unroll
-    for (int c = 0; c < kClusterSplits; ++c) {
-      const float f = (ms[c] == -INFINITY) ? 0.f : exp2f(ms[c] - m);
-      l += ld_shared_cluster_f32(map_to_cta(ml_addr + 4u * (R + r), c)) * f;
-      o += ld_shared_cluster_f32(map_to_cta(acc_addr + 4u * (r * D + d), c)) * f;
+    for (int c = 0; c < kMaxClusterSplits; ++c) {
+      if (c < cs) {
+        const float f = (ms[c] == -INFINITY) ? 0.f : exp2f(ms[c] - m);
+        l += ld_shared_cluster_f32(map_to_cta(ml_addr + 4u * (R + r), c)) * f;
+        o += ld_shared_cluster_f32(map_to_cta(acc_addr + 4u * (r * D + d), c)) * f;
+      }
     }
     const int g = r / p.sq, sidx = r % p.sq;
     T* orow = static_cast<T*>(p.out) + b * p.o_stride_b + static_cast<int64_t>(hkv * p.group + g) * p.o_stride_h +
@@ -308,6 +399,7 @@ fmha_decode_merge_kernel(const DecodeParams p) {
   // one round trip for all maxima and sums, one (unrolled) for the accumulators
   __shared__ float sm_m[kMaxMergeSplits], sm_f[kMaxMergeSplits];
   __shared__ float sm_l;
+  pdl_wait();   // the partial results come from the kernel launched just before
   for (int s = d; s < p.splits; s += D) {
     sm_m[s] = src[s * (D + 2)];
     sm_f[s] = src[s * (D + 2) + 1];
@@ -338,18 +430,28 @@ fmha_decode_merge_kernel(const DecodeParams p) {
 
 struct DecodePlan {
   int splits, chunk;
-  bool cluster;    // one kernel, eight CTAs per (batch, KV head) merged over DSMEM
+  bool cluster;    // one kernel, `splits` CTAs per (batch, KV head) merged over DSMEM
 };
 
 DecodePlan plan_decode(int64_t batch, int64_t heads_kv, int64_t sk, int sms) {
   const int64_t groups = batch * heads_kv;
   DecodePlan plan;
-  // enough (batch, KV head) pairs to fill the GPU with clusters of eight: no scratch, no
-  // second launch
-  if (groups * kClusterSplits >= sms) {
+  int forced = 0;   // B200K_DECODE_PLAN=1|2|4|8 (cluster size) or s (two kernels): measurements
+  bool force_two = false;
+  if (const char* e = getenv("B200K_DECODE_PLAN")) {
+    if (e[0] == 's') force_two = true;
+    else forced = atoi(e);
+  }
+  // One kernel, no scratch: the smallest cluster that gives every SM a CTA of four warps.
+  // More CTAs than that only add rounds of launch, warp merge and cluster barriers.
+  if (!force_two && (forced > 0 || groups * kMaxClusterSplits * 2 >= sms)) {
+    int cs = 1;
+    while (cs < kMaxClusterSplits && groups * cs < sms) cs *= 2;
+    while (cs > 1 && ceil_div(sk, cs) < 64) cs /= 2;   // at least 64 keys per CTA
+    if (forced > 0) cs = forced;
     plan.cluster = true;
-    plan.splits = kClusterSplits;
-    plan.chunk = static_cast<int>(ceil_div(ceil_div(sk, kClusterSplits), 16) * 16);
+    plan.splits = cs;
+    plan.chunk = static_cast<int>(ceil_div(ceil_div(sk, cs), 16) * 16);
     return plan;
   }
   plan.cluster = false;
@@ -369,11 +471,24 @@ template <typename T, int D>
 int launch_decode(const DecodeParams& p, bool cluster, int64_t batch, cudaStream_t stream) {
   const dim3 grid(p.splits, static_cast<unsigned>(batch * p.heads_kv));
   if (cluster) {
-    if (p.rows <= 1) fmha_decode_cluster_kernel<T, D, 1><<<grid, kClusterThreads, 0, stream>>>(p);
-    else if (p.rows <= 2) fmha_decode_cluster_kernel<T, D, 2><<<grid, kClusterThreads, 0, stream>>>(p);
-    else if (p.rows <= 4) fmha_decode_cluster_kernel<T, D, 4><<<grid, kClusterThreads, 0, stream>>>(p);
-    else fmha_decode_cluster_kernel<T, D, 8><<<grid, kClusterThreads, 0, stream>>>(p);
-    B200K_CHECK_LAUNCH("fmha decode (cluster) launch");
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(p.splits);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kClusterThreads);
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e;
+    if (p.rows <= 1) e = cudaLaunchKernelEx(&cfg, fmha_decode_cluster_kernel<T, D, 1>, p);
+    else if (p.rows <= 2) e = cudaLaunchKernelEx(&cfg, fmha_decode_cluster_kernel<T, D, 2>, p);
+    else if (p.rows <= 4) e = cudaLaunchKernelEx(&cfg, fmha_decode_cluster_kernel<T, D, 4>, p);
+    else e = cudaLaunchKernelEx(&cfg, fmha_decode_cluster_kernel<T, D, 8>, p);
+    if (e != cudaSuccess)
+      return fail(B200K_CUDA_ERROR, "fmha decode (cluster of %d) launch: %s", p.splits, cudaGetErrorString(e));
     return B200K_OK;
   }
   if (p.rows <= 1) fmha_decode_kernel<T, D, 1><<<grid, kDecThreads, 0, stream>>>(p);
@@ -381,8 +496,10 @@ int launch_decode(const DecodeParams& p, bool cluster, int64_t batch, cudaStream
   else if (p.rows <= 4) fmha_decode_kernel<T, D, 4><<<grid, kDecThreads, 0, stream>>>(p);
   else fmha_decode_kernel<T, D, 8><<<grid, kDecThreads, 0, stream>>>(p);
   B200K_CHECK_LAUNCH("fmha decode launch");
-  fmha_decode_merge_kernel<T, D><<<static_cast<unsigned>(batch * p.heads_kv * p.rows), D, 0, stream>>>(p);
-  B200K_CHECK_LAUNCH("fmha decode merge launch");
+  const cudaError_t e = launch_after_predecessor(fmha_decode_merge_kernel<T, D>,
+                                                 dim3(static_cast<unsigned>(batch * p.heads_kv * p.rows)), dim3(D), 0,
+                                                 stream, p);
+  if (e != cudaSuccess) return fail(B200K_CUDA_ERROR, "fmha decode merge launch: %s", cudaGetErrorString(e));
   return B200K_OK;
 }
 
@@ -396,7 +513,13 @@ int64_t visible_keys(const b200k_fmha_args* a) {
 }  // namespace
 
 bool fmha_decode_applies(const b200k_fmha_args* a) {
-  return a->seq_q * a->query_group_size <= kFmhaDecodeMaxRows && a->batch * a->heads_kv <= 65535;
+  // K and V rows are read with 16-byte loads
+  const auto rows16 = [](const void* base, int64_t sb, int64_t sh, int64_t ss) {
+    return (reinterpret_cast<uintptr_t>(base) & 15) == 0 && sb % 8 == 0 && sh % 8 == 0 && ss % 8 == 0;
+  };
+  return a->seq_q * a->query_group_size <= kFmhaDecodeMaxRows && a->batch * a->heads_kv <= 65535 &&
+         rows16(a->k, a->k_stride_b, a->k_stride_h, a->k_stride_s) &&
+         rows16(a->v, a->v_stride_b, a->v_stride_h, a->v_stride_s);
 }
 
 int64_t fmha_decode_workspace_bytes(const b200k_fmha_args* a, int sms) {

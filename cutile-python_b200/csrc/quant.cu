@@ -266,6 +266,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 absmax_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t ldx,
               uint32_t* __restrict__ amax_bits) {
+  pdl_launch_dependents();   // the quantising kernel may be set up now; it waits for this grid
   float m = block_strided_absmax<T>(x, k, ldx, 0, rows * k,
                                     blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x,
                                     static_cast<int64_t>(gridDim.x) * blockDim.x);
@@ -290,6 +291,7 @@ nvfp4_quantize_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t 
                       uint8_t* __restrict__ q, int64_t ldq_bytes, uint8_t* __restrict__ sf_logical,
                       uint8_t* __restrict__ sf_swizzled, int64_t k_atoms,
                       const uint32_t* __restrict__ amax_bits, float* __restrict__ tensor_scale) {
+  pdl_wait();   // the maximum comes from the kernel launched just before
   const float amax_t = __uint_as_float(*amax_bits);
   const float s_t = __fdiv_rn(amax_t, 2688.0f);  // 448 * 6
   if (blockIdx.x == 0 && threadIdx.x == 0 && tensor_scale != nullptr) *tensor_scale = s_t;
@@ -485,12 +487,15 @@ void launch_nvfp4_quantize(const b200k_quantize_args* a, const uint32_t* amax, c
                      ((a->ldx * sizeof(T)) % 16 == 0) && (reinterpret_cast<uintptr_t>(q) % 16 == 0) &&
                      (a->ldq % 16 == 0) && (reinterpret_cast<uintptr_t>(sl) % 2 == 0) &&
                      (reinterpret_cast<uintptr_t>(ss) % 2 == 0);
+  // (errors of these launches surface through the caller's cudaGetLastError check)
   if (pairs) {
-    nvfp4_quantize_kernel<T, 2><<<grid_for(a->rows * kblocks / 2, 256), 256, 0, stream>>>(
-        x, a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, amax, a->tensor_scale);
+    launch_after_predecessor(nvfp4_quantize_kernel<T, 2>, dim3(grid_for(a->rows * kblocks / 2, 256)), dim3(256), 0,
+                             stream, x, a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, amax,
+                             a->tensor_scale);
   } else {
-    nvfp4_quantize_kernel<T, 1><<<grid_for(a->rows * kblocks, 256), 256, 0, stream>>>(
-        x, a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, amax, a->tensor_scale);
+    launch_after_predecessor(nvfp4_quantize_kernel<T, 1>, dim3(grid_for(a->rows * kblocks, 256)), dim3(256), 0,
+                             stream, x, a->rows, a->k, a->ldx, q, a->ldq, sl, ss, a->sf_k_atoms, amax,
+                             a->tensor_scale);
   }
 }
 
