@@ -1,14 +1,15 @@
 // Attention forward for a handful of query rows per key/value head (decode steps, short
-// query chunks, grouped-query heads that share one KV head): HBM-bound, so no tensor
-// cores.  The keys of one (batch, KV head) are split over several CTAs ("flash
-// decoding"): every CTA streams its chunk of K and V once, keeps an online softmax per
-// query row and writes an unnormalised partial (max, sum, accumulator) to scratch memory;
-// a second kernel merges the partials.
+// query chunks, grouped-query heads that share one KV head): HBM-bound.  The keys of one
+// (batch, KV head) are split over several CTAs ("flash decoding"): every CTA streams its
+// chunk of K and V once, straight from global memory into MMA fragments (no shared-memory
+// staging, no TMA), keeps an online softmax per query row and leaves an unnormalised partial
+// (max, sum, accumulator); the partials are merged over distributed shared memory by the
+// CTAs of a cluster, or by a second kernel.
 //
 // Same semantics as the tensor-core kernels in fmha.cu (reference:
 // test/kernels/attention.py:20-128): scores in the exp2 domain, causal mask with query
-// positions offset by input_pos, grouped-query heads by integer division.  P stays in
-// fp32 here (the tensor-core path rounds it to the input type before P V).
+// positions offset by input_pos, grouped-query heads by integer division, P rounded to the
+// input type before P V.
 #include "fmha_decode.h"
 
 #include <cuda_bf16.h>
@@ -55,237 +56,265 @@ __device__ __forceinline__ float decode_exp2(float x) {   // exp2(-inf) = 0
   return y;
 }
 
-// Eight 16-bit elements (one 16-byte load) widened to fp32.
-template <typename T>
-__device__ __forceinline__ void widen8(const uint4& raw, float* dst) {
-  const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) dst[i] = to_float<T>(e[i]);
+// ---- tensor-core fragments (legacy mma.sync m16n8k16: the work is HBM-bound, the point is
+// the instruction count - one MMA replaces 8 x 16 x 16 fused multiply-adds spread over a
+// warp's CUDA cores, conversions and shuffles included) -------------------------------------
+template <typename T> struct Frag;
+template <> struct Frag<__half> {
+  static __device__ __forceinline__ void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+};
+template <> struct Frag<__nv_bfloat16> {
+  static __device__ __forceinline__ void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+};
+// 8 x 8 transpose of 16-bit elements inside a warp: lane (g, t) gives row g, columns 2t, 2t+1
+// and receives the same of the transposed matrix.
+__device__ __forceinline__ uint32_t transpose_8x8_b16(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t comp(const uint4& v, int i) {
+  return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
 }
 
-// How a warp is laid over keys and head dimension.  L lanes share one key: lane `sub` of a
-// group holds the elements [v * 8 L + 8 sub, + 8) for v < VEC of that key's row (16-byte
-// loads; the L lanes of a group read whole 128-byte lines).  A warp therefore takes G = 32 / L
-// keys per step, a dot product needs log2(L) shuffle steps - shared by the G keys - instead of
-// five per key, and every group keeps its own online-softmax state (maximum, sum, its slice
-// of the accumulator), merged once at the end: nothing crosses groups in the loop.
-template <int D, int R>
-struct DecodeLayout {
-  static constexpr int L = (D == 128 && R > 4) ? 16 : 8;   // eight rows: halve the accumulator slice
-  static constexpr int G = 32 / L;
-  static constexpr int EPL = D / L;        // 16 or 8 elements per lane
-  static constexpr int VEC = EPL / 8;      // 16-byte loads per row and lane
-  // steps per batch: 16 keys (2 x 4 KB of rows) in flight per warp; 32 keys for one or two
-  // rows, whose accumulators leave the registers for it
-  static constexpr int KS = (R <= 2 ? 32 : 16) / G;
-};
+constexpr int kDecRows = kFmhaDecodeMaxRows;   // 8 = the N of the MMAs
 
-// The CTA-wide partial softmax state of the keys [c0, c1) of one (batch, KV head) for up to R
-// query rows: on return cta_ml[r] = running maximum, cta_ml[R + r] = running sum and
+// The CTA-wide partial softmax state of the keys [c0, c1) of one (batch, KV head) for up to
+// eight query rows: on return cta_ml[r] = running maximum, cta_ml[8 + r] = running sum and
 // cta_acc[r * D + d] = unnormalised output, in shared memory, visible to the whole CTA.
-// q_smem: R * D floats of scratch (the pre-scaled query rows).
-template <typename T, int D, int R, int WARPS>
+//
+// A warp takes 16 keys per step, lane = (g, t) = (lane / 4, lane % 4):
+//   S^T (16 keys x 8 rows) = K (16 keys x D) . Q^T       A = K rows g, g + 8; B = Q row g
+//   O^T (D x 8 rows)      += V^T (D x 16 keys) . P^T     A = V^T, B = P^T
+// Both contractions only sum over their K index, so the order of the head dimension inside a
+// k-step (first product) and of the output dimensions (second) is free: lanes read K, Q and V
+// rows as 16-byte vectors and use their 32-bit components directly as fragments, no shuffles,
+// no shared memory.  The S^T accumulator gives lane (g, t) the scores of keys g, g + 8 for the
+// rows 2t, 2t + 1 - the same two rows whose O^T columns the lane holds, so the online-softmax
+// rescale needs no exchange; P^T becomes the B operand of the second product through two
+// 8 x 8 register transposes.  P is rounded to the input type before P V, as in the
+// tensor-core prefill kernels.
+template <typename T, int D, int WARPS>
 __device__ __forceinline__ void decode_cta_partial(const DecodeParams& p, int b, int hkv, int c0, int c1,
-                                                   float* cta_ml, float* cta_acc, float* q_smem) {
-  using Lay = DecodeLayout<D, R>;
-  constexpr int L = Lay::L, G = Lay::G, EPL = Lay::EPL, VEC = Lay::VEC, KS = Lay::KS;
-  constexpr int KPB = KS * G;   // keys per warp and batch
+                                                   float* cta_ml, float* cta_acc) {
+  constexpr int R = kDecRows;
+  constexpr int KV = D / 32;        // 16-byte vectors of a K (or Q) row per lane: dims [(t + 4 i) * 8, + 8)
+  constexpr int VV = D / 64;        // 16-byte vectors of a V row per lane: dims [(g + 8 i) * 8, + 8)
+  constexpr int NB = 2;             // 16-key blocks per step: 2 x 8 KB of rows in flight per warp
+  constexpr int KPB = 16 * NB;      // keys per warp and step
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int grp = lane / L, sub = lane % L;
+  const int g = lane >> 2, t = lane & 3;
   const T* kbase = static_cast<const T*>(p.k) + b * p.k_stride_b + hkv * p.k_stride_h;
   const T* vbase = static_cast<const T*>(p.v) + b * p.v_stride_b + hkv * p.v_stride_h;
+  const int64_t kstep = p.k_stride_s / 8, vstep = p.v_stride_s / 8;   // rows in 16-byte units
+  const uint4* k16 = reinterpret_cast<const uint4*>(kbase) + t;
+  const uint4* v16 = reinterpret_cast<const uint4*>(vbase) + g;
 
-  // K / V rows in 16-byte units; this lane's first element of the key `grp` of step 0
-  const int64_t kstep = p.k_stride_s / 8, vstep = p.v_stride_s / 8;
-  const uint4* k16 = reinterpret_cast<const uint4*>(kbase) + sub;
-  const uint4* v16 = reinterpret_cast<const uint4*>(vbase) + sub;
-
-  uint4 kreg[KS][VEC], vreg[KS][VEC];
-  // FULL: the whole batch lies inside [c0, c1) (one multiply per batch, adds per step);
-  // otherwise rows past the end repeat the last key of the chunk and are masked below
-  auto load_rows = [&](const uint4* base16, int64_t step16, int base, bool full, uint4 (&reg)[KS][VEC]) {
-    if (full) {
-      const uint4* row = base16 + static_cast<int64_t>(base + grp) * step16;
+  uint4 kreg[NB][2][KV];   // per block: keys blk + g, blk + g + 8
+  uint4 vreg[NB][4][VV];   // per block: keys blk + 2t, 2t + 1, 2t + 8, 2t + 9
+  // rows past the end of the chunk repeat its last key; they are masked below
+  auto load_k = [&](int base) {
 #pragma unroll
-      for (int st = 0; st < KS; ++st) {
+    for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
-        for (int v = 0; v < VEC; ++v) reg[st][v] = __ldg(row + v * L);
-        row += G * step16;
+      for (int j = 0; j < 2; ++j) {
+        const uint4* row = k16 + static_cast<int64_t>(min(base + 16 * nb + g + 8 * j, c1 - 1)) * kstep;
+#pragma unroll
+        for (int i = 0; i < KV; ++i) kreg[nb][j][i] = __ldg(row + 4 * i);
       }
-    } else {
+    }
+  };
+  auto load_v = [&](int base) {
 #pragma unroll
-      for (int st = 0; st < KS; ++st) {
-        const uint4* row = base16 + static_cast<int64_t>(min(base + st * G + grp, c1 - 1)) * step16;
+    for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
-        for (int v = 0; v < VEC; ++v) reg[st][v] = __ldg(row + v * L);
+      for (int j = 0; j < 4; ++j) {
+        const int key = base + 16 * nb + 2 * t + (j & 1) + 8 * (j >> 1);
+        const uint4* row = v16 + static_cast<int64_t>(min(key, c1 - 1)) * vstep;
+#pragma unroll
+        for (int i = 0; i < VV; ++i) vreg[nb][j][i] = __ldg(row + 8 * i);
       }
     }
   };
   int base = c0 + warp * KPB;
   if (base < c1) {   // in flight before anything else is fetched
-    load_rows(k16, kstep, base, base + KPB <= c1, kreg);
-    load_rows(v16, vstep, base, base + KPB <= c1, vreg);
+    load_k(base);
+    load_v(base);
   }
 
-  // Query rows of this KV head, pre-scaled, to shared memory; row r = g * sq + s (head
-  // hkv * group + g, query s).  Layout [row][v][half][sub][4]: the eight (sixteen) lanes of a
-  // group read consecutive 16-byte pieces, so a 128-bit load has no bank conflicts.
-  for (int idx = threadIdx.x; idx < R * D; idx += WARPS * 32) {
-    const int r = idx / D, d = idx % D;
-    float qf = 0.f;
-    if (r < p.rows) {
-      const int g = r / p.sq, sq_i = r % p.sq;
-      const T* qrow = static_cast<const T*>(p.q) + b * p.q_stride_b +
-                      static_cast<int64_t>(hkv * p.group + g) * p.q_stride_h + sq_i * p.q_stride_s;
-      qf = to_float<T>(qrow[d]) * p.scale_log2;
-    }
-    const int v = d / (8 * L), lane_sub = (d / 8) % L, j = d % 8;
-    q_smem[r * D + ((v * 2 + j / 4) * L + lane_sub) * 4 + (j % 4)] = qf;
-  }
-  __syncthreads();
-
-  float m_run[R], l_run[R], acc[R][EPL];
-  int row_pos[R];   // last key a row may see under the causal mask
+  // this lane's query row g (row r = grp * sq + s: head hkv * group + grp, query s), raw
+  uint4 qreg[KV];
+  {
+    const bool real = g < p.rows;
+    const int grp = real ? g / p.sq : 0, s_i = real ? g % p.sq : 0;
+    const T* qrow = static_cast<const T*>(p.q) + b * p.q_stride_b +
+                    static_cast<int64_t>(hkv * p.group + grp) * p.q_stride_h + s_i * p.q_stride_s;
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    m_run[r] = -INFINITY;
-    l_run[r] = 0.f;
-    row_pos[r] = p.input_pos + (r % p.sq);
+    for (int i = 0; i < KV; ++i) {
+      qreg[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (real) {
+        // the query row need not be 16-byte aligned: element loads, once per CTA and lane
+        const T* src = qrow + (t + 4 * i) * 8;
+        uint32_t w[4];
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) acc[r][e] = 0.f;
-  }
-  // every key of the chunk visible to every row (always so for a decode step), all R rows real
-  const bool plain = (!p.causal || c1 - 1 <= p.input_pos) && p.rows == R;
-
-  // One batch: PLAIN = no masks and no row predicates.
-  auto batch = [&](auto plain_tag, bool full) {
-    constexpr bool PLAIN = decltype(plain_tag)::value;
-    // scores of this group's key in every step, for every row (two partial sums per dot
-    // product: half the dependent chain)
-    float sc[R][KS];
-#pragma unroll
-    for (int st = 0; st < KS; ++st) {
-      float kf[EPL];
-#pragma unroll
-      for (int v = 0; v < VEC; ++v) widen8<T>(kreg[st][v], kf + v * 8);
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        float p0 = 0.f, p1 = 0.f;
-        if (PLAIN || r < p.rows) {
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) {
-            const float4 q0 = *reinterpret_cast<const float4*>(q_smem + r * D + ((v * 2 + 0) * L + sub) * 4);
-            const float4 q1 = *reinterpret_cast<const float4*>(q_smem + r * D + ((v * 2 + 1) * L + sub) * 4);
-            p0 = fmaf(q0.x, kf[v * 8 + 0], p0);
-            p1 = fmaf(q1.x, kf[v * 8 + 4], p1);
-            p0 = fmaf(q0.y, kf[v * 8 + 1], p0);
-            p1 = fmaf(q1.y, kf[v * 8 + 5], p1);
-            p0 = fmaf(q0.z, kf[v * 8 + 2], p0);
-            p1 = fmaf(q1.z, kf[v * 8 + 6], p1);
-            p0 = fmaf(q0.w, kf[v * 8 + 3], p0);
-            p1 = fmaf(q1.w, kf[v * 8 + 7], p1);
-          }
+        for (int c = 0; c < 4; ++c) {
+          const uint16_t lo = *reinterpret_cast<const uint16_t*>(src + 2 * c);
+          const uint16_t hi = *reinterpret_cast<const uint16_t*>(src + 2 * c + 1);
+          w[c] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
         }
-        sc[r][st] = p0 + p1;
+        qreg[i] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  }
+
+  // rows 2t, 2t + 1 of this lane: softmax state and the last key each may see
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  int row_pos[2];
+#pragma unroll
+  for (int c = 0; c < 2; ++c) row_pos[c] = p.input_pos + ((2 * t + c) % p.sq);
+  float acc[VV * 4][4];   // m-tile (i, jj): dims (g + 8 i) * 8 + 2 jj (+ 1) x rows 2t, 2t + 1
+#pragma unroll
+  for (int m = 0; m < VV * 4; ++m) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[m][c] = 0.f;
+  }
+  // every key of the chunk visible to every row: always so for a decode step
+  const bool unmasked = !p.causal || c1 - 1 <= p.input_pos;
+
+  while (base < c1) {
+    // S^T per block: sc[.][0], [1] = key blk + g x rows 2t, 2t + 1; sc[.][2], [3] = key blk + g + 8
+    float sc[NB][4];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) sc[nb][c] = 0.f;
+#pragma unroll
+      for (int i = 0; i < KV; ++i) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          Frag<T>::mma(sc[nb], comp(kreg[nb][0][i], 2 * h), comp(kreg[nb][1][i], 2 * h),
+                       comp(kreg[nb][0][i], 2 * h + 1), comp(kreg[nb][1][i], 2 * h + 1), comp(qreg[i], 2 * h),
+                       comp(qreg[i], 2 * h + 1));
       }
     }
     const int next = base + WARPS * KPB;
-    // the K registers are free: next batch's keys are fetched behind the P V below
-    if (next < c1) load_rows(k16, kstep, next, next + KPB <= c1, kreg);
+    if (next < c1) load_k(next);   // the K registers are free: next keys behind the softmax and P V
+    const bool mask = !unmasked || base + KPB > c1;
 #pragma unroll
-    for (int o = L / 2; o > 0; o >>= 1) {
+    for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-#pragma unroll
-        for (int st = 0; st < KS; ++st) sc[r][st] += __shfl_xor_sync(0xffffffffu, sc[r][st], o);
-      }
-    }
-    // online softmax of this group's KS keys, per row
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      if (PLAIN || r < p.rows) {
-        float m_new = m_run[r];
-#pragma unroll
-        for (int st = 0; st < KS; ++st) {
-          if (!PLAIN || !full) {
-            const int key = base + st * G + grp;
-            if (key >= c1 || (!PLAIN && p.causal && key > row_pos[r])) sc[r][st] = -INFINITY;
-          }
-          m_new = fmaxf(m_new, sc[r][st]);
-        }
-        if (m_new > m_run[r]) {   // also the first block: exp2(-inf) = 0
-          const float corr = decode_exp2(m_run[r] - m_new);
-          l_run[r] *= corr;
-#pragma unroll
-          for (int e = 0; e < EPL; ++e) acc[r][e] *= corr;
-          m_run[r] = m_new;
-        }
-#pragma unroll
-        for (int st = 0; st < KS; ++st) {
-          // a masked key (or every key so far masked, m_new = -inf) weighs 0, not exp2(nan)
-          float w = decode_exp2(sc[r][st] - m_new);
-          if ((!PLAIN || !full) && sc[r][st] == -INFINITY) w = 0.f;
-          sc[r][st] = w;
-          l_run[r] += w;
+      for (int c = 0; c < 4; ++c) {
+        sc[nb][c] *= p.scale_log2;
+        if (mask) {
+          const int key = base + 16 * nb + g + 8 * (c >> 1);
+          if (key >= c1 || (p.causal && key > row_pos[c & 1])) sc[nb][c] = -INFINITY;
         }
       }
     }
+    // row maxima over the step's keys: 2 NB in this lane, the rest in the lanes of equal t
+    float m_new[2], corr[2];
+    bool grew = false;
 #pragma unroll
-    for (int st = 0; st < KS; ++st) {
-      float vf[EPL];
+    for (int c = 0; c < 2; ++c) {
+      float m = fmaxf(sc[0][c], sc[0][c + 2]);
 #pragma unroll
-      for (int v = 0; v < VEC; ++v) widen8<T>(vreg[st][v], vf + v * 8);
+      for (int nb = 1; nb < NB; ++nb) m = fmaxf(m, fmaxf(sc[nb][c], sc[nb][c + 2]));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+      m_new[c] = fmaxf(m_run[c], m);
+      grew = grew || (m_new[c] > m_run[c]);
+      corr[c] = decode_exp2(m_run[c] - m_new[c]);   // exp2(-inf - x) = 0 on the first block
+      if (m_new[c] == -INFINITY) corr[c] = 1.f;      // every key so far masked: nothing to rescale
+      m_run[c] = m_new[c];
+    }
+    if (__any_sync(0xffffffffu, grew)) {
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        if (PLAIN || r < p.rows) {
+      for (int c = 0; c < 2; ++c) l_run[c] *= corr[c];
 #pragma unroll
-          for (int e = 0; e < EPL; ++e) acc[r][e] = fmaf(sc[r][st], vf[e], acc[r][e]);
+      for (int m = 0; m < VV * 4; ++m) {
+        acc[m][0] *= corr[0];
+        acc[m][1] *= corr[1];
+        acc[m][2] *= corr[0];
+        acc[m][3] *= corr[1];
+      }
+    }
+    const float mref[2] = {m_new[0] == -INFINITY ? 0.f : m_new[0], m_new[1] == -INFINITY ? 0.f : m_new[1]};
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      float pw[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) pw[c] = decode_exp2(sc[nb][c] - mref[c & 1]);   // masked: exp2(-inf) = 0
+      // the sums use the rounded weights, like the prefill kernels
+      const uint32_t p_lo = Frag<T>::pack(pw[0], pw[1]), p_hi = Frag<T>::pack(pw[2], pw[3]);
+      const T* e = reinterpret_cast<const T*>(&p_lo);
+      const T* f = reinterpret_cast<const T*>(&p_hi);
+      l_run[0] += to_float<T>(e[0]) + to_float<T>(f[0]);
+      l_run[1] += to_float<T>(e[1]) + to_float<T>(f[1]);
+      const uint32_t b0 = transpose_8x8_b16(p_lo), b1 = transpose_8x8_b16(p_hi);
+#pragma unroll
+      for (int i = 0; i < VV; ++i) {
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const uint32_t w0 = comp(vreg[nb][0][i], jj), w1 = comp(vreg[nb][1][i], jj);
+          const uint32_t w2 = comp(vreg[nb][2][i], jj), w3 = comp(vreg[nb][3][i], jj);
+          Frag<T>::mma(acc[i * 4 + jj], __byte_perm(w0, w1, 0x5410), __byte_perm(w0, w1, 0x7632),
+                       __byte_perm(w2, w3, 0x5410), __byte_perm(w2, w3, 0x7632), b0, b1);
         }
       }
     }
     base = next;
-    if (base < c1) load_rows(v16, vstep, base, base + KPB <= c1, vreg);
-  };
-
-  while (base < c1) {
-    const bool full = base + KPB <= c1;
-    if (plain) batch(std::true_type{}, full);
-    else batch(std::false_type{}, full);
+    if (base < c1) load_v(base);
   }
 
-  // merge the G groups of the warp (same rule as between warps and between CTAs)
+  // row sums over the lanes of equal t
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    float m_all = m_run[r];
-#pragma unroll
-    for (int o = L; o < 32; o <<= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, o));
-    const float f = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - m_all);
-    float l = l_run[r] * f;
-#pragma unroll
-    for (int o = L; o < 32; o <<= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      float a = acc[r][e] * f;
-#pragma unroll
-      for (int o = L; o < 32; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-      acc[r][e] = a;
-    }
-    m_run[r] = m_all;
-    l_run[r] = l;
+  for (int c = 0; c < 2; ++c) {
+    l_run[c] += __shfl_xor_sync(0xffffffffu, l_run[c], 4);
+    l_run[c] += __shfl_xor_sync(0xffffffffu, l_run[c], 8);
+    l_run[c] += __shfl_xor_sync(0xffffffffu, l_run[c], 16);
   }
 
   // merge the warps
   __shared__ float sm_m[WARPS][R], sm_l[WARPS][R];
   __shared__ float sm_acc[WARPS][R][D];
+  if (g == 0) {
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    if (lane == 0) {
-      sm_m[warp][r] = m_run[r];
-      sm_l[warp][r] = l_run[r];
+    for (int c = 0; c < 2; ++c) {
+      sm_m[warp][2 * t + c] = m_run[c];
+      sm_l[warp][2 * t + c] = l_run[c];
     }
-    if (grp == 0) {
+  }
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) sm_acc[warp][r][(e / 8) * 8 * L + sub * 8 + (e % 8)] = acc[r][e];
+  for (int i = 0; i < VV; ++i) {
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      const int d = (g + 8 * i) * 8 + 2 * jj;
+      const float* a = acc[i * 4 + jj];
+      sm_acc[warp][2 * t][d] = a[0];
+      sm_acc[warp][2 * t + 1][d] = a[1];
+      sm_acc[warp][2 * t][d + 1] = a[2];
+      sm_acc[warp][2 * t + 1][d + 1] = a[3];
     }
   }
   __syncthreads();
@@ -311,18 +340,18 @@ __device__ __forceinline__ void decode_cta_partial(const DecodeParams& p, int b,
 }
 
 // Split-KV, two kernels: grid (splits, batch * heads_kv); every CTA writes its partial
-// [max, sum, acc[D]] per row to scratch memory.  R = compile-time bound on the query rows.
-template <typename T, int D, int R>
+// [max, sum, acc[D]] per row to scratch memory.
+template <typename T, int D>
 __global__ void __launch_bounds__(kDecThreads, 2)
 fmha_decode_kernel(const DecodeParams p) {
+  constexpr int R = kDecRows;
   __shared__ float cta_ml[2 * R];
   __shared__ float cta_acc[R * D];
-  __shared__ __align__(16) float q_smem[R * D];
   pdl_launch_dependents();   // the merge kernel may be set up now; it waits for this grid
   const int split = blockIdx.x;
   const int b = blockIdx.y / p.heads_kv, hkv = blockIdx.y % p.heads_kv;
   const int c0 = split * p.chunk;
-  decode_cta_partial<T, D, R, kDecWarps>(p, b, hkv, c0, min(p.sk, c0 + p.chunk), cta_ml, cta_acc, q_smem);
+  decode_cta_partial<T, D, kDecWarps>(p, b, hkv, c0, min(p.sk, c0 + p.chunk), cta_ml, cta_acc);
   for (int idx = threadIdx.x; idx < p.rows * D; idx += kDecThreads) {
     const int r = idx / D, d = idx % D;
     float* dst = p.ws + ((static_cast<int64_t>(blockIdx.y) * p.rows + r) * p.splits + split) * (D + 2);
@@ -341,18 +370,17 @@ fmha_decode_kernel(const DecodeParams p) {
 constexpr int kMaxClusterSplits = 8;
 constexpr int kClusterThreads = 128;
 
-template <typename T, int D, int R>
+template <typename T, int D>
 __global__ void __launch_bounds__(kClusterThreads, 2)
 fmha_decode_cluster_kernel(const DecodeParams p) {
+  constexpr int R = kDecRows;
   __shared__ float cta_ml[2 * R];
   __shared__ float cta_acc[R * D];
-  __shared__ __align__(16) float q_smem[R * D];
   const int split = static_cast<int>(cluster_ctarank());
   const int cs = p.splits;   // == the cluster size of this launch
   const int b = blockIdx.y / p.heads_kv, hkv = blockIdx.y % p.heads_kv;
   const int c0 = split * p.chunk;
-  decode_cta_partial<T, D, R, kClusterThreads / 32>(p, b, hkv, c0, min(p.sk, c0 + p.chunk), cta_ml, cta_acc,
-                                                    q_smem);
+  decode_cta_partial<T, D, kClusterThreads / 32>(p, b, hkv, c0, min(p.sk, c0 + p.chunk), cta_ml, cta_acc);
   cluster_sync_all();   // every partial of the cluster is in place
   const int cols = D / cs;
   const uint32_t ml_addr = smem_u32(cta_ml), acc_addr = smem_u32(cta_acc);
@@ -482,19 +510,12 @@ int launch_decode(const DecodeParams& p, bool cluster, int64_t batch, cudaStream
     cfg.stream = stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e;
-    if (p.rows <= 1) e = cudaLaunchKernelEx(&cfg, fmha_decode_cluster_kernel<T, D, 1>, p);
-    else if (p.rows <= 2) e = cudaLaunchKernelEx(&cfg, fmha_decode_cluster_kernel<T, D, 2>, p);
-    else if (p.rows <= 4) e = cudaLaunchKernelEx(&cfg, fmha_decode_cluster_kernel<T, D, 4>, p);
-    else e = cudaLaunchKernelEx(&cfg, fmha_decode_cluster_kernel<T, D, 8>, p);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, fmha_decode_cluster_kernel<T, D>, p);
     if (e != cudaSuccess)
       return fail(B200K_CUDA_ERROR, "fmha decode (cluster of %d) launch: %s", p.splits, cudaGetErrorString(e));
     return B200K_OK;
   }
-  if (p.rows <= 1) fmha_decode_kernel<T, D, 1><<<grid, kDecThreads, 0, stream>>>(p);
-  else if (p.rows <= 2) fmha_decode_kernel<T, D, 2><<<grid, kDecThreads, 0, stream>>>(p);
-  else if (p.rows <= 4) fmha_decode_kernel<T, D, 4><<<grid, kDecThreads, 0, stream>>>(p);
-  else fmha_decode_kernel<T, D, 8><<<grid, kDecThreads, 0, stream>>>(p);
+  fmha_decode_kernel<T, D><<<grid, kDecThreads, 0, stream>>>(p);
   B200K_CHECK_LAUNCH("fmha decode launch");
   const cudaError_t e = launch_after_predecessor(fmha_decode_merge_kernel<T, D>,
                                                  dim3(static_cast<unsigned>(batch * p.heads_kv * p.rows)), dim3(D), 0,

@@ -80,6 +80,20 @@ def test_fmha_decode_split_kv(dtype, d, b, hq, hkv, sq, sk, causal, device_ok, m
     torch.testing.assert_close(out.float(), out_tc.float(), **TOL)
 
 
+@pytest.mark.parametrize("plan", ["1", "2", "4", "8", "s"])
+@pytest.mark.parametrize("b,hq,hkv,sq,sk,causal", [
+    (2, 8, 8, 1, 777, True),        # one row, ragged last batch, masked tail CTAs for large clusters
+    (1, 16, 4, 2, 1300, True),      # eight rows (sixteen lanes per key), two query positions under the mask
+    (3, 12, 4, 1, 96, False)])      # three rows of a four-row kernel (row predicates), short keys
+def test_fmha_decode_every_plan(plan, b, hq, hkv, sq, sk, causal, device_ok, monkeypatch):
+    # every cluster size of the one-kernel path and the two-kernel path give the oracle's result
+    monkeypatch.setenv("B200K_DECODE_PLAN", plan)
+    q, k, v = _qkv(b, hq, hkv, sq, sk, 128, torch.bfloat16, 3 * b + sk)
+    args = dict(query_group_size=hq // hkv, causal=causal, input_pos=sk - sq if causal else 0)
+    out = b200k.cutile_fmha(q.cuda(), k.cuda(), v.cuda(), **args)
+    torch.testing.assert_close(out.float().cpu(), oracle.fmha_ref(q, k, v, **args), **TOL)
+
+
 def test_fmha_decode_mid_sequence_position(device_ok):
     # input_pos in the middle of a longer cache: keys beyond the position are never read
     q, k, v = _qkv(1, 8, 8, 1, 2048, 128, torch.bfloat16, 77)
