@@ -1,7 +1,7 @@
 """Benchmark of the hot path on B200: TFLOPS of the block-scaled / dense contraction kernels.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload mxfp8_gemm|nvfp4_gemm|dense_f16|ag_nvfp4_gemm|moe_ep_bf16|ref_shapes|
+                    [--workload mxfp8_gemm|nvfp4_gemm|dense_f16|ag_nvfp4_gemm|moe_ep_bf16|ref_shapes|fmha_decode|
                                 fmha_causal|moe_bf16|moe_mxfp8|mxfp8_quantize|nvfp4_quantize]
 
 One step = one pass of the workload's kernel over one batch of seeded synthetic input.
@@ -566,6 +566,78 @@ class Mxfp8Quantize(Workload):
                 "l2": f"{self.sets} rotating inputs of 128 MiB each (> 126 MiB L2)"}
 
 
+class FmhaDecode(Mxfp8Quantize):
+    """One decode step of grouped-query attention over a long KV cache: the reference's decode
+    bench shapes (test/bench_attention.py:33-44: one query per sequence, 32 query heads on 8 KV
+    heads) at a serving-size batch.  K and V are read once: HBM-bound."""
+    name = "fmha_decode_bf16_b32_hq32_hkv8_s2048_d128"
+    dtype = "bf16, fp32 softmax"
+    B, HQ, HKV, S, D = 32, 32, 8, 2048, 128
+    seed = 5
+    sets = 2
+    launches_per_step = 1
+
+    def algorithmic_bytes(self):
+        return 2 * self.B * self.HKV * self.S * self.D * 2 + 2 * self.B * self.HQ * self.D * 2
+
+    def setup(self, device):
+        import b200k
+        g = torch.Generator(device=device).manual_seed(self.seed)
+        mk = lambda *sh: torch.randn(*sh, device=device, generator=g).bfloat16()
+        self.xs = [(mk(self.B, self.HQ, 1, self.D), mk(self.B, self.HKV, self.S, self.D),
+                    mk(self.B, self.HKV, self.S, self.D)) for _ in range(self.sets)]
+        self.out = torch.empty(self.B, self.HQ, 1, self.D, device=device, dtype=torch.bfloat16)
+        self.b200k = b200k
+        self.i = 0
+
+    def _run(self, q, k, v):
+        return self.b200k.cutile_fmha(q, k, v, causal=True, input_pos=self.S - 1,
+                                      query_group_size=self.HQ // self.HKV, Out=self.out)
+
+    def step(self):
+        q, k, v = self.xs[self.i % self.sets]
+        self.i += 1
+        return self._run(q, k, v)
+
+    def setup_e2e(self, device):
+        # a decode step's KV cache lives on the device; the step's own traffic is the new query
+        # in and the attention output back
+        self.host_in = [self.xs[0][0].cpu().pin_memory()]
+        self.host_out = [torch.empty_like(self.out, device="cpu").pin_memory()]
+        self.h2d = self.host_in[0].numel() * 2
+        self.d2h = self.host_out[0].numel() * 2
+
+    def step_e2e(self):
+        q, k, v = self.xs[0]
+        q.copy_(self.host_in[0], non_blocking=True)
+        self.host_out[0].copy_(self._run(q, k, v), non_blocking=True)
+
+    def cpu_setup(self):
+        import oracle
+        g = torch.Generator().manual_seed(self.seed)
+        mk = lambda *sh: torch.randn(*sh, generator=g).bfloat16()
+        self.cpu_ops = (mk(self.B, self.HQ, 1, self.D), mk(self.B, self.HKV, self.S, self.D),
+                        mk(self.B, self.HKV, self.S, self.D))
+        self.oracle = oracle
+
+    def cpu_step(self, s):
+        q, k, v = self.cpu_ops
+        s = min(s, self.B)
+        return self.oracle.fmha_ref(q[:s], k[:s], v[:s], causal=True, input_pos=self.S - 1,
+                                    query_group_size=self.HQ // self.HKV)
+
+    def cpu_flops(self, s):
+        return float(self.algorithmic_bytes()) * min(s, self.B) / self.B
+
+    def cpu_sample_desc(self, s):
+        return f"{min(s, self.B)} of {self.B} sequences through fp32 softmax(q k^T) v (torch CPU)"
+
+    def config(self):
+        return {"workload": self.name, "batch": self.B, "heads_q": self.HQ, "heads_kv": self.HKV,
+                "keys": self.S, "head_dim": self.D, "seed": self.seed,
+                "l2": f"{self.sets} rotating K/V sets of 268 MB each (> 126 MiB L2)"}
+
+
 class Nvfp4Quantize(Mxfp8Quantize):
     """bf16 8192 x 8192 -> packed e2m1 + swizzled ue4m3 scales + fp32 tensor scale.  Two kernels
     (tensor maximum, then the quantiser), so the input is read twice: HBM-bound."""
@@ -666,7 +738,7 @@ class DenseF16(Mxfp8Gemm):
 WORKLOADS = {"mxfp8_gemm": Mxfp8Gemm, "nvfp4_gemm": Nvfp4Gemm, "dense_f16": DenseF16,
              "ag_nvfp4_gemm": AgNvfp4Gemm, "moe_ep_bf16": MoeEpBf16, "fmha_causal": FmhaCausal,
              "moe_bf16": MoeBf16, "moe_mxfp8": MoeMxfp8, "mxfp8_quantize": Mxfp8Quantize,
-             "nvfp4_quantize": Nvfp4Quantize}
+             "nvfp4_quantize": Nvfp4Quantize, "fmha_decode": FmhaDecode}
 
 
 # --------------------------------------------------------------------------------------
@@ -1001,6 +1073,7 @@ TRAFFIC_BYTES: dict[str, float | None] = {
     "fmha_causal_bf16_b4_h32_s8192_d128": 1066.0e6,        # profiles/fmha_fwd_pair_causal_b4_h32_s8192_d128.md
     "mxfp8_quantize_bf16_8192x8192": 173.0e6,              # profiles/mxfp8_quantize_bf16_8192x8192.md
     "dense_f16_gemm_2048x2048x2048": 16.8e6,               # profiles/gemm_dense_f16_2048.md
+    "fmha_decode_bf16_b32_hq32_hkv8_s2048_d128": 272.0e6,  # profiles/fmha_decode_bf16_b32_hq32_hkv8_s2048_d128.md
     "nvfp4_quantize_bf16_8192x8192": 293.0e6,              # profiles/nvfp4_quantize_bf16_8192x8192.md (both kernels)
 }
 
