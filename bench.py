@@ -1068,8 +1068,8 @@ def run_ref_shapes(args):
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
 # ncu captures summarised under profiles/ (None until captured)
 TRAFFIC_BYTES: dict[str, float | None] = {
-    "mxfp8_gemm_8192x8192x8192_bf16out": 466.0e6,          # profiles/gemm_pair_mxfp8_8192.md
-    "nvfp4_gemm_8192x28672x8192_bf16out": 1005.0e6,        # profiles/gemm_pair_nvfp4_8192x28672x8192.md
+    "mxfp8_gemm_8192x8192x8192_bf16out": 477.0e6,          # profiles/gemm_pair_mxfp8_8192.md
+    "nvfp4_gemm_8192x28672x8192_bf16out": 1007.0e6,        # profiles/gemm_pair_nvfp4_8192x28672x8192.md
     "fmha_causal_bf16_b4_h32_s8192_d128": 1066.0e6,        # profiles/fmha_fwd_pair_causal_b4_h32_s8192_d128.md
     "mxfp8_quantize_bf16_8192x8192": 173.0e6,              # profiles/mxfp8_quantize_bf16_8192x8192.md
     "dense_f16_gemm_2048x2048x2048": 16.8e6,               # profiles/gemm_dense_f16_2048.md
