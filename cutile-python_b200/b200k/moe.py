@@ -28,9 +28,15 @@ ROW_TILE = 128          # row tile of the one-CTA grouped GEMM
 ROW_TILES = (128, 256)  # 256: the CTA-pair grouped GEMM
 
 
-def _moe_tile() -> int:
-    """Row tile the FFN entry points align with."""
+def _moe_tile(replicas: int | None = None, experts: int | None = None) -> int:
+    """Row tile the FFN entry points align with: 256 (the CTA-pair grouped GEMM), or 128 when
+    the routing is so sparse that most of a tile would be padding (fewer than 64 token replicas
+    per expert on average - the reference's 1408-expert bench shape has about one)."""
     if os.environ.get("B200K_SINGLE_CTA") == "1" or os.environ.get("B200K_MOE_TILE") == "128":
+        return 128
+    if os.environ.get("B200K_MOE_TILE") == "256":
+        return 256
+    if replicas is not None and experts and replicas < 64 * experts:
         return 128
     return 256
 
@@ -192,7 +198,7 @@ def cutile_moe(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
     x = hidden_states if hidden_states.stride(1) == 1 else hidden_states.contiguous()
     w1c, w2c = _check_weight(w1), _check_weight(w2)
 
-    tile = _moe_tile()
+    tile = _moe_tile(tokens * topk, experts)
     sorted_ids, expert_ids, num_blocks = moe_align_device(topk_ids, tile, experts)
     cap = sorted_ids.numel()
     a_sorted = _gather_rows(x, sorted_ids, topk, cap, num_blocks, tile)
@@ -286,7 +292,7 @@ def cutile_moe_mxfp8(hidden_states: torch.Tensor, w1_q: torch.Tensor, w1_sf: tor
     if tokens == 0:
         return torch.empty_like(hidden_states)
     x = hidden_states if hidden_states.stride(1) == 1 else hidden_states.contiguous()
-    tile = _moe_tile()
+    tile = _moe_tile(tokens * topk, experts)
     sorted_ids, expert_ids, num_blocks = moe_align_device(topk_ids, tile, experts)
     cap = sorted_ids.numel()
     a_q, a_sf = _quantize_rows(x, rows=cap, gather=sorted_ids, divisor=topk, num_blocks=num_blocks,

@@ -260,6 +260,48 @@ topk_sum_kernel(const uint16_t* __restrict__ x, const int* __restrict__ index, i
   }
 }
 
+// fp32 forms of the two kernels above (the grouped GEMMs multiply fp32 operands as tf32 and
+// keep fp32 results; these stay in fp32 throughout).
+__global__ void __launch_bounds__(256)
+silu_and_mul_f32_kernel(const float* __restrict__ ab, int64_t rows, int64_t n, int64_t ld_ab,
+                        float* __restrict__ c, int64_t ld_c) {
+  const int64_t pairs = n / 2;
+  const int64_t total = rows * pairs;
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = idx / pairs;
+    const int64_t j = (idx - r * pairs) * 2;
+    const float2 gf = *reinterpret_cast<const float2*>(ab + r * ld_ab + j);
+    const float2 uf = *reinterpret_cast<const float2*>(ab + r * ld_ab + n + j);
+    float2 o;
+    o.x = gf.x / (1.0f + __expf(-gf.x)) * uf.x;
+    o.y = gf.y / (1.0f + __expf(-gf.y)) * uf.y;
+    *reinterpret_cast<float2*>(c + r * ld_c + j) = o;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+topk_sum_f32_kernel(const float* __restrict__ x, const int* __restrict__ index, int64_t tokens, int topk,
+                    int64_t h, float* __restrict__ out) {
+  const int64_t vecs = h / 4;
+  const int64_t total = tokens * vecs;
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t t = idx / vecs;
+    const int64_t v = idx - t * vecs;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < topk; ++j) {
+      const int64_t src = index != nullptr ? index[t * topk + j] : t * topk + j;
+      const float4 q = *reinterpret_cast<const float4*>(x + src * h + v * 4);
+      acc.x += q.x;
+      acc.y += q.y;
+      acc.z += q.z;
+      acc.w += q.w;
+    }
+    *reinterpret_cast<float4*>(out + t * h + v * 4) = acc;
+  }
+}
+
 int blocks_for(int64_t items, int threads, int per_sm = 8) {
   int sms = current_sm_count();
   if (sms <= 0) sms = 148;
@@ -357,17 +399,20 @@ extern "C" int b200k_silu_and_mul(const void* ab, int64_t rows, int64_t n, int64
   if (rows == 0 || n == 0) return B200K_OK;
   if (!ab || !c) return fail(B200K_INVALID_ARG, "null pointer");
   if (n % 2 || ld_ab % 2 || ld_c % 2 ||
-      (reinterpret_cast<uintptr_t>(ab) | reinterpret_cast<uintptr_t>(c)) % 4)
+      (reinterpret_cast<uintptr_t>(ab) | reinterpret_cast<uintptr_t>(c)) % (dtype == B200K_F32 ? 8 : 4))
     return fail(B200K_UNSUPPORTED, "columns and leading dimensions must be even");
   const int grid = blocks_for(rows * n / 2, 256);
-  if (dtype == B200K_BF16)
+  if (dtype == B200K_F32)
+    silu_and_mul_f32_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(ab), rows, n, ld_ab,
+                                                      static_cast<float*>(c), ld_c);
+  else if (dtype == B200K_BF16)
     silu_and_mul_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(ab), rows, n, ld_ab,
                                                         static_cast<uint16_t*>(c), ld_c);
   else if (dtype == B200K_F16)
     silu_and_mul_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(ab), rows, n, ld_ab,
                                                          static_cast<uint16_t*>(c), ld_c);
   else
-    return fail(B200K_INVALID_ARG, "dtype must be f16 or bf16");
+    return fail(B200K_INVALID_ARG, "dtype must be f16, bf16 or f32");
   B200K_CHECK_LAUNCH("silu_and_mul launch");
   return B200K_OK;
 }
@@ -381,14 +426,17 @@ extern "C" int b200k_topk_sum(const void* x, const int32_t* index, int64_t token
   if (hidden % 8 || (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) % 16)
     return fail(B200K_UNSUPPORTED, "hidden must be a multiple of 8 and buffers 16-byte aligned");
   const int grid = blocks_for(tokens * hidden / 8, 256);
-  if (dtype == B200K_BF16)
+  if (dtype == B200K_F32)
+    topk_sum_f32_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(x), index, tokens, topk, hidden,
+                                                  static_cast<float*>(out));
+  else if (dtype == B200K_BF16)
     topk_sum_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), index, tokens, topk, hidden,
                                                     static_cast<uint16_t*>(out));
   else if (dtype == B200K_F16)
     topk_sum_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), index, tokens, topk, hidden,
                                                      static_cast<uint16_t*>(out));
   else
-    return fail(B200K_INVALID_ARG, "dtype must be f16 or bf16");
+    return fail(B200K_INVALID_ARG, "dtype must be f16, bf16 or f32");
   B200K_CHECK_LAUNCH("topk_sum launch");
   return B200K_OK;
 }

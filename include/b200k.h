@@ -285,7 +285,7 @@ int b200k_gather_rows(const void* src, int64_t src_rows, int64_t row_bytes,
                       const int32_t* num_blocks, int32_t tile_m, int64_t max_rows, void* dst,
                       int64_t dst_stride_bytes, b200k_stream stream);
 
-/* C[r, j] = silu(AB[r, j]) * AB[r, j + n], f16/bf16; replaces silu_and_mul_kernel
+/* C[r, j] = silu(AB[r, j]) * AB[r, j + n], f16/bf16/f32; replaces silu_and_mul_kernel
  * (reference: test/kernels/fused_moe.py:85-108). */
 int b200k_silu_and_mul(const void* ab, int64_t rows, int64_t n, int64_t ld_ab, void* c,
                        int64_t ld_c, int32_t dtype, b200k_stream stream);

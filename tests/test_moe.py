@@ -90,6 +90,21 @@ def test_cutile_moe_bf16(tokens, hidden, experts, inter, topk, row_tile, device_
     assert oracle.rel_frobenius(out, ref) < 2e-2
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("tokens,hidden,experts,inter,topk", [
+    (110, 1024, 16, 512, 4),      # the reference's bench shapes (test/bench_moe.py:16-19) ...
+    (256, 2048, 1408, 32, 6)])    # ... about one token per expert: the automatic row tile is 128
+def test_cutile_moe_reference_bench_shapes(tokens, hidden, experts, inter, topk, dtype, device_ok):
+    x, w1, w2, tw, ids = _problem(tokens, hidden, experts, inter, topk, 3 * tokens, dtype)
+    out = b200k.cutile_moe(x.cuda(), w1.cuda(), w2.cuda(), tw.cuda(), ids.cuda())
+    assert out.shape == x.shape and out.dtype == dtype
+    ref = oracle.moe_ref(x, w1, w2, tw, ids)
+    # the reference bench's own tolerances (test/bench_moe.py:60-66); fp32 operands are
+    # multiplied as tf32 here
+    tol = {torch.float16: 5e-2, torch.bfloat16: 1e-1, torch.float32: 1e-2}[dtype]
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=tol, atol=tol)
+
+
 @pytest.mark.parametrize("tile_m", [128, 256])
 def test_invoke_fused_moe_kernel_matches_manual_pipeline(tile_m, device_ok):
     # the sample's three-launch pipeline driven through the reference-named helpers
