@@ -37,7 +37,10 @@ namespace b200k {
 // Debug build only: cycle counters summed over all CTAs.
 // 0 producer wait(empty), 1 producer total, 2 mma wait(full), 3 mma wait(acc), 4 mma total,
 // 5 epilogue wait(acc_full), 6 epilogue total, 7 mma issue (descs + cp + mma + commit);
-// 2, 3, 4 and 7 are those of the first issuer; 12 / 13 cycles and nanoseconds of CTA 0's producer
+// 2, 3, 4 and 7 are those of the first issuer; 12 / 13 cycles and nanoseconds of CTA 0's producer;
+// 8 - 11, 14, 15: nanoseconds from kernel entry in CTA 0 (prologue done, first load issued, first
+// operands landed, first tile's MMAs issued, first accumulator complete, last tile stored; each
+// stamp is a %globaltimer read of a few hundred nanoseconds itself)
 __device__ unsigned long long g_trace[16];
 #define TRACE_T0(var) long long var = clock64()
 #define TRACE_ADD(idx, var) atomicAdd(&g_trace[idx], static_cast<unsigned long long>(clock64() - (var)))
@@ -105,6 +108,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
+#ifdef B200K_TRACE
+  const unsigned long long ns_entry = global_timer_ns();
+#define TRACE_STAMP(idx) do { if (blockIdx.x == 0 && lane == 0) g_trace[idx] = global_timer_ns() - ns_entry; } while (0)
+#else
+#define TRACE_STAMP(idx)
+#endif
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -131,6 +140,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (warp == 0) TRACE_STAMP(8);   // prologue done
 
   // grouped mode: 256-row tiles, the live count comes from the device
   int tiles_m = (p.m + 255) / 256;
@@ -186,6 +196,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (elected) {
             if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * (Cfg::kABytes + b_rows * 128 + Cfg::kSfBytes));
             tma_load_3d_pair(a_dst, &tmap_a, lead_full, kx, m0, a_batch);
+            if (it == 0) TRACE_STAMP(9);   // first load issued
             if (!p.b_mn) {
               tma_load_3d_pair(b_dst, &tmap_b, lead_full, kx, nb, group);   // box of b_rows rows
             } else {
@@ -284,6 +295,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             break;
           }
           TRACE_ACC(w_full, t_f);
+          if (q == 0 && it == 0) TRACE_STAMP(10);   // first operands landed
           TRACE_T0(t_i);
           tc_fence_after_sync();
           const uint32_t a_addr = tiles_base + s * Cfg::kStageBytes;
@@ -338,6 +350,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (elected) {
             tc_commit_pair(f0);
             tc_commit_pair(f1);
+            if (q == 0 && lt == 0) TRACE_STAMP(11);   // first tile's MMAs issued
           }
         }
         ++lt;
@@ -387,6 +400,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         break;
       }
       TRACE_ACC(w_accf, t_e);
+      if (warp == 2 && lt == 0) TRACE_STAMP(14);   // first accumulator complete
       tc_fence_after_sync();
       const int row = tc.pid_m * 256 + rank * 128 + quarter * 32 + lane;
       int64_t out_row = row;
@@ -590,6 +604,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster_relaxed(map_to_cta(acc_empty_bar(w), 0));
+      if (warp == 2) TRACE_STAMP(15);   // a tile stored (the last one stays)
       ++lt;
     }
 #ifdef B200K_TRACE
