@@ -51,14 +51,12 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, alpha: float = 1
     if a3.stride(2) != 1 or not _aligned(a3, a3.stride(1)) or (nb > 1 and (a3.stride(0) * a3.element_size()) % 16):
         a3 = _pad_last(a3)
     # B: (K, N) N-contiguous, or a transposed view of an (N, K) K-contiguous tensor.
-    # tf32 operands exist only K-contiguous on the tensor core, so an N-contiguous fp32 B
-    # is re-laid out once here.
     def rows_ok(t):
         return (t.stride(2) == 1 and _aligned(t, t.stride(1))
                 and (nb == 1 or (t.stride(0) * t.element_size()) % 16 == 0))
 
     is_kn, is_nk = b3.stride(2) == 1, b3.stride(1) == 1
-    if b3.dtype == torch.float32 or (is_nk and (not is_kn or n == 1)):
+    if is_nk and (not is_kn or n == 1):
         layout = _lib.B_NK
         bt = b3.transpose(1, 2)
         if not rows_ok(bt):

@@ -384,6 +384,9 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
 //   [49,52) base offset               [61,64) swizzle: 0 none, 2 128B, 4 64B, 6 32B
 constexpr uint32_t kSwizzleNone = 0;
 constexpr uint32_t kSwizzle128B = 2;
+// 128-byte rows swizzled in 32-byte pieces over four rows: the only form an MN-major 32-bit
+// (tf32) operand has; TMA writes it with CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.
+constexpr uint32_t kSwizzle128BBase32B = 1;
 
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes,
                                                    uint32_t sbo_bytes, uint32_t swizzle) {

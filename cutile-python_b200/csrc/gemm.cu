@@ -197,7 +197,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const uint32_t a_addr = tiles_base + s * Cfg::kStageBytes;
           const uint32_t b_addr = a_addr + Cfg::kABytes;
           const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024, kSwizzle128B);
-          const uint64_t b_desc = B_MN ? make_smem_desc(b_addr, Cfg::kBBoxBytes, 1024, kSwizzle128B)
+          // MN-major: groups of eight k-rows 1024 bytes apart; tf32: groups of four, 512 apart
+          const uint64_t b_desc = B_MN ? make_smem_desc(b_addr, Cfg::kBBoxBytes, KIND == kKindTF32 ? 512 : 1024,
+                                                        KIND == kKindTF32 ? kSwizzle128BBase32B : kSwizzle128B)
                                        : make_smem_desc(b_addr, 16, 1024, kSwizzle128B);
           const int n_mma = (kb == p.k_iters - 1) ? p.k_tail_mmas : 4;
           uint32_t tsfa = 0, tsfb = 0;
@@ -568,10 +570,6 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
     default: return fail(B200K_INVALID_ARG, "unsupported operand dtype %d", a->ab_dtype);
   }
   const bool b_mn = a->b_layout == B200K_B_KN;
-  if (b_mn && kind == kKindTF32)
-    return fail(B200K_UNSUPPORTED,
-                "fp32 (tf32) operands need B stored (N, K): the N-contiguous layout is only "
-                "available for 8- and 16-bit operands");
   if (a->epilogue == B200K_EPI_SWIGLU && (b_mn || a->n % 256 != 0))
     return fail(B200K_UNSUPPORTED, "SwiGLU epilogue needs B stored (N, K) and N a multiple of 256");
   if ((a->lda * elem_bytes) % 16 || (a->ldb * elem_bytes) % 16 || !aligned16(a->a) || !aligned16(a->b))
@@ -624,7 +622,7 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
   if (b_mn) {
     const uint64_t sb = (b_batches > 1 ? a->stride_b : a->k * a->ldb) * elem_bytes;
     if (!encode_tmap_3d(&tb, tdt, a->b, a->n, a->k, b_batches, a->ldb * elem_bytes, sb, bk, bk, 1,
-                        CU_TENSOR_MAP_SWIZZLE_128B))
+                        kind == kKindTF32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B))
       return B200K_INVALID_ARG;
   } else {
     const uint64_t sb = (b_batches > 1 ? a->stride_b : a->n * a->ldb) * elem_bytes;
@@ -659,7 +657,8 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
         rc = b_mn ? launch<kKindF16, BN, true, kOutF32>(ta, tb, ps, sgrid, stream)
                   : launch<kKindF16, BN, false, kOutF32>(ta, tb, ps, sgrid, stream);
       else if (kind == kKindTF32)
-        rc = launch<kKindTF32, BN, false, kOutF32>(ta, tb, ps, sgrid, stream);
+        rc = b_mn ? launch<kKindTF32, BN, true, kOutF32>(ta, tb, ps, sgrid, stream)
+                  : launch<kKindTF32, BN, false, kOutF32>(ta, tb, ps, sgrid, stream);
       else
         rc = b_mn ? launch<kKindF8, BN, true, kOutF32>(ta, tb, ps, sgrid, stream)
                   : launch<kKindF8, BN, false, kOutF32>(ta, tb, ps, sgrid, stream);
@@ -670,8 +669,8 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
   }
   const bool pair_plain = !grouped && a->epilogue == B200K_EPI_STORE && a->row_map == nullptr;
   const bool pair_grouped = grouped && a->tile_rows == 256 && !b_mn;
-  // N-contiguous B on the pair kernel: 8- and 16-bit operands, plain problems
-  const bool pair_b_ok = !b_mn || (pair_plain && kind != kKindTF32);
+  // N-contiguous B on the pair kernel: plain problems
+  const bool pair_b_ok = !b_mn || pair_plain;
   // (a grouped problem over 256-row tiles exists on the pair kernel only: a request for the
   // one-CTA kernel is not honoured there)
   if (pair_b_ok && ((pair_plain && cfg.kernel != 1) || pair_grouped)) {
@@ -681,7 +680,7 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
     // 512 narrow tiles 7 half rounds), but a narrow tile re-reads A twice as often and
     // pays the per-tile hand-offs twice: measured 113 against 96 us there.
     // (an N-contiguous B is loaded in boxes of 128 bytes of N: each CTA's half of a narrow
-    // tile, 64 columns, is a whole box only for 16-bit operands)
+    // tile, 64 columns, is less than one box of 8-bit operands)
     // Left to the library, narrow tiles are taken when the wide ones would leave more than
     // half of the CTA pairs without work (1024 cubed, 16-bit: 16.4 -> 14.1 us).
     int want_bn = cfg.tile_n;
@@ -689,7 +688,7 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
       const int64_t wide_tiles = ceil_div(a->m, 256) * ceil_div(a->n, 256) * a->batch;
       want_bn = wide_tiles * 2 <= sms / 2 ? 128 : 256;
     }
-    const int bn = (want_bn == 128 && pair_plain && !(b_mn && elem_bytes != 2)) ? 128 : 256;
+    const int bn = (want_bn == 128 && pair_plain && !(b_mn && elem_bytes == 1)) ? 128 : 256;
     pp.pair_bn = bn;
     pp.b_mn = b_mn ? 1 : 0;
     pp.tiles_n = static_cast<int>(ceil_div(a->n, bn));
@@ -710,7 +709,9 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
   if (kind == kKindF16)
     return b_mn ? launch_out<kKindF16, BN, true>(out, ta, tb, p, grid, stream)
                 : launch_out<kKindF16, BN, false>(out, ta, tb, p, grid, stream);
-  if (kind == kKindTF32) return launch_out<kKindTF32, BN, false>(out, ta, tb, p, grid, stream);
+  if (kind == kKindTF32)
+    return b_mn ? launch_out<kKindTF32, BN, true>(out, ta, tb, p, grid, stream)
+                : launch_out<kKindTF32, BN, false>(out, ta, tb, p, grid, stream);
   return b_mn ? launch_out<kKindF8, BN, true>(out, ta, tb, p, grid, stream)
               : launch_out<kKindF8, BN, false>(out, ta, tb, p, grid, stream);
 }

@@ -301,7 +301,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t a_addr = tiles_base + s * Cfg::kStageBytes;
           const uint32_t b_addr = a_addr + Cfg::kABytes;
           const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024, kSwizzle128B);
-          const uint64_t b_desc = p.b_mn ? make_smem_desc(b_addr, Cfg::kBBoxBytes, 1024, kSwizzle128B)
+          // MN-major: groups of eight k-rows 1024 bytes apart; tf32: groups of four, 512 apart
+          const uint64_t b_desc = p.b_mn ? make_smem_desc(b_addr, Cfg::kBBoxBytes, KIND == kKindTF32 ? 512 : 1024,
+                                                          KIND == kKindTF32 ? kSwizzle128BBase32B : kSwizzle128B)
                                          : make_smem_desc(b_addr, 16, 1024, kSwizzle128B);
           const uint32_t b_step = p.b_mn ? Cfg::kMmaK * 128 / 16 : 2;   // descriptor advance per MMA
           const int n_mma = (kb == p.k_iters - 1) ? p.k_tail_mmas : 4;
