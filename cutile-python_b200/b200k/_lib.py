@@ -82,6 +82,7 @@ class QuantizeArgs(Structure):
         ("x_dtype", c_int32), ("q_dtype", c_int32),
         ("gather_index", c_void_p), ("gather_divisor", c_int32), ("tile_m", c_int32),
         ("src_rows", c_int64), ("live_blocks", c_void_p),
+        ("tensor_scale_given", c_int32),
     ]
 
 

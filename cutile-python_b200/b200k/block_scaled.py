@@ -121,9 +121,12 @@ def block_quantize(x: torch.Tensor, block_size: int = 32,
     return x_q, scale
 
 
-def nvfp4_quantize(x: torch.Tensor, *, swizzled_scale: bool = True):
+def nvfp4_quantize(x: torch.Tensor, *, swizzled_scale: bool = True,
+                   tensor_scale: torch.Tensor | None = None):
     """bf16/fp16/fp32 (rows, K) -> (packed e2m1 (rows, K/2) uint8, ue4m3 block scales,
-    fp32 tensor scale (1,) on the device).  The rule is stated in include/b200k.h."""
+    fp32 tensor scale (1,) on the device).  The rule is stated in include/b200k.h.
+    ``tensor_scale`` (one fp32 value on the device) given: it is used as the per-tensor scale
+    and returned as is; x is then read once instead of twice."""
     if x.dim() != 2:
         raise ValueError("nvfp4_quantize expects a 2-D tensor")
     if not x.is_cuda:
@@ -135,11 +138,17 @@ def nvfp4_quantize(x: torch.Tensor, *, swizzled_scale: bool = True):
         x = x.contiguous()
     kblocks = _cdiv(k, 16)
     q = torch.empty((rows, k // 2), dtype=torch.uint8, device=x.device)
-    tensor_scale = torch.empty((1,), dtype=torch.float32, device=x.device)
-    scratch = torch.empty((1,), dtype=torch.int32, device=x.device)
     args = _lib.QuantizeArgs()
+    if tensor_scale is not None:
+        if tensor_scale.dtype != torch.float32 or tensor_scale.numel() != 1 or tensor_scale.device != x.device:
+            raise ValueError("tensor_scale must be one fp32 value on the device of x")
+        args.tensor_scale_given = 1
+        scratch = None
+    else:
+        tensor_scale = torch.empty((1,), dtype=torch.float32, device=x.device)
+        scratch = torch.empty((1,), dtype=torch.int32, device=x.device)
     args.x, args.q = x.data_ptr(), q.data_ptr()
-    args.tensor_scale, args.scratch = tensor_scale.data_ptr(), scratch.data_ptr()
+    args.tensor_scale, args.scratch = tensor_scale.data_ptr(), _lib.ptr(scratch)
     args.rows, args.k, args.ldx, args.ldq = rows, k, x.stride(0), k // 2
     args.x_dtype = _lib.dtype_enum(x.dtype)
     if swizzled_scale:

@@ -292,9 +292,14 @@ nvfp4_quantize_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t 
                       uint8_t* __restrict__ sf_swizzled, int64_t k_atoms,
                       const uint32_t* __restrict__ amax_bits, float* __restrict__ tensor_scale) {
   pdl_wait();   // the maximum comes from the kernel launched just before
-  const float amax_t = __uint_as_float(*amax_bits);
-  const float s_t = __fdiv_rn(amax_t, 2688.0f);  // 448 * 6
-  if (blockIdx.x == 0 && threadIdx.x == 0 && tensor_scale != nullptr) *tensor_scale = s_t;
+  float s_t;
+  if (amax_bits != nullptr) {
+    const float amax_t = __uint_as_float(*amax_bits);
+    s_t = __fdiv_rn(amax_t, 2688.0f);  // 448 * 6
+    if (blockIdx.x == 0 && threadIdx.x == 0 && tensor_scale != nullptr) *tensor_scale = s_t;
+  } else {
+    s_t = *tensor_scale;               // given by the caller: nothing to find, nothing to write
+  }
   const float six_st = __fmul_rn(6.0f, s_t);
   const int64_t kblocks = (k + 15) >> 4;
   const int64_t per_row = kblocks / BPT;          // BPT == 2 only with an even block count
@@ -504,11 +509,24 @@ extern "C" int b200k_nvfp4_quantize(const b200k_quantize_args* a, b200k_stream s
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (a->rows < 0 || a->k < 0) return fail(B200K_INVALID_ARG, "negative dimension");
   if (a->rows == 0 || a->k == 0) return B200K_OK;
-  if (!a->x || !a->q || !a->scratch) return fail(B200K_INVALID_ARG, "null pointer");
+  if (!a->x || !a->q || (!a->scratch && !a->tensor_scale_given))
+    return fail(B200K_INVALID_ARG, "null pointer");
+  if (a->tensor_scale_given && !a->tensor_scale)
+    return fail(B200K_INVALID_ARG, "tensor_scale_given without tensor_scale");
   if (a->k % 2) return fail(B200K_UNSUPPORTED, "K must be even (two e2m1 values per byte)");
   const int64_t kblocks = ceil_div(a->k, 16);
   if (a->sf_swizzled && a->sf_k_atoms < ceil_div(kblocks, 4))
     return fail(B200K_INVALID_ARG, "sf_k_atoms too small");
+  if (a->tensor_scale_given) {   // one pass: the scale is the caller's
+    switch (a->x_dtype) {
+      case B200K_F32: launch_nvfp4_quantize<float>(a, nullptr, stream); break;
+      case B200K_BF16: launch_nvfp4_quantize<__nv_bfloat16>(a, nullptr, stream); break;
+      case B200K_F16: launch_nvfp4_quantize<__half>(a, nullptr, stream); break;
+      default: return fail(B200K_INVALID_ARG, "x_dtype must be f32, bf16 or f16");
+    }
+    B200K_CHECK_LAUNCH("nvfp4_quantize launch");
+    return B200K_OK;
+  }
   uint32_t* amax = static_cast<uint32_t*>(a->scratch);
   cudaError_t e = cudaMemsetAsync(amax, 0, sizeof(uint32_t), stream);
   if (e != cudaSuccess) return fail(B200K_CUDA_ERROR, "memset: %s", cudaGetErrorString(e));

@@ -210,6 +210,10 @@ typedef struct {
   int32_t tile_m;
   int64_t src_rows;
   const int32_t* live_blocks;
+  /* nvfp4 only: non-zero = `tensor_scale` is an input (a calibrated scale, or the one an
+   * earlier call produced): the pass that finds the tensor maximum is skipped, `scratch` may
+   * be NULL, x is read once.  Values beyond 6 * 448 * scale saturate. */
+  int32_t tensor_scale_given;
 } b200k_quantize_args;
 
 /* MXFP8: replaces block_quantize(x, 32) (reference: test/kernels/kernel_utils.py:38-80)

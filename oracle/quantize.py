@@ -69,16 +69,17 @@ def mxfp8_dequantize_ref(q: torch.Tensor, scale: torch.Tensor, block_size: int =
     return q.detach().cpu().float() * s.repeat_interleave(block_size, dim=-1)[..., : q.shape[-1]]
 
 
-def nvfp4_quantize_ref(x: torch.Tensor):
+def nvfp4_quantize_ref(x: torch.Tensor, tensor_scale=None):
     """Returns (packed e2m1 uint8 (rows, K/2), ue4m3 scale bytes (rows, K/16) uint8,
-    tensor scale float32 scalar)."""
+    tensor scale float32 scalar).  `tensor_scale` given: used instead of amax / (448 * 6);
+    block scales and codes then saturate (448, +-6)."""
     x = x.detach().cpu().float().numpy()
     rows, k = x.shape
     pad = (-k) % 16
     xp = np.pad(x, ((0, 0), (0, pad))) if pad else x
     f32 = np.float32
     amax_t = f32(np.abs(x).max()) if x.size else f32(0)
-    s_t = f32(amax_t / f32(2688.0))
+    s_t = f32(amax_t / f32(2688.0)) if tensor_scale is None else f32(tensor_scale)
     six_st = f32(f32(6.0) * s_t)
     blocks = xp.reshape(rows, -1, 16)
     amax_b = np.abs(blocks).max(axis=-1).astype(f32)

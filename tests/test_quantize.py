@@ -98,6 +98,30 @@ def test_nvfp4_quantize_vs_oracle(dtype, rows, k, device_ok):
     assert np.array_equal(q.cpu().numpy(), qr)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("factor", [1.0, 0.25, 3.0])
+def test_nvfp4_quantize_with_given_tensor_scale(dtype, factor, device_ok):
+    # one pass under a caller-given per-tensor scale: the scale the two-pass form would find
+    # (same bytes), a quarter of it (block scales and codes saturate), three times it
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(200, 96, generator=g).to(dtype)
+    _, _, own = oracle.nvfp4_quantize_ref(x)
+    given = np.float32(own) * np.float32(factor)
+    scale = torch.tensor([float(given)], dtype=torch.float32, device="cuda")
+    q, sf, ts = b200k.nvfp4_quantize(x.cuda(), swizzled_scale=False, tensor_scale=scale)
+    qr, sfr, tsr = oracle.nvfp4_quantize_ref(x, tensor_scale=given)
+    assert ts is scale and ts.item() == float(tsr)
+    assert np.array_equal(_u8(sf), sfr)
+    assert np.array_equal(q.cpu().numpy(), qr)
+    if factor == 1.0:
+        q2, sf2, _ = b200k.nvfp4_quantize(x.cuda(), swizzled_scale=False)
+        assert torch.equal(q, q2) and torch.equal(_as(sf), _as(sf2))
+
+
+def _as(t):
+    return t.view(torch.uint8)
+
+
 def test_nvfp4_quantize_all_zero_tensor(device_ok):
     x = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
     q, sf, ts = b200k.nvfp4_quantize(x, swizzled_scale=False)
