@@ -472,10 +472,12 @@ DecodePlan plan_decode(int64_t batch, int64_t heads_kv, int64_t sk, int sms) {
   }
   // One kernel, no scratch: the smallest cluster that gives every SM a CTA of four warps.
   // More CTAs than that only add rounds of launch, warp merge and cluster barriers.
-  if (!force_two && (forced > 0 || groups * kMaxClusterSplits * 2 >= sms)) {
+  if (!force_two && (forced > 0 || groups * kMaxClusterSplits * 4 >= sms)) {
     int cs = 1;
     while (cs < kMaxClusterSplits && groups * cs < sms) cs *= 2;
-    while (cs > 1 && ceil_div(sk, cs) < 64) cs /= 2;   // at least 64 keys per CTA
+    // at least two steps per warp (256 keys per CTA): q (1,32,1,128) against 1024 keys took
+    // 16.4 us in clusters of eight and 14.4 us in clusters of four
+    while (cs > 1 && ceil_div(sk, cs) < 256) cs /= 2;
     if (forced > 0) cs = forced;
     plan.cluster = true;
     plan.splits = cs;
