@@ -37,6 +37,10 @@ __global__ void __launch_bounds__(kAlignWarps * 32)
 moe_count_kernel(const IdT* __restrict__ ids, int64_t total, int num_experts,
                  int* __restrict__ counts, int* status) {
   extern __shared__ int smem_counts[];
+  // The alignment kernels and the row gather behind them are launched with programmatic
+  // stream serialisation: each is set up while the one before it runs and waits for it in
+  // pdl_wait(), which takes the launch gaps out of a chain of four short kernels.
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int* mine = smem_counts + warp * num_experts;
   const int64_t chunk = static_cast<int64_t>(blockIdx.x) * kAlignWarps + warp;
@@ -63,6 +67,8 @@ moe_offsets_kernel(int* __restrict__ counts, int num_chunks, int num_experts, in
                    int* __restrict__ sorted_expert_ids, int64_t block_capacity,
                    int* __restrict__ num_blocks_out) {
   extern __shared__ int sm[];
+  pdl_wait();
+  pdl_launch_dependents();
   int* totals = sm;                      // [E] replicas per expert
   int* starts = sm + num_experts;        // [E] first slot of the expert's padded run
   int* partial = sm + 2 * num_experts;   // [groups][E] replicas per expert in a group of chunks
@@ -150,6 +156,8 @@ moe_scatter_kernel(const IdT* __restrict__ ids, int64_t total, int num_experts,
                    const int* __restrict__ offsets, int* __restrict__ sorted_token_ids,
                    int* status) {
   extern __shared__ int smem_counts[];
+  pdl_wait();
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int* next = smem_counts + warp * num_experts;
   const int64_t chunk = static_cast<int64_t>(blockIdx.x) * kAlignWarps + warp;
@@ -176,6 +184,7 @@ gather_rows_kernel(const uint8_t* __restrict__ src, int64_t src_rows, int64_t ro
                    int64_t src_stride, const int* __restrict__ index, int divisor,
                    const int* __restrict__ num_blocks, int tile_m, int64_t max_rows,
                    uint8_t* __restrict__ dst, int64_t dst_stride) {
+  pdl_wait();
   int64_t rows = max_rows;
   if (num_blocks != nullptr) {
     const int64_t live = static_cast<int64_t>(*num_blocks) * tile_m;
@@ -356,19 +365,22 @@ extern "C" int b200k_moe_align(const b200k_moe_align_args* a, b200k_stream strea
       moe_count_kernel<int><<<grid, kAlignWarps * 32, smem, stream>>>(
           static_cast<const int*>(a->topk_ids), a->num_replicas, a->num_experts, counts, status);
   }
-  moe_offsets_kernel<<<1, 1024, (2 + (1024 / a->num_experts > 1 ? 1024 / a->num_experts : 1)) * a->num_experts * sizeof(int), stream>>>(
-      counts, chunks, a->num_experts, a->tile_m, a->num_replicas, a->sorted_token_ids, a->capacity,
-      a->sorted_expert_ids, a->block_capacity, a->num_blocks);
-  if (a->num_replicas > 0) {
+  const size_t offsets_smem =
+      (2 + (1024 / a->num_experts > 1 ? 1024 / a->num_experts : 1)) * a->num_experts * sizeof(int);
+  e = launch_after_predecessor(moe_offsets_kernel, dim3(1), dim3(1024), offsets_smem, stream, counts, chunks,
+                               a->num_experts, a->tile_m, a->num_replicas, a->sorted_token_ids, a->capacity,
+                               a->sorted_expert_ids, a->block_capacity, a->num_blocks);
+  if (e == cudaSuccess && a->num_replicas > 0) {
     if (a->ids_are_int64)
-      moe_scatter_kernel<long long><<<grid, kAlignWarps * 32, smem, stream>>>(
-          static_cast<const long long*>(a->topk_ids), a->num_replicas, a->num_experts, counts,
-          a->sorted_token_ids, status);
+      e = launch_after_predecessor(moe_scatter_kernel<long long>, dim3(grid), dim3(kAlignWarps * 32), smem, stream,
+                                   static_cast<const long long*>(a->topk_ids), a->num_replicas, a->num_experts,
+                                   counts, a->sorted_token_ids, status);
     else
-      moe_scatter_kernel<int><<<grid, kAlignWarps * 32, smem, stream>>>(
-          static_cast<const int*>(a->topk_ids), a->num_replicas, a->num_experts, counts,
-          a->sorted_token_ids, status);
+      e = launch_after_predecessor(moe_scatter_kernel<int>, dim3(grid), dim3(kAlignWarps * 32), smem, stream,
+                                   static_cast<const int*>(a->topk_ids), a->num_replicas, a->num_experts, counts,
+                                   a->sorted_token_ids, status);
   }
+  if (e != cudaSuccess) return fail(B200K_CUDA_ERROR, "moe_align launch: %s", cudaGetErrorString(e));
   B200K_CHECK_LAUNCH("moe_align launch");
   return B200K_OK;
 }
@@ -385,10 +397,11 @@ extern "C" int b200k_gather_rows(const void* src, int64_t src_rows, int64_t row_
       (reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) % 16)
     return fail(B200K_UNSUPPORTED, "rows must be multiples of 16 bytes on 16-byte boundaries");
   const int grid = blocks_for(max_rows * 256, 256, 16);
-  gather_rows_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(src), src_rows, row_bytes,
-                                               src_stride_bytes, index, divisor, num_blocks, tile_m,
-                                               max_rows, static_cast<uint8_t*>(dst), dst_stride_bytes);
-  B200K_CHECK_LAUNCH("gather_rows launch");
+  const cudaError_t e = launch_after_predecessor(gather_rows_kernel, dim3(grid), dim3(256), 0, stream,
+                                                 static_cast<const uint8_t*>(src), src_rows, row_bytes,
+                                                 src_stride_bytes, index, divisor, num_blocks, tile_m, max_rows,
+                                                 static_cast<uint8_t*>(dst), dst_stride_bytes);
+  if (e != cudaSuccess) return fail(B200K_CUDA_ERROR, "gather_rows launch: %s", cudaGetErrorString(e));
   return B200K_OK;
 }
 
