@@ -531,10 +531,6 @@ extern "C" int b200k_nvfp4_quantize(const b200k_quantize_args* a, b200k_stream s
   cudaError_t e = cudaMemsetAsync(amax, 0, sizeof(uint32_t), stream);
   if (e != cudaSuccess) return fail(B200K_CUDA_ERROR, "memset: %s", cudaGetErrorString(e));
   const int grid_r = grid_for(a->rows * a->k / 16, 256);
-  const int grid_q = grid_for(a->rows * kblocks, 256);
-  uint8_t* q = static_cast<uint8_t*>(a->q);
-  uint8_t* sl = static_cast<uint8_t*>(a->sf_logical);
-  uint8_t* ss = static_cast<uint8_t*>(a->sf_swizzled);
 #define B200K_NVFP4_CASE(T)                                                                       \
   absmax_kernel<T><<<grid_r, 256, 0, stream>>>(static_cast<const T*>(a->x), a->rows, a->k, a->ldx, \
                                                amax);                                             \
@@ -568,10 +564,6 @@ extern "C" int b200k_nvfp4_quantize_noalloc(const b200k_quantize_args* a, b200k_
                 (long long)(a->rows * a->k), (long long)(kNoAllocSlots * kNoAllocSlabElems));
   uint32_t* slots = noalloc_slots();
   if (slots == nullptr) return B200K_CUDA_ERROR;
-  const int grid_q = grid_for(a->rows * kblocks, 256);
-  uint8_t* q = static_cast<uint8_t*>(a->q);
-  uint8_t* sl = static_cast<uint8_t*>(a->sf_logical);
-  uint8_t* ss = static_cast<uint8_t*>(a->sf_swizzled);
 #define B200K_NVFP4_NOALLOC_CASE(T)                                                               \
   absmax_slab_kernel<T><<<static_cast<int>(slabs), 256, 0, stream>>>(                             \
       static_cast<const T*>(a->x), a->rows, a->k, a->ldx, slots);                                 \
