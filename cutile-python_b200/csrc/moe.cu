@@ -49,9 +49,18 @@ moe_count_kernel(const IdT* __restrict__ ids, int64_t total, int num_experts,
   for (int e = lane; e < num_experts; e += 32) mine[e] = 0;
   __syncwarp();
   const int64_t end = begin + kChunk < total ? begin + kChunk : total;
-  for (int64_t i = begin + lane; i - lane < end; i += 32) {
-    const bool active = i < end;
-    const int e = active ? load_expert(ids, i, num_experts, status) : -1;
+  // the chunk's ids are fetched up front (sixteen independent loads per lane): one load per
+  // round of the loop below would put a memory latency into each of its sixteen rounds
+  int mine_e[kChunk / 32];
+#pragma unroll
+  for (int j = 0; j < kChunk / 32; ++j) {
+    const int64_t i = begin + j * 32 + lane;
+    mine_e[j] = i < end ? load_expert(ids, i, num_experts, status) : -1;
+  }
+#pragma unroll
+  for (int j = 0; j < kChunk / 32; ++j) {
+    if (begin + j * 32 >= end) break;
+    const int e = mine_e[j];
     const unsigned peers = __match_any_sync(0xffffffffu, e);
     if (e >= 0 && (peers & ((1u << lane) - 1)) == 0) mine[e] += __popc(peers);
     __syncwarp();
@@ -166,9 +175,17 @@ moe_scatter_kernel(const IdT* __restrict__ ids, int64_t total, int num_experts,
   for (int e = lane; e < num_experts; e += 32) next[e] = offsets[chunk * num_experts + e];
   __syncwarp();
   const int64_t end = begin + kChunk < total ? begin + kChunk : total;
-  for (int64_t i = begin + lane; i - lane < end; i += 32) {
-    const bool active = i < end;
-    const int e = active ? load_expert(ids, i, num_experts, status) : -1;
+  int mine_e[kChunk / 32];   // fetched up front, as in the count kernel
+#pragma unroll
+  for (int j = 0; j < kChunk / 32; ++j) {
+    const int64_t i = begin + j * 32 + lane;
+    mine_e[j] = i < end ? load_expert(ids, i, num_experts, status) : -1;
+  }
+#pragma unroll
+  for (int j = 0; j < kChunk / 32; ++j) {
+    if (begin + j * 32 >= end) break;
+    const int64_t i = begin + j * 32 + lane;
+    const int e = mine_e[j];
     const unsigned peers = __match_any_sync(0xffffffffu, e);
     const unsigned before = peers & ((1u << lane) - 1);
     if (e >= 0) sorted_token_ids[next[e] + __popc(before)] = static_cast<int>(i);
