@@ -123,6 +123,49 @@ def test_search_space_always_starts_with_automatic():
     assert all(c.tile_n == 0 and c.split_k <= 1 for c in scaled)
 
 
+def test_override_is_per_thread():
+    import threading
+    parts = ("gemm", _lib.F16, _lib.F16, _lib.B_KN, 64, 64, 64, 1)
+    seen = {}
+    ready, done = threading.Event(), threading.Event()
+
+    def other():
+        ready.wait()
+        seen["other"] = tune.config_for(*parts)     # the main thread's override is not visible here
+        done.set()
+
+    t = threading.Thread(target=other)
+    t.start()
+    prev = tune.get_db()
+    try:
+        tune.set_db(None)
+        with tune.use_config(tune.GemmConfig(kernel=1)):
+            ready.set()
+            done.wait()
+            assert tune.config_for(*parts) == tune.GemmConfig(kernel=1)
+    finally:
+        tune.set_db(prev)
+        t.join()
+    assert seen["other"] is None
+
+
+def test_moe_row_tile_choice(monkeypatch):
+    from b200k import moe
+    monkeypatch.delenv("B200K_MOE_TILE", raising=False)
+    monkeypatch.delenv("B200K_SINGLE_CTA", raising=False)
+    assert moe._moe_tile() == 256
+    assert moe._moe_tile(16384 * 8, 64) == 256          # 2048 replicas per expert
+    assert moe._moe_tile(256 * 6, 1408) == 128          # about one replica per expert
+    assert moe._moe_tile(110 * 4, 16) == 128            # 27 per expert
+    monkeypatch.setenv("B200K_MOE_TILE", "256")
+    assert moe._moe_tile(256 * 6, 1408) == 256
+    monkeypatch.setenv("B200K_MOE_TILE", "128")
+    assert moe._moe_tile(16384 * 8, 64) == 128
+    monkeypatch.delenv("B200K_MOE_TILE")
+    monkeypatch.setenv("B200K_SINGLE_CTA", "1")
+    assert moe._moe_tile(16384 * 8, 64) == 128
+
+
 # ---- GPU: every kernel form a search may pick computes the same product ----------------------
 def _rand(shape, dtype, seed):
     g = torch.Generator().manual_seed(seed)
