@@ -42,17 +42,6 @@ struct FmhaParams {
   int* status;
 };
 
-#ifdef B200K_TRACE
-// Debug build only: cycles per softmax thread summed over threads of lane 0, quarter 0.
-// 0 wait S_FULL, 1 TMEM load, 2 max + bookkeeping, 3 exp / pack / store, 4 tiles
-__device__ unsigned long long g_fmha_trace[8];
-#define FT0(v) long long v = clock64()
-#define FTADD(i, v) do { if (trace_me) atomicAdd(&g_fmha_trace[i], static_cast<unsigned long long>(clock64() - (v))); } while (0)
-#else
-#define FT0(v)
-#define FTADD(i, v)
-#endif
-
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -108,12 +97,8 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
     float m_used = -INFINITY;
     float l = 0.0f;
     bool ok = true;
-#ifdef B200K_TRACE
-    const bool trace_me = (lane == 0) && (quarter == 0);
-#endif
     for (int j = 0; j < n_kv; ++j) {
       const uint32_t ph = j & 1;
-      FT0(t_w);
       if (!mbar_wait(s_full, ph, abort_flag)) {
         report_status(p.status, 31, j);
         *abort_flag = 1;
@@ -121,8 +106,6 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
         break;
       }
       tc_fence_after_sync();
-      FTADD(0, t_w);
-      FT0(t_l);
       float s[128];
       {
         uint32_t r[128];
@@ -131,8 +114,6 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
 #pragma unroll
         for (int i = 0; i < 128; ++i) s[i] = __uint_as_float(r[i]);
       }
-      FTADD(1, t_l);
-      FT0(t_m);
       const int key0 = j * kFmhaBN;
       const bool need_mask = (key0 + kFmhaBN > p.sk) || (p.causal && key0 + kFmhaBN - 1 > p.input_pos + q0);
       if (need_mask) {
@@ -176,8 +157,6 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
         }
       }
       const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;
-      FTADD(2, t_m);
-      FT0(t_e);
       // packed fp32 pairs: one FFMA2 scales and shifts two scores, one FADD2 adds two
       // probabilities into the running sums
       const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
@@ -210,10 +189,6 @@ __device__ __forceinline__ void softmax_tile(const FmhaParams& p, int warp, int 
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
-      FTADD(3, t_e);
-#ifdef B200K_TRACE
-      if (trace_me) atomicAdd(&g_fmha_trace[4], 1ull);
-#endif
     }
     // epilogue: O / l
     if (ok && n_kv > 0) {
@@ -784,13 +759,3 @@ extern "C" int64_t b200k_fmha_workspace_bytes(const b200k_fmha_args* a) {
   if (sms <= 0) return 0;
   return fmha_decode_workspace_bytes(a, sms);
 }
-
-#ifdef B200K_TRACE
-extern "C" int b200k_debug_fmha_trace(unsigned long long* out8) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out8, b200k::g_fmha_trace, sizeof(unsigned long long) * 8);
-  unsigned long long zero[8] = {};
-  cudaMemcpyToSymbol(b200k::g_fmha_trace, zero, sizeof(zero));
-  return 0;
-}
-#endif

@@ -33,23 +33,6 @@
 
 namespace b200k {
 
-#ifdef B200K_TRACE
-// Debug build only: cycle counters summed over all CTAs.
-// 0 producer wait(empty), 1 producer total, 2 mma wait(full), 3 mma wait(acc), 4 mma total,
-// 5 epilogue wait(acc_full), 6 epilogue total, 7 mma issue (descs + cp + mma + commit);
-// 2, 3, 4 and 7 are those of the first issuer; 12 / 13 cycles and nanoseconds of CTA 0's producer;
-// 8 - 11, 14, 15: nanoseconds from kernel entry in CTA 0 (prologue done, first load issued, first
-// operands landed, first tile's MMAs issued, first accumulator complete, last tile stored; each
-// stamp is a %globaltimer read of a few hundred nanoseconds itself)
-__device__ unsigned long long g_trace[16];
-#define TRACE_T0(var) long long var = clock64()
-#define TRACE_ADD(idx, var) atomicAdd(&g_trace[idx], static_cast<unsigned long long>(clock64() - (var)))
-#define TRACE_ACC(acc, var) acc += clock64() - (var)
-#else
-#define TRACE_T0(var)
-#define TRACE_ADD(idx, var)
-#define TRACE_ACC(acc, var)
-#endif
 
 template <int KIND>
 struct PairCfg {
@@ -108,12 +91,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-#ifdef B200K_TRACE
-  const unsigned long long ns_entry = global_timer_ns();
-#define TRACE_STAMP(idx) do { if (blockIdx.x == 0 && lane == 0) g_trace[idx] = global_timer_ns() - ns_entry; } while (0)
-#else
-#define TRACE_STAMP(idx)
-#endif
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -140,7 +117,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  if (warp == 0) TRACE_STAMP(8);   // prologue done
 
   // grouped mode: 256-row tiles, the live count comes from the device
   int tiles_m = (p.m + 255) / 256;
@@ -159,11 +135,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const bool elected = elect_one();
       uint32_t it = 0;
       bool ok = true;
-      TRACE_T0(t_total);
-#ifdef B200K_TRACE
-      long long w_empty = 0;
-      const unsigned long long ns0 = global_timer_ns();
-#endif
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
         int group = tc.batch, a_batch = tc.batch;
@@ -180,14 +151,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int kb = 0; kb < p.k_iters; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          TRACE_T0(t_w);
           if (!mbar_wait_relaxed(empty_bar(s), ph ^ 1, abort_flag, 64)) {
             report_status(p.status, 51, s);
             *abort_flag = 1;
             ok = false;
             break;
           }
-          TRACE_ACC(w_empty, t_w);
           // the leader's barrier collects the bytes of both CTAs
           const uint32_t lead_full = map_to_cta(full_bar(s), 0);
           const uint32_t a_dst = tiles_base + s * Cfg::kStageBytes;
@@ -196,7 +165,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (elected) {
             if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * (Cfg::kABytes + b_rows * 128 + Cfg::kSfBytes));
             tma_load_3d_pair(a_dst, &tmap_a, lead_full, kx, m0, a_batch);
-            if (it == 0) TRACE_STAMP(9);   // first load issued
             if (!p.b_mn) {
               tma_load_3d_pair(b_dst, &tmap_b, lead_full, kx, nb, group);   // box of b_rows rows
             } else {
@@ -222,16 +190,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
       }
-#ifdef B200K_TRACE
-      if (elected) {
-        atomicAdd(&g_trace[0], static_cast<unsigned long long>(w_empty));
-        TRACE_ADD(1, t_total);
-        if (blockIdx.x == 0) {   // SM clock seen by this kernel: cycles / nanoseconds of one producer
-          g_trace[12] = static_cast<unsigned long long>(clock64() - t_total);
-          g_trace[13] = global_timer_ns() - ns0;
-        }
-      }
-#endif
     }
     __syncwarp();
   } else if (warp == 1 || warp == 6) {
@@ -245,10 +203,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t it_base = 0;
       uint32_t lt = 0;
       bool ok = true;
-      TRACE_T0(t_total);
-#ifdef B200K_TRACE
-      long long w_full = 0, w_acc = 0, t_issue = 0;
-#endif
       uint32_t tsfa = 0, tsfb = 0;
       if constexpr (Cfg::kScaled) {
         tsfa = tmem_base + Cfg::kSfBase + q * Cfg::kSfSlotCols;
@@ -258,7 +212,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         if (p.tile_group != nullptr && p.tile_group[tile_coord(tile, tiles_m, p.tiles_n).pid_m] < 0) continue;
         const int w = lt & 1;
-        TRACE_T0(t_a);
         if (!mbar_wait(acc_empty_bar(w), ((lt >> 1) & 1) ^ 1, abort_flag)) {
           report_status(p.status, 52, 100 + w);
           *abort_flag = 1;
@@ -281,22 +234,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
         tc_fence_after_sync();
-        TRACE_ACC(w_acc, t_a);
         const uint32_t tmem_acc = tmem_base + w * Cfg::kAccStride;
         for (int kb = q; kb < p.k_iters; kb += 2) {
           const uint32_t it = it_base + kb;
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          TRACE_T0(t_f);
           if (!mbar_wait(full_bar(s), ph, abort_flag)) {
             report_status(p.status, 52, s);
             *abort_flag = 1;
             ok = false;
             break;
           }
-          TRACE_ACC(w_full, t_f);
-          if (q == 0 && it == 0) TRACE_STAMP(10);   // first operands landed
-          TRACE_T0(t_i);
           tc_fence_after_sync();
           const uint32_t a_addr = tiles_base + s * Cfg::kStageBytes;
           const uint32_t b_addr = a_addr + Cfg::kABytes;
@@ -345,27 +293,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tc_commit_pair(e1);
             if (kb == 0 && p.k_iters > 1) tc_commit_pair(map_to_cta(tile_open_bar(w), 0));
           }
-          TRACE_ACC(t_issue, t_i);
         }
         if (ok) {
           const uint32_t f0 = map_to_cta(acc_full_bar(w), 0), f1 = map_to_cta(acc_full_bar(w), 1);
           if (elected) {
             tc_commit_pair(f0);
             tc_commit_pair(f1);
-            if (q == 0 && lt == 0) TRACE_STAMP(11);   // first tile's MMAs issued
           }
         }
         ++lt;
         it_base += p.k_iters;
       }
-#ifdef B200K_TRACE
-      if (elected && q == 0) {
-        atomicAdd(&g_trace[2], static_cast<unsigned long long>(w_full));
-        atomicAdd(&g_trace[3], static_cast<unsigned long long>(w_acc));
-        atomicAdd(&g_trace[7], static_cast<unsigned long long>(t_issue));
-        TRACE_ADD(4, t_total);
-      }
-#endif
     }
     __syncwarp();
   } else if (warp < 6) {
@@ -387,22 +325,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     const uint32_t lead_ovl = map_to_cta(ovl_free_bar, 0);
     uint32_t lt = 0;
-    TRACE_T0(t_total);
-#ifdef B200K_TRACE
-    long long w_accf = 0;
-#endif
     for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
       const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
       if (p.tile_group != nullptr && p.tile_group[tc.pid_m] < 0) continue;
       const int w = lt & 1;
-      TRACE_T0(t_e);
       if (!mbar_wait_relaxed(acc_full_bar(w), (lt >> 1) & 1, abort_flag, 64)) {
         report_status(p.status, 53, w);
         *abort_flag = 1;
         break;
       }
-      TRACE_ACC(w_accf, t_e);
-      if (warp == 2 && lt == 0) TRACE_STAMP(14);   // first accumulator complete
       tc_fence_after_sync();
       const int row = tc.pid_m * 256 + rank * 128 + quarter * 32 + lane;
       int64_t out_row = row;
@@ -606,15 +537,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster_relaxed(map_to_cta(acc_empty_bar(w), 0));
-      if (warp == 2) TRACE_STAMP(15);   // a tile stored (the last one stays)
       ++lt;
     }
-#ifdef B200K_TRACE
-    if (threadIdx.x == 64) {
-      atomicAdd(&g_trace[5], static_cast<unsigned long long>(w_accf));
-      TRACE_ADD(6, t_total);
-    }
-#endif
   }
 
   tc_fence_before_sync();
@@ -690,13 +614,3 @@ int launch_gemm_pair(int kind, int out_dtype, const CUtensorMap* maps, const Gem
 }
 
 }  // namespace b200k
-
-#ifdef B200K_TRACE
-extern "C" int b200k_debug_trace(unsigned long long* out16) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out16, b200k::g_trace, sizeof(unsigned long long) * 16);
-  unsigned long long zero[16] = {};
-  cudaMemcpyToSymbol(b200k::g_trace, zero, sizeof(zero));
-  return 0;
-}
-#endif

@@ -556,6 +556,19 @@ extern "C" int b200k_nvfp4_quantize_noalloc(const b200k_quantize_args* a, b200k_
   const int64_t kblocks = ceil_div(a->k, 16);
   if (a->sf_swizzled && a->sf_k_atoms < ceil_div(kblocks, 4))
     return fail(B200K_INVALID_ARG, "sf_k_atoms too small");
+  if (a->tensor_scale_given) {
+    // The scale is the caller's: there is no maximum to find, so the built-in scratch is
+    // not touched and the size limit does not apply.  Same launch as b200k_nvfp4_quantize.
+    if (!a->tensor_scale) return fail(B200K_INVALID_ARG, "tensor_scale_given without tensor_scale");
+    switch (a->x_dtype) {
+      case B200K_F32: launch_nvfp4_quantize<float>(a, nullptr, stream); break;
+      case B200K_BF16: launch_nvfp4_quantize<__nv_bfloat16>(a, nullptr, stream); break;
+      case B200K_F16: launch_nvfp4_quantize<__half>(a, nullptr, stream); break;
+      default: return fail(B200K_INVALID_ARG, "x_dtype must be f32, bf16 or f16");
+    }
+    B200K_CHECK_LAUNCH("nvfp4_quantize_noalloc launch");
+    return B200K_OK;
+  }
   const int64_t slabs = ceil_div(a->rows * a->k, kNoAllocSlabElems);
   if (slabs > kNoAllocSlots)
     return fail(B200K_UNSUPPORTED,

@@ -245,7 +245,10 @@ int b200k_nvfp4_quantize(const b200k_quantize_args* args, b200k_stream stream);
  *     runtime query, no allocation); make that first call outside any stream capture.
  *   - All calls on a device share the array.  Each call overwrites the slots it later
  *     reads, so nothing needs clearing, but two calls that overlap on the GPU (different
- *     streams) race on it: serialise them. */
+ *     streams) race on it: serialise them.
+ *   - With `tensor_scale_given` the caller's scale is used as in b200k_nvfp4_quantize (it is
+ *     read, never written): no maximum is searched, the built-in array is not touched, and
+ *     neither the size limit nor the overlap rule applies. */
 int b200k_nvfp4_quantize_noalloc(const b200k_quantize_args* args, b200k_stream stream);
 
 /* Logical (rows, kblocks) scale bytes (row stride ld) -> swizzle_32_4_4 atoms; replaces
