@@ -1,18 +1,30 @@
 """Benchmark of the hot path on B200: TFLOPS of the block-scaled / dense contraction kernels.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload mxfp8_gemm|nvfp4_gemm|dense_f16|ag_nvfp4_gemm|moe_ep_bf16|ref_shapes|fmha_decode|
-                                fmha_causal|moe_bf16|moe_mxfp8|mxfp8_quantize|nvfp4_quantize]
+                    [--workload ag_nvfp4_gemm|mxfp8_gemm|nvfp4_gemm|dense_f16|fmha_causal|fmha_decode|
+                                moe_bf16|moe_mxfp8|moe_ep_bf16|moe_ep_mxfp8|mxfp8_quantize|nvfp4_quantize|
+                                ref_shapes]
 
-One step = one pass of the workload's kernel over one batch of seeded synthetic input.
-The default workload is the headline configuration: MXFP8 GEMM, M = N = K = 8192, e4m3 operands
-with ue8m0 scales per 32 elements of K, fp32 accumulation, bf16 output.  With N > 1 every
-rank runs the same problem on its own GPU (the GEMM does not shard: replicas only) and the
-value is the sum over ranks divided by the slowest rank's time.
+One step = one pass of the workload's kernels over one batch of seeded synthetic input.  Inputs
+are drawn on the CPU from torch.Generator().manual_seed(seed) and copied to the device, so the
+GPU arm, its parity check and the CPU arm see the same numbers.
+
+The default workload is the path that shards: the NVFP4 FFN up-projection (M = 8192 tokens,
+N = 28672, K = 8192, e2m1 operands with ue4m3 scales per 16 elements of K and one fp32 scale
+per tensor, bf16 output) run as the AllGather GEMM.  A is row-sharded M / N_gpus per rank and
+gathered over NVLink out of the peers' symmetric-memory buffers while the rank's own rows are
+already being multiplied; every rank computes the full (M, N) product against its own
+weights, so the work per rank is fixed (weak scaling) and at one GPU the workload is the plain
+8192 x 28672 x 8192 NVFP4 GEMM.  The same JSON line carries the MXFP8 8192-cubed GEMM as a
+secondary record (`also`).
+
+Before anything is timed, one step's output is compared with the CPU oracle on sampled rows
+(`parity_checked`, `max_err`), as the reference's benches do (test/bench_matmul.py:34-36,
+111-112, test/bench_attention.py:58-69, test/bench_moe.py:58-68); a mismatch aborts the run.
 
 `--impl reference` times the reference's CPU ground truth for the same workload (the
-de-quantised fp32 matmul of samples/BlockScaledMatMul.py:359-361, restated in oracle/) on
-the host cores, on a bounded block of the output.
+de-quantised fp32 matmul of samples/BlockScaledMatMul.py:359-361 and its siblings, restated in
+oracle/) on the host cores, on a bounded block of the same inputs.
 
 Prints ONE JSON line (rank 0).
 """
@@ -33,6 +45,7 @@ for p in (ROOT, os.path.join(ROOT, "cutile-python_b200")):
 import torch  # noqa: E402
 
 L2_BYTES = 126 * 1024 * 1024
+NVLINK_PEER_COPY_GBS = 770.0    # measured peer copy per direction on this pool (nominal 900)
 
 
 def load_peaks():
@@ -41,8 +54,56 @@ def load_peaks():
         with open(path) as f:
             d = json.load(f)
         return {"bf16_tflops": float(d["bf16_tflops"]), "hbm_gbs": float(d["hbm_gbs"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
                 "source": "measured"}
-    return {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def bind_near_gpu(device) -> str:
+    """Runs this process on the cores of the NUMA node the GPU hangs off, so that the pinned
+    host buffers of the end-to-end leg are allocated there (first touch) and the ranks of one
+    box do not all stream through one socket.  Best effort: returns what it did."""
+    try:
+        props = torch.cuda.get_device_properties(device)
+        bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return "no NUMA information"
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return f"node {node}: none of its cores are available to this process"
+        os.sched_setaffinity(0, allowed)
+        return f"node {node}, {len(allowed)} cores"
+    except Exception as e:  # pragma: no cover - depends on the box
+        return f"unavailable ({type(e).__name__})"
+
+
+def randn_rows(gen, rows: int, cols: int, take: int | None = None) -> torch.Tensor:
+    """The first `take` rows of torch.randn(rows, cols, generator=gen).  For column counts that
+    are multiples of 16 the CPU generator fills a tensor front to back in blocks of 16, so the
+    leading rows of a large draw equal a smaller draw from the same state; a partial draw leaves
+    the generator short of the full one, so only the LAST tensor of a sequence may be cut."""
+    assert cols % 16 == 0
+    return torch.randn(rows if take is None else min(take, rows), cols, generator=gen)
+
+
+def close_or_die(name: str, got: torch.Tensor, ref: torch.Tensor, rtol: float, atol_rel: float) -> float:
+    """Asserts |got - ref| <= atol_rel * max|ref| + rtol * |ref| elementwise; returns the
+    largest error relative to max|ref|."""
+    got, ref = got.detach().float().cpu(), ref.detach().float().cpu()
+    scale = float(ref.abs().max()) or 1.0
+    err = (got - ref).abs()
+    bad = err > (atol_rel * scale + rtol * ref.abs())
+    if bool(bad.any()) or not bool(torch.isfinite(got).all()):
+        raise SystemExit(f"bench.py: parity check failed for {name}: {int(bad.sum())} of {bad.numel()} sampled "
+                         f"values differ from the oracle (max error {float(err.max()):.4g}, scale {scale:.4g})")
+    return float(err.max()) / scale
 
 
 # --------------------------------------------------------------------------------------
@@ -53,9 +114,16 @@ class Workload:
     dtype = ""
     tensor_rate_vs_bf16 = 1.0   # tensor-core rate of the operand format relative to bf16
     distributed = False         # needs a process group even on one GPU
+    world, rank = 1, 0
 
     def config(self):
         raise NotImplementedError
+
+    def parity(self) -> dict:
+        raise NotImplementedError
+
+    def launches(self) -> int:
+        return getattr(self, "launches_per_step", 1)
 
     # ---- end-to-end leg as a two-slot software pipeline ---------------------------------
     # Every step still copies its inputs from pinned host memory and its result back to
@@ -108,8 +176,15 @@ class Workload:
                 torch.cuda.current_stream().wait_stream(st)
 
 
+def _sample(n: int, fixed, count: int, seed: int) -> torch.Tensor:
+    """Sorted sample of `count` indices below n that always contains `fixed` (tile seams)."""
+    g = torch.Generator().manual_seed(seed)
+    pick = torch.randperm(n, generator=g)[:count].tolist()
+    return torch.tensor(sorted(set(i for i in fixed if 0 <= i < n) | set(pick)))
+
+
 class Mxfp8Gemm(Workload):
-    """The headline MXFP8 configuration (8192 cubed, bf16 output)."""
+    """BASELINE config 2: MXFP8 GEMM 8192 cubed, bf16 output."""
     name = "mxfp8_gemm_8192x8192x8192_bf16out"
     dtype = "e4m3 x e4m3 (ue8m0 scale / 32) -> fp32 accumulate -> bf16"
     tensor_rate_vs_bf16 = 2.0
@@ -117,6 +192,8 @@ class Mxfp8Gemm(Workload):
     seed = 1
     sets = 2   # rotating operand/output sets, so that no step finds its inputs in L2
     cpu_block_limit = 8192
+    b_std = 1.0
+    launches_per_step = 1
 
     def flops(self):
         return 2.0 * self.M * self.N * self.K
@@ -125,18 +202,26 @@ class Mxfp8Gemm(Workload):
         ks = self.K // 32
         return self.M * self.K + self.N * self.K + (self.M + self.N) * ks + 2 * self.M * self.N
 
+    def draw(self, gen, take_a=None, take_b=None):
+        """A (M, K) activations and B (N, K) weights as bf16 CPU tensors, A first."""
+        a = randn_rows(gen, self.M, self.K)                      # always whole: B follows it
+        b = randn_rows(gen, self.N, self.K, take_b)
+        if self.b_std != 1.0:
+            b = self.b_std * b
+        return (a if take_a is None else a[:take_a]).bfloat16(), b.bfloat16()
+
     def setup(self, device):
         import b200k
-        g = torch.Generator(device=device).manual_seed(self.seed)
+        g = torch.Generator().manual_seed(self.seed)
         self.inputs = []
         for i in range(self.sets):
-            a = torch.randn(self.M, self.K, device=device, generator=g).bfloat16()
-            b = torch.randn(self.N, self.K, device=device, generator=g).bfloat16()
-            aq, sa = b200k.block_quantize(a, 32, swizzled_scale=True)
-            bq, sb = b200k.block_quantize(b, 32, swizzled_scale=True)
+            a, b = self.draw(g)
+            if i == 0:
+                self.a_cpu, self.b_cpu = a, b
+            aq, sa = b200k.block_quantize(a.to(device), 32, swizzled_scale=True)
+            bq, sb = b200k.block_quantize(b.to(device), 32, swizzled_scale=True)
             c = torch.empty(self.M, self.N, device=device, dtype=torch.bfloat16)
             self.inputs.append((aq, sa, bq, sb, c))
-            del a, b
         self.b200k = b200k
         self.i = 0
 
@@ -146,7 +231,23 @@ class Mxfp8Gemm(Workload):
         self.b200k.cutile_block_scaled_matmul(aq, sa, bq.T, sb, C=c)
         return c
 
-    launches_per_step = 1
+    def parity(self):
+        import oracle
+        self.i = 0
+        c = self.step()
+        rows = _sample(self.M, (0, 127, 128, 255, 256, self.M - 1), 10, 11)
+        cols = _sample(self.N, (0, 255, 256, self.N - 1), 256, 12)
+        aq, sa = oracle.block_quantize_ref(self.a_cpu[rows])
+        bq, sb = oracle.block_quantize_ref(self.b_cpu[cols])
+        got_q = self.inputs[0][0][rows.to(c.device)].cpu().view(torch.uint8)
+        if not torch.equal(got_q, aq.view(torch.uint8)):
+            raise SystemExit("bench.py: parity check failed: quantised bytes differ from the oracle's")
+        ref = oracle.block_scaled_matmul_ref(aq, sa, bq, sb)
+        got = c[rows.to(c.device)][:, cols.to(c.device)]
+        self.i = 0
+        return {"max_err": close_or_die(self.name, got, ref, 2e-2, 2e-2), "tol": "rtol 2e-2, atol 2e-2 of max|ref|",
+                "what": f"{len(rows)} rows x {len(cols)} columns of one step's output against the de-quantised "
+                        "fp32 product of the oracle-quantised operands; quantised bytes of those rows bit-exact"}
 
     # ---- end-to-end: host buffers in, host buffer out, through the public call
     def setup_e2e(self, device):
@@ -159,13 +260,12 @@ class Mxfp8Gemm(Workload):
             self.b200k.cutile_block_scaled_matmul(aq, sa, bq.T, sb, C=dev_out)
         self.pipe_step(compute)
 
-    # ---- CPU ground truth on an S x S block of the output
+    # ---- CPU ground truth on an S x S block of the output, same numbers as the GPU arm
     def cpu_setup(self):
         import oracle
         g = torch.Generator().manual_seed(self.seed)
         s = self.cpu_block_limit
-        a = torch.randn(s, self.K, generator=g).bfloat16()
-        b = torch.randn(s, self.K, generator=g).bfloat16()
+        a, b = self.draw(g, take_a=s, take_b=s)
         self.cpu_ops = oracle.block_quantize_ref(a) + oracle.block_quantize_ref(b)
         self.oracle = oracle
 
@@ -183,47 +283,75 @@ class Mxfp8Gemm(Workload):
     def config(self):
         return {"workload": self.name, "M": self.M, "N": self.N, "K": self.K,
                 "scale_block": 32, "out": "bf16", "seed": self.seed,
+                "inputs": "torch.Generator().manual_seed(seed) on the CPU, copied to the device",
                 "l2": f"{self.sets} rotating operand/output sets of "
                       f"{self.algorithmic_bytes() / 2**20:.0f} MiB each (> 126 MiB L2)"}
 
 
 class Nvfp4Gemm(Mxfp8Gemm):
-    """The NVFP4 FFN up-projection (8192 x 28672 x 8192) on one GPU: the per-rank problem of
-    the AllGather GEMM."""
+    """BASELINE config 3 on one GPU: the NVFP4 FFN up-projection 8192 x 28672 x 8192."""
     name = "nvfp4_gemm_8192x28672x8192_bf16out"
     dtype = "e2m1 x e2m1 (ue4m3 scale / 16, fp32 tensor scale) -> fp32 accumulate -> bf16"
     tensor_rate_vs_bf16 = 4.0
     M, N, K = 8192, 28672, 8192
     seed = 2
+    sets = 1
+    b_std = 0.02
+    cpu_block_limit = 2048
 
     def algorithmic_bytes(self):
         return (self.M + self.N) * (self.K // 2 + self.K // 16) + 2 * self.M * self.N
 
     def setup(self, device):
         import b200k
-        g = torch.Generator(device=device).manual_seed(self.seed)
-        self.inputs = []
-        for i in range(self.sets):
-            a = torch.randn(self.M, self.K, device=device, generator=g).bfloat16()
-            b = (0.02 * torch.randn(self.N, self.K, device=device, generator=g)).bfloat16()
-            qa = b200k.nvfp4_quantize(a)
-            qb = b200k.nvfp4_quantize(b)
-            c = torch.empty(self.M, self.N, device=device, dtype=torch.bfloat16)
-            self.inputs.append((qa, qb, c))
-            del a, b
+        g = torch.Generator().manual_seed(self.seed)
+        self.a_cpu, self.b_cpu = self.draw(g)
+        self.qa = b200k.nvfp4_quantize(self.a_cpu.to(device))
+        self.qb = b200k.nvfp4_quantize(self.b_cpu.to(device))
+        self.c = torch.empty(self.M, self.N, device=device, dtype=torch.bfloat16)
         self.b200k = b200k
-        self.i = 0
 
     def step(self):
-        qa, qb, c = self.inputs[self.i % self.sets]
-        self.i += 1
-        self.b200k.cutile_nvfp4_matmul(*qa, *qb, C=c)
-        return c
+        self.b200k.cutile_nvfp4_matmul(*self.qa, *self.qb, C=self.c)
+        return self.c
+
+    def _nvfp4_parity(self, c, shard_rows, shard_scales, w_scale):
+        """Sampled rows x columns of c against the oracle: the rows' operands quantised by the
+        oracle under their shard's tensor scale (amax / 2688 of the shard, checked against the
+        scale the device found), the de-quantised fp32 product as the reference."""
+        import numpy as np
+        import oracle
+        m = self.M
+        seams = (0, 127, 128, 255, 256, shard_rows - 1, shard_rows, m - shard_rows, m - 256, m - 1)
+        rows = _sample(m, seams, 6, 21)
+        cols = _sample(self.N, (0, 255, 256, self.N - 1), 256, 22)
+        f32 = np.float32
+        ts_b = f32(f32(self.b_cpu.float().abs().max()) / f32(2688.0))
+        if float(w_scale) != float(ts_b):
+            raise SystemExit("bench.py: parity check failed: tensor scale of the weights differs from amax / 2688")
+        bq = oracle.nvfp4_quantize_ref(self.b_cpu[cols], tensor_scale=ts_b)
+        worst = 0.0
+        for p in sorted(set((rows // shard_rows).tolist())):
+            mine = rows[(rows // shard_rows) == p]
+            shard = self.a_cpu[p * shard_rows:(p + 1) * shard_rows]
+            ts_a = f32(f32(shard.float().abs().max()) / f32(2688.0))
+            if float(shard_scales[p]) != float(ts_a):
+                raise SystemExit(f"bench.py: parity check failed: tensor scale of shard {p} differs from amax / 2688")
+            aq = oracle.nvfp4_quantize_ref(self.a_cpu[mine], tensor_scale=ts_a)
+            ref = oracle.nvfp4_matmul_ref(*aq, *bq)
+            got = c[mine.to(c.device)][:, cols.to(c.device)]
+            worst = max(worst, close_or_die(self.name, got, ref, 2e-2, 2e-2))
+        return {"max_err": worst, "tol": "rtol 2e-2, atol 2e-2 of max|ref|",
+                "what": f"{len(rows)} rows (tile and shard seams) x {len(cols)} columns of one step's output "
+                        "against the de-quantised fp32 product of the oracle-quantised operands"}
+
+    def parity(self):
+        c = self.step()
+        return self._nvfp4_parity(c, self.M, [float(self.qa[2])], float(self.qb[2]))
 
     def setup_e2e(self, device):
-        qa, qb, c = self.inputs[0]
-        flat = list(qa) + list(qb)
-        self.pipe_setup(device, [t.cpu().pin_memory() for t in flat], c)
+        flat = list(self.qa) + list(self.qb)
+        self.pipe_setup(device, [t.cpu().pin_memory() for t in flat], self.c)
 
     def step_e2e(self):
         self.pipe_step(lambda dev_in, dev_out: self.b200k.cutile_nvfp4_matmul(*dev_in, C=dev_out))
@@ -231,9 +359,8 @@ class Nvfp4Gemm(Mxfp8Gemm):
     def cpu_setup(self):
         import oracle
         g = torch.Generator().manual_seed(self.seed)
-        s = 2048
-        a = torch.randn(s, self.K, generator=g).bfloat16()
-        b = (0.02 * torch.randn(s, self.K, generator=g)).bfloat16()
+        s = self.cpu_block_limit
+        a, b = self.draw(g, take_a=s, take_b=s)
         self.cpu_ops = (oracle.nvfp4_quantize_ref(a), oracle.nvfp4_quantize_ref(b))
         self.oracle = oracle
 
@@ -244,200 +371,112 @@ class Nvfp4Gemm(Mxfp8Gemm):
     def config(self):
         c = super().config()
         c["scale_block"] = 16
+        c["l2"] = "operands and output of one step are 610 MiB (> 126 MiB L2)"
         return c
 
 
 class AgNvfp4Gemm(Nvfp4Gemm):
-    """The NVFP4 FFN up-projection as the AllGather GEMM: A row-sharded M / world per rank, gathered
-    over NVLink from the peers' symmetric-memory buffers, every rank computing the full
-    (M, N) product against its own weights (fixed work per rank: weak scaling)."""
+    """BASELINE config 3 as it is stated: the NVFP4 FFN up-projection as the AllGather GEMM.  A is
+    row-sharded M / world per rank (every rank quantises its own rows), gathered over NVLink from
+    the peers' symmetric-memory buffers, every rank computing the full (M, N) product against
+    its own weights (fixed work per rank: weak scaling).  One GPU: the plain GEMM."""
     name = "allgather_nvfp4_gemm_8192x28672x8192_bf16out"
-    distributed = True
-    sets = 1
-    launches_per_step = 3   # two gather kernels + the GEMM
+
+    def launches(self):
+        if self.world == 1:
+            return 1
+        return 3 + 1 + (1 if self.rank in (0, self.world - 1) else 2)   # gathers, local GEMM, remote GEMMs
+
+    def gathered_bytes(self):
+        return (self.world - 1) * (self.M // self.world) * (self.K // 2 + self.K // 16)
 
     def setup(self, device):
-        import torch.distributed as dist
-        import torch.distributed._symmetric_memory as symm_mem
         import b200k
-        world, rank = dist.get_world_size(), dist.get_rank()
+        world, rank = self.world, self.rank
+        if self.M % (128 * world):
+            raise SystemExit(f"{self.M} rows do not split into 128-row scale tiles over {world} ranks")
         rows = self.M // world
-        g = torch.Generator(device=device).manual_seed(self.seed + 1000 * rank)
-        a = torch.randn(rows, self.K, device=device, generator=g).bfloat16()
-        gw = torch.Generator(device=device).manual_seed(self.seed)
-        b = (0.02 * torch.randn(self.N, self.K, device=device, generator=gw)).bfloat16()
-        aq, asf, ats = b200k.nvfp4_quantize(a)
-        self.wq = b200k.nvfp4_quantize(b)
-        del a, b
-        self.s_q = symm_mem.empty(aq.shape, device=device, dtype=torch.uint8).copy_(aq)
-        self.s_sf = symm_mem.empty(asf.shape, device=device, dtype=torch.uint8).copy_(asf.view(torch.uint8))
-        self.s_ts = symm_mem.empty(1, device=device, dtype=torch.float32).copy_(ats)
+        g = torch.Generator().manual_seed(self.seed)
+        self.a_cpu, self.b_cpu = self.draw(g)           # the whole problem, the same on every rank
+        mine = self.a_cpu[rank * rows:(rank + 1) * rows].to(device)
+        aq, asf, ats = b200k.nvfp4_quantize(mine)       # each rank quantises its own rows
+        self.qb = b200k.nvfp4_quantize(self.b_cpu.to(device))
+        del mine
+        if world > 1:
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm_mem
+            self.s_q = symm_mem.empty(aq.shape, device=device, dtype=torch.uint8).copy_(aq)
+            self.s_sf = symm_mem.empty(asf.shape, device=device, dtype=torch.uint8).copy_(asf.view(torch.uint8))
+            self.s_ts = symm_mem.empty(1, device=device, dtype=torch.float32).copy_(ats)
+        else:
+            self.s_q, self.s_sf, self.s_ts = aq, asf.view(torch.uint8), ats
         self.plan = b200k.Nvfp4GatherMatmul(self.s_q, self.s_sf, self.s_ts)
         self.c = torch.empty(self.M, self.N, device=device, dtype=torch.bfloat16)
-        self.flush = torch.empty(L2_BYTES * 2, dtype=torch.uint8, device=device)
-        dist.barrier()
+        if world > 1:
+            dist.barrier()
         torch.cuda.synchronize()
         self.b200k = b200k
 
     def step(self):
-        return self.plan.run(*self.wq, out=self.c)
+        return self.plan.run(*self.qb, out=self.c)
+
+    def parity(self):
+        c = self.step()
+        torch.cuda.synchronize()
+        rows = self.M // self.world
+        if self.world > 1:   # the gathered per-row scale vector holds every shard's own scale
+            scales = self.plan.row_scale[::rows].cpu().tolist()
+        else:
+            scales = [float(self.s_ts)]
+        return self._nvfp4_parity(c, self.M // self.world, scales, float(self.qb[2]))
+
+    def gather_only_us(self, reps=10):
+        """Device time of the peer gather alone (the bytes that cross NVLink per step)."""
+        if self.world == 1:
+            return None
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(2):
+            self.plan.gather()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            self.plan.gather()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
 
     def setup_e2e(self, device):
-        self.host_in = [t.cpu().pin_memory() for t in (self.s_q, self.s_sf, self.s_ts)]
-        self.host_out = torch.empty_like(self.c, device="cpu").pin_memory()
-        self.h2d = sum(t.numel() * t.element_size() for t in self.host_in)
-        self.d2h = self.host_out.numel() * self.host_out.element_size()
+        host = [t.cpu().pin_memory() for t in (self.s_q, self.s_sf, self.s_ts)]
+        self.pipe_setup(device, host, self.c)
 
     def step_e2e(self):
-        for d, h in zip((self.s_q, self.s_sf, self.s_ts), self.host_in):
-            d.copy_(h, non_blocking=True)
-        self.plan.run(*self.wq, out=self.c)
-        self.host_out.copy_(self.c, non_blocking=True)
+        def compute(dev_in, dev_out):
+            # this rank's freshly uploaded shard goes into the buffers the peers read
+            for dst, src in zip((self.s_q, self.s_sf, self.s_ts), dev_in):
+                dst.copy_(src, non_blocking=True)
+            self.plan.run(*self.qb, out=dev_out)
+        self.pipe_step(compute)
 
     def config(self):
         c = super().config()
-        c["l2"] = "operands and output of one step are 610 MiB (> 126 MiB L2)"
-        c["sharding"] = "A rows M/world per rank, gathered by peer loads; B replicated"
+        c["sharding"] = ("A rows M / n_gpus per rank, each rank's shard quantised by its owner and "
+                         "gathered by peer loads over NVLink; B replicated; every rank computes (M, N)")
         return c
 
 
-class MoeEpBf16(Workload):
-    """The MoE FFN configuration (16384 tokens, hidden 4096, 64 experts, intermediate 1536,
-    top-8) with experts and tokens sharded over the ranks and an NVLink all-to-all for
-    dispatch and combine.  The whole problem is fixed, so this scales strongly."""
-    name = "moe_ffn_ep_16384tok_h4096_e64_i1536_top8_bf16"
-    dtype = "bf16 x bf16 -> fp32 accumulate -> bf16"
-    tensor_rate_vs_bf16 = 1.0
-    distributed = True
-    scaling = "strong"
-    T, H, E, I, K = 16384, 4096, 64, 1536, 8
-    seed = 4
-    launches_per_step = 8
-
-    def flops(self):
-        return 6.0 * self.T * self.K * self.H * self.I / self.world   # per rank
-
-    def algorithmic_bytes(self):
-        return 2 * (self.E * 3 * self.I * self.H + 2 * self.T * self.H) // self.world
-
-    def setup(self, device):
-        import torch.distributed as dist
-        import b200k
-        self.world, rank = dist.get_world_size(), dist.get_rank()
-        tl, el = self.T // self.world, self.E // self.world
-        g = torch.Generator(device=device).manual_seed(self.seed + 1000 * rank)
-        self.x = torch.randn(tl, self.H, device=device, generator=g).bfloat16()
-        w1 = (0.02 * torch.randn(el, 2 * self.I, self.H, device=device, generator=g)).bfloat16()
-        w2 = (0.02 * torch.randn(el, self.H, self.I, device=device, generator=g)).bfloat16()
-        logits = torch.randn(tl, self.E, device=device, generator=g)
-        vals, self.ids = torch.topk(logits, self.K, dim=-1)
-        self.tw = torch.softmax(vals, dim=-1).bfloat16()
-        self.ep = b200k.ExpertParallelMoE(w1, w2, self.E)
-        self.b200k = b200k
-
-    def step(self):
-        return self.ep.forward(self.x, self.tw, self.ids)
-
-    def setup_e2e(self, device):
-        self.host_in = [t.cpu().pin_memory() for t in (self.x, self.tw, self.ids)]
-        self.dev_in = [torch.empty_like(t) for t in (self.x, self.tw, self.ids)]
-        self.host_out = torch.empty_like(self.x, device="cpu").pin_memory()
-        self.h2d = sum(t.numel() * t.element_size() for t in self.host_in)
-        self.d2h = self.host_out.numel() * self.host_out.element_size()
-
-    def step_e2e(self):
-        for d, h in zip(self.dev_in, self.host_in):
-            d.copy_(h, non_blocking=True)
-        out = self.ep.forward(*self.dev_in)
-        self.host_out.copy_(out, non_blocking=True)
-
-    def cpu_setup(self):
-        import oracle
-        g = torch.Generator().manual_seed(self.seed)
-        t, e = 512, 8
-        self.cpu_ops = ((0.5 * torch.randn(t, self.H, generator=g)),
-                        0.02 * torch.randn(e, 2 * self.I, self.H, generator=g),
-                        0.02 * torch.randn(e, self.H, self.I, generator=g))
-        self.cpu_route = oracle.moe_route_ref(torch.randn(t, e, generator=g), 2)
-        self.oracle = oracle
-
-    def cpu_step(self, s):
-        x, w1, w2 = self.cpu_ops
-        tw, ids = self.cpu_route
-        return self.oracle.moe_ref(x[:s], w1, w2, tw[:s], ids[:s])
-
-    def cpu_flops(self, s):
-        return 6.0 * s * 2 * self.H * self.I
-
-    def cpu_sample_desc(self, s):
-        return f"{s} tokens, 8 experts, top-2 of the same FFN in fp32 (torch CPU)"
-
-    def config(self):
-        return {"workload": self.name, "tokens": self.T, "hidden": self.H, "experts": self.E,
-                "intermediate": self.I, "topk": self.K, "seed": self.seed,
-                "sharding": "experts E/world and tokens T/world per rank; all_to_all dispatch + combine",
-                "l2": "expert weights alone are 2.4 GB / world per rank (> 126 MiB L2)"}
-
-
-class FmhaCausal(Workload):
-    """Causal attention forward, bf16, batch 4, 32 heads, sequence 8192, head dim 128."""
-    name = "fmha_causal_bf16_b4_h32_s8192_d128"
-    dtype = "bf16 x bf16 -> fp32 softmax / accumulate -> bf16"
-    tensor_rate_vs_bf16 = 1.0
-    B, H, S, D = 4, 32, 8192, 128
-    seed = 3
-    sets = 1
-    cpu_limit = 4096
-    launches_per_step = 1
-
-    def flops(self):
-        return 4.0 * self.B * self.H * self.S * self.S * self.D * 0.5
-
-    def algorithmic_bytes(self):
-        return 4 * self.B * self.H * self.S * self.D * 2
-
-    def setup(self, device):
-        import b200k
-        g = torch.Generator(device=device).manual_seed(self.seed)
-        shape = (self.B, self.H, self.S, self.D)
-        self.q, self.k, self.v = (torch.randn(shape, device=device, generator=g).bfloat16() for _ in range(3))
-        self.o = torch.empty_like(self.q)
-        self.b200k = b200k
-
-    def step(self):
-        return self.b200k.cutile_fmha(self.q, self.k, self.v, causal=True, Out=self.o)
-
-    def setup_e2e(self, device):
-        self.pipe_setup(device, [t.cpu().pin_memory() for t in (self.q, self.k, self.v)], self.o)
-
-    def step_e2e(self):
-        self.pipe_step(lambda dev_in, dev_out: self.b200k.cutile_fmha(*dev_in, causal=True, Out=dev_out))
-
-    def cpu_setup(self):
-        import oracle
-        g = torch.Generator().manual_seed(self.seed)
-        self.cpu_ops = tuple(torch.randn(1, 1, 4096, self.D, generator=g).bfloat16() for _ in range(3))
-        self.oracle = oracle
-
-    def cpu_step(self, s):
-        q, k, v = self.cpu_ops
-        return self.oracle.fmha_ref(q[:, :, :s], k[:, :, :s], v[:, :, :s], causal=True)
-
-    def cpu_flops(self, s):
-        return 4.0 * s * s * self.D * 0.5
-
-    def cpu_sample_desc(self, s):
-        return f"one head, sequence {s}: fp32 softmax(QK^T + causal mask)V (torch CPU)"
-
-    def config(self):
-        return {"workload": self.name, "batch": self.B, "heads": self.H, "seq": self.S,
-                "head_dim": self.D, "causal": True, "seed": self.seed,
-                "l2": "Q, K, V and O are 268 MB each (> 126 MiB L2)"}
+def _expert_weights(seed, e, inter, hidden):
+    """w1[e] (2I, H) and w2[e] (H, I) of one expert, N(0, 0.02), from their own generator: any
+    rank (and the CPU arm) can rebuild any expert without drawing the others."""
+    g = torch.Generator().manual_seed(seed * 1000 + 1 + e)
+    w1 = (0.02 * torch.randn(2 * inter, hidden, generator=g)).bfloat16()
+    w2 = (0.02 * torch.randn(hidden, inter, generator=g)).bfloat16()
+    return w1, w2
 
 
 class MoeBf16(Workload):
-    """The MoE FFN (16384 tokens, hidden 4096, 64 experts, intermediate 1536, top-8) on one GPU,
-    bf16 weights: align -> gather -> grouped GEMM + SwiGLU -> grouped GEMM + scatter -> sum."""
+    """BASELINE config 5 on one GPU, bf16 weights: the MoE FFN (16384 tokens, hidden 4096, 64
+    experts, intermediate 1536, top-8): align -> gather -> grouped GEMM + SwiGLU -> grouped GEMM
+    + scatter -> sum."""
     name = "moe_ffn_16384tok_h4096_e64_i1536_top8_bf16"
     dtype = "bf16 x bf16 -> fp32 accumulate -> bf16"
     tensor_rate_vs_bf16 = 1.0
@@ -447,19 +486,34 @@ class MoeBf16(Workload):
     launches_per_step = 8
 
     def flops(self):
-        return 6.0 * self.T * self.K * self.H * self.I
+        return 6.0 * self.T * self.K * self.H * self.I / self.world   # per rank
 
     def algorithmic_bytes(self):
-        return 2 * (self.E * 3 * self.I * self.H + 2 * self.T * self.H)
+        return 2 * (self.E * 3 * self.I * self.H + 2 * self.T * self.H) // self.world
+
+    def draw_tokens(self):
+        """Router outcome and hidden states of the whole problem (CPU)."""
+        import oracle
+        g = torch.Generator().manual_seed(self.seed)
+        tw, ids = oracle.moe_route_ref(torch.randn(self.T, self.E, generator=g), self.K)
+        x = torch.randn(self.T, self.H, generator=g).bfloat16()
+        return x, tw.bfloat16(), ids
+
+    def expert_range(self):
+        per = self.E // self.world
+        return range(self.rank * per, (self.rank + 1) * per)
+
+    def load_weights(self, device):
+        w = [_expert_weights(self.seed, e, self.I, self.H) for e in self.expert_range()]
+        w1 = torch.stack([a for a, _ in w]).to(device)
+        w2 = torch.stack([b for _, b in w]).to(device)
+        return w1, w2
 
     def setup(self, device):
         import b200k
-        g = torch.Generator(device=device).manual_seed(self.seed)
-        self.x = torch.randn(self.T, self.H, device=device, generator=g).bfloat16()
-        w1 = (0.02 * torch.randn(self.E, 2 * self.I, self.H, device=device, generator=g)).bfloat16()
-        w2 = (0.02 * torch.randn(self.E, self.H, self.I, device=device, generator=g)).bfloat16()
-        vals, self.ids = torch.topk(torch.randn(self.T, self.E, device=device, generator=g), self.K, dim=-1)
-        self.tw = torch.softmax(vals, dim=-1).bfloat16()
+        self.x_cpu, self.tw_cpu, self.ids_cpu = self.draw_tokens()
+        self.x, self.tw, self.ids = (t.to(device) for t in (self.x_cpu, self.tw_cpu, self.ids_cpu))
+        w1, w2 = self.load_weights(device)
         if self.mxfp8:
             self.w = b200k.quantize_expert_weights(w1) + b200k.quantize_expert_weights(w2)
         else:
@@ -470,6 +524,34 @@ class MoeBf16(Workload):
         if self.mxfp8:
             return self.b200k.cutile_moe_mxfp8(self.x, *self.w, self.tw, self.ids)
         return self.b200k.cutile_moe(self.x, *self.w, self.tw, self.ids)
+
+    def _moe_parity(self, out, x_cpu, tw_cpu, ids_cpu):
+        """Sampled tokens against the oracle's FFN evaluated for those tokens only, with the
+        experts they use rebuilt from their seeds."""
+        import oracle
+        tok = _sample(x_cpu.shape[0], (0, x_cpu.shape[0] - 1), 2, 31)
+        used = sorted(set(ids_cpu[tok].reshape(-1).tolist()))
+        remap = {e: i for i, e in enumerate(used)}
+        ids = torch.tensor([[remap[int(e)] for e in row] for row in ids_cpu[tok]])
+        w = [_expert_weights(self.seed, e, self.I, self.H) for e in used]
+        w1, w2 = torch.stack([a for a, _ in w]), torch.stack([b for _, b in w])
+        if self.mxfp8:
+            q1, s1 = oracle.block_quantize_ref(w1)
+            q2, s2 = oracle.block_quantize_ref(w2)
+            ref = oracle.moe_mxfp8_ref(x_cpu[tok], q1, s1, q2, s2, tw_cpu[tok], ids)
+        else:
+            ref = oracle.moe_ref(x_cpu[tok], w1, w2, tw_cpu[tok], ids)
+        got = out[tok.to(out.device)]
+        err = oracle.rel_frobenius(got, ref)
+        if not err < 2e-2:
+            raise SystemExit(f"bench.py: parity check failed for {self.name}: relative Frobenius error {err:.4g}")
+        close_or_die(self.name, got, ref, 1e-1, 1e-1 / max(float(ref.abs().max()), 1e-30))
+        return {"max_err": err, "tol": "relative Frobenius error < 2e-2; rtol 1e-1, atol 1e-1 elementwise",
+                "what": f"{len(tok)} tokens ({len(used)} experts) of one step's output against the oracle's FFN "
+                        "for those tokens"}
+
+    def parity(self):
+        return self._moe_parity(self.step(), self.x_cpu, self.tw_cpu, self.ids_cpu)
 
     def setup_e2e(self, device):
         self.host_in = [t.cpu().pin_memory() for t in (self.x, self.tw, self.ids)]
@@ -483,14 +565,32 @@ class MoeBf16(Workload):
             d.copy_(h, non_blocking=True)
         self.host_out.copy_(self.step(), non_blocking=True)
 
-    cpu_setup = MoeEpBf16.cpu_setup
-    cpu_step = MoeEpBf16.cpu_step
-    cpu_flops = MoeEpBf16.cpu_flops
-    cpu_sample_desc = MoeEpBf16.cpu_sample_desc
+    # CPU arm: the same tokens, routed among the first 8 experts, top-2 (a bounded slice)
+    def cpu_setup(self):
+        import oracle
+        t, e = 512, 8
+        x, _, _ = self.draw_tokens()
+        g = torch.Generator().manual_seed(self.seed + 77)
+        w = [_expert_weights(self.seed, i, self.I, self.H) for i in range(e)]
+        self.cpu_ops = (x[:t].float(), torch.stack([a for a, _ in w]).float(), torch.stack([b for _, b in w]).float())
+        self.cpu_route = oracle.moe_route_ref(torch.randn(t, e, generator=g), 2)
+        self.oracle = oracle
+
+    def cpu_step(self, s):
+        x, w1, w2 = self.cpu_ops
+        tw, ids = self.cpu_route
+        return self.oracle.moe_ref(x[:s], w1, w2, tw[:s], ids[:s])
+
+    def cpu_flops(self, s):
+        return 6.0 * s * 2 * self.H * self.I
+
+    def cpu_sample_desc(self, s):
+        return f"the first {s} tokens through 8 of the experts, top-2, same FFN in fp32 (torch CPU)"
 
     def config(self):
         return {"workload": self.name, "tokens": self.T, "hidden": self.H, "experts": self.E,
                 "intermediate": self.I, "topk": self.K, "seed": self.seed,
+                "inputs": "torch.Generator().manual_seed(seed) on the CPU (one generator per expert)",
                 "l2": "expert weights alone are 2.4 GB (> 126 MiB L2)"}
 
 
@@ -502,8 +602,122 @@ class MoeMxfp8(MoeBf16):
     launches_per_step = 9
 
 
+class MoeEpBf16(MoeBf16):
+    """BASELINE config 5 expert-parallel: experts E / world and tokens T / world per rank, an
+    NVLink exchange for dispatch and one for combine.  The whole problem is fixed, so this
+    scales strongly."""
+    name = "moe_ffn_ep_16384tok_h4096_e64_i1536_top8_bf16"
+    distributed = True
+    scaling = "strong"
+    launches_per_step = 10
+
+    def setup(self, device):
+        import b200k
+        x, tw, ids = self.draw_tokens()
+        tl = self.T // self.world
+        sl = slice(self.rank * tl, (self.rank + 1) * tl)
+        self.x_cpu, self.tw_cpu, self.ids_cpu = x[sl], tw[sl], ids[sl]
+        self.x, self.tw, self.ids = (t.to(device) for t in (self.x_cpu, self.tw_cpu, self.ids_cpu))
+        w1, w2 = self.load_weights(device)
+        self.ep = b200k.ExpertParallelMoE(w1, w2, self.E, mxfp8=self.mxfp8)
+        self.b200k = b200k
+
+    def step(self):
+        return self.ep.forward(self.x, self.tw, self.ids)
+
+    def config(self):
+        c = super().config()
+        c["sharding"] = "experts E / n_gpus and tokens T / n_gpus per rank; dispatch and combine over NVLink"
+        return c
+
+
+class MoeEpMxfp8(MoeEpBf16):
+    name = "moe_ffn_ep_16384tok_h4096_e64_i1536_top8_mxfp8"
+    dtype = MoeMxfp8.dtype
+    tensor_rate_vs_bf16 = 2.0
+    mxfp8 = True
+
+
+class FmhaCausal(Workload):
+    """BASELINE config 4: causal attention forward, bf16, batch 4, 32 heads, sequence 8192, head dim 128."""
+    name = "fmha_causal_bf16_b4_h32_s8192_d128"
+    dtype = "bf16 x bf16 -> fp32 softmax / accumulate -> bf16"
+    tensor_rate_vs_bf16 = 1.0
+    B, H, S, D = 4, 32, 8192, 128
+    seed = 3
+    cpu_limit = 4096
+    launches_per_step = 1
+
+    def flops(self):
+        return 4.0 * self.B * self.H * self.S * self.S * self.D * 0.5
+
+    def algorithmic_bytes(self):
+        return 4 * self.B * self.H * self.S * self.D * 2
+
+    def draw(self, gen, batch=None):
+        shape = (self.B if batch is None else batch, self.H, self.S, self.D)
+        return tuple(torch.randn(shape, generator=gen).bfloat16() for _ in range(3))
+
+    def setup(self, device):
+        import b200k
+        g = torch.Generator().manual_seed(self.seed)
+        self.cpu_qkv = self.draw(g)
+        self.q, self.k, self.v = (t.to(device) for t in self.cpu_qkv)
+        self.o = torch.empty_like(self.q)
+        self.b200k = b200k
+
+    def step(self):
+        return self.b200k.cutile_fmha(self.q, self.k, self.v, causal=True, Out=self.o)
+
+    def parity(self):
+        import oracle
+        out = self.step()
+        q, k, v = self.cpu_qkv
+        worst = 0.0
+        for (b, h), (lo, hi) in zip([(0, 0), (self.B - 1, self.H - 1)], [(4032, 4160), (self.S - 128, self.S)]):
+            ref = oracle.fmha_ref(q[b:b + 1, h:h + 1, lo:hi], k[b:b + 1, h:h + 1, :hi], v[b:b + 1, h:h + 1, :hi],
+                                  causal=True, input_pos=lo)
+            got = out[b:b + 1, h:h + 1, lo:hi]
+            worst = max(worst, close_or_die(self.name, got, ref, 5e-2, 1e-2 / max(float(ref.abs().max()), 1e-30)))
+        return {"max_err": worst, "tol": "rtol 5e-2, atol 1e-2",
+                "what": "two 128-row query blocks (one across a 256-row tile seam, the last one) in the first "
+                        "and the last (batch, head) against fp32 softmax(QK^T + mask)V"}
+
+    def setup_e2e(self, device):
+        self.pipe_setup(device, [t.pin_memory() for t in self.cpu_qkv], self.o)
+
+    def step_e2e(self):
+        self.pipe_step(lambda dev_in, dev_out: self.b200k.cutile_fmha(*dev_in, causal=True, Out=dev_out))
+
+    def cpu_setup(self):
+        import oracle
+        g = torch.Generator().manual_seed(self.seed)
+        # head (0, 0) of the same draw: only the first batch entry is needed
+        q = torch.randn(self.B, self.H, self.S, self.D, generator=g)[0:1, 0:1].bfloat16()
+        k = torch.randn(self.B, self.H, self.S, self.D, generator=g)[0:1, 0:1].bfloat16()
+        v = torch.randn(self.B, self.H, self.S, self.D, generator=g)[0:1, 0:1].bfloat16()
+        self.cpu_ops = (q, k, v)
+        self.oracle = oracle
+
+    def cpu_step(self, s):
+        q, k, v = self.cpu_ops
+        return self.oracle.fmha_ref(q[:, :, :s], k[:, :, :s], v[:, :, :s], causal=True)
+
+    def cpu_flops(self, s):
+        return 4.0 * s * s * self.D * 0.5
+
+    def cpu_sample_desc(self, s):
+        return f"head (0, 0), first {s} positions: fp32 softmax(QK^T + causal mask)V (torch CPU)"
+
+    def config(self):
+        return {"workload": self.name, "batch": self.B, "heads": self.H, "seq": self.S,
+                "head_dim": self.D, "causal": True, "seed": self.seed,
+                "inputs": "torch.Generator().manual_seed(seed) on the CPU, copied to the device",
+                "l2": "Q, K, V and O are 268 MB each (> 126 MiB L2)"}
+
+
 class Mxfp8Quantize(Workload):
-    """The quantiser that feeds the headline GEMM: bf16 8192 x 8192 -> e4m3 + swizzled ue8m0
+    """The quantiser that feeds the MXFP8 GEMM: bf16 8192 x 8192 -> e4m3 + swizzled ue8m0
     scales.  One pass over the data: HBM-bound."""
     name = "mxfp8_quantize_bf16_8192x8192"
     dtype = "bf16 -> e4m3 + ue8m0 / 32"
@@ -522,8 +736,9 @@ class Mxfp8Quantize(Workload):
 
     def setup(self, device):
         import b200k
-        g = torch.Generator(device=device).manual_seed(self.seed)
-        self.xs = [torch.randn(self.M, self.K, device=device, generator=g).bfloat16() for _ in range(self.sets)]
+        g = torch.Generator().manual_seed(self.seed)
+        self.x_cpu = [torch.randn(self.M, self.K, generator=g).bfloat16() for _ in range(self.sets)]
+        self.xs = [x.to(device) for x in self.x_cpu]
         self.b200k = b200k
         self.i = 0
 
@@ -531,6 +746,18 @@ class Mxfp8Quantize(Workload):
         x = self.xs[self.i % self.sets]
         self.i += 1
         return self.b200k.block_quantize(x, 32, swizzled_scale=True)
+
+    def parity(self):
+        import oracle
+        q, s = self.b200k.block_quantize(self.xs[0], 32)
+        rows = _sample(self.M, (0, 127, 128, self.M - 1), 28, 41)
+        q_ref, s_ref = oracle.block_quantize_ref(self.x_cpu[0][rows])
+        same = (torch.equal(q[rows.to(q.device)].cpu().view(torch.uint8), q_ref.view(torch.uint8)) and
+                torch.equal(s[rows.to(q.device)].cpu().view(torch.uint8), s_ref.view(torch.uint8)))
+        if not same:
+            raise SystemExit(f"bench.py: parity check failed for {self.name}: bytes differ from the oracle's")
+        return {"max_err": 0.0, "tol": "bit-exact",
+                "what": f"codes and scale bytes of {len(rows)} rows against the oracle's block_quantize"}
 
     def setup_e2e(self, device):
         self.host_in = [self.xs[0].cpu().pin_memory()]
@@ -549,7 +776,7 @@ class Mxfp8Quantize(Workload):
     def cpu_setup(self):
         import oracle
         g = torch.Generator().manual_seed(self.seed)
-        self.cpu_ops = (torch.randn(4096, self.K, generator=g).bfloat16(),)
+        self.cpu_ops = (torch.randn(self.M, self.K, generator=g)[:4096].bfloat16(),)
         self.oracle = oracle
 
     def cpu_step(self, s):
@@ -563,79 +790,8 @@ class Mxfp8Quantize(Workload):
 
     def config(self):
         return {"workload": self.name, "rows": self.M, "K": self.K, "seed": self.seed,
+                "inputs": "torch.Generator().manual_seed(seed) on the CPU, copied to the device",
                 "l2": f"{self.sets} rotating inputs of 128 MiB each (> 126 MiB L2)"}
-
-
-class FmhaDecode(Mxfp8Quantize):
-    """One decode step of grouped-query attention over a long KV cache: the reference's decode
-    bench shapes (test/bench_attention.py:33-44: one query per sequence, 32 query heads on 8 KV
-    heads) at a serving-size batch.  K and V are read once: HBM-bound."""
-    name = "fmha_decode_bf16_b32_hq32_hkv8_s2048_d128"
-    dtype = "bf16, fp32 softmax"
-    B, HQ, HKV, S, D = 32, 32, 8, 2048, 128
-    seed = 5
-    sets = 2
-    launches_per_step = 1
-
-    def algorithmic_bytes(self):
-        return 2 * self.B * self.HKV * self.S * self.D * 2 + 2 * self.B * self.HQ * self.D * 2
-
-    def setup(self, device):
-        import b200k
-        g = torch.Generator(device=device).manual_seed(self.seed)
-        mk = lambda *sh: torch.randn(*sh, device=device, generator=g).bfloat16()
-        self.xs = [(mk(self.B, self.HQ, 1, self.D), mk(self.B, self.HKV, self.S, self.D),
-                    mk(self.B, self.HKV, self.S, self.D)) for _ in range(self.sets)]
-        self.out = torch.empty(self.B, self.HQ, 1, self.D, device=device, dtype=torch.bfloat16)
-        self.b200k = b200k
-        self.i = 0
-
-    def _run(self, q, k, v):
-        return self.b200k.cutile_fmha(q, k, v, causal=True, input_pos=self.S - 1,
-                                      query_group_size=self.HQ // self.HKV, Out=self.out)
-
-    def step(self):
-        q, k, v = self.xs[self.i % self.sets]
-        self.i += 1
-        return self._run(q, k, v)
-
-    def setup_e2e(self, device):
-        # a decode step's KV cache lives on the device; the step's own traffic is the new query
-        # in and the attention output back
-        self.host_in = [self.xs[0][0].cpu().pin_memory()]
-        self.host_out = [torch.empty_like(self.out, device="cpu").pin_memory()]
-        self.h2d = self.host_in[0].numel() * 2
-        self.d2h = self.host_out[0].numel() * 2
-
-    def step_e2e(self):
-        q, k, v = self.xs[0]
-        q.copy_(self.host_in[0], non_blocking=True)
-        self.host_out[0].copy_(self._run(q, k, v), non_blocking=True)
-
-    def cpu_setup(self):
-        import oracle
-        g = torch.Generator().manual_seed(self.seed)
-        mk = lambda *sh: torch.randn(*sh, generator=g).bfloat16()
-        self.cpu_ops = (mk(self.B, self.HQ, 1, self.D), mk(self.B, self.HKV, self.S, self.D),
-                        mk(self.B, self.HKV, self.S, self.D))
-        self.oracle = oracle
-
-    def cpu_step(self, s):
-        q, k, v = self.cpu_ops
-        s = min(s, self.B)
-        return self.oracle.fmha_ref(q[:s], k[:s], v[:s], causal=True, input_pos=self.S - 1,
-                                    query_group_size=self.HQ // self.HKV)
-
-    def cpu_flops(self, s):
-        return float(self.algorithmic_bytes()) * min(s, self.B) / self.B
-
-    def cpu_sample_desc(self, s):
-        return f"{min(s, self.B)} of {self.B} sequences through fp32 softmax(q k^T) v (torch CPU)"
-
-    def config(self):
-        return {"workload": self.name, "batch": self.B, "heads_q": self.HQ, "heads_kv": self.HKV,
-                "keys": self.S, "head_dim": self.D, "seed": self.seed,
-                "l2": f"{self.sets} rotating K/V sets of 268 MB each (> 126 MiB L2)"}
 
 
 class Nvfp4Quantize(Mxfp8Quantize):
@@ -653,6 +809,21 @@ class Nvfp4Quantize(Mxfp8Quantize):
         x = self.xs[self.i % self.sets]
         self.i += 1
         return self.b200k.nvfp4_quantize(x)
+
+    def parity(self):
+        import numpy as np
+        import oracle
+        q, s, ts = self.b200k.nvfp4_quantize(self.xs[0], swizzled_scale=False)
+        rows = _sample(self.M, (0, 127, 128, self.M - 1), 28, 42)
+        want_ts = np.float32(np.float32(self.x_cpu[0].float().abs().max()) / np.float32(2688.0))
+        q_ref, s_ref, _ = oracle.nvfp4_quantize_ref(self.x_cpu[0][rows], tensor_scale=want_ts)
+        same = (float(ts) == float(want_ts) and
+                np.array_equal(q[rows.to(q.device)].cpu().numpy(), q_ref) and
+                np.array_equal(s[rows.to(q.device)].cpu().view(torch.uint8).numpy(), s_ref))
+        if not same:
+            raise SystemExit(f"bench.py: parity check failed for {self.name}: bytes differ from the oracle's")
+        return {"max_err": 0.0, "tol": "bit-exact",
+                "what": f"tensor scale, codes and scale bytes of {len(rows)} rows against the oracle's quantiser"}
 
     def setup_e2e(self, device):
         self.host_in = [self.xs[0].cpu().pin_memory()]
@@ -678,27 +849,126 @@ class Nvfp4Quantize(Mxfp8Quantize):
         return f"{s} rows of {self.K} bf16 values through the NVFP4 quantiser's restatement (numpy CPU)"
 
 
-class DenseF16(Mxfp8Gemm):
-    """The sample-sized dense fp16 matmul (2048 cubed)."""
+class FmhaDecode(Workload):
+    """One decode step of grouped-query attention over a long KV cache: the reference's decode
+    bench shapes (test/bench_attention.py:33-44: one query per sequence, 32 query heads on 8 KV
+    heads) at a serving-size batch.  K and V are read once: HBM-bound."""
+    name = "fmha_decode_bf16_b32_hq32_hkv8_s2048_d128"
+    dtype = "bf16, fp32 softmax"
+    bound = "hbm"
+    B, HQ, HKV, S, D = 32, 32, 8, 2048, 128
+    seed = 5
+    sets = 2
+    launches_per_step = 1
+    cuda_graph = True
+
+    def flops(self):
+        return float(self.algorithmic_bytes())
+
+    def algorithmic_bytes(self):
+        return 2 * self.B * self.HKV * self.S * self.D * 2 + 2 * self.B * self.HQ * self.D * 2
+
+    def draw(self, gen):
+        mk = lambda *sh: torch.randn(*sh, generator=gen).bfloat16()
+        return (mk(self.B, self.HQ, 1, self.D), mk(self.B, self.HKV, self.S, self.D),
+                mk(self.B, self.HKV, self.S, self.D))
+
+    def setup(self, device):
+        import b200k
+        g = torch.Generator().manual_seed(self.seed)
+        self.x_cpu = [self.draw(g) for _ in range(self.sets)]
+        self.xs = [tuple(t.to(device) for t in qkv) for qkv in self.x_cpu]
+        self.out = torch.empty(self.B, self.HQ, 1, self.D, device=device, dtype=torch.bfloat16)
+        self.b200k = b200k
+        self.i = 0
+
+    def _run(self, q, k, v):
+        return self.b200k.cutile_fmha(q, k, v, causal=True, input_pos=self.S - 1,
+                                      query_group_size=self.HQ // self.HKV, Out=self.out)
+
+    def step(self):
+        q, k, v = self.xs[self.i % self.sets]
+        self.i += 1
+        return self._run(q, k, v)
+
+    def parity(self):
+        import oracle
+        out = self._run(*self.xs[0])
+        q, k, v = self.x_cpu[0]
+        sel = [0, self.B - 1]
+        ref = oracle.fmha_ref(q[sel], k[sel], v[sel], causal=True, input_pos=self.S - 1,
+                              query_group_size=self.HQ // self.HKV)
+        err = close_or_die(self.name, out[sel], ref, 5e-2, 1e-2 / max(float(ref.abs().max()), 1e-30))
+        return {"max_err": err, "tol": "rtol 5e-2, atol 1e-2",
+                "what": "the first and the last sequence of the batch against fp32 softmax(q k^T) v"}
+
+    def setup_e2e(self, device):
+        # a decode step's KV cache lives on the device; the step's own traffic is the new query
+        # in and the attention output back
+        self.host_in = [self.xs[0][0].cpu().pin_memory()]
+        self.host_out = [torch.empty_like(self.out, device="cpu").pin_memory()]
+        self.h2d = self.host_in[0].numel() * 2
+        self.d2h = self.host_out[0].numel() * 2
+
+    def step_e2e(self):
+        q, k, v = self.xs[0]
+        q.copy_(self.host_in[0], non_blocking=True)
+        self.host_out[0].copy_(self._run(q, k, v), non_blocking=True)
+
+    def cpu_setup(self):
+        import oracle
+        g = torch.Generator().manual_seed(self.seed)
+        self.cpu_ops = self.draw(g)
+        self.oracle = oracle
+
+    def cpu_step(self, s):
+        q, k, v = self.cpu_ops
+        s = min(s, self.B)
+        return self.oracle.fmha_ref(q[:s], k[:s], v[:s], causal=True, input_pos=self.S - 1,
+                                    query_group_size=self.HQ // self.HKV)
+
+    def cpu_flops(self, s):
+        return float(self.algorithmic_bytes()) * min(s, self.B) / self.B
+
+    def cpu_sample_desc(self, s):
+        return f"{min(s, self.B)} of {self.B} sequences through fp32 softmax(q k^T) v (torch CPU)"
+
+    cpu_limit = 32
+
+    def config(self):
+        return {"workload": self.name, "batch": self.B, "heads_q": self.HQ, "heads_kv": self.HKV,
+                "keys": self.S, "head_dim": self.D, "seed": self.seed,
+                "inputs": "torch.Generator().manual_seed(seed) on the CPU, copied to the device",
+                "l2": f"{self.sets} rotating K/V sets of 268 MB each (> 126 MiB L2)"}
+
+
+class DenseF16(Workload):
+    """BASELINE config 1: the sample-sized dense fp16 matmul (2048 cubed), B row-major (K, N)."""
     name = "dense_f16_gemm_2048x2048x2048"
     dtype = "f16 x f16 -> fp32 accumulate -> f16"
     tensor_rate_vs_bf16 = 1.0
     M = N = K = 2048
     seed = 0
     sets = 12   # 12 x 24 MiB > L2
-    cuda_graph = True
+    launches_per_step = 1
+
+    def flops(self):
+        return 2.0 * self.M * self.N * self.K
 
     def algorithmic_bytes(self):
         return 2 * (self.M * self.K + self.K * self.N + self.M * self.N)
 
     def setup(self, device):
         import b200k
-        g = torch.Generator(device=device).manual_seed(self.seed)
+        g = torch.Generator().manual_seed(self.seed)
         self.inputs = []
         for i in range(self.sets):
-            a = torch.randn(self.M, self.K, device=device, generator=g).half()
-            b = torch.randn(self.K, self.N, device=device, generator=g).half()
-            self.inputs.append((a, b, torch.empty(self.M, self.N, device=device, dtype=torch.float16)))
+            a = torch.randn(self.M, self.K, generator=g).half()
+            b = torch.randn(self.K, self.N, generator=g).half()
+            if i == 0:
+                self.a_cpu, self.b_cpu = a, b
+            self.inputs.append((a.to(device), b.to(device),
+                                torch.empty(self.M, self.N, device=device, dtype=torch.float16)))
         self.b200k = b200k
         self.i = 0
 
@@ -706,6 +976,17 @@ class DenseF16(Mxfp8Gemm):
         a, b, c = self.inputs[self.i % self.sets]
         self.i += 1
         return self.b200k.cutile_matmul(a, b, C=c)
+
+    def parity(self):
+        import oracle
+        self.i = 0
+        c = self.step()
+        self.i = 0
+        rows = _sample(self.M, (0, 127, 128, 255, 256, self.M - 1), 26, 51)
+        ref = oracle.matmul_ref(self.a_cpu[rows], self.b_cpu)
+        return {"max_err": close_or_die(self.name, c[rows.to(c.device)], ref, 2e-2, 2e-2),
+                "tol": "rtol 2e-2, atol 2e-2 of max|ref|",
+                "what": f"{len(rows)} whole rows of one step's output against A.float() @ B.float()"}
 
     def setup_e2e(self, device):
         a, b, c = self.inputs[0]
@@ -725,20 +1006,23 @@ class DenseF16(Mxfp8Gemm):
         a, b = self.cpu_ops
         return self.oracle.matmul_ref(a[:s], b[:, :s])
 
+    def cpu_flops(self, s):
+        return 2.0 * s * s * self.K
+
     def cpu_sample_desc(self, s):
         return f"{s}x{s} block of the output, K={self.K}: A.float() @ B.float() (torch CPU)"
 
     def config(self):
-        c = super().config()
-        c.pop("scale_block")
-        c["out"] = "f16"
-        return c
+        return {"workload": self.name, "M": self.M, "N": self.N, "K": self.K, "out": "f16", "seed": self.seed,
+                "inputs": "torch.Generator().manual_seed(seed) on the CPU, copied to the device",
+                "l2": f"{self.sets} rotating operand/output sets of 24 MiB each (> 126 MiB L2)"}
 
 
-WORKLOADS = {"mxfp8_gemm": Mxfp8Gemm, "nvfp4_gemm": Nvfp4Gemm, "dense_f16": DenseF16,
-             "ag_nvfp4_gemm": AgNvfp4Gemm, "moe_ep_bf16": MoeEpBf16, "fmha_causal": FmhaCausal,
-             "moe_bf16": MoeBf16, "moe_mxfp8": MoeMxfp8, "mxfp8_quantize": Mxfp8Quantize,
-             "nvfp4_quantize": Nvfp4Quantize, "fmha_decode": FmhaDecode}
+WORKLOADS = {"ag_nvfp4_gemm": AgNvfp4Gemm, "mxfp8_gemm": Mxfp8Gemm, "nvfp4_gemm": Nvfp4Gemm,
+             "dense_f16": DenseF16, "fmha_causal": FmhaCausal, "fmha_decode": FmhaDecode,
+             "moe_bf16": MoeBf16, "moe_mxfp8": MoeMxfp8, "moe_ep_bf16": MoeEpBf16,
+             "moe_ep_mxfp8": MoeEpMxfp8, "mxfp8_quantize": Mxfp8Quantize, "nvfp4_quantize": Nvfp4Quantize}
+DEFAULT_WORKLOAD = "ag_nvfp4_gemm"
 
 
 # --------------------------------------------------------------------------------------
@@ -751,8 +1035,9 @@ class ClockSampler:
         0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting",
     }
 
-    def __init__(self, device):
+    def __init__(self, device, period_s=0.002):
         self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.period_s = period_s
         self._stop = threading.Event()
         self._thread = None
         self.ok = False
@@ -772,7 +1057,7 @@ class ClockSampler:
     def _run(self):
         while not self._stop.is_set():
             self.sample()
-            time.sleep(0.02)
+            time.sleep(self.period_s)
 
     def sample(self):
         if not self.ok:
@@ -787,20 +1072,24 @@ class ClockSampler:
             pass
 
     def start(self):
+        self.samples, self.reasons = [], set()
+        self._stop.clear()
         if self.ok:
             self._thread = threading.Thread(target=self._run, daemon=True)
             self._thread.start()
 
     def stop(self):
+        self.sample()
         self._stop.set()
         if self._thread:
             self._thread.join()
+            self._thread = None
 
     def summary(self):
         if not self.ok or not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
         s = sorted(self.samples)
-        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz,
+        return {"sm_mhz": s[len(s) // 2], "sm_min_mhz": s[0], "sm_max_mhz": self.max_mhz,
                 "reasons": sorted(self.reasons), "samples": len(s)}
 
 
@@ -853,6 +1142,32 @@ def run_reference(args, w):
     print(json.dumps(line), flush=True)
 
 
+def timed_steps(w, steps, barrier, graph=False):
+    """Device time in ms per step of `steps` back-to-back steps, events on the launching stream."""
+    ev0 = torch.cuda.Event(enable_timing=True)
+    ev1 = torch.cuda.Event(enable_timing=True)
+    if graph:
+        # launch-bound workloads (kernels of a few tens of microseconds): the steps are
+        # captured once and replayed as one graph, so the device never waits for the host
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(steps):
+                w.step()
+        g.replay()
+        barrier()
+        ev0.record()
+        g.replay()
+        ev1.record()
+    else:
+        barrier()
+        ev0.record()
+        for _ in range(steps):
+            w.step()
+        ev1.record()
+    barrier()
+    return ev0.elapsed_time(ev1) / steps
+
+
 def run_ours(args, w):
     import torch.distributed as dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -860,6 +1175,8 @@ def run_ours(args, w):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
+    affinity = os.sched_getaffinity(0)
+    numa = bind_near_gpu(device)
     distributed = world > 1 or getattr(w, "distributed", False)
     if distributed:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -867,50 +1184,60 @@ def run_ours(args, w):
         os.environ.setdefault("RANK", "0")
         os.environ.setdefault("WORLD_SIZE", "1")
         dist.init_process_group("nccl", device_id=device)
+    w.world, w.rank = world, rank
 
     def barrier():
         if distributed:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(values):
+        if world == 1:
+            return values
+        t = torch.tensor(values, device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
     import b200k
+    warmup = max(3, args.warmup)
     w.setup(device)
-    for _ in range(max(3, args.warmup)):
+    for _ in range(warmup):
         w.step()
     barrier()
+    b200k.raise_on_device_error()
+    # the output is checked before it is timed
+    parity = w.parity()
+    barrier()
+    b200k.raise_on_device_error()
+
+    use_graph = (args.launch == "graph" or (args.launch == "auto" and bool(getattr(w, "cuda_graph", False)))) \
+        and not distributed
     sampler = ClockSampler(device)
     sampler.start()
-    ev0 = torch.cuda.Event(enable_timing=True)
-    ev1 = torch.cuda.Event(enable_timing=True)
-    use_graph = bool(getattr(w, "cuda_graph", False)) and not distributed
-    if use_graph:
-        # launch-bound workloads (kernels of a few tens of microseconds): the K steps are
-        # captured once and replayed as one graph, so the device never waits for the host
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            for _ in range(args.steps):
-                w.step()
-        graph.replay()
-        barrier()
-        ev0.record()
-        graph.replay()
-        ev1.record()
-    else:
-        ev0.record()
-        for _ in range(args.steps):
-            w.step()
-        ev1.record()
-    barrier()
-    sampler.sample()
+    ms = timed_steps(w, args.steps, barrier, use_graph)
     sampler.stop()
-    ms = ev0.elapsed_time(ev1) / args.steps
+    clocks = sampler.summary()
     b200k.raise_on_device_error()
+
+    # the same loop for at least a second: the burst above runs at boost clocks, this one at
+    # what the power cap sustains
+    sustained = None
+    if not args.kernel_only and args.sustain_s > 0:
+        n = int(min(2000 if use_graph else 20000, max(args.steps, args.sustain_s * 1e3 / max(ms, 1e-3))))
+        sampler.start()
+        ms_s = timed_steps(w, n, barrier, use_graph)
+        sampler.stop()
+        sustained = {"steps": n, "ms_per_step": ms_s, "clocks": sampler.summary()}
+
+    gather_us = w.gather_only_us() if hasattr(w, "gather_only_us") else None
 
     # end to end: pinned host buffers -> device -> kernel -> pinned host buffer
     e2e_steps = max(3, min(args.steps, 20))
     if args.kernel_only:
         ms_e2e, w.h2d, w.d2h = float("nan"), 0, 0
     else:
+        ev0 = torch.cuda.Event(enable_timing=True)
+        ev1 = torch.cuda.Event(enable_timing=True)
         w.setup_e2e(device)
         w.e2e_begin()
         for _ in range(2):
@@ -926,10 +1253,21 @@ def run_ours(args, w):
         barrier()
         ms_e2e = ev0.elapsed_time(ev1) / e2e_steps
 
-    if world > 1:
-        t = torch.tensor([ms, ms_e2e], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = t.tolist()
+    # secondary record of the default workload: BASELINE config 2 (MXFP8 8192 cubed) on this GPU
+    also = None
+    if args.workload == DEFAULT_WORKLOAD and not args.kernel_only and not args.no_also:
+        w2 = Mxfp8Gemm()
+        w2.setup(device)
+        for _ in range(warmup):
+            w2.step()
+        p2 = w2.parity()
+        ms2 = timed_steps(w2, args.steps, barrier)
+        also = (w2, p2, ms2)
+        b200k.raise_on_device_error()
+
+    vals = [ms, ms_e2e, sustained["ms_per_step"] if sustained else 0.0, also[2] if also else 0.0,
+            gather_us or 0.0]
+    ms, ms_e2e, ms_sus, ms_also, gather_us_max = max_over_ranks(vals)
 
     if rank == 0:
         peaks = load_peaks()
@@ -948,31 +1286,56 @@ def run_ours(args, w):
                            f"(tensor-core rate of the operand format relative to bf16)")
         line = {
             "metric": "hbm_gbs" if hbm else "tflops", "value": value, "unit": unit, "n_gpus": world,
-            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": getattr(w, "scaling", "weak"), "vs_baseline": None,
             "dtype": w.dtype, "data": "synthetic",
-            "config": dict(w.config(), launch="cuda_graph" if use_graph else "stream"),
+            "config": w.config(),
+            "launch": "cuda_graph" if use_graph else "stream",
+            "parity_checked": True, "max_err": parity["max_err"], "parity": parity,
             "e2e": {"value": world * flops / (ms_e2e * 1e-3) / scale, "unit": unit,
                     "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h,
-                    "ms_per_step": ms_e2e, "steps": e2e_steps,
+                    "ms_per_step": ms_e2e, "steps": e2e_steps, "host_numa": numa,
                     "overlap": "H2D, kernel and D2H of consecutive steps on three streams"
                                if w.e2e_pipelined else "none (one stream)"},
-            "gpu_launches": args.steps * w.launches_per_step,
-            "clocks": sampler.summary(),
+            "gpu_launches": args.steps * w.launches(),
+            "clocks": clocks,
             "roofline": {"bound": "hbm" if hbm else "tensor", "achieved": per_gpu, "peak": peak,
                          "unit": unit, "frac": per_gpu / peak, "peak_source": peak_source,
                          "traffic": TRAFFIC_BYTES.get(w.name),
                          "algorithmic_bytes": w.algorithmic_bytes()},
         }
+        if sustained:
+            sus_rate = flops / (ms_sus * 1e-3) / scale
+            sus_peak = peak if hbm else peaks["bf16_tflops_sustained"] * w.tensor_rate_vs_bf16
+            line["sustained"] = {"value": world * sus_rate, "unit": unit, "ms_per_step": ms_sus,
+                                 "steps": sustained["steps"], "clocks": sustained["clocks"],
+                                 "frac_of_sustained_peak": sus_rate / sus_peak,
+                                 "note": "the same steps back to back for at least a second (power-capped clocks)"}
+        if gather_us:
+            gb = w.gathered_bytes()
+            line["nvlink"] = {"gathered_bytes_per_step": gb, "gather_us": gather_us_max,
+                              "achieved_gbs": gb / (gather_us_max * 1e-6) / 1e9,
+                              "peak_gbs": NVLINK_PEER_COPY_GBS,
+                              "note": "peer_gather kernels alone (inbound bytes per rank); in a step they run "
+                                      "under the GEMM of the rank's own rows"}
+        if also:
+            w2, p2, _ = also
+            r2 = w2.flops() / (ms_also * 1e-3) / 1e12
+            line["also"] = {w2.name: {"value": world * r2, "unit": "TFLOP/s", "ms_per_step": ms_also,
+                                      "frac": r2 / (peaks["bf16_tflops"] * 2.0), "parity_checked": True,
+                                      "max_err": p2["max_err"], "traffic": TRAFFIC_BYTES.get(w2.name),
+                                      "note": "independent replica per GPU, device-resident operands"}}
         if args.kernel_only:
             line["e2e"] = None
         if world == 1 and not args.no_cpu_baseline and not args.kernel_only:
+            os.sched_setaffinity(0, affinity)      # the CPU baseline may use every core again
             dt, s = time_cpu(w, 1, 1, budget_s=30.0)
             line["cpu_baseline"] = {"value": w.cpu_flops(s) / dt / scale, "unit": unit,
                                     "cores": torch.get_num_threads(), "kind": "port",
                                     "sample": w.cpu_sample_desc(s)}
         print(json.dumps(line), flush=True)
     if distributed:
+        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -1065,16 +1428,18 @@ def run_ref_shapes(args):
     print(json.dumps(line), flush=True)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
-# ncu captures summarised under profiles/ (None until captured)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's dominant kernel,
+# from one ncu capture of that kernel (None until captured).  The two AllGather / plain NVFP4
+# entries are the same kernel on the same problem.
 TRAFFIC_BYTES: dict[str, float | None] = {
-    "mxfp8_gemm_8192x8192x8192_bf16out": 477.0e6,          # profiles/gemm_pair_mxfp8_8192.md
-    "nvfp4_gemm_8192x28672x8192_bf16out": 1007.0e6,        # profiles/gemm_pair_nvfp4_8192x28672x8192.md
-    "fmha_causal_bf16_b4_h32_s8192_d128": 1066.0e6,        # profiles/fmha_fwd_pair_causal_b4_h32_s8192_d128.md
-    "mxfp8_quantize_bf16_8192x8192": 173.0e6,              # profiles/mxfp8_quantize_bf16_8192x8192.md
-    "dense_f16_gemm_2048x2048x2048": 16.8e6,               # profiles/gemm_dense_f16_2048.md
-    "fmha_decode_bf16_b32_hq32_hkv8_s2048_d128": 272.0e6,  # profiles/fmha_decode_bf16_b32_hq32_hkv8_s2048_d128.md
-    "nvfp4_quantize_bf16_8192x8192": 293.0e6,              # profiles/nvfp4_quantize_bf16_8192x8192.md (both kernels)
+    "mxfp8_gemm_8192x8192x8192_bf16out": 477.0e6,
+    "nvfp4_gemm_8192x28672x8192_bf16out": 1007.0e6,
+    "allgather_nvfp4_gemm_8192x28672x8192_bf16out": 1007.0e6,
+    "fmha_causal_bf16_b4_h32_s8192_d128": 1066.0e6,
+    "mxfp8_quantize_bf16_8192x8192": 173.0e6,
+    "dense_f16_gemm_2048x2048x2048": 16.8e6,
+    "fmha_decode_bf16_b32_hq32_hkv8_s2048_d128": 272.0e6,
+    "nvfp4_quantize_bf16_8192x8192": 293.0e6,    # both kernels
 }
 
 
@@ -1084,10 +1449,16 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["ref_shapes"], default="mxfp8_gemm")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["ref_shapes"], default=DEFAULT_WORKLOAD)
+    ap.add_argument("--launch", choices=["auto", "stream", "graph"], default="auto",
+                    help="graph = the K steps replayed as one CUDA graph; auto = graph for the "
+                         "workloads whose kernels are shorter than their launch path")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-also", action="store_true", help="skip the secondary MXFP8 record")
+    ap.add_argument("--sustain-s", type=float, default=1.0,
+                    help="seconds of the back-to-back loop reported under `sustained` (0 = skip)")
     ap.add_argument("--kernel-only", action="store_true",
-                    help="skip the end-to-end and CPU legs (for profiler runs)")
+                    help="skip the end-to-end, sustained and CPU legs (for profiler runs)")
     args = ap.parse_args()
     if args.workload == "ref_shapes":
         if not torch.cuda.is_available():

@@ -35,7 +35,7 @@ class B200KError(RuntimeError):
 
 class GemmConfig(Structure):
     _fields_ = [("kernel", c_int32), ("tile_n", c_int32), ("epilogue_store", c_int32),
-                ("split_k", c_int32)]
+                ("split_k", c_int32), ("wait_budget_us", c_int32), ("withhold_arrival", c_int32)]
 
 
 class GemmArgs(Structure):
@@ -126,6 +126,8 @@ SIGNATURES = {
     "b200k_last_error": (c_char_p, []),
     "b200k_sm_count": (c_int, []),
     "b200k_device_status": (c_int, [POINTER(c_int), POINTER(c_int)]),
+    "b200k_tensor_map_cache_stats": (c_int, [POINTER(ctypes.c_uint64), POINTER(ctypes.c_uint64),
+                                             POINTER(ctypes.c_uint64)]),
     "b200k_gemm": (c_int, [POINTER(GemmArgs), c_void_p]),
     "b200k_gemm_workspace_bytes": (c_int64, [POINTER(GemmArgs)]),
     "b200k_block_scaled_gemm": (c_int, [POINTER(BlockScaledGemmArgs), c_void_p]),
@@ -138,7 +140,8 @@ SIGNATURES = {
                                   c_int32, c_int64, c_void_p, c_int64, c_void_p]),
     "b200k_silu_and_mul": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int32,
                                    c_void_p]),
-    "b200k_topk_sum": (c_int, [c_void_p, c_void_p, c_int64, c_int32, c_int64, c_void_p, c_int32, c_void_p]),
+    "b200k_topk_sum": (c_int, [c_void_p, c_void_p, c_int64, c_int32, c_int64, c_void_p, c_int32, c_void_p,
+                               c_int32, c_int32, c_void_p]),
     "b200k_peer_gather": (c_int, [POINTER(PeerGatherArgs), c_void_p]),
     "b200k_peer_scalar_expand": (c_int, [POINTER(c_void_p), c_int32, c_int64, c_void_p, c_void_p]),
     "b200k_fmha_fwd": (c_int, [POINTER(FmhaArgs), c_void_p]),
@@ -181,6 +184,13 @@ def device_status() -> tuple[int, int]:
     code, info = c_int(0), c_int(0)
     check(lib().b200k_device_status(ctypes.byref(code), ctypes.byref(info)))
     return code.value, info.value
+
+
+def tensor_map_cache_stats() -> tuple[int, int, int]:
+    """(hits, misses, entries) of the library's tensor-map cache."""
+    h, m, e = ctypes.c_uint64(0), ctypes.c_uint64(0), ctypes.c_uint64(0)
+    check(lib().b200k_tensor_map_cache_stats(ctypes.byref(h), ctypes.byref(m), ctypes.byref(e)))
+    return h.value, m.value, e.value
 
 
 def raise_on_device_error() -> None:

@@ -8,6 +8,11 @@ staging buffer with one kernel (plain peer loads over NVLink, all peers at once)
 the tcgen05 GEMM on the staged A; the NVFP4 form multiplies its own rows while the gather
 is in flight.  As in the sample, the caller makes the peers' inputs
 visible first (a barrier) and keeps them unchanged until every rank has finished.
+
+The kernels only need pointers this process can dereference, so every entry point also takes
+the shards explicitly (``peers=[...]``, ``rank=``): the buffers of all ranks as this process
+sees them.  With one process and plain local tensors that runs the whole multi-rank path on
+one GPU (no kernel here waits on another, so emulated ranks may run one after the other).
 """
 from __future__ import annotations
 
@@ -69,32 +74,51 @@ def _round_tf32(t: torch.Tensor) -> torch.Tensor:
     return ((bits + 0x1000) & ~0x1FFF).view(torch.float32)
 
 
+def _world_and_rank(group, peers, rank):
+    """(world, rank, group): from explicit peers, else from the process group, else a world of
+    one (no process group initialised: the gather degenerates to the local shard)."""
+    if peers is not None:
+        if rank is None or not 0 <= rank < len(peers):
+            raise ValueError("explicit peers need rank in [0, len(peers))")
+        return len(peers), rank, None
+    if group is None:
+        if not (dist.is_available() and dist.is_initialized()):
+            return 1, 0, None
+        group = dist.group.WORLD
+    return dist.get_world_size(group), dist.get_rank(group), group
+
+
 def cutile_gather_matmul(inp: torch.Tensor, w: torch.Tensor, group=None, *,
-                         transport: str = "p2p") -> torch.Tensor:
+                         transport: str = "p2p", peers: list[torch.Tensor] | None = None,
+                         rank: int | None = None) -> torch.Tensor:
     """out (M * world, N) = concat over ranks of inp_p (M, K) @ w (K, N).
 
     ``inp`` must live in symmetric memory (``torch.distributed._symmetric_memory.empty``)
     for the default "p2p" transport; "nccl" gathers with ``all_gather_into_tensor``
-    instead and accepts any tensor.  fp32 operands are rounded to tf32 and multiplied on
-    the tensor cores, as in the reference kernel (samples/AllGatherMatmul.py:57)."""
-    if group is None:
-        group = dist.group.WORLD
+    instead and accepts any tensor.  ``peers`` (every rank's ``inp`` as this process can
+    address it) with ``rank`` replaces the symmetric-memory rendezvous.  fp32 operands are
+    rounded to tf32 and multiplied on the tensor cores, as in the reference kernel
+    (samples/AllGatherMatmul.py:57)."""
     if inp.dim() != 2 or w.dim() != 2:
         raise ValueError("inp and w must be 2-D")
     if inp.shape[1] != w.shape[0]:
         raise ValueError("reduction dimension mismatch")
     if not inp.is_cuda or inp.device != w.device:
         raise ValueError("Input tensors must be on the same CUDA device.")
-    world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
+    world, rank, group = _world_and_rank(group, peers, rank)
     m, k = inp.shape
     n = w.shape[1]
     fp32 = inp.dtype == torch.float32
     if transport == "p2p":
-        staged = peer_gather(peer_buffers(inp, group), rank, round_tf32=fp32)
+        if peers is None:
+            peers = [inp] if world == 1 else peer_buffers(inp, group)
+        staged = peer_gather(peers, rank, round_tf32=fp32)
     elif transport == "nccl":
         staged = torch.empty((world * m, k), dtype=inp.dtype, device=inp.device)
-        dist.all_gather_into_tensor(staged, inp.contiguous(), group=group)
+        if world == 1:
+            staged.copy_(inp)
+        else:
+            dist.all_gather_into_tensor(staged, inp.contiguous(), group=group)
         if fp32:
             staged = _round_tf32(staged)
     else:
@@ -115,18 +139,29 @@ class Nvfp4GatherMatmul:
     (1,) — all three whole symmetric-memory allocations; M a multiple of 128 so that scale
     atoms do not straddle ranks."""
 
-    def __init__(self, a_q: torch.Tensor, a_sf: torch.Tensor, a_ts: torch.Tensor, group=None):
-        if group is None:
-            group = dist.group.WORLD
-        self.world = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
+    def __init__(self, a_q: torch.Tensor, a_sf: torch.Tensor, a_ts: torch.Tensor, group=None, *,
+                 peers=None, rank: int | None = None):
+        """``peers`` = (list of every rank's a_q, of a_sf, of a_ts) as this process can address
+        them, with ``rank``, replaces the symmetric-memory rendezvous."""
+        self.world, self.rank, group = _world_and_rank(group, None if peers is None else peers[0], rank)
         self.m = a_q.shape[0]
         if self.m % 128:
             raise ValueError("rows per rank must be a multiple of 128")
         self.sf_shape = tuple(a_sf.shape)
-        self.q_peers = peer_buffers(_as_u8(a_q), group)
-        self.sf_peers = peer_buffers(_as_u8(a_sf).reshape(a_sf.shape[0], -1), group)
-        self.ts_peers = peer_buffers(a_ts.reshape(1, 1), group)
+        if peers is not None:
+            q_list, sf_list, ts_list = peers
+        elif self.world == 1:
+            q_list, sf_list, ts_list = [a_q], [a_sf], [a_ts]
+        else:
+            q_list = sf_list = ts_list = None
+        if q_list is not None:
+            self.q_peers = [_as_u8(t) for t in q_list]
+            self.sf_peers = [_as_u8(t).reshape(t.shape[0], -1) for t in sf_list]
+            self.ts_peers = [t.reshape(1, 1) for t in ts_list]
+        else:
+            self.q_peers = peer_buffers(_as_u8(a_q), group)
+            self.sf_peers = peer_buffers(_as_u8(a_sf).reshape(a_sf.shape[0], -1), group)
+            self.ts_peers = peer_buffers(a_ts.reshape(1, 1), group)
         dev = a_q.device
         self.q = torch.empty((self.world * self.m, a_q.shape[1]), dtype=torch.uint8, device=dev)
         self.sf = torch.empty((self.world * a_sf.shape[0], self.sf_peers[0].shape[1]),
@@ -180,6 +215,8 @@ class Nvfp4GatherMatmul:
 
 def cutile_gather_matmul_nvfp4(a_q: torch.Tensor, a_sf: torch.Tensor, a_ts: torch.Tensor,
                                w_q: torch.Tensor, w_sf: torch.Tensor, w_ts: torch.Tensor,
-                               group=None, *, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+                               group=None, *, out_dtype: torch.dtype = torch.bfloat16,
+                               peers=None, rank: int | None = None) -> torch.Tensor:
     """One-shot form of Nvfp4GatherMatmul: returns (M * world, N)."""
-    return Nvfp4GatherMatmul(a_q, a_sf, a_ts, group).run(w_q, w_sf, w_ts, out_dtype=out_dtype)
+    return Nvfp4GatherMatmul(a_q, a_sf, a_ts, group, peers=peers, rank=rank).run(
+        w_q, w_sf, w_ts, out_dtype=out_dtype)

@@ -109,13 +109,25 @@ def _validate(A: torch.Tensor, B: torch.Tensor) -> None:
         raise ValueError("Input tensors must be on a CUDA device.")
 
 
+def _round_tf32(t: torch.Tensor) -> torch.Tensor:
+    """fp32 -> nearest tf32 value (ties away from zero), kept in fp32; same strides."""
+    bits = t.view(torch.int32)
+    return ((bits + 0x1000) & ~0x1FFF).view(torch.float32)
+
+
 def cutile_matmul(A: torch.Tensor, B: torch.Tensor, persistent: bool = False,
-                  C: torch.Tensor | None = None) -> torch.Tensor:
+                  C: torch.Tensor | None = None, *, round_tf32: bool = False) -> torch.Tensor:
     """C = A @ B with fp32 accumulation; C has A's dtype and shape (M, N).
 
     fp32 operands are multiplied as tf32, like the reference kernel
-    (test/kernels/matmul.py:74).  ``persistent`` is accepted for signature
-    compatibility; the kernel is always persistent (one CTA per SM).
+    (test/kernels/matmul.py:74).  The tensor core reads the fp32 words as they are and
+    ignores the low 13 mantissa bits, i.e. it TRUNCATES to tf32, where the reference's
+    ``astype(tf32)`` rounds to nearest: each operand value is then up to 2^-10 (instead of
+    2^-11) off in relative terms, always toward zero, so same-sign data (the sample's
+    uniform [0, 1) inputs) carries a one-sided relative bias of about 2^-11 per operand.
+    ``round_tf32=True`` rounds both operands to the nearest tf32 value first (one extra pass
+    over A and B), which is what ``cutile_gather_matmul`` always does.  ``persistent`` is
+    accepted for signature compatibility; the kernel is always persistent (one CTA per SM).
     """
     _validate(A, B)
     if A.dim() != 2 or B.dim() != 2:
@@ -129,6 +141,8 @@ def cutile_matmul(A: torch.Tensor, B: torch.Tensor, persistent: bool = False,
         return C
     if A.shape[1] == 0:
         return C.zero_()
+    if round_tf32 and A.dtype == torch.float32:
+        A, B = _round_tf32(A), _round_tf32(B)
     return _gemm(A, B, C)
 
 

@@ -164,11 +164,22 @@ def invoke_silu_and_mul_kernel(AB: torch.Tensor, C: torch.Tensor) -> None:
 
 
 def _topk_sum(x: torch.Tensor, tokens: int, topk: int, hidden: int,
-              index: torch.Tensor | None = None) -> torch.Tensor:
+              index: torch.Tensor | None = None, *, expert_ids: torch.Tensor | None = None,
+              num_experts: int = 0) -> torch.Tensor:
+    """out[t] = sum over the token's slots of its rows of x.  With `expert_ids` (the routing
+    ids) entries routed outside [0, num_experts) count as zero: the alignment dropped them, so
+    their rows were never written."""
     out = torch.empty((tokens, hidden), dtype=x.dtype, device=x.device)
+    ids = None
+    if expert_ids is not None:
+        ids = expert_ids.contiguous()
+        if ids.dtype not in (torch.int32, torch.int64):
+            raise TypeError("topk_ids must be int32 or int64")
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().b200k_topk_sum(x.data_ptr(), _lib.ptr(index), tokens, topk, hidden, out.data_ptr(),
-                                             _lib.dtype_enum(x.dtype), _lib.stream_ptr(x.device)))
+                                             _lib.dtype_enum(x.dtype), _lib.ptr(ids),
+                                             1 if (ids is not None and ids.dtype == torch.int64) else 0,
+                                             num_experts, _lib.stream_ptr(x.device)))
     return out
 
 
@@ -213,7 +224,7 @@ def cutile_moe(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
     _grouped_gemm(act, w2c, per_replica, expert_ids, num_blocks=num_blocks, row_map=sorted_ids,
                   row_scale=topk_weights.reshape(-1).float().contiguous(), c_rows=tokens * topk,
                   tile=tile)
-    return _topk_sum(per_replica, tokens, topk, hidden)
+    return _topk_sum(per_replica, tokens, topk, hidden, expert_ids=topk_ids, num_experts=experts)
 
 
 # ---- MXFP8 experts -----------------------------------------------------------------
@@ -314,4 +325,4 @@ def cutile_moe_mxfp8(hidden_states: torch.Tensor, w1_q: torch.Tensor, w1_sf: tor
                          num_blocks=num_blocks, row_map=sorted_ids,
                          row_scale=topk_weights.reshape(-1).float().contiguous(),
                          c_rows=tokens * topk, tile=tile)
-    return _topk_sum(per_replica, tokens, topk, hidden)
+    return _topk_sum(per_replica, tokens, topk, hidden, expert_ids=topk_ids, num_experts=experts)

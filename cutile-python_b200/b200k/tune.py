@@ -228,15 +228,18 @@ class _EventTimer:
 
 def exhaustive_search(search_space: Sequence[T], stream, run_fn: Callable[[T], Any], *, quiet: bool = True,
                       warmup: int = 3, batch: int = 5, max_samples: int = 200,
-                      budget_us_per_config: float = 2e6, timer: Callable | None = None) -> TuningResult[T]:
+                      budget_us_per_config: float = 2e6, timer: Callable | None = None,
+                      validate: Callable[[T], None] | None = None) -> TuningResult[T]:
     """Measure `run_fn(config)` for every config of `search_space` and return the fastest.
 
     `run_fn` enqueues the work on the current stream.  Every config gets `warmup` untimed
     calls and a first batch of samples; after that, rounds of `batch` samples go to the
     configs that are neither settled (95 % interval within 1 % of the mean or 0.5 us, or out
     of samples/time) nor beaten (their interval lies wholly above the current best's).  A
-    config whose call raises is recorded under `failures` and skipped.  `timer(run_fn, config)
-    -> microseconds` replaces the CUDA-event timer (host-side tests)."""
+    config whose call raises is recorded under `failures` and skipped.  `validate(config)`, if
+    given, runs after a config's warm-up calls and raises when the config must not win (a
+    wrong result, a device-side wait that gave up): time alone admits nobody.  `timer(run_fn,
+    config) -> microseconds` replaces the CUDA-event timer (host-side tests)."""
     space = list(search_space)
     if not space:
         raise ValueError("Search space is empty.")
@@ -250,6 +253,8 @@ def exhaustive_search(search_space: Sequence[T], stream, run_fn: Callable[[T], A
         try:
             for _ in range(warmup):
                 run_fn(cfg)
+            if validate is not None:
+                validate(cfg)
             for _ in range(batch):
                 cand.add(timer(run_fn, cfg))
         except Exception as e:  # noqa: BLE001 - a config the problem cannot take is data, not an error
@@ -311,6 +316,33 @@ def _sm_count(device) -> int:
     return torch.cuda.get_device_properties(device).multi_processor_count
 
 
+class _ResultGuard:
+    """`validate` of the tune_* wrappers: a config may win only if, after its warm-up calls,
+    the device status word is clean and the output equals the automatic form's (same product
+    up to fp32 summation order).  A status word found set is cleared by the read, so it is
+    not blamed on a later call."""
+
+    def __init__(self, run, out: torch.Tensor, rtol: float = 2e-2):
+        from . import _lib
+        self._lib, self.run, self.out, self.rtol = _lib, run, out, rtol
+        run(AUTO)
+        torch.cuda.synchronize(out.device)
+        code, info = _lib.device_status()
+        if code != 0:
+            raise _lib.B200KError(code, f"the automatic form tripped a device-side wait (info {info:#x})")
+        self.want = out.float().clone()
+        self.atol = rtol * float(self.want.abs().max()) if self.want.numel() else 0.0
+
+    def __call__(self, cfg) -> None:
+        self.out.zero_()
+        self.run(cfg)
+        torch.cuda.synchronize(self.out.device)
+        code, info = self._lib.device_status()
+        if code != 0:
+            raise self._lib.B200KError(code, f"device-side wait gave up (info {info:#x})")
+        torch.testing.assert_close(self.out.float(), self.want, rtol=self.rtol, atol=self.atol)
+
+
 def tune_matmul(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor | None = None, *,
                 db: TuneDB | None = None, search_space: Iterable[GemmConfig] | None = None,
                 quiet: bool = True, **search_kw) -> TuningResult[GemmConfig]:
@@ -330,6 +362,7 @@ def tune_matmul(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor | None = None,
         with use_config(cfg):
             matmul._gemm(A, B, C)
 
+    search_kw.setdefault("validate", _ResultGuard(run, C))
     result = exhaustive_search(space, torch.cuda.current_stream(A.device), run, quiet=quiet, **search_kw)
     target = db if db is not None else _db
     if target is not None and last_key() is not None:
@@ -353,6 +386,7 @@ def tune_block_scaled_matmul(A, A_scale, B, B_scale, C=None, *, out_dtype=torch.
         with use_config(cfg):
             block_scaled.cutile_block_scaled_matmul(A, A_scale, B, B_scale, C=C)
 
+    search_kw.setdefault("validate", _ResultGuard(run, C))
     result = exhaustive_search(space, torch.cuda.current_stream(A.device), run, quiet=quiet, **search_kw)
     target = db if db is not None else _db
     if target is not None and last_key() is not None:

@@ -2,7 +2,9 @@
 // encoding.  See include/b200k.h for the contract.
 #include <stdarg.h>
 #include <stdio.h>
+#include <string.h>
 #include <mutex>
+#include <unordered_map>
 
 #include "host.h"
 
@@ -71,9 +73,77 @@ int current_sm_count() {
   return g_sm_count[dev];
 }
 
+// ---- tensor-map cache ------------------------------------------------------
+// A tensor map is a pure function of (base, data type, rank, dims, strides, box, swizzle):
+// it holds no device state, so a map encoded once stays valid for every later call with the
+// same arguments, whatever happened to the memory in between.  Steady-state callers (the
+// same buffers call after call) then pay a hash lookup instead of a driver call per operand,
+// which is what the reference's launch path keeps per kernel as hoisted descriptors
+// (cext/tile_kernel.cpp:2884-2945, 3816-3844).  The library owns nothing else.
+namespace {
+struct TmapKey {
+  uint64_t w[12];   // base, dtype | rank << 8 | swizzle << 16, dims[4], strides[3], box packed
+  bool operator==(const TmapKey& o) const { return memcmp(w, o.w, sizeof(w)) == 0; }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = 0x9E3779B97F4A7C15ull;
+    for (uint64_t v : k.w) {
+      h ^= v + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+      h *= 0xFF51AFD7ED558CCDull;
+    }
+    return static_cast<size_t>(h ^ (h >> 32));
+  }
+};
+constexpr size_t kTmapCacheEntries = 8192;   // 128 bytes each; cleared when full
+std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmap_cache;
+std::mutex g_tmap_mutex;
+uint64_t g_tmap_hits = 0, g_tmap_misses = 0;
+}  // namespace
+
+static bool encode_tmap_uncached(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base,
+                                 const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                                 CUtensorMapSwizzle swizzle);
+
 static bool encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base,
                         const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                         CUtensorMapSwizzle swizzle) {
+  TmapKey key = {};
+  key.w[0] = reinterpret_cast<uint64_t>(base);
+  key.w[1] = static_cast<uint64_t>(dtype) | (static_cast<uint64_t>(rank) << 8) |
+             (static_cast<uint64_t>(swizzle) << 16);
+  for (int i = 0; i < rank; ++i) {
+    key.w[2 + i] = dims[i];
+    key.w[9 + i / 2] |= static_cast<uint64_t>(box[i]) << (32 * (i & 1));
+  }
+  for (int i = 0; i + 1 < rank; ++i) key.w[6 + i] = strides_bytes[i];
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mutex);
+    auto it = g_tmap_cache.find(key);
+    if (it != g_tmap_cache.end()) {
+      *out = it->second;
+      ++g_tmap_hits;
+      return true;
+    }
+  }
+  if (!encode_tmap_uncached(out, dtype, rank, base, dims, strides_bytes, box, swizzle)) return false;
+  std::lock_guard<std::mutex> lock(g_tmap_mutex);
+  if (g_tmap_cache.size() >= kTmapCacheEntries) g_tmap_cache.clear();
+  g_tmap_cache.emplace(key, *out);
+  ++g_tmap_misses;
+  return true;
+}
+
+void tmap_cache_stats(uint64_t* hits, uint64_t* misses, uint64_t* entries) {
+  std::lock_guard<std::mutex> lock(g_tmap_mutex);
+  *hits = g_tmap_hits;
+  *misses = g_tmap_misses;
+  *entries = g_tmap_cache.size();
+}
+
+static bool encode_tmap_uncached(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base,
+                                 const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                                 CUtensorMapSwizzle swizzle) {
   EncodeTiledFn fn = get_encode();
   if (fn == nullptr) {
     fail(B200K_CUDA_ERROR, "cuTensorMapEncodeTiled entry point unavailable");
@@ -136,6 +206,15 @@ int b200k_sm_count(void) {
   int n = b200k::current_sm_count();
   if (n < 0) return b200k::fail(B200K_CUDA_ERROR, "no current CUDA device");
   return n;
+}
+
+int b200k_tensor_map_cache_stats(uint64_t* hits, uint64_t* misses, uint64_t* entries) {
+  uint64_t h = 0, m = 0, e = 0;
+  b200k::tmap_cache_stats(&h, &m, &e);
+  if (hits) *hits = h;
+  if (misses) *misses = m;
+  if (entries) *entries = e;
+  return B200K_OK;
 }
 
 int b200k_device_status(int* code, int* info) {

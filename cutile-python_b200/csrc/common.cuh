@@ -107,9 +107,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Time budget of one wait.  Two seconds is three orders of magnitude above the
+// Default time budget of one wait.  Two seconds is three orders of magnitude above the
 // longest legitimate wait in these kernels (one full mainloop of the largest
-// tile) and still far below any watchdog.
+// tile) and still far below any watchdog.  The CTA-pair GEMM takes its budget from the
+// launch parameters (b200k_gemm_config.wait_budget_us).
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;
 
 // Bounded wait on an mbarrier phase.  `abort_flag` is a CTA-shared word that any
@@ -122,7 +123,8 @@ constexpr uint64_t kWaitBudgetNs = 2000000000ull;
 // is per lane; after a failure the lanes may leave a loop a few polls apart, which the
 // __syncwarp() that closes every role tolerates.
 __device__ __forceinline__ bool mbar_wait_lane(uint32_t bar, uint32_t parity,
-                                               volatile int* abort_flag) {
+                                               volatile int* abort_flag,
+                                               uint64_t budget_ns = kWaitBudgetNs) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
@@ -131,14 +133,15 @@ __device__ __forceinline__ bool mbar_wait_lane(uint32_t bar, uint32_t parity,
       if (*abort_flag) return false;
       uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitBudgetNs) return false;
+      else if (now - t0 > budget_ns) return false;
     }
   }
 }
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile int* abort_flag) {
-  const bool ok = mbar_wait_lane(bar, parity, abort_flag);
+                                          volatile int* abort_flag,
+                                          uint64_t budget_ns = kWaitBudgetNs) {
+  const bool ok = mbar_wait_lane(bar, parity, abort_flag, budget_ns);
   __syncwarp();
   return ok;
 }
@@ -147,7 +150,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
 // for a whole tile, producers waiting for a free stage): the thread sleeps between polls,
 // so a waiting warp costs no issue slots and little power.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
-                                                  volatile int* abort_flag, uint32_t sleep_ns) {
+                                                  volatile int* abort_flag, uint32_t sleep_ns,
+                                                  uint64_t budget_ns = kWaitBudgetNs) {
   bool ok = mbar_try_wait(bar, parity);
   if (!ok) {
     uint64_t t0 = 0;
@@ -158,7 +162,7 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
         if (*abort_flag) break;
         uint64_t now = global_timer_ns();
         if (t0 == 0) t0 = now;
-        else if (now - t0 > kWaitBudgetNs) break;
+        else if (now - t0 > budget_ns) break;
       }
     }
   }

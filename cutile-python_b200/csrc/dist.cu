@@ -9,12 +9,12 @@
 // peers' writes exactly as the sample does (a barrier before, a barrier after).
 #include "common.cuh"
 #include "host.h"
+#include "peer_gather_index.h"
 
 namespace b200k {
 namespace {
 
 constexpr int kMaxPeers = 16;
-constexpr int kChunkVecs = 256;   // 4 KB runs per peer keep every link busy at once
 
 struct PeerPtrs {
   const uint8_t* p[kMaxPeers];
@@ -32,20 +32,13 @@ __global__ void __launch_bounds__(256)
 peer_gather_kernel(PeerPtrs peers, int world, int rank, int64_t rows, int64_t row_vecs,
                    int64_t src_stride, uint8_t* __restrict__ dst, int64_t dst_stride,
                    int round_to_tf32) {
-  const int64_t shard_vecs = rows * row_vecs;
-  const int64_t chunks = (shard_vecs + kChunkVecs - 1) / kChunkVecs;
-  const int64_t items = chunks * world * kChunkVecs;
+  const int64_t items = peer_gather_items(world, rows, row_vecs);
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < items;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t within = i % kChunkVecs;
-    const int64_t run = i / kChunkVecs;
-    const int slot = static_cast<int>(run % world);
-    const int64_t chunk = run / world;
-    const int64_t v = chunk * kChunkVecs + within;
-    if (v >= shard_vecs) continue;
-    const int peer = (rank + 1 + slot) % world;   // remote shards first, own shard last
-    const int64_t r = v / row_vecs;
-    const int64_t c = v - r * row_vecs;
+    const PeerGatherItem it = peer_gather_item(i, world, rank, rows, row_vecs);
+    if (!it.valid) continue;
+    const int peer = it.peer;
+    const int64_t r = it.row, c = it.col;
     uint4 q = *reinterpret_cast<const uint4*>(peers.p[peer] + r * src_stride + c * 16);
     if (round_to_tf32) {
       q.x = round_tf32(q.x);

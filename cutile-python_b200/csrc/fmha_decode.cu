@@ -469,6 +469,9 @@ DecodePlan plan_decode(int64_t batch, int64_t heads_kv, int64_t sk, int sms) {
   if (const char* e = getenv("B200K_DECODE_PLAN")) {
     if (e[0] == 's') force_two = true;
     else forced = atoi(e);
+    // only the cluster sizes the kernel has (powers of two up to kMaxClusterSplits): anything
+    // else is ignored, since D / cluster columns per CTA must divide evenly
+    if (forced != 1 && forced != 2 && forced != 4 && forced != 8) forced = 0;
   }
   // One kernel, no scratch: the smallest cluster that gives every SM a CTA of four warps.
   // More CTAs than that only add rounds of launch, warp merge and cluster barriers.

@@ -526,7 +526,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 // diagnostic switches: B200K_SINGLE_CTA=1 (one-CTA kernels), B200K_PAIR_BN=128 (narrow
 // pair tiles), B200K_EPILOGUE=c|d (staged / direct stores).
 b200k_gemm_config effective_config(const b200k_gemm_config* c) {
-  b200k_gemm_config r = {0, 0, 0, 0};
+  b200k_gemm_config r = {};
   if (c != nullptr) r = *c;
   if (r.kernel == 0) {
     const char* v = getenv("B200K_SINGLE_CTA");
@@ -609,6 +609,8 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
   p.status = device_status_word();
   const b200k_gemm_config cfg = effective_config(a->config);
   p.store_mode = cfg.epilogue_store;
+  p.wait_budget_ns = cfg.wait_budget_us > 0 ? static_cast<uint64_t>(cfg.wait_budget_us) * 1000ull : 0;
+  p.withhold_arrival = cfg.withhold_arrival;
   const bool grouped = a->tile_group != nullptr;
   if (grouped) p.batch = 1;
 
@@ -784,6 +786,8 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
   p.status = device_status_word();
   const b200k_gemm_config cfg = effective_config(a->config);
   p.store_mode = cfg.epilogue_store;
+  p.wait_budget_ns = cfg.wait_budget_us > 0 ? static_cast<uint64_t>(cfg.wait_budget_us) * 1000ull : 0;
+  p.withhold_arrival = cfg.withhold_arrival;
   const bool grouped = a->tile_group != nullptr;
   if (grouped) p.batch = 1;
   const bool mx_out = a->c_dtype == B200K_E4M3;

@@ -53,6 +53,11 @@ struct GemmParams {
   int c_sf_k_atoms;
   const float* c_scale; // kOutNVF4: the output's per-tensor scale (device scalar)
   int* status;
+  // CTA-pair kernel: time budget of every pipeline wait, and the test hook of
+  // b200k_gemm_config.withhold_arrival (1 = the arrival that opens a tile to the second MMA
+  // issuer is never made, so that issuer's wait runs out of its budget)
+  uint64_t wait_budget_ns;
+  int withhold_arrival;
 };
 
 template <int KIND>

@@ -151,7 +151,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int kb = 0; kb < p.k_iters; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          if (!mbar_wait_relaxed(empty_bar(s), ph ^ 1, abort_flag, 64)) {
+          if (!mbar_wait_relaxed(empty_bar(s), ph ^ 1, abort_flag, 64, p.wait_budget_ns)) {
             report_status(p.status, 51, s);
             *abort_flag = 1;
             ok = false;
@@ -212,13 +212,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         if (p.tile_group != nullptr && p.tile_group[tile_coord(tile, tiles_m, p.tiles_n).pid_m] < 0) continue;
         const int w = lt & 1;
-        if (!mbar_wait(acc_empty_bar(w), ((lt >> 1) & 1) ^ 1, abort_flag)) {
+        if (!mbar_wait(acc_empty_bar(w), ((lt >> 1) & 1) ^ 1, abort_flag, p.wait_budget_ns)) {
           report_status(p.status, 52, 100 + w);
           *abort_flag = 1;
           break;
         }
         if (Cfg::kOverlapChunks > 0 && lt > 0) {
-          if (!mbar_wait(ovl_free_bar, (lt - 1) & 1, abort_flag)) {
+          if (!mbar_wait(ovl_free_bar, (lt - 1) & 1, abort_flag, p.wait_budget_ns)) {
             report_status(p.status, 52, 200);
             *abort_flag = 1;
             break;
@@ -227,7 +227,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (q == 1) {
           // the k-step that overwrites the accumulator must be complete before this
           // issuer adds to it
-          if (!mbar_wait(tile_open_bar(w), (lt >> 1) & 1, abort_flag)) {
+          if (!mbar_wait(tile_open_bar(w), (lt >> 1) & 1, abort_flag, p.wait_budget_ns)) {
             report_status(p.status, 52, 300 + w);
             *abort_flag = 1;
             break;
@@ -239,7 +239,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t it = it_base + kb;
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          if (!mbar_wait(full_bar(s), ph, abort_flag)) {
+          if (!mbar_wait(full_bar(s), ph, abort_flag, p.wait_budget_ns)) {
             report_status(p.status, 52, s);
             *abort_flag = 1;
             ok = false;
@@ -291,7 +291,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (elected) {
             tc_commit_pair(e0);
             tc_commit_pair(e1);
-            if (kb == 0 && p.k_iters > 1) tc_commit_pair(map_to_cta(tile_open_bar(w), 0));
+            if (kb == 0 && p.k_iters > 1 && !p.withhold_arrival) tc_commit_pair(map_to_cta(tile_open_bar(w), 0));
           }
         }
         if (ok) {
@@ -329,7 +329,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
       if (p.tile_group != nullptr && p.tile_group[tc.pid_m] < 0) continue;
       const int w = lt & 1;
-      if (!mbar_wait_relaxed(acc_full_bar(w), (lt >> 1) & 1, abort_flag, 64)) {
+      if (!mbar_wait_relaxed(acc_full_bar(w), (lt >> 1) & 1, abort_flag, 64, p.wait_budget_ns)) {
         report_status(p.status, 53, w);
         *abort_flag = 1;
         break;
@@ -593,6 +593,7 @@ int launch_gemm_pair(int kind, int out_dtype, const CUtensorMap* maps, const Gem
                      cudaStream_t stream) {
   GemmParams p = p_in;
   if (p.pair_bn != 128) p.pair_bn = 256;
+  if (p.wait_budget_ns == 0) p.wait_budget_ns = kWaitBudgetNs;
   // Stores staged through shared memory unless the caller asks for the direct form: direct
   // stores take about 8000 cycles per tile (16-bit output; twice the store instructions for
   // fp32) against about 530 per k-step, which decides short-K problems, and measured on

@@ -31,6 +31,9 @@ bool encode_tmap_4d(CUtensorMap* out, CUtensorMapDataType dtype, const void* bas
                     uint64_t stride2_bytes, uint64_t stride3_bytes, uint32_t box0, uint32_t box1,
                     uint32_t box2, uint32_t box3, CUtensorMapSwizzle swizzle);
 
+// Counters of the tensor-map cache behind encode_tmap_3d / encode_tmap_4d.
+void tmap_cache_stats(uint64_t* hits, uint64_t* misses, uint64_t* entries);
+
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 // Launches `kernel` with programmatic stream serialisation: it may become resident while

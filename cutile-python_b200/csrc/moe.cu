@@ -254,11 +254,26 @@ silu_and_mul_kernel(const uint16_t* __restrict__ ab, int64_t rows, int64_t n, in
   }
 }
 
+// Which (token, slot) entries take part in the sum: with routing ids given, an entry whose
+// expert id lies outside [0, num_experts) was dropped by the alignment, its row was never
+// written, and it contributes nothing.
+struct SlotFilter {
+  const void* ids;
+  int ids_are_int64;
+  int num_experts;
+  __device__ __forceinline__ bool live(int64_t entry) const {
+    if (ids == nullptr) return true;
+    const long long e = ids_are_int64 ? static_cast<const long long*>(ids)[entry]
+                                      : static_cast<long long>(static_cast<const int*>(ids)[entry]);
+    return e >= 0 && e < num_experts;
+  }
+};
+
 // out[t, :] = sum_j x[t, j, :], fp32 accumulation, 8 columns per thread.
 template <bool BF16>
 __global__ void __launch_bounds__(256)
 topk_sum_kernel(const uint16_t* __restrict__ x, const int* __restrict__ index, int64_t tokens,
-                int topk, int64_t h, uint16_t* __restrict__ out) {
+                int topk, int64_t h, uint16_t* __restrict__ out, const SlotFilter filter) {
   const int64_t vecs = h / 8;
   const int64_t total = tokens * vecs;
   for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
@@ -267,6 +282,7 @@ topk_sum_kernel(const uint16_t* __restrict__ x, const int* __restrict__ index, i
     const int64_t v = idx - t * vecs;
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int j = 0; j < topk; ++j) {
+      if (!filter.live(t * topk + j)) continue;
       const int64_t src = index != nullptr ? index[t * topk + j] : t * topk + j;
       const uint4 q = *reinterpret_cast<const uint4*>(x + src * h + v * 8);
       const uint32_t w[4] = {q.x, q.y, q.z, q.w};
@@ -308,7 +324,7 @@ silu_and_mul_f32_kernel(const float* __restrict__ ab, int64_t rows, int64_t n, i
 
 __global__ void __launch_bounds__(256)
 topk_sum_f32_kernel(const float* __restrict__ x, const int* __restrict__ index, int64_t tokens, int topk,
-                    int64_t h, float* __restrict__ out) {
+                    int64_t h, float* __restrict__ out, const SlotFilter filter) {
   const int64_t vecs = h / 4;
   const int64_t total = tokens * vecs;
   for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
@@ -317,6 +333,7 @@ topk_sum_f32_kernel(const float* __restrict__ x, const int* __restrict__ index, 
     const int64_t v = idx - t * vecs;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int j = 0; j < topk; ++j) {
+      if (!filter.live(t * topk + j)) continue;
       const int64_t src = index != nullptr ? index[t * topk + j] : t * topk + j;
       const float4 q = *reinterpret_cast<const float4*>(x + src * h + v * 4);
       acc.x += q.x;
@@ -325,6 +342,30 @@ topk_sum_f32_kernel(const float* __restrict__ x, const int* __restrict__ index, 
       acc.w += q.w;
     }
     *reinterpret_cast<float4*>(out + t * h + v * 4) = acc;
+  }
+}
+
+// Any hidden size / alignment: one output element per thread.  DT: 0 = f16, 1 = bf16, 2 = f32.
+template <int DT>
+__global__ void __launch_bounds__(256)
+topk_sum_scalar_kernel(const void* __restrict__ x_, const int* __restrict__ index, int64_t tokens, int topk,
+                       int64_t h, void* __restrict__ out_, const SlotFilter filter) {
+  const int64_t total = tokens * h;
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t t = idx / h;
+    const int64_t c = idx - t * h;
+    float acc = 0.0f;
+    for (int j = 0; j < topk; ++j) {
+      if (!filter.live(t * topk + j)) continue;
+      const int64_t src = index != nullptr ? index[t * topk + j] : t * topk + j;
+      if constexpr (DT == 2) acc += static_cast<const float*>(x_)[src * h + c];
+      else if constexpr (DT == 1) acc += __bfloat162float(static_cast<const __nv_bfloat16*>(x_)[src * h + c]);
+      else acc += __half2float(static_cast<const __half*>(x_)[src * h + c]);
+    }
+    if constexpr (DT == 2) static_cast<float*>(out_)[idx] = acc;
+    else if constexpr (DT == 1) static_cast<__nv_bfloat16*>(out_)[idx] = __float2bfloat16_rn(acc);
+    else static_cast<__half*>(out_)[idx] = __float2half_rn(acc);
   }
 }
 
@@ -448,25 +489,38 @@ extern "C" int b200k_silu_and_mul(const void* ab, int64_t rows, int64_t n, int64
 }
 
 extern "C" int b200k_topk_sum(const void* x, const int32_t* index, int64_t tokens, int32_t topk,
-                              int64_t hidden, void* out, int32_t dtype, b200k_stream stream_) {
+                              int64_t hidden, void* out, int32_t dtype, const void* expert_ids,
+                              int32_t ids_are_int64, int32_t num_experts, b200k_stream stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (tokens < 0 || topk <= 0 || hidden < 0) return fail(B200K_INVALID_ARG, "bad sizes");
   if (tokens == 0 || hidden == 0) return B200K_OK;
   if (!x || !out) return fail(B200K_INVALID_ARG, "null pointer");
-  if (hidden % 8 || (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) % 16)
-    return fail(B200K_UNSUPPORTED, "hidden must be a multiple of 8 and buffers 16-byte aligned");
+  if (dtype != B200K_F32 && dtype != B200K_BF16 && dtype != B200K_F16)
+    return fail(B200K_INVALID_ARG, "dtype must be f16, bf16 or f32");
+  const SlotFilter filter = {expert_ids, ids_are_int64, num_experts};
+  const bool vectors = hidden % 8 == 0 &&
+                       (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
+  if (!vectors) {   // odd hidden sizes or unaligned buffers: one element per thread
+    const int grid = blocks_for(tokens * hidden, 256);
+    if (dtype == B200K_F32)
+      topk_sum_scalar_kernel<2><<<grid, 256, 0, stream>>>(x, index, tokens, topk, hidden, out, filter);
+    else if (dtype == B200K_BF16)
+      topk_sum_scalar_kernel<1><<<grid, 256, 0, stream>>>(x, index, tokens, topk, hidden, out, filter);
+    else
+      topk_sum_scalar_kernel<0><<<grid, 256, 0, stream>>>(x, index, tokens, topk, hidden, out, filter);
+    B200K_CHECK_LAUNCH("topk_sum launch");
+    return B200K_OK;
+  }
   const int grid = blocks_for(tokens * hidden / 8, 256);
   if (dtype == B200K_F32)
     topk_sum_f32_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(x), index, tokens, topk, hidden,
-                                                  static_cast<float*>(out));
+                                                  static_cast<float*>(out), filter);
   else if (dtype == B200K_BF16)
     topk_sum_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), index, tokens, topk, hidden,
-                                                    static_cast<uint16_t*>(out));
-  else if (dtype == B200K_F16)
-    topk_sum_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), index, tokens, topk, hidden,
-                                                     static_cast<uint16_t*>(out));
+                                                    static_cast<uint16_t*>(out), filter);
   else
-    return fail(B200K_INVALID_ARG, "dtype must be f16, bf16 or f32");
+    topk_sum_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), index, tokens, topk, hidden,
+                                                     static_cast<uint16_t*>(out), filter);
   B200K_CHECK_LAUNCH("topk_sum launch");
   return B200K_OK;
 }

@@ -1,0 +1,60 @@
+// Work decomposition of the peer gather, shared by the kernel and by a host-side test
+// harness (this header is plain C++: no CUDA types).
+//
+// Every shard is rows x row_vecs 16-byte vectors.  The flat vector index v of a shard is cut
+// into chunks of kPeerGatherChunkVecs vectors (4 KB); work item i addresses one vector:
+//
+//   within = i % chunk            position inside a 4 KB run
+//   run    = i / chunk            runs are dealt round-robin over the peers ...
+//   slot   = run % world          ... so consecutive runs hit different NVLink peers
+//   chunk# = run / world
+//   peer   = (rank + 1 + slot) % world    remote shards first, this rank's own shard last
+//
+// Items whose vector index falls behind the end of the shard (the last chunk's tail) are
+// invalid.  Every (peer, vector) pair is produced by exactly one valid item.
+#ifndef B200K_PEER_GATHER_INDEX_H_
+#define B200K_PEER_GATHER_INDEX_H_
+
+#include <stdint.h>
+
+#ifndef B200K_HD
+#ifdef __CUDACC__
+#define B200K_HD __host__ __device__ __forceinline__
+#else
+#define B200K_HD inline
+#endif
+#endif
+
+namespace b200k {
+
+constexpr int kPeerGatherChunkVecs = 256;   // 4 KB runs per peer keep every link busy at once
+
+struct PeerGatherItem {
+  int peer;       // shard the vector comes from; also its slot in the gathered tensor
+  int64_t row;    // row inside the shard
+  int64_t col;    // 16-byte vector inside the row
+  bool valid;
+};
+
+B200K_HD int64_t peer_gather_items(int world, int64_t rows, int64_t row_vecs) {
+  const int64_t shard_vecs = rows * row_vecs;
+  const int64_t chunks = (shard_vecs + kPeerGatherChunkVecs - 1) / kPeerGatherChunkVecs;
+  return chunks * world * kPeerGatherChunkVecs;
+}
+
+B200K_HD PeerGatherItem peer_gather_item(int64_t i, int world, int rank, int64_t rows, int64_t row_vecs) {
+  PeerGatherItem it;
+  const int64_t within = i % kPeerGatherChunkVecs;
+  const int64_t run = i / kPeerGatherChunkVecs;
+  const int slot = static_cast<int>(run % world);
+  const int64_t chunk = run / world;
+  const int64_t v = chunk * kPeerGatherChunkVecs + within;
+  it.valid = v < rows * row_vecs;
+  it.peer = (rank + 1 + slot) % world;
+  it.row = v / row_vecs;
+  it.col = v - it.row * row_vecs;
+  return it;
+}
+
+}  // namespace b200k
+#endif  // B200K_PEER_GATHER_INDEX_H_

@@ -59,6 +59,13 @@ int b200k_sm_count(void);                       /* SMs of the current device, <0
 /* Reads and clears the current device's status word.  *code is 0 or B200K_TIMEOUT,
  * *info packs (role << 8 | detail << 16) of the wait that gave up. */
 int b200k_device_status(int* code, int* info);
+/* The one piece of state the library owns: a mutex-guarded cache of encoded TMA tensor maps
+ * keyed by (base pointer, data type, dims, strides, box, swizzle), at most 8192 entries of
+ * 128 bytes of host memory.  A call whose operands were seen before pays a hash lookup per
+ * operand instead of a driver call; the reference keeps the same per-kernel state as hoisted
+ * descriptors (cext/tile_kernel.cpp:2884-2945, 3816-3844).  This reads its counters (any
+ * pointer may be NULL). */
+int b200k_tensor_map_cache_stats(uint64_t* hits, uint64_t* misses, uint64_t* entries);
 
 /* ---- kernel-form selection ------------------------------------------------
  * Which of the library's kernel forms a GEMM call uses.  Every field is 0 for "choose
@@ -74,6 +81,15 @@ typedef struct {
   int32_t epilogue_store;  /* 1 = straight from registers, 2 = staged through shared memory */
   int32_t split_k;         /* 1 = never split K, n > 1 = split K into (up to) n slices; needs the
                             * workspace b200k_gemm_workspace_bytes reports for the same args */
+  /* CTA-pair kernel: time budget in microseconds of every wait between the kernel's roles
+   * (0 = the default of two seconds).  A wait that runs out makes the kernel return normally
+   * with the device status word set (b200k_device_status -> B200K_TIMEOUT, info = role and
+   * stage); the output of that call is then undefined, later calls are unaffected. */
+  int32_t wait_budget_us;
+  /* Test hook for that path, leave 0: 1 = on the CTA-pair kernel the arrival that opens a
+   * tile to the second MMA issuer is never made (a flag that nothing sets), so its wait runs
+   * out of the budget.  Nothing faults, traps or spins without limit. */
+  int32_t withhold_arrival;
 } b200k_gemm_config;
 
 /* ---- dense GEMM -------------------------------------------------------
@@ -299,9 +315,13 @@ int b200k_silu_and_mul(const void* ab, int64_t rows, int64_t n, int64_t ld_ab, v
 
 /* out[t, :] = sum over slot of x[row(t, slot), :] with fp32 accumulation, where
  * row(t, slot) = index[t * topk + slot], or t * topk + slot when index is NULL; replaces
- * torch.sum(intermediate_cache3, dim=1) (reference: samples/MoE.py:288). */
+ * torch.sum(intermediate_cache3, dim=1) (reference: samples/MoE.py:288).  With `expert_ids`
+ * (the routing ids, (tokens, topk) int32 or int64) an entry whose id lies outside
+ * [0, num_experts) contributes nothing: b200k_moe_align drops such entries (and records it in
+ * the device status word), so their rows of x were never written. */
 int b200k_topk_sum(const void* x, const int32_t* index, int64_t tokens, int32_t topk,
-                   int64_t hidden, void* out, int32_t dtype, b200k_stream stream);
+                   int64_t hidden, void* out, int32_t dtype, const void* expert_ids,
+                   int32_t ids_are_int64, int32_t num_experts, b200k_stream stream);
 
 /* ---- peer-memory gather (AllGather GEMM) -------------------------------
  * dst rows [p * rows, (p + 1) * rows) = shard p, read through `shards[p]`, a pointer this

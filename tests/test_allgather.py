@@ -2,7 +2,9 @@
 (samples/AllGatherMatmul.py:85-175: 256 x 1024 fp32 per rank, w 1024 x 512, checked against
 all_gather_into_tensor + matmul with atol = rtol = 1e-3).
 
-CPU part: layout helpers and a world-size-2 gloo run of the gather semantics.
+CPU part: layout helpers, the peer-gather kernel's index arithmetic run on the host over
+fake shards (the header the kernel includes, compiled with g++), and a world-size-2 gloo run
+of the gather semantics.
 GPU part (needs >= 2 GPUs, one process per GPU over NCCL): the p2p and nccl transports
 against the fp32 CPU oracle, for fp32 (tf32), bf16 and NVFP4 operands.
 """
@@ -29,6 +31,95 @@ def test_shard_rows():
     assert shard_rows(8192, 8, 7) == (7168, 8192)
     with pytest.raises(ValueError):
         shard_rows(100, 8, 0)
+
+
+_HARNESS = r"""
+#include <stdint.h>
+#include <string.h>
+#include "peer_gather_index.h"
+// The kernel's loop nest on the host: `threads` grid-stride workers walk the items exactly as
+// the CUDA threads do and move 16 bytes per valid item.  hits[] counts writes per destination
+// vector, first_peer[] records the peer of each worker's first valid item.
+extern "C" void host_peer_gather(const uint8_t* const* shards, int world, int rank, int64_t rows,
+                                 int64_t row_vecs, int64_t src_stride, uint8_t* dst,
+                                 int64_t dst_stride, int64_t threads, int32_t* hits,
+                                 int32_t* first_peer) {
+  const int64_t items = b200k::peer_gather_items(world, rows, row_vecs);
+  for (int64_t t = 0; t < threads; ++t) {
+    first_peer[t] = -1;
+    for (int64_t i = t; i < items; i += threads) {
+      const b200k::PeerGatherItem it = b200k::peer_gather_item(i, world, rank, rows, row_vecs);
+      if (!it.valid) continue;
+      if (first_peer[t] < 0) first_peer[t] = it.peer;
+      memcpy(dst + (int64_t(it.peer) * rows + it.row) * dst_stride + it.col * 16,
+             shards[it.peer] + it.row * src_stride + it.col * 16, 16);
+      hits[(int64_t(it.peer) * rows + it.row) * row_vecs + it.col] += 1;
+    }
+  }
+}
+"""
+
+
+@pytest.fixture(scope="module")
+def host_gather(tmp_path_factory):
+    """The index arithmetic of peer_gather_kernel (csrc/peer_gather_index.h, the header the
+    kernel itself includes) compiled for the host."""
+    import ctypes
+    import shutil
+    import subprocess
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if cxx is None:
+        pytest.skip("no C++ compiler")
+    d = tmp_path_factory.mktemp("peer_gather")
+    src = d / "harness.cpp"
+    src.write_text(_HARNESS)
+    lib = d / "harness.so"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    subprocess.run([cxx, "-O1", "-shared", "-fPIC", "-I", os.path.join(root, "cutile-python_b200", "csrc"),
+                    str(src), "-o", str(lib)], check=True)
+    fn = ctypes.CDLL(str(lib)).host_peer_gather
+    fn.restype = None
+
+    def run(shards, rank, threads, dst_cols=None):
+        world = len(shards)
+        rows, cols = shards[0].shape
+        row_vecs = cols * shards[0].element_size() // 16
+        dst_cols = dst_cols or cols
+        dst = torch.full((world * rows, dst_cols), -1, dtype=shards[0].dtype)
+        hits = torch.zeros(world * rows * row_vecs, dtype=torch.int32)
+        first = torch.zeros(threads, dtype=torch.int32)
+        ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in shards])
+        fn(ptrs, ctypes.c_int(world), ctypes.c_int(rank), ctypes.c_int64(rows), ctypes.c_int64(row_vecs),
+           ctypes.c_int64(shards[0].stride(0) * shards[0].element_size()), ctypes.c_void_p(dst.data_ptr()),
+           ctypes.c_int64(dst.stride(0) * dst.element_size()), ctypes.c_int64(threads),
+           ctypes.c_void_p(hits.data_ptr()), ctypes.c_void_p(first.data_ptr()))
+        return dst, hits, first
+
+    return run
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 8])
+@pytest.mark.parametrize("rows,cols", [(8, 64), (5, 36), (96, 260), (1, 4)])   # fp32 columns
+def test_peer_gather_index_math_on_fake_shards(host_gather, world, rows, cols):
+    # shards with a row pitch wider than the payload, as a view into a larger allocation
+    g = torch.Generator().manual_seed(world * 1000 + rows)
+    backing = [torch.randn(rows, cols + 8, generator=g) for _ in range(world)]
+    shards = [b[:, :cols] for b in backing]
+    want = torch.cat(shards)
+    for rank in range(world):
+        for threads in (1, 7, 256 * 3):
+            dst, hits, first = host_gather(shards, rank, threads, dst_cols=cols + 4)
+            assert torch.equal(dst[:, :cols], want)                 # shard p -> rows [p * rows, ...)
+            assert bool((dst[:, cols:] == -1).all())                # nothing outside the payload
+            assert bool((hits == 1).all())                          # every vector moved exactly once
+        # runs of 256 vectors are dealt round-robin over the peers, remote shards first
+        _, _, first = host_gather(shards, rank, 256 * world)
+        vecs = rows * cols * 4 // 16
+        for slot in range(world):
+            if vecs > 0:
+                assert int(first[256 * slot]) == (rank + 1 + slot) % world
+        if world > 1:
+            assert int(first[0]) != rank and int(first[256 * (world - 1)]) == rank
 
 
 def _gloo_worker(rank, world, port, q):
@@ -164,3 +255,56 @@ def test_gather_matmul_two_gpus():
         p.join(120)
     for rank, failures in results:
         assert not failures, f"rank {rank}: {failures}"
+
+
+# ---------------------------------------------------------------------------------------
+# The same path on ONE GPU: the shards of all ranks are local buffers handed over as explicit
+# peers, and the ranks run one after the other (no kernel of this path waits on another).
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 3, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gather_matmul_emulated_ranks_one_gpu(world, dtype, device_ok):
+    import b200k
+    g = torch.Generator().manual_seed(52 + world)
+    m, k, n = (256, 1024, 512) if dtype == torch.float32 else (384, 512, 768)
+    draw = torch.rand if dtype == torch.float32 else torch.randn    # the sample feeds uniform fp32
+    shards = [draw(m, k, generator=g).to(dtype) for _ in range(world)]
+    w = draw(k, n, generator=g).to(dtype)
+    want = oracle.matmul_ref(torch.cat(shards), w)
+    dev_shards = [s.cuda() for s in shards]
+    tol = dict(atol=1e-3, rtol=1e-3) if dtype == torch.float32 else dict(atol=2e-1, rtol=2e-2)
+    if dtype == torch.float32:      # tf32 products: the sample's tolerance holds for its [0, 1) data
+        tol = dict(atol=1e-3 * float(want.abs().max()), rtol=1e-3)
+    for rank in range(world):
+        out = b200k.cutile_gather_matmul(dev_shards[rank], w.cuda(), peers=dev_shards, rank=rank)
+        assert out.shape == (m * world, n) and out.dtype == dtype
+        torch.testing.assert_close(out.float().cpu(), want, **tol)
+    # the staging gather alone is a byte-exact concatenation, whatever the rank
+    for rank in (0, world - 1):
+        staged = b200k.peer_gather(dev_shards, rank)
+        assert torch.equal(staged.cpu(), torch.cat(shards))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4])
+def test_gather_matmul_nvfp4_emulated_ranks_one_gpu(world, device_ok):
+    import b200k
+    g = torch.Generator().manual_seed(200 + world)
+    m, k, n = 256, 1024, 512
+    shards = [(torch.randn(m, k, generator=g) * (1 + p)).bfloat16() for p in range(world)]
+    wn = (0.02 * torch.randn(n, k, generator=g)).bfloat16()
+    quant = [b200k.nvfp4_quantize(s.cuda()) for s in shards]     # each rank quantises its own rows
+    wq, wsf, wts = b200k.nvfp4_quantize(wn.cuda())
+    w_ref = oracle.nvfp4_quantize_ref(wn)
+    want = torch.cat([oracle.nvfp4_matmul_ref(*oracle.nvfp4_quantize_ref(s), *w_ref) for s in shards])
+    peers = ([q[0] for q in quant], [q[1] for q in quant], [q[2] for q in quant])
+    for rank in range(world):
+        out = b200k.cutile_gather_matmul_nvfp4(*quant[rank], wq, wsf, wts, out_dtype=torch.float32,
+                                               peers=peers, rank=rank)
+        assert out.shape == (m * world, n)
+        torch.testing.assert_close(out.cpu(), want, atol=1e-4 * float(want.abs().max()), rtol=1e-3)
+    # a plan kept across calls gives the same result again (staging buffers are reused)
+    plan = b200k.Nvfp4GatherMatmul(*quant[1], peers=peers, rank=1)
+    first = plan.run(wq, wsf, wts).clone()
+    assert torch.equal(first, plan.run(wq, wsf, wts))
+    torch.testing.assert_close(first.float().cpu(), want, atol=2e-2 * float(want.abs().max()), rtol=2e-2)

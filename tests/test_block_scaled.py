@@ -223,10 +223,15 @@ def test_quantise_in_epilogue_equals_two_steps(m, n, k, device_ok):
     aq, sa = b200k.block_quantize(a, 32, swizzled_scale=True)
     bq, sb = b200k.block_quantize(b, 32, swizzled_scale=True)
     c_bf16 = b200k.cutile_block_scaled_matmul(aq, sa, bq.T, sb, out_dtype=torch.bfloat16)
-    q_ref, s_ref = b200k.block_quantize(c_bf16, 32, swizzled_scale=True)
+    # the oracle's quantiser over the bf16 result is the reference of this step
+    q_ref, s_ref = oracle.block_quantize_ref(c_bf16.cpu())
     q, s = b200k.cutile_block_scaled_matmul(aq, sa, bq.T, sb, out_dtype=torch.float8_e4m3fn)
-    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+    assert q.shape == (m, n) and q.dtype == torch.float8_e4m3fn
+    assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8))
     # scale atoms: compare the bytes that belong to real rows / blocks
     lo = oracle.unswizzle_32_4_4_ref(s.cpu().view(torch.uint8))[:m, : n // 32]
-    lo_ref = oracle.unswizzle_32_4_4_ref(s_ref.cpu().view(torch.uint8))[:m, : n // 32]
-    assert torch.equal(lo, lo_ref)
+    assert torch.equal(lo, s_ref.view(torch.uint8))
+    # and the library's own two-step path gives the same bytes
+    q2, s2 = b200k.block_quantize(c_bf16, 32)
+    assert torch.equal(q2.view(torch.uint8), q.view(torch.uint8))
+    assert torch.equal(s2.cpu().view(torch.uint8), s_ref.view(torch.uint8))

@@ -80,7 +80,7 @@ def test_fmha_decode_split_kv(dtype, d, b, hq, hkv, sq, sk, causal, device_ok, m
     torch.testing.assert_close(out.float(), out_tc.float(), **TOL)
 
 
-@pytest.mark.parametrize("plan", ["1", "2", "4", "8", "s"])
+@pytest.mark.parametrize("plan", ["1", "2", "4", "8", "s", "3", "16"])   # 3 and 16 are ignored
 @pytest.mark.parametrize("b,hq,hkv,sq,sk,causal", [
     (2, 8, 8, 1, 777, True),        # one row, ragged last batch, masked tail CTAs for large clusters
     (1, 16, 4, 2, 1300, True),      # eight rows (sixteen lanes per key), two query positions under the mask

@@ -215,3 +215,28 @@ def test_linearity_at_full_size(device_ok):
     rows = torch.tensor([0, 127, 128, 2049, 4095])
     ref = oracle.matmul_ref(a1[rows].cpu(), b.cpu())
     torch.testing.assert_close(c1[rows].cpu(), ref, **TOL[torch.float16])
+
+
+def test_fp32_operands_truncate_to_tf32_unless_rounding_is_asked_for(device_ok):
+    # same-sign data shows the difference: truncation biases every product low, rounding to
+    # nearest does not; both stay within the tf32 error bound of the fp32 product
+    g = torch.Generator().manual_seed(12)
+    a = torch.rand(256, 1024, generator=g)
+    b = torch.rand(1024, 384, generator=g)
+    ref = oracle.matmul_ref(a, b)
+
+    def tf32(t, nearest):
+        bits = t.contiguous().view(torch.int32)
+        return ((bits + 0x1000) & ~0x1FFF if nearest else bits & ~0x1FFF).view(torch.float32)
+
+    plain = b200k.cutile_matmul(a.cuda(), b.cuda()).cpu()
+    rounded = b200k.cutile_matmul(a.cuda(), b.cuda(), round_tf32=True).cpu()
+    # each form equals the fp32 product of operands cut to tf32 its way, up to summation order
+    torch.testing.assert_close(plain, oracle.matmul_ref(tf32(a, False), tf32(b, False)), rtol=2e-5, atol=0)
+    torch.testing.assert_close(rounded, oracle.matmul_ref(tf32(a, True), tf32(b, True)), rtol=2e-5, atol=0)
+    assert float(((plain - ref) / ref).mean()) < -2e-4           # one-sided
+    assert abs(float(((rounded - ref) / ref).mean())) < 5e-5     # centred
+    torch.testing.assert_close(plain, ref, rtol=2e-3, atol=0)
+    # the gather form at a world of one rounds, like the reference's cast: same result as round_tf32
+    gathered = b200k.cutile_gather_matmul(a.cuda(), b.cuda(), peers=[a.cuda()], rank=0).cpu()
+    torch.testing.assert_close(gathered, rounded, rtol=2e-5, atol=0)

@@ -148,3 +148,38 @@ def test_cutile_moe_mxfp8(tokens, hidden, experts, inter, topk, row_tile, device
     assert oracle.rel_frobenius(out, ref) < 2e-2
     # and the quantised pipeline stays close to the unquantised FFN
     assert oracle.rel_frobenius(out, oracle.moe_ref(x, w1, w2, tw, ids)) < 1e-1
+
+
+@pytest.mark.parametrize("mxfp8", [False, True])
+def test_routing_entries_outside_the_expert_range_contribute_zero(mxfp8):
+    # a sentinel-padded or corrupt topk_ids: the alignment drops the entry and records it in the
+    # status word; the token's output is the sum over its remaining slots (never stale memory)
+    x, w1, w2, tw, ids = _problem(200, 256, 8, 128, 2, 21)
+    bad = ids.clone()
+    bad[3, 0], bad[77, 1], bad[199, 0], bad[199, 1] = -1, 8, 1000, -5
+    tw_eff = tw.clone()
+    tw_eff[(bad < 0) | (bad >= 8)] = 0
+    poison = torch.full((4096, 256), float("nan"), dtype=torch.bfloat16, device="cuda")
+    del poison                                     # the caching allocator hands these pages out next
+    if mxfp8:
+        w1q, w1s = b200k.quantize_expert_weights(w1.cuda())
+        w2q, w2s = b200k.quantize_expert_weights(w2.cuda())
+        out = b200k.cutile_moe_mxfp8(x.cuda(), w1q, w1s, w2q, w2s, tw.cuda(), bad.cuda())
+    else:
+        out = b200k.cutile_moe(x.cuda(), w1.cuda(), w2.cuda(), tw.cuda(), bad.cuda())
+    torch.cuda.synchronize()
+    code, info = b200k.device_status()
+    assert code != 0 and (info >> 8) & 0xff == 40      # reported, and cleared by the read
+    assert b200k.device_status()[0] == 0
+    ref = oracle.moe_ref(x, w1, w2, tw_eff, bad.clamp(0, 7))
+    assert bool(torch.isfinite(out).all())
+    assert float(out[199].abs().max()) == 0.0          # both slots dropped
+    assert oracle.rel_frobenius(out, ref) < (1e-1 if mxfp8 else 2e-2)   # mxfp8: against the unquantised FFN
+
+
+def test_cutile_moe_hidden_not_a_multiple_of_eight_elements(device_ok):
+    # fp32 rows of 20 elements are 16-byte multiples for the gather and the GEMMs, but not a
+    # multiple of 8 elements: the top-k sum takes its one-element-per-thread form
+    x, w1, w2, tw, ids = _problem(64, 20, 4, 12, 2, 5, torch.float32)
+    out = b200k.cutile_moe(x.cuda(), w1.cuda(), w2.cuda(), tw.cuda(), ids.cuda())
+    torch.testing.assert_close(out.cpu(), oracle.moe_ref(x, w1, w2, tw, ids), rtol=1e-2, atol=1e-2)

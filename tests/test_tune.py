@@ -53,6 +53,26 @@ def test_search_stops_sampling_beaten_configs():
     assert calls["fast"] == 40           # 20 % noise: never within 1 %, runs out of samples
 
 
+def test_search_admits_no_config_on_time_alone():
+    # the fastest config returns a wrong result (it "loads nothing"): validate rejects it after
+    # its warm-up, it is listed under failures and never timed
+    times = {"good": 50.0, "wrong_but_fast": 1.0, "slow": 80.0}
+    timed = []
+
+    def timer(run_fn, cfg):
+        timed.append(cfg)
+        return times[cfg]
+
+    def validate(cfg):
+        if cfg == "wrong_but_fast":
+            raise AssertionError("result differs from the automatic form's")
+
+    res = tune.exhaustive_search(list(times), None, lambda cfg: None, timer=timer, validate=validate)
+    assert res.best.config == "good"
+    assert [(c, t) for c, t, _ in res.failures] == [("wrong_but_fast", AssertionError)]
+    assert "wrong_but_fast" not in timed
+
+
 def test_search_rejects_empty_and_all_failing_spaces():
     with pytest.raises(ValueError, match="empty"):
         tune.exhaustive_search([], None, lambda cfg: None, timer=lambda r, c: 1.0)
