@@ -15,5 +15,5 @@ from .moe import (cutile_moe, cutile_moe_mxfp8, invoke_fused_moe_kernel,  # noqa
                   quantize_expert_weights)
 from .allgather import (Nvfp4GatherMatmul, cutile_gather_matmul, cutile_gather_matmul_nvfp4, peer_buffers,  # noqa: F401
                         peer_gather, shard_rows)
-from .moe_ep import ExpertParallelMoE  # noqa: F401
+from .moe_ep import ExpertParallelMoE, emulate_ranks  # noqa: F401
 from . import tune  # noqa: F401

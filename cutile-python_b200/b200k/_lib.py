@@ -51,6 +51,7 @@ class GemmArgs(Structure):
         ("tile_rows", c_int32),
         ("workspace", c_void_p), ("workspace_bytes", c_int64),
         ("config", POINTER(GemmConfig)),
+        ("c_peers", POINTER(c_void_p)), ("num_c_peers", c_int32), ("c_peer_rows", c_int64),
     ]
 
 
@@ -70,6 +71,7 @@ class BlockScaledGemmArgs(Structure):
         ("c_sf", c_void_p), ("c_sf_k_atoms", c_int64),
         ("config", POINTER(GemmConfig)),
         ("c_scale", c_void_p),
+        ("c_peers", POINTER(c_void_p)), ("num_c_peers", c_int32), ("c_peer_rows", c_int64),
     ]
 
 
@@ -92,6 +94,36 @@ class MoeAlignArgs(Structure):
         ("num_blocks", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_int64),
         ("num_replicas", c_int64), ("capacity", c_int64), ("block_capacity", c_int64),
         ("num_experts", c_int32), ("tile_m", c_int32), ("ids_are_int64", c_int32),
+    ]
+
+
+class MoeEpCountArgs(Structure):
+    _fields_ = [
+        ("topk_ids", c_void_p), ("num_replicas", c_int64), ("ids_are_int64", c_int32),
+        ("num_experts", c_int32), ("world", c_int32), ("rank", c_int32),
+        ("scratch", c_void_p), ("hist_peers", POINTER(c_void_p)),
+    ]
+
+
+class MoeEpPlanArgs(Structure):
+    _fields_ = [
+        ("hist", c_void_p), ("world", c_int32), ("rank", c_int32), ("num_experts", c_int32),
+        ("tile_rows", c_int32), ("capacity_rows", c_int64),
+        ("first_row", c_void_p), ("cursor", c_void_p), ("tile_group", c_void_p),
+        ("num_row_tiles", c_void_p), ("meta", c_void_p),
+    ]
+
+
+class MoeEpDispatchArgs(Structure):
+    _fields_ = [
+        ("topk_ids", c_void_p), ("weights", c_void_p), ("num_replicas", c_int64),
+        ("topk", c_int32), ("ids_are_int64", c_int32), ("num_experts", c_int32),
+        ("world", c_int32), ("rank", c_int32),
+        ("src", c_void_p), ("src_stride_bytes", c_int64), ("row_bytes", c_int64),
+        ("aux", c_void_p), ("aux_stride_bytes", c_int64), ("aux_bytes", c_int64),
+        ("first_row", c_void_p), ("cursor", c_void_p), ("capacity_rows", c_int64),
+        ("row_peers", POINTER(c_void_p)), ("aux_peers", POINTER(c_void_p)),
+        ("meta_peers", POINTER(c_void_p)), ("weight_peers", POINTER(c_void_p)),
     ]
 
 
@@ -144,6 +176,11 @@ SIGNATURES = {
                                c_int32, c_int32, c_void_p]),
     "b200k_peer_gather": (c_int, [POINTER(PeerGatherArgs), c_void_p]),
     "b200k_peer_scalar_expand": (c_int, [POINTER(c_void_p), c_int32, c_int64, c_void_p, c_void_p]),
+    "b200k_moe_ep_capacity_rows": (c_int64, [c_int64, c_int32, c_int32, c_int32]),
+    "b200k_moe_ep_count": (c_int, [POINTER(MoeEpCountArgs), c_void_p]),
+    "b200k_moe_ep_plan": (c_int, [POINTER(MoeEpPlanArgs), c_void_p]),
+    "b200k_moe_ep_dispatch": (c_int, [POINTER(MoeEpDispatchArgs), c_void_p]),
+    "b200k_peer_barrier": (c_int, [POINTER(c_void_p), c_int32, c_int32, c_void_p, c_int32, c_void_p]),
     "b200k_fmha_fwd": (c_int, [POINTER(FmhaArgs), c_void_p]),
     "b200k_fmha_workspace_bytes": (c_int64, [POINTER(FmhaArgs)]),
     "b200k_sf_swizzle": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int32,

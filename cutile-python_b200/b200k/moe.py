@@ -101,8 +101,19 @@ def _gather_rows(src: torch.Tensor, index: torch.Tensor, divisor: int, rows: int
     return dst
 
 
+def _set_c_peers(args, c_peers, c_peer_rows):
+    """Output rows scattered over several buffers (b200k_gemm_args.c_peers).  Returns the
+    pointer array, which must stay alive until the call has returned."""
+    if c_peers is None:
+        return None
+    arr = (ctypes.c_void_p * len(c_peers))(*[t.data_ptr() for t in c_peers])
+    args.c_peers = ctypes.cast(arr, ctypes.POINTER(ctypes.c_void_p))
+    args.num_c_peers, args.c_peer_rows = len(c_peers), c_peer_rows
+    return arr
+
+
 def _grouped_gemm(a_sorted, w, c, expert_ids, *, num_blocks=None, row_map=None, row_scale=None,
-                  c_rows=0, swiglu=False, tile=ROW_TILE):
+                  c_rows=0, swiglu=False, tile=ROW_TILE, c_peers=None, c_peer_rows=0):
     """a_sorted (Mp, K) x w (E, N, K)^T with the expert of each `tile`-row tile in expert_ids."""
     mp, k = a_sorted.shape
     e, n, _ = w.shape
@@ -122,8 +133,10 @@ def _grouped_gemm(a_sorted, w, c, expert_ids, *, num_blocks=None, row_map=None, 
     args.row_scale = _lib.ptr(row_scale)
     args.c_rows = c_rows
     args.tile_rows = tile
+    keep = _set_c_peers(args, c_peers, c_peer_rows)
     with torch.cuda.device(c.device):
         _lib.check(_lib.lib().b200k_gemm(ctypes.byref(args), _lib.stream_ptr(c.device)))
+    del keep
     return c
 
 
@@ -258,7 +271,8 @@ def _quantize_rows(x, *, rows, gather=None, divisor=1, num_blocks=None, tile=ROW
 
 
 def _grouped_scaled_gemm(a_q, a_sf, w_q, w_sf, c, expert_ids, *, num_blocks, row_map=None,
-                         row_scale=None, c_rows=0, swiglu=False, tile=ROW_TILE, c_sf=None):
+                         row_scale=None, c_rows=0, swiglu=False, tile=ROW_TILE, c_sf=None,
+                         c_peers=None, c_peer_rows=0):
     """`c` of dtype float8_e4m3fn together with `c_sf` (swizzled scale bytes) asks for the
     quantise-in-epilogue form: the result leaves the GEMM as an MXFP8 operand."""
     mp, k = a_q.shape
@@ -282,8 +296,10 @@ def _grouped_scaled_gemm(a_q, a_sf, w_q, w_sf, c, expert_ids, *, num_blocks, row
     args.tile_rows = tile
     if c_sf is not None:
         args.c_sf, args.c_sf_k_atoms = c_sf.data_ptr(), c_sf.shape[1]
+    keep = _set_c_peers(args, c_peers, c_peer_rows)
     with torch.cuda.device(c.device):
         _lib.check(_lib.lib().b200k_block_scaled_gemm(ctypes.byref(args), _lib.stream_ptr(c.device)))
+    del keep
     return c
 
 

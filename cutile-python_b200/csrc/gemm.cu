@@ -522,6 +522,27 @@ int launch_splitk_reduce(int out, const float* ws, int split, int64_t m, int64_t
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// Output rows scattered over several (peer) buffers: checks the request and copies the
+// pointer table into the launch parameters.
+int set_c_peers(GemmParams* p, const void* const* c_peers, int32_t n, int64_t rows, bool grouped_pair,
+                const void* row_map, int out_dtype) {
+  if (c_peers == nullptr) return B200K_OK;
+  if (!grouped_pair || row_map == nullptr)
+    return fail(B200K_UNSUPPORTED, "c_peers needs a grouped problem over 256-row tiles (CTA-pair kernel) "
+                "with row_map");
+  if (out_dtype != B200K_F16 && out_dtype != B200K_BF16 && out_dtype != B200K_F32)
+    return fail(B200K_UNSUPPORTED, "c_peers needs an f16, bf16 or f32 output");
+  if (n <= 0 || n > 16 || rows <= 0) return fail(B200K_INVALID_ARG, "c_peers: 1 to 16 buffers of at least one row");
+  for (int i = 0; i < n; ++i) {
+    if (c_peers[i] == nullptr || !aligned16(c_peers[i]))
+      return fail(B200K_INVALID_ARG, "c_peers[%d] is null or not 16-byte aligned", i);
+    p->c_peers[i] = const_cast<void*>(c_peers[i]);
+  }
+  p->num_c_peers = n;
+  p->c_peer_rows = rows;
+  return B200K_OK;
+}
+
 // The caller's b200k_gemm_config, or, where it leaves a choice open, the process-wide
 // diagnostic switches: B200K_SINGLE_CTA=1 (one-CTA kernels), B200K_PAIR_BN=128 (narrow
 // pair tiles), B200K_EPILOGUE=c|d (staged / direct stores).
@@ -554,7 +575,7 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
   if (a->m < 0 || a->n < 0 || a->k < 0 || a->batch < 0)
     return fail(B200K_INVALID_ARG, "negative dimension");
   if (a->m == 0 || a->n == 0 || a->batch == 0) return B200K_OK;
-  if (a->a == nullptr || a->b == nullptr || a->c == nullptr)
+  if (a->a == nullptr || a->b == nullptr || (a->c == nullptr && a->c_peers == nullptr))
     return fail(B200K_INVALID_ARG, "null operand pointer");
   if (a->k == 0) return fail(B200K_UNSUPPORTED, "K == 0 is not supported (C would be all zeros)");
 
@@ -671,6 +692,8 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
   }
   const bool pair_plain = !grouped && a->epilogue == B200K_EPI_STORE && a->row_map == nullptr;
   const bool pair_grouped = grouped && a->tile_rows == 256 && !b_mn;
+  if (int rc = set_c_peers(&p, a->c_peers, a->num_c_peers, a->c_peer_rows, pair_grouped, a->row_map, out))
+    return rc;
   // N-contiguous B on the pair kernel: plain problems
   const bool pair_b_ok = !b_mn || pair_plain;
   // (a grouped problem over 256-row tiles exists on the pair kernel only: a request for the
@@ -725,7 +748,7 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
   if (a->m < 0 || a->n < 0 || a->k < 0 || a->batch < 0)
     return fail(B200K_INVALID_ARG, "negative dimension");
   if (a->m == 0 || a->n == 0 || a->batch == 0) return B200K_OK;
-  if (!a->a || !a->b || !a->c || !a->sfa || !a->sfb)
+  if (!a->a || !a->b || (!a->c && !a->c_peers) || !a->sfa || !a->sfb)
     return fail(B200K_INVALID_ARG, "null operand pointer");
   if (a->k == 0) return fail(B200K_UNSUPPORTED, "K == 0 is not supported");
 
@@ -836,6 +859,8 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
   const int64_t sfb_tile_bytes = a->sf_k_atoms * 512;
   const bool pair_grouped = grouped && a->tile_rows == 256 && !(swiglu && fp4) &&
                             a->stride_sfb % sfb_tile_bytes == 0;
+  if (int rc = set_c_peers(&p, a->c_peers, a->num_c_peers, a->c_peer_rows, pair_grouped, a->row_map, a->c_dtype))
+    return rc;
   // (256-row grouped tiles and quantised outputs exist on the pair kernel only: a request for
   // the one-CTA kernel is not honoured there)
   if ((pair_plain && (cfg.kernel != 1 || mx_out || nv_out)) || pair_grouped) {

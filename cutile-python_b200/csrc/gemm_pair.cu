@@ -338,13 +338,27 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int row = tc.pid_m * 256 + rank * 128 + quarter * 32 + lane;
       int64_t out_row = row;
       bool row_ok = row < p.m;
+      float scale = alpha;
+      uint8_t* c_base = static_cast<uint8_t*>(p.c);
       if (p.row_map != nullptr && row_ok) {
         out_row = p.row_map[row];
-        row_ok = out_row >= 0 && out_row < p.c_rows;
+        if (p.num_c_peers > 0) {
+          // the row belongs to buffer out_row / c_peer_rows (a peer's, or this GPU's own)
+          row_ok = out_row >= 0 && out_row < p.c_peer_rows * p.num_c_peers;
+          if (row_ok) {
+            const int64_t buf = out_row / p.c_peer_rows;
+            out_row -= buf * p.c_peer_rows;
+            c_base = static_cast<uint8_t*>(p.c_peers[buf]);
+            if (p.row_scale != nullptr) scale *= p.row_scale[row];
+          }
+        } else {
+          row_ok = out_row >= 0 && out_row < p.c_rows;
+          if (p.row_scale != nullptr && row_ok) scale *= p.row_scale[out_row];
+        }
+      } else if (p.row_scale != nullptr && row_ok) {
+        scale *= p.row_scale[out_row];
       }
-      float scale = alpha;
-      if (p.row_scale != nullptr && row_ok) scale *= p.row_scale[out_row];
-      uint8_t* c_row = static_cast<uint8_t*>(p.c) +
+      uint8_t* c_row = c_base +
                        out_bytes(static_cast<int64_t>(p.tile_group ? 0 : tc.batch) * p.stride_c + out_row * p.ldc);
       const uint32_t taddr = tmem_base + w * Cfg::kAccStride + (uint32_t(quarter * 32) << 16);
       // Columns shared with the other window first (the last chunks of window 0, the first

@@ -132,6 +132,17 @@ typedef struct {
   void* workspace;
   int64_t workspace_bytes;
   const b200k_gemm_config* config;  /* host pointer, read during the call; NULL = automatic */
+  /* Output rows scattered over several buffers (grouped problems on the CTA-pair kernel, i.e.
+   * tile_rows = 256, with row_map): `c_peers` is a host array of `num_c_peers` (<= 16) device
+   * pointers this process can store through - its own buffers or peer-mapped ones - each of
+   * `c_peer_rows` rows with leading dimension ldc.  row_map[i] = g then sends product row i to
+   * row g % c_peer_rows of c_peers[g / c_peer_rows] (dropped when g is outside
+   * [0, num_c_peers * c_peer_rows)), and row_scale is indexed by i.  This is the combine step
+   * of the expert-parallel MoE fused into the down projection: results leave the epilogue
+   * over NVLink to the rank their token came from.  `c` is ignored then.  NULL = off. */
+  const void* const* c_peers;
+  int32_t num_c_peers;
+  int64_t c_peer_rows;
 } b200k_gemm_args;
 
 int b200k_gemm(const b200k_gemm_args* args, b200k_stream stream);
@@ -196,6 +207,10 @@ typedef struct {
    * above (nvfp4_gemm_2_quantize_fp4.py:136-192,976-991 quantises to fp4 with a given global
    * scale). */
   const float* c_scale;
+  /* as in b200k_gemm_args */
+  const void* const* c_peers;
+  int32_t num_c_peers;
+  int64_t c_peer_rows;
 } b200k_block_scaled_gemm_args;
 
 int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* args, b200k_stream stream);
@@ -345,6 +360,87 @@ int b200k_peer_gather(const b200k_peer_gather_args* args, b200k_stream stream);
  * of the gather GEMM).  `shards` as in b200k_peer_gather_args. */
 int b200k_peer_scalar_expand(const void* const* shards, int32_t world, int64_t rows, float* out,
                              b200k_stream stream);
+
+/* ---- expert-parallel MoE (experts and tokens sharded over the ranks of one node) --------
+ * No counterpart in the reference, whose only multi-GPU code is the AllGather sample; the
+ * single-GPU pipeline these calls must reproduce is cutile_moe (samples/MoE.py:197-288).
+ * Per layer every rank runs: count -> barrier -> plan -> dispatch -> barrier -> the two
+ * grouped GEMMs on the rows it received (the second with c_peers) -> barrier -> b200k_topk_sum.
+ * Nothing is read back by the host; all "peers" arguments are host arrays of `world` device
+ * pointers this process can dereference (index = rank; its own buffer for its own rank).
+ *
+ * Layout of a rank's receive buffers (`capacity_rows` rows, see b200k_moe_ep_capacity_rows):
+ * the rank's experts one after the other, every expert's rows padded to whole `tile_rows`-row
+ * tiles, inside an expert the rows of source rank 0 first.  Row r carries meta[r] = source
+ * rank * replicas_per_rank + replica id (token * topk + slot) at the source, or -1 for a
+ * padding row, and weight[r], the replica's routing weight. */
+
+/* Rows a receive buffer needs in the worst case (all replicas of all ranks routed to one
+ * rank, every expert wasting tile_rows - 1 rows), a multiple of tile_rows. */
+int64_t b200k_moe_ep_capacity_rows(int64_t replicas_per_rank, int32_t world, int32_t num_experts,
+                                   int32_t tile_rows);
+
+/* hist_peers[p][rank * num_experts + e] = number of this rank's routing ids equal to e, for
+ * every rank p.  Ids outside [0, num_experts) are dropped and recorded in the status word. */
+typedef struct {
+  const void* topk_ids;            /* (num_replicas) int32 or int64 global expert ids */
+  int64_t num_replicas;            /* tokens * topk of this rank */
+  int32_t ids_are_int64;
+  int32_t num_experts;
+  int32_t world, rank;
+  void* scratch;                   /* (num_experts + 1) ints of device memory, zero before the first call */
+  const void* const* hist_peers;   /* every rank's table, (world, num_experts) int32 each */
+} b200k_moe_ep_count_args;
+int b200k_moe_ep_count(const b200k_moe_ep_count_args* args, b200k_stream stream);
+
+/* From the complete table `hist` (this rank's own copy, after a barrier): first_row[e] = row of
+ * the owner's receive buffer where this rank's rows for expert e start, cursor[e] = 0, and for
+ * the experts this rank owns tile_group (local expert per row tile), *num_row_tiles, and
+ * meta = -1 on the padding rows. */
+typedef struct {
+  const int32_t* hist;             /* (world, num_experts) */
+  int32_t world, rank, num_experts, tile_rows;
+  int64_t capacity_rows;
+  int64_t* first_row;              /* [num_experts] */
+  int32_t* cursor;                 /* [num_experts] */
+  int32_t* tile_group;             /* [capacity_rows / tile_rows] */
+  int32_t* num_row_tiles;          /* device scalar */
+  int32_t* meta;                   /* this rank's receive-buffer meta, [capacity_rows] */
+} b200k_moe_ep_plan_args;
+int b200k_moe_ep_plan(const b200k_moe_ep_plan_args* args, b200k_stream stream);
+
+/* Replica i (token i / topk) goes to the rank that owns expert topk_ids[i]: `row_bytes` of
+ * src row (i / topk) and, when aux_bytes > 0, `aux_bytes` of aux row (i / topk) (the scale
+ * bytes of a quantised row) are stored at row first_row[e] + cursor[e]++ of that rank's
+ * buffers, with meta and weight as described above. */
+typedef struct {
+  const void* topk_ids;
+  const float* weights;            /* (num_replicas) routing weights, NULL = 1 */
+  int64_t num_replicas;
+  int32_t topk, ids_are_int64, num_experts, world, rank;
+  const void* src;                 /* (tokens, row_bytes) with row stride src_stride_bytes */
+  int64_t src_stride_bytes, row_bytes;
+  const void* aux;
+  int64_t aux_stride_bytes, aux_bytes;
+  const int64_t* first_row;
+  int32_t* cursor;
+  int64_t capacity_rows;
+  void* const* row_peers;          /* (capacity_rows, row_bytes) each */
+  void* const* aux_peers;          /* (capacity_rows, aux_bytes) each */
+  void* const* meta_peers;         /* (capacity_rows) int32 each */
+  void* const* weight_peers;       /* (capacity_rows) fp32 each */
+} b200k_moe_ep_dispatch_args;
+int b200k_moe_ep_dispatch(const b200k_moe_ep_dispatch_args* args, b200k_stream stream);
+
+/* Barrier between the ranks of one node, as a kernel in stream order: everything the rank
+ * stored into peer memory before it is visible to a peer once that peer's barrier has
+ * passed.  flag_peers[p] = rank p's flag array (`world` int32, zero before the first call),
+ * *epoch_counter a device int32 of this rank (zero before the first call).  Every rank must
+ * launch the same sequence of barriers.  A rank that does not hear from a peer within
+ * budget_us (0 = two seconds) records role 60 in the status word and goes on.  One GPU per
+ * rank: ranks that share a GPU must not use it (their kernels need not run at the same time). */
+int b200k_peer_barrier(const void* const* flag_peers, int32_t world, int32_t rank,
+                       int32_t* epoch_counter, int32_t budget_us, b200k_stream stream);
 
 /* ---- attention forward ------------------------------------------------
  * Out = softmax(qk_scale * Q K^T + mask) V per (batch, head); replaces fmha_kernel
