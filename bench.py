@@ -1223,7 +1223,10 @@ def run_ours(args, w):
     # what the power cap sustains
     sustained = None
     if not args.kernel_only and args.sustain_s > 0:
-        n = int(min(2000 if use_graph else 20000, max(args.steps, args.sustain_s * 1e3 / max(ms, 1e-3))))
+        # every rank must run the same number of steps (the expert-parallel layers meet in
+        # barriers): size the loop from the slowest rank's burst time
+        ms_all = max_over_ranks([ms])[0]
+        n = int(min(2000 if use_graph else 20000, max(args.steps, args.sustain_s * 1e3 / max(ms_all, 1e-3))))
         sampler.start()
         ms_s = timed_steps(w, n, barrier, use_graph)
         sampler.stop()

@@ -167,10 +167,24 @@ def nvfp4_quantize(x: torch.Tensor, *, swizzled_scale: bool = True,
     return q, sf.view(torch.float8_e4m3fn), tensor_scale
 
 
+_SCALED_LAUNCHES = _lib.LaunchCache("b200k_block_scaled_gemm")
+
+
 def _scaled_gemm(a_km, sfa, b_nk, sfb, c, *, fp4: bool, alpha: float = 1.0, alpha_a=None,
                  alpha_b=None, max_ctas: int = 0, row_scale=None, c_sf=None, c_scale=None):
     """a_km (M, Kp), b_nk (N, Kp) K-contiguous byte tensors (Kp = K or K/2 bytes);
     sfa/sfb swizzled 4-D byte tensors."""
+    key = None
+    if not tune.in_use():
+        ptr = _lib.ptr
+        key = (a_km.data_ptr(), b_nk.data_ptr(), c.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), a_km.shape,
+               a_km.stride(), b_nk.shape, b_nk.stride(), c.stride(), sfa.shape, sfb.shape, a_km.dtype, c.dtype,
+               fp4, alpha, ptr(alpha_a), ptr(alpha_b), max_ctas, ptr(row_scale), ptr(c_sf),
+               None if c_sf is None else c_sf.shape, ptr(c_scale))
+        plan = _SCALED_LAUNCHES.get(key)
+        if plan is not None:
+            _SCALED_LAUNCHES.launch(plan, c.device)
+            return c
     m, kp = a_km.shape
     n = b_nk.shape[0]
     k = kp * 2 if fp4 else kp
@@ -202,6 +216,8 @@ def _scaled_gemm(a_km, sfa, b_nk, sfb, c, *, fp4: bool, alpha: float = 1.0, alph
         args.config = ctypes.pointer(c_cfg)
     with torch.cuda.device(c.device):
         _lib.check(_lib.lib().b200k_block_scaled_gemm(ctypes.byref(args), _lib.stream_ptr(c.device)))
+    if key is not None:
+        _SCALED_LAUNCHES.put(key, args)
     return c
 
 

@@ -34,9 +34,21 @@ def _pad_last(t: torch.Tensor) -> torch.Tensor:
     return buf[..., :cols]
 
 
+_GEMM_LAUNCHES = _lib.LaunchCache("b200k_gemm")
+
+
 def _gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, alpha: float = 1.0,
           max_ctas: int = 0) -> torch.Tensor:
     """a: (B, M, K) or (M, K); b: (B, K, N) or (K, N) as a view; c likewise (M, N)."""
+    key = None
+    if not tune.in_use():
+        key = (a.data_ptr(), b.data_ptr(), c.data_ptr(), a.shape, a.stride(), b.shape, b.stride(),
+               c.stride(), a.dtype, b.dtype, c.dtype, alpha, max_ctas)
+        plan = _GEMM_LAUNCHES.get(key)
+        if plan is not None:
+            _GEMM_LAUNCHES.launch(plan, c.device)
+            return c
+    copied = False
     batched = a.dim() == 3
     if not batched:
         a3, b3, c3 = a.unsqueeze(0), b.unsqueeze(0), c.unsqueeze(0)
@@ -49,7 +61,7 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, alpha: float = 1
 
     # A must be K-contiguous
     if a3.stride(2) != 1 or not _aligned(a3, a3.stride(1)) or (nb > 1 and (a3.stride(0) * a3.element_size()) % 16):
-        a3 = _pad_last(a3)
+        a3, copied = _pad_last(a3), True
     # B: (K, N) N-contiguous, or a transposed view of an (N, K) K-contiguous tensor.
     def rows_ok(t):
         return (t.stride(2) == 1 and _aligned(t, t.stride(1))
@@ -60,12 +72,12 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, alpha: float = 1
         layout = _lib.B_NK
         bt = b3.transpose(1, 2)
         if not rows_ok(bt):
-            bt = _pad_last(bt)
+            bt, copied = _pad_last(bt), True
         b3, ldb = bt, bt.stride(1)
     else:
         layout = _lib.B_KN
         if not rows_ok(b3):
-            b3 = _pad_last(b3)
+            b3, copied = _pad_last(b3), True
         ldb = b3.stride(1)
     if c3.stride(2) != 1:
         raise ValueError("output must be row-major")
@@ -95,6 +107,10 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, alpha: float = 1
                 workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
                 args.workspace, args.workspace_bytes = workspace.data_ptr(), ws_bytes
         _lib.check(_lib.lib().b200k_gemm(ctypes.byref(args), _lib.stream_ptr(a.device)))
+    # remembered for the next identical call, unless this one needed a repacked operand (whose
+    # contents are a copy) or scratch memory (which concurrent streams must not share)
+    if key is not None and not copied and workspace is None:
+        _GEMM_LAUNCHES.put(key, args)
     return c
 
 
@@ -181,49 +197,61 @@ def cutile_batch_matmul(bs: int, A: torch.Tensor, B: torch.Tensor, C: torch.Tens
 
 
 def cutile_group_matmul(As, Bs, Cs=None):
-    """Cs[g] = As[g] @ Bs[g] for a list of independent problems of any shapes
-    (grouped_matmul_kernel, test/kernels/group_gemm.py:10-38, which walks the tiles of all
-    problems with one persistent grid).  Here every problem is one launch of the GEMM;
-    problems too small to fill the GPU are spread over a few side streams so that they
-    overlap, and the caller's stream waits for all of them."""
+    """Cs[g] = As[g] @ Bs[g] for a list of independent problems of any shapes, in ONE persistent
+    launch that walks the tiles of all problems (grouped_matmul_kernel,
+    test/kernels/group_gemm.py:10-38).  The problems of a list share dtypes; lists that mix the
+    layout of B (row-major (K, N) and transposed views of (N, K) tensors), or hold more problems
+    than one launch takes, become one launch per layout and chunk.  Operands whose rows do not
+    start on 16-byte boundaries (TMA's rule) are repacked first."""
     if len(As) != len(Bs) or (Cs is not None and len(Cs) != len(As)):
         raise ValueError("As, Bs and Cs must list the same number of problems")
     if Cs is None:
         Cs = [torch.empty((a.shape[0], b.shape[1]), device=a.device, dtype=a.dtype) for a, b in zip(As, Bs)]
     if not As:
         return Cs
+    dev, ab_dtype, c_dtype = As[0].device, As[0].dtype, Cs[0].dtype
+    by_layout: dict[int, list] = {_lib.B_KN: [], _lib.B_NK: []}
+    keep = []
     for a, b, c in zip(As, Bs, Cs):
         _validate(a, b)
+        if a.dim() != 2 or b.dim() != 2:
+            raise ValueError("cutile_group_matmul expects 2-D operands")
         if c.shape != (a.shape[0], b.shape[1]):
             raise ValueError("output shape does not match its problem")
-    dev = As[0].device
-    main = torch.cuda.current_stream(dev)
-    small = [g for g, (a, b) in enumerate(zip(As, Bs))
-             if -(-a.shape[0] // 256) * -(-b.shape[1] // 256) < 64 and a.shape[0] and b.shape[1] and a.shape[1]]
-    side = _side_streams(dev, min(4, len(small))) if len(small) > 1 else []
-    for st in side:
-        st.wait_stream(main)
-    for i, (a, b, c) in enumerate(zip(As, Bs, Cs)):
-        if c.numel() == 0:
+        if a.dtype != ab_dtype or b.dtype != ab_dtype or c.dtype != c_dtype or a.device != dev:
+            raise TypeError("all problems of a list share operand dtype, output dtype and device")
+        if c.stride(1) != 1 and c.numel():
+            raise ValueError("output must be row-major")
+        m, k = a.shape
+        n = b.shape[1]
+        if m == 0 or n == 0:
             continue
-        if a.shape[1] == 0:
+        if k == 0:
             c.zero_()
             continue
-        if side and i in small:
-            with torch.cuda.stream(side[small.index(i) % len(side)]):
-                _gemm(a, b, c)
+        if a.stride(1) != 1 or not _aligned(a, a.stride(0)):
+            a = _pad_last(a)
+        if b.stride(0) == 1 and (b.stride(1) != 1 or n == 1):      # a transposed view of (N, K)
+            layout, bt = _lib.B_NK, b.T
+            if not _aligned(bt, bt.stride(0)):
+                bt = _pad_last(bt)
+            b, ldb = bt, bt.stride(0)
         else:
-            _gemm(a, b, c)
-    for st in side:
-        main.wait_stream(st)
+            layout = _lib.B_KN
+            if b.stride(1) != 1 or not _aligned(b, b.stride(0)):
+                b = _pad_last(b)
+            ldb = b.stride(0)
+        keep += [a, b]
+        by_layout[layout].append(_lib.GroupProblem(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k,
+                                                   a.stride(0), ldb, c.stride(0)))
+    lib = _lib.lib()
+    limit = lib.b200k_group_gemm_max_problems()
+    with torch.cuda.device(dev):
+        for layout, problems in by_layout.items():
+            for lo in range(0, len(problems), limit):
+                chunk = problems[lo:lo + limit]
+                table = (_lib.GroupProblem * len(chunk))(*chunk)
+                args = _lib.GroupGemmArgs(ctypes.cast(table, ctypes.POINTER(_lib.GroupProblem)), len(chunk),
+                                          _lib.dtype_enum(ab_dtype), _lib.dtype_enum(c_dtype), layout)
+                _lib.check(lib.b200k_group_gemm(ctypes.byref(args), _lib.stream_ptr(dev)))
     return Cs
-
-
-_SIDE_STREAMS: dict = {}
-
-
-def _side_streams(dev, n: int):
-    pool = _SIDE_STREAMS.setdefault(dev, [])
-    while len(pool) < n:
-        pool.append(torch.cuda.Stream(dev))
-    return pool[:n]

@@ -196,6 +196,45 @@ def _topk_sum(x: torch.Tensor, tokens: int, topk: int, hidden: int,
     return out
 
 
+def _sparse_routing(replicas: int, experts: int, hidden: int, inter: int, elem_bytes: int) -> bool:
+    """True where the routed experts hold about one token each (at most two replicas per expert
+    on average): a 128-row tile per expert would then be almost all padding, and streaming the
+    expert's weights once per replica is cheaper.  B200K_MOE_SPARSE=0 / 1 forces the choice."""
+    forced = os.environ.get("B200K_MOE_SPARSE")
+    fits = (replicas <= 65535 and hidden <= 12288 and inter <= 12288 and
+            (hidden * elem_bytes) % 16 == 0 and (inter * elem_bytes) % 16 == 0)
+    if forced in ("0", "1"):
+        return forced == "1" and fits
+    return fits and replicas <= 2 * experts
+
+
+def _moe_sparse(x, w1, w2, topk_weights, topk_ids) -> torch.Tensor:
+    """cutile_moe for sparse routing (b200k_moe_sparse): two kernels that stream each replica's
+    expert once, then the top-k sum."""
+    tokens, hidden = x.shape
+    experts, _, inter = w2.shape
+    topk = topk_ids.shape[1]
+    ids = topk_ids.contiguous()
+    if ids.dtype not in (torch.int32, torch.int64):
+        raise TypeError("topk_ids must be int32 or int64")
+    weights = topk_weights.reshape(-1).float().contiguous()
+    act = torch.empty((tokens * topk, inter), dtype=x.dtype, device=x.device)
+    per_replica = torch.empty((tokens * topk, hidden), dtype=x.dtype, device=x.device)
+    a = _lib.MoeSparseArgs()
+    a.hidden_states, a.w1, a.w2 = x.data_ptr(), w1.data_ptr(), w2.data_ptr()
+    a.topk_ids, a.topk_weights = ids.data_ptr(), weights.data_ptr()
+    a.act, a.per_replica = act.data_ptr(), per_replica.data_ptr()
+    a.tokens, a.hidden, a.intermediate = tokens, hidden, inter
+    a.hidden_stride = x.stride(0)
+    a.w1_stride_e, a.w1_ld, a.w2_stride_e, a.w2_ld = w1.stride(0), w1.stride(1), w2.stride(0), w2.stride(1)
+    a.topk, a.num_experts = topk, experts
+    a.ids_are_int64 = 1 if ids.dtype == torch.int64 else 0
+    a.dtype = _lib.dtype_enum(x.dtype)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().b200k_moe_sparse(ctypes.byref(a), _lib.stream_ptr(x.device)))
+    return _topk_sum(per_replica, tokens, topk, hidden)
+
+
 def _validate(hidden_states, w1, w2, topk_weights, topk_ids):
     if w1.shape[1] != w2.shape[2] * 2:
         raise ValueError("w1 must have 2 * intermediate_size rows (gate + up projection)")
@@ -221,6 +260,8 @@ def cutile_moe(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
         return torch.empty_like(hidden_states)
     x = hidden_states if hidden_states.stride(1) == 1 else hidden_states.contiguous()
     w1c, w2c = _check_weight(w1), _check_weight(w2)
+    if _sparse_routing(tokens * topk, experts, hidden, inter, x.element_size()):
+        return _moe_sparse(x, w1c, w2c, topk_weights, topk_ids)
 
     tile = _moe_tile(tokens * topk, experts)
     sorted_ids, expert_ids, num_blocks = moe_align_device(topk_ids, tile, experts)

@@ -111,6 +111,12 @@ def config_for(op: str, ab_dtype: int, c_dtype: int, layout: int, m: int, n: int
     return _db.get(key)
 
 
+def in_use() -> bool:
+    """True while this thread runs under an override or a database is installed: the GEMM
+    wrappers then look a config up per call instead of replaying a remembered launch."""
+    return _db is not None or getattr(_tls, "override", None) is not None
+
+
 def last_key() -> str | None:
     """Key of the last GEMM this thread issued under an override or with a database."""
     return getattr(_tls, "last_key", None)

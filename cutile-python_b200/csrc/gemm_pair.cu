@@ -91,6 +91,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
+  // Launched with programmatic stream serialisation: the kernel behind this one in the stream
+  // may be set up while this one runs, and this one's own set-up (barriers, tensor memory)
+  // overlaps the tail of the kernel before it.  Nothing below touches global memory before
+  // pdl_wait() has seen that kernel complete.
+  pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -117,6 +122,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
 
   // grouped mode: 256-row tiles, the live count comes from the device
   int tiles_m = (p.m + 255) / 256;
@@ -579,7 +585,9 @@ int launch_pair(const CUtensorMap* maps, const GemmParams& p, int grid, cudaStre
       return fail(B200K_CUDA_ERROR, "cudaFuncSetAttribute(%d bytes): %s", Cfg::kSmemBytes, cudaGetErrorString(e));
     configured[dev] = true;
   }
-  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+  cudaError_t e = launch_after_predecessor(kernel, dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream,
+                                           maps[0], maps[1], maps[2], maps[3], p);
+  if (e != cudaSuccess) return fail(B200K_CUDA_ERROR, "gemm (CTA pair) launch: %s", cudaGetErrorString(e));
   B200K_CHECK_LAUNCH("gemm (CTA pair) launch");
   return B200K_OK;
 }

@@ -154,6 +154,34 @@ int b200k_gemm(const b200k_gemm_args* args, b200k_stream stream);
  * second kernel. */
 int64_t b200k_gemm_workspace_bytes(const b200k_gemm_args* args);
 
+/* ---- grouped GEMM over a list of problems --------------------------------
+ * C_i = A_i . B_i for i < num_problems, every problem with its own sizes, in ONE persistent
+ * launch whose CTAs walk the output tiles of all problems with a running tile offset.
+ * Replaces grouped_matmul_kernel (reference: test/kernels/group_gemm.py:10-38, shapes of
+ * test/test_group_gemm.py:14-33).  All problems of a call share the operand type, the output
+ * type and the layout of B; at most b200k_group_gemm_max_problems() problems per call (the
+ * table travels in the kernel parameters: nothing is staged or allocated, and the call can be
+ * captured in a CUDA graph, which the reference's list arguments cannot).  Problems with
+ * m == 0 or n == 0 are skipped. */
+typedef struct {
+  const void* a;      /* (m, k), k contiguous, leading dimension lda */
+  const void* b;      /* per b_layout, leading dimension ldb */
+  void* c;            /* (m, n) row-major, leading dimension ldc */
+  int64_t m, n, k;
+  int64_t lda, ldb, ldc;   /* in elements */
+} b200k_group_problem;
+
+typedef struct {
+  const b200k_group_problem* problems;   /* host array, read during the call */
+  int32_t num_problems;
+  int32_t ab_dtype;   /* B200K_F16 | BF16 | F32 | E4M3 | E5M2 */
+  int32_t c_dtype;    /* B200K_F16 | BF16 | F32 */
+  int32_t b_layout;   /* b200k_b_layout */
+} b200k_group_gemm_args;
+
+int32_t b200k_group_gemm_max_problems(void);
+int b200k_group_gemm(const b200k_group_gemm_args* args, b200k_stream stream);
+
 /* ---- block-scaled GEMM ------------------------------------------------
  * C = alpha * (A (.) sA) . (B (.) sB), fp32 accumulation.  Replaces
  * block_scaled_matmul_kernel / ct.mma_scaled (reference:
@@ -337,6 +365,32 @@ int b200k_silu_and_mul(const void* ab, int64_t rows, int64_t n, int64_t ld_ab, v
 int b200k_topk_sum(const void* x, const int32_t* index, int64_t tokens, int32_t topk,
                    int64_t hidden, void* out, int32_t dtype, const void* expert_ids,
                    int32_t ids_are_int64, int32_t num_experts, b200k_stream stream);
+
+/* The MoE FFN for sparse routing - about one token per expert, the reference's second bench
+ * shape (test/bench_moe.py:16-19: 256 tokens x 1408 experts x top-6) - without the grouped
+ * GEMM: every token replica r = token * topk + slot streams the weights of its expert
+ * e = topk_ids[r] once,
+ *   act[r, i]         = silu(w1[e][i, :] . x[token]) * (w1[e][I + i, :] . x[token])
+ *   per_replica[r, h] = topk_weights[r] * (w2[e][h, :] . act[r, :])
+ * (fp32 accumulation, both results rounded to `dtype`), which replaces the gather, the two
+ * fused_moe_kernel launches and silu_and_mul_kernel of cutile_moe (samples/MoE.py:197-288)
+ * where their 128-row tiles would hold one real row each; b200k_topk_sum follows.  Replicas
+ * routed outside [0, num_experts) give zero rows.  At most 65535 replicas, hidden and
+ * intermediate at most 12288 and multiples of 16 bytes. */
+typedef struct {
+  const void* hidden_states;   /* (tokens, hidden), row stride hidden_stride (elements) */
+  const void* w1;              /* (experts, 2 * intermediate, hidden): w1_stride_e, w1_ld (elements) */
+  const void* w2;              /* (experts, hidden, intermediate): w2_stride_e, w2_ld (elements) */
+  const void* topk_ids;        /* (tokens, topk) int32 or int64 */
+  const float* topk_weights;   /* (tokens, topk) fp32, NULL = 1 */
+  void* act;                   /* scratch: (tokens * topk, intermediate), dense */
+  void* per_replica;           /* (tokens * topk, hidden), dense */
+  int64_t tokens, hidden, intermediate;
+  int64_t hidden_stride, w1_stride_e, w1_ld, w2_stride_e, w2_ld;
+  int32_t topk, num_experts, ids_are_int64;
+  int32_t dtype;               /* B200K_F16 | BF16 | F32, of activations and weights */
+} b200k_moe_sparse_args;
+int b200k_moe_sparse(const b200k_moe_sparse_args* args, b200k_stream stream);
 
 /* ---- peer-memory gather (AllGather GEMM) -------------------------------
  * dst rows [p * rows, (p + 1) * rows) = shard p, read through `shards[p]`, a pointer this

@@ -76,7 +76,8 @@ def test_ctypes_mirrors_match_the_header_layout(tmp_path):
     pairs = {"b200k_gemm_args": _lib.GemmArgs, "b200k_block_scaled_gemm_args": _lib.BlockScaledGemmArgs,
              "b200k_quantize_args": _lib.QuantizeArgs, "b200k_moe_align_args": _lib.MoeAlignArgs,
              "b200k_fmha_args": _lib.FmhaArgs, "b200k_peer_gather_args": _lib.PeerGatherArgs,
-             "b200k_gemm_config": _lib.GemmConfig, "b200k_moe_ep_count_args": _lib.MoeEpCountArgs,
+             "b200k_gemm_config": _lib.GemmConfig, "b200k_group_problem": _lib.GroupProblem,
+             "b200k_group_gemm_args": _lib.GroupGemmArgs, "b200k_moe_sparse_args": _lib.MoeSparseArgs, "b200k_moe_ep_count_args": _lib.MoeEpCountArgs,
              "b200k_moe_ep_plan_args": _lib.MoeEpPlanArgs, "b200k_moe_ep_dispatch_args": _lib.MoeEpDispatchArgs}
     lines = ["#include <stdio.h>", "#include <stddef.h>", '#include "b200k.h"', "int main(void) {"]
     for cname, mirror in pairs.items():

@@ -94,7 +94,7 @@ def test_batch_matmul_fp8_replays():
 
 def test_group_matmul_replays():
     # a list of problems (the reference's launch refuses list arguments under capture:
-    # test/test_cudagraph.py:60-75); the small ones fork onto side streams inside the capture
+    # test/test_cudagraph.py:60-75): one launch, its problem table carried in the kernel parameters
     shapes = [(128, 256, 512), (300, 200, 256), (64, 64, 64), (1024, 1024, 256)]
 
     def make():

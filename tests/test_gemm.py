@@ -137,6 +137,40 @@ def test_group_matmul_list_of_problems(dtype, mnk, device_ok):
         torch.testing.assert_close(c.float().cpu(), oracle.matmul_ref(a, b), **tol)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("mnk", [[(4, 4, 4)], [(2, 4, 4), (8, 6, 6), (12, 16, 8)]])
+def test_group_matmul_reference_test_shapes(dtype, mnk, device_ok):
+    # test/test_group_gemm.py:14-33 as they are: rows of 4 or 6 elements start off the 16-byte
+    # boundaries TMA needs, so the wrapper repacks them; tolerances of that test
+    As = [torch.rand(m, k, generator=torch.Generator().manual_seed(i)).to(dtype) for i, (m, n, k) in enumerate(mnk)]
+    Bs = [torch.rand(k, n, generator=torch.Generator().manual_seed(9 + i)).to(dtype) for i, (m, n, k) in enumerate(mnk)]
+    Cs = [torch.rand(m, n).to(dtype).cuda() for (m, n, k) in mnk]
+    out = b200k.cutile_group_matmul([a.cuda() for a in As], [b.cuda() for b in Bs], Cs)
+    tol = 5e-3 if dtype == torch.float32 else 1e-2      # fp32 operands multiply as (truncated) tf32 here
+    for a, b, c, c_in in zip(As, Bs, out, Cs):
+        assert c is c_in
+        torch.testing.assert_close(c.float().cpu(), oracle.matmul_ref(a, b), atol=tol, rtol=tol)
+
+
+def test_group_matmul_many_problems_mixed_layouts_and_empty_ones(device_ok):
+    # more problems than one launch takes, B given both row-major and as transposed views, a
+    # problem without rows and one without a reduction dimension
+    g = torch.Generator().manual_seed(77)
+    mnk = [(8 + 13 * i, 24 + 8 * (i % 7), 64 + 32 * (i % 5)) for i in range(60)] + [(0, 16, 32), (16, 24, 0)]
+    As = [torch.randn(m, k, generator=g).bfloat16() for m, n, k in mnk]
+    Bs = [torch.randn(k, n, generator=g).bfloat16() for m, n, k in mnk]
+    dev_b = [b.cuda() if i % 3 else b.T.contiguous().cuda().T for i, b in enumerate(Bs)]
+    Cs = b200k.cutile_group_matmul([a.cuda() for a in As], dev_b)
+    for a, b, c, (m, n, k) in zip(As, Bs, Cs, mnk):
+        assert c.shape == (m, n)
+        if m and k:
+            torch.testing.assert_close(c.float().cpu(), oracle.matmul_ref(a, b), atol=2e-3 * k ** 0.5 + 0.05, rtol=2e-2)
+        elif m:
+            assert float(c.abs().max()) == 0.0
+    with pytest.raises(TypeError, match="share"):
+        b200k.cutile_group_matmul([As[0].cuda(), As[1].cuda().half()], [Bs[0].cuda(), Bs[1].cuda().half()])
+
+
 def test_all_ones_known_answer(device_ok):
     # mma of all-ones tiles: every output equals K
     a = torch.ones(128, 448, dtype=torch.float16, device="cuda")

@@ -183,3 +183,44 @@ def test_cutile_moe_hidden_not_a_multiple_of_eight_elements(device_ok):
     x, w1, w2, tw, ids = _problem(64, 20, 4, 12, 2, 5, torch.float32)
     out = b200k.cutile_moe(x.cuda(), w1.cuda(), w2.cuda(), tw.cuda(), ids.cuda())
     torch.testing.assert_close(out.cpu(), oracle.moe_ref(x, w1, w2, tw, ids), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("tokens,hidden,experts,inter,topk", [
+    (256, 2048, 1408, 32, 6),      # the reference's sparse bench shape (test/bench_moe.py:16-19)
+    (8, 512, 64, 384, 8),          # a decode-sized batch over many experts
+    (5, 264, 40, 24, 3)])          # row lengths that are not powers of two
+def test_sparse_routing_path_matches_the_oracle_and_the_grouped_path(tokens, hidden, experts, inter, topk, dtype,
+                                                                    device_ok, monkeypatch):
+    x, w1, w2, tw, ids = _problem(tokens, hidden, experts, inter, topk, 17 + tokens, dtype)
+    dev = [t.cuda() for t in (x, w1, w2, tw, ids)]
+    monkeypatch.setenv("B200K_MOE_SPARSE", "1")
+    out = b200k.cutile_moe(*dev)
+    assert out.shape == x.shape and out.dtype == dtype
+    ref = oracle.moe_ref(x, w1, w2, tw, ids)
+    tol = {torch.float16: 5e-2, torch.bfloat16: 1e-1, torch.float32: 1e-2}[dtype]   # test/bench_moe.py:60-66
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=tol, atol=tol)
+    assert oracle.rel_frobenius(out, ref) < (1e-3 if dtype == torch.float32 else 2e-2)
+    # the automatic choice takes this path exactly where routing is sparse
+    from b200k import moe
+    monkeypatch.delenv("B200K_MOE_SPARSE")
+    assert moe._sparse_routing(256 * 6, 1408, 2048, 32, 2) and not moe._sparse_routing(110 * 4, 16, 1024, 512, 2)
+    if inter % 8 == 0 and hidden % 8 == 0:
+        monkeypatch.setenv("B200K_MOE_SPARSE", "0")
+        dense = b200k.cutile_moe(*dev)
+        torch.testing.assert_close(out.float(), dense.float(), rtol=tol, atol=tol)
+
+
+def test_sparse_routing_path_drops_entries_outside_the_expert_range(monkeypatch):
+    monkeypatch.setenv("B200K_MOE_SPARSE", "1")
+    x, w1, w2, tw, ids = _problem(40, 256, 64, 64, 2, 3)
+    bad = ids.clone()
+    bad[0, 0], bad[39, 1] = -3, 64
+    tw_eff = tw.clone()
+    tw_eff[(bad < 0) | (bad >= 64)] = 0
+    out = b200k.cutile_moe(x.cuda(), w1.cuda(), w2.cuda(), tw.cuda(), bad.cuda())
+    torch.cuda.synchronize()
+    code, info = b200k.device_status()
+    assert code != 0 and (info >> 8) & 0xff == 40
+    ref = oracle.moe_ref(x, w1, w2, tw_eff, bad.clamp(0, 63))
+    assert oracle.rel_frobenius(out, ref) < 2e-2
