@@ -1035,7 +1035,7 @@ class ClockSampler:
         0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting",
     }
 
-    def __init__(self, device, period_s=0.002):
+    def __init__(self, device, period_s=0.005):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self.period_s = period_s
         self._stop = threading.Event()
@@ -1199,16 +1199,25 @@ def run_ours(args, w):
         return t.tolist()
 
     import b200k
+
+    def check_device(phase):
+        """A device-side wait that gave up (status word) ends the run, naming the phase."""
+        torch.cuda.synchronize()
+        code, info = b200k.device_status()
+        if code != 0:
+            raise SystemExit(f"bench.py: rank {rank}: device-side wait gave up during '{phase}' "
+                             f"(role {(info >> 8) & 0xff}, detail {(info >> 16) & 0xffff})")
+
     warmup = max(3, args.warmup)
     w.setup(device)
     for _ in range(warmup):
         w.step()
     barrier()
-    b200k.raise_on_device_error()
+    check_device("warm-up")
     # the output is checked before it is timed
     parity = w.parity()
     barrier()
-    b200k.raise_on_device_error()
+    check_device("parity check")
 
     use_graph = (args.launch == "graph" or (args.launch == "auto" and bool(getattr(w, "cuda_graph", False)))) \
         and not distributed
@@ -1217,7 +1226,7 @@ def run_ours(args, w):
     ms = timed_steps(w, args.steps, barrier, use_graph)
     sampler.stop()
     clocks = sampler.summary()
-    b200k.raise_on_device_error()
+    check_device("timed steps")
 
     # the same loop for at least a second: the burst above runs at boost clocks, this one at
     # what the power cap sustains
@@ -1231,6 +1240,7 @@ def run_ours(args, w):
         ms_s = timed_steps(w, n, barrier, use_graph)
         sampler.stop()
         sustained = {"steps": n, "ms_per_step": ms_s, "clocks": sampler.summary()}
+        check_device("sustained loop")
 
     gather_us = w.gather_only_us() if hasattr(w, "gather_only_us") else None
 
@@ -1255,6 +1265,7 @@ def run_ours(args, w):
         ev1.record()
         barrier()
         ms_e2e = ev0.elapsed_time(ev1) / e2e_steps
+        check_device("end-to-end steps")
 
     # secondary record of the default workload: BASELINE config 2 (MXFP8 8192 cubed) on this GPU
     also = None
@@ -1266,7 +1277,7 @@ def run_ours(args, w):
         p2 = w2.parity()
         ms2 = timed_steps(w2, args.steps, barrier)
         also = (w2, p2, ms2)
-        b200k.raise_on_device_error()
+        check_device("secondary MXFP8 record")
 
     vals = [ms, ms_e2e, sustained["ms_per_step"] if sustained else 0.0, also[2] if also else 0.0,
             gather_us or 0.0]

@@ -35,7 +35,8 @@ class B200KError(RuntimeError):
 
 class GemmConfig(Structure):
     _fields_ = [("kernel", c_int32), ("tile_n", c_int32), ("epilogue_store", c_int32),
-                ("split_k", c_int32), ("wait_budget_us", c_int32), ("withhold_arrival", c_int32)]
+                ("split_k", c_int32), ("wait_budget_us", c_int32), ("withhold_arrival", c_int32),
+                ("programmatic_launch", c_int32)]
 
 
 class GemmArgs(Structure):
@@ -209,7 +210,7 @@ SIGNATURES = {
     "b200k_fmha_fwd": (c_int, [POINTER(FmhaArgs), c_void_p]),
     "b200k_fmha_workspace_bytes": (c_int64, [POINTER(FmhaArgs)]),
     "b200k_sf_swizzle": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int32,
-                                 c_void_p]),
+                                 c_void_p, c_int32, c_void_p]),
 }
 
 _lib = None

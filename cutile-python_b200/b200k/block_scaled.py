@@ -58,7 +58,7 @@ def swizzle_32_4_4(scale: torch.Tensor, fill: int | None = None) -> torch.Tensor
     if rows and kblocks:
         with torch.cuda.device(scale.device):
             _lib.check(_lib.lib().b200k_sf_swizzle(src.data_ptr(), rows, kblocks, src.stride(0),
-                                                   out.data_ptr(), shape[1], fill,
+                                                   out.data_ptr(), shape[1], fill, None, 0,
                                                    _lib.stream_ptr(scale.device)))
     return out.view(scale.dtype)
 

@@ -94,9 +94,11 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, alpha: float = 1
     args.alpha = alpha
     args.max_ctas = max_ctas
     cfg = tune.config_for("gemm", args.ab_dtype, args.c_dtype, layout, m, n, k, nb)
-    if cfg is not None:
-        c_cfg = cfg.to_c()                      # kept alive until the call has returned
-        args.config = ctypes.pointer(c_cfg)
+    # plain dense GEMMs launch programmatically: a chain of short ones on one stream then runs
+    # without launch gaps (2048 cubed fp16: 20.2 -> 18.0 us per call, the CUDA-graph figure)
+    c_cfg = cfg.to_c() if cfg is not None else _lib.GemmConfig()
+    c_cfg.programmatic_launch = 1
+    args.config = ctypes.pointer(c_cfg)         # kept alive with the remembered launch
     with torch.cuda.device(a.device):
         # a few output tiles with a long K: split-K over the idle SMs needs fp32 scratch
         workspace = None
@@ -110,7 +112,7 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, alpha: float = 1
     # remembered for the next identical call, unless this one needed a repacked operand (whose
     # contents are a copy) or scratch memory (which concurrent streams must not share)
     if key is not None and not copied and workspace is None:
-        _GEMM_LAUNCHES.put(key, args)
+        _GEMM_LAUNCHES.put(key, args, keep=(c_cfg,))
     return c
 
 

@@ -231,6 +231,7 @@ class ExpertParallelMoE:
             with torch.cuda.device(dev):
                 _lib.check(_lib.lib().b200k_sf_swizzle(own["aux"].data_ptr(), cap, kblocks, kblocks,
                                                        self.a_sf.data_ptr(), self.a_sf.shape[1], 127,
+                                                       self.num_row_tiles.data_ptr(), TILE,
                                                        _lib.stream_ptr(dev)))
             a_q = own["rows"].view(torch.float8_e4m3fn)
             moe._grouped_scaled_gemm(a_q, self.a_sf, self.w1, moe._as_u8(self.w1_sf), self.act, self.tile_group,

@@ -632,6 +632,7 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
   p.store_mode = cfg.epilogue_store;
   p.wait_budget_ns = cfg.wait_budget_us > 0 ? static_cast<uint64_t>(cfg.wait_budget_us) * 1000ull : 0;
   p.withhold_arrival = cfg.withhold_arrival;
+  p.programmatic_launch = cfg.programmatic_launch;
   const bool grouped = a->tile_group != nullptr;
   if (grouped) p.batch = 1;
 
@@ -811,6 +812,7 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
   p.store_mode = cfg.epilogue_store;
   p.wait_budget_ns = cfg.wait_budget_us > 0 ? static_cast<uint64_t>(cfg.wait_budget_us) * 1000ull : 0;
   p.withhold_arrival = cfg.withhold_arrival;
+  p.programmatic_launch = cfg.programmatic_launch;
   const bool grouped = a->tile_group != nullptr;
   if (grouped) p.batch = 1;
   const bool mx_out = a->c_dtype == B200K_E4M3;

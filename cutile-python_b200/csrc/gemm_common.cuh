@@ -58,6 +58,7 @@ struct GemmParams {
   // issuer is never made, so that issuer's wait runs out of its budget)
   uint64_t wait_budget_ns;
   int withhold_arrival;
+  int programmatic_launch;   // host side only: launch with programmatic stream serialisation
   // CTA-pair kernel, grouped: output rows scattered over up to 16 buffers (peer-mapped or
   // local); row_map values are then buffer * c_peer_rows + row
   int num_c_peers;

@@ -91,10 +91,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  // Launched with programmatic stream serialisation: the kernel behind this one in the stream
-  // may be set up while this one runs, and this one's own set-up (barriers, tensor memory)
-  // overlaps the tail of the kernel before it.  Nothing below touches global memory before
-  // pdl_wait() has seen that kernel complete.
+  // Where the caller asks for a programmatic launch (b200k_gemm_config): the kernel behind
+  // this one in the stream may be set up while this one runs, and this one's own set-up
+  // (barriers, tensor memory) overlaps the tail of the kernel before it.  Nothing below
+  // touches global memory before pdl_wait() has seen that kernel complete.  Both calls are
+  // no-ops under an ordinary launch.
   pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
@@ -585,9 +586,13 @@ int launch_pair(const CUtensorMap* maps, const GemmParams& p, int grid, cudaStre
       return fail(B200K_CUDA_ERROR, "cudaFuncSetAttribute(%d bytes): %s", Cfg::kSmemBytes, cudaGetErrorString(e));
     configured[dev] = true;
   }
-  cudaError_t e = launch_after_predecessor(kernel, dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream,
-                                           maps[0], maps[1], maps[2], maps[3], p);
-  if (e != cudaSuccess) return fail(B200K_CUDA_ERROR, "gemm (CTA pair) launch: %s", cudaGetErrorString(e));
+  if (!p.programmatic_launch) {
+    kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+  } else {
+    cudaError_t e = launch_after_predecessor(kernel, dim3(grid), dim3(Cfg::kThreads), Cfg::kSmemBytes, stream,
+                                             maps[0], maps[1], maps[2], maps[3], p);
+    if (e != cudaSuccess) return fail(B200K_CUDA_ERROR, "gemm (CTA pair) launch: %s", cudaGetErrorString(e));
+  }
   B200K_CHECK_LAUNCH("gemm (CTA pair) launch");
   return B200K_OK;
 }

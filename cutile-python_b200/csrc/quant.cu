@@ -236,7 +236,13 @@ mxfp8_quantize_kernel(const T* __restrict__ x, int64_t rows, int64_t k, int64_t 
 // One thread per 16 output bytes of the swizzled tensor (one row of an atom).
 __global__ void __launch_bounds__(256)
 sf_swizzle_kernel(const uint8_t* __restrict__ src, int64_t rows, int64_t kblocks, int64_t ld,
-                  uint8_t* __restrict__ dst, int64_t row_tiles, int64_t k_atoms, int fill) {
+                  uint8_t* __restrict__ dst, int64_t row_tiles, int64_t k_atoms, int fill,
+                  const int32_t* __restrict__ live_tiles, int live_tile_rows) {
+  // only the first *live_tiles * live_tile_rows rows are in use (a device-side count)
+  if (live_tiles != nullptr) {
+    const int64_t live = (static_cast<int64_t>(*live_tiles) * live_tile_rows + 127) / 128;
+    if (live < row_tiles) row_tiles = live;
+  }
   const int64_t total = row_tiles * k_atoms * 32;
   for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
        idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -465,7 +471,8 @@ extern "C" int b200k_mxfp8_quantize(const b200k_quantize_args* a, b200k_stream s
 }
 
 extern "C" int b200k_sf_swizzle(const void* sf, int64_t rows, int64_t kblocks, int64_t ld,
-                                void* out, int64_t k_atoms, int32_t fill, b200k_stream stream_) {
+                                void* out, int64_t k_atoms, int32_t fill, const int32_t* live_tiles,
+                                int32_t live_tile_rows, b200k_stream stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (rows < 0 || kblocks < 0) return fail(B200K_INVALID_ARG, "negative dimension");
   if (rows == 0 || kblocks == 0) return B200K_OK;
@@ -475,7 +482,8 @@ extern "C" int b200k_sf_swizzle(const void* sf, int64_t rows, int64_t kblocks, i
   const int64_t row_tiles = ceil_div(rows, 128);
   const int grid = grid_for(row_tiles * k_atoms * 32, 256);
   sf_swizzle_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(sf), rows, kblocks, ld,
-                                              static_cast<uint8_t*>(out), row_tiles, k_atoms, fill);
+                                              static_cast<uint8_t*>(out), row_tiles, k_atoms, fill,
+                                              live_tiles, live_tile_rows);
   B200K_CHECK_LAUNCH("sf_swizzle launch");
   return B200K_OK;
 }

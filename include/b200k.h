@@ -90,6 +90,12 @@ typedef struct {
    * tile to the second MMA issuer is never made (a flag that nothing sets), so its wait runs
    * out of the budget.  Nothing faults, traps or spins without limit. */
   int32_t withhold_arrival;
+  /* CTA-pair kernel: 1 = launch with programmatic stream serialisation, so that the kernel's
+   * set-up (barriers, tensor memory) overlaps the tail of the kernel before it in the stream
+   * and a chain of short GEMMs on one stream leaves no launch gaps (the kernel waits for its
+   * predecessor before it touches global memory).  0 = ordinary launch.  The Python wrappers
+   * set it for plain dense GEMMs. */
+  int32_t programmatic_launch;
 } b200k_gemm_config;
 
 /* ---- dense GEMM -------------------------------------------------------
@@ -312,9 +318,13 @@ int b200k_nvfp4_quantize_noalloc(const b200k_quantize_args* args, b200k_stream s
 
 /* Logical (rows, kblocks) scale bytes (row stride ld) -> swizzle_32_4_4 atoms; replaces
  * swizzle_32_4_4 (reference: test/kernels/kernel_utils.py:83-98).  Rows beyond `rows`
- * and blocks beyond `kblocks` inside the padded atoms are set to `fill`. */
+ * and blocks beyond `kblocks` inside the padded atoms are set to `fill`.  `live_tiles`
+ * (optional device scalar): only the first *live_tiles * live_tile_rows rows are converted,
+ * the rest of `out` is left as it is (worst-case-sized buffers whose live row count is only
+ * known on the device). */
 int b200k_sf_swizzle(const void* sf, int64_t rows, int64_t kblocks, int64_t ld, void* out,
-                     int64_t k_atoms, int32_t fill, b200k_stream stream);
+                     int64_t k_atoms, int32_t fill, const int32_t* live_tiles, int32_t live_tile_rows,
+                     b200k_stream stream);
 
 /* ---- mixture-of-experts plumbing ---------------------------------------
  * b200k_moe_align replaces moe_align_tile_size_torch (reference:
