@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload ag_nvfp4_gemm|mxfp8_gemm|nvfp4_gemm|dense_f16|fmha_causal|fmha_decode|
-                                moe_bf16|moe_mxfp8|moe_ep_bf16|moe_ep_mxfp8|mxfp8_quantize|nvfp4_quantize|
+                                moe_bf16|moe_mxfp8|moe_sparse|moe_ep_bf16|moe_ep_mxfp8|mxfp8_quantize|nvfp4_quantize|
                                 ref_shapes]
 
 One step = one pass of the workload's kernels over one batch of seeded synthetic input.  Inputs
@@ -602,6 +602,51 @@ class MoeMxfp8(MoeBf16):
     launches_per_step = 9
 
 
+class MoeSparse(MoeBf16):
+    """The reference's sparse MoE bench shape (test/bench_moe.py:16-19): 256 tokens, 1408 experts,
+    top-6, hidden 2048, intermediate 32 - about one token per expert.  Every replica streams
+    its expert's weights once on the CUDA cores: HBM-bound, the algorithmic bytes are the
+    routed experts' weights."""
+    name = "moe_ffn_sparse_256tok_h2048_e1408_i32_top6_bf16"
+    dtype = "bf16 x bf16 -> fp32 accumulate -> bf16 (CUDA cores)"
+    bound = "hbm"
+    T, H, E, I, K = 256, 2048, 1408, 32, 6
+    seed = 6
+    launches_per_step = 3
+    cuda_graph = True
+
+    def flops(self):
+        return float(self.algorithmic_bytes())
+
+    def algorithmic_bytes(self):
+        # per replica the expert's W1 and W2 once, its token in, its row out and back in for the sum
+        return self.T * self.K * (3 * self.I * self.H * 2 + 3 * self.H * 2) + self.T * self.H * 2
+
+    def cpu_setup(self):
+        import oracle
+        x, tw, ids = self.draw_tokens()
+        t = 64
+        used = sorted(set(ids[:t].reshape(-1).tolist()))
+        remap = {e: i for i, e in enumerate(used)}
+        w = [_expert_weights(self.seed, e, self.I, self.H) for e in used]
+        self.cpu_ops = (x[:t].float(), torch.stack([a for a, _ in w]).float(), torch.stack([b for _, b in w]).float())
+        self.cpu_route = (tw[:t].float(), torch.tensor([[remap[int(e)] for e in row] for row in ids[:t]]))
+        self.oracle = oracle
+
+    def cpu_flops(self, s):
+        return float(s * self.K * 3 * self.I * self.H * 2)
+
+    def cpu_sample_desc(self, s):
+        return f"the first {s} tokens of the same problem through torch_moe's restatement in fp32 (torch CPU)"
+
+    cpu_limit = 64
+
+    def config(self):
+        c = super().config()
+        c["l2"] = "the routed experts' weights are 0.6 GB per step (> 126 MiB L2)"
+        return c
+
+
 class MoeEpBf16(MoeBf16):
     """BASELINE config 5 expert-parallel: experts E / world and tokens T / world per rank, an
     NVLink exchange for dispatch and one for combine.  The whole problem is fixed, so this
@@ -1020,7 +1065,7 @@ class DenseF16(Workload):
 
 WORKLOADS = {"ag_nvfp4_gemm": AgNvfp4Gemm, "mxfp8_gemm": Mxfp8Gemm, "nvfp4_gemm": Nvfp4Gemm,
              "dense_f16": DenseF16, "fmha_causal": FmhaCausal, "fmha_decode": FmhaDecode,
-             "moe_bf16": MoeBf16, "moe_mxfp8": MoeMxfp8, "moe_ep_bf16": MoeEpBf16,
+             "moe_bf16": MoeBf16, "moe_mxfp8": MoeMxfp8, "moe_sparse": MoeSparse, "moe_ep_bf16": MoeEpBf16,
              "moe_ep_mxfp8": MoeEpMxfp8, "mxfp8_quantize": Mxfp8Quantize, "nvfp4_quantize": Nvfp4Quantize}
 DEFAULT_WORKLOAD = "ag_nvfp4_gemm"
 

@@ -281,16 +281,28 @@ topk_sum_kernel(const uint16_t* __restrict__ x, const int* __restrict__ index, i
     const int64_t t = idx / vecs;
     const int64_t v = idx - t * vecs;
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int j = 0; j < topk; ++j) {
-      if (!filter.live(t * topk + j)) continue;
-      const int64_t src = index != nullptr ? index[t * topk + j] : t * topk + j;
-      const uint4 q = *reinterpret_cast<const uint4*>(x + src * h + v * 8);
-      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    // eight slots at a time: their loads are issued together (a zero vector stands in for a
+    // slot that is absent or dropped), then summed in slot order
+    for (int j0 = 0; j0 < topk; j0 += 8) {
+      uint4 q[8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = unpack2<BF16>(w[i]);
-        acc[2 * i] += f.x;
-        acc[2 * i + 1] += f.y;
+      for (int u = 0; u < 8; ++u) {
+        const int j = j0 + u;
+        q[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (j < topk && filter.live(t * topk + j)) {
+          const int64_t src = index != nullptr ? index[t * topk + j] : t * topk + j;
+          q[u] = *reinterpret_cast<const uint4*>(x + src * h + v * 8);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = unpack2<BF16>(w[i]);
+          acc[2 * i] += f.x;
+          acc[2 * i + 1] += f.y;
+        }
       }
     }
     uint4 o;

@@ -74,28 +74,36 @@ ep_count_kernel(const IdT* __restrict__ ids, int64_t total, int experts, int32_t
   if (threadIdx.x == 0) *ticket = 0;
 }
 
+// One warp per expert (the lanes compute the same few sums, then share the stores: up to a
+// tile of padding marks and the expert's tile list).
 __global__ void __launch_bounds__(1024)
 ep_plan_kernel(const int32_t* __restrict__ hist, int world, int rank, int experts, int tile,
                int64_t capacity_rows, int64_t* __restrict__ first_row, int32_t* __restrict__ cursor,
                int32_t* __restrict__ tile_group, int32_t* __restrict__ num_row_tiles,
                int32_t* __restrict__ meta, int* status) {
   const int local = experts / world;
-  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-    first_row[e] = ep_first_row(hist, world, experts, local, tile, rank, e);
-    cursor[e] = 0;
+  const int lane = threadIdx.x & 31;
+  for (int e = threadIdx.x >> 5; e < experts; e += blockDim.x >> 5) {
+    const int64_t start = ep_tile_start(hist, world, experts, local, tile, e);
+    if (lane == 0) {
+      first_row[e] = start * tile + ep_before(hist, experts, rank, e);
+      cursor[e] = 0;
+    }
     if (ep_owner(e, local) != rank) continue;
     // an expert this rank owns: its row tiles, and the padding rows behind its last real row
     const int64_t total = ep_total(hist, world, experts, e);
     const int64_t tiles = ep_tiles(total, tile);
-    const int64_t start = ep_tile_start(hist, world, experts, local, tile, e);
+    const bool last = e == (rank + 1) * local - 1;
     if ((start + tiles) * tile > capacity_rows) {
-      report_status(status, 61, e);   // more rows than the receive buffer holds: plan nothing
-      if (e == (rank + 1) * local - 1) *num_row_tiles = 0;
+      if (lane == 0) {
+        report_status(status, 61, e);   // more rows than the receive buffer holds: plan nothing
+        if (last) *num_row_tiles = 0;
+      }
       continue;
     }
-    for (int64_t t = 0; t < tiles; ++t) tile_group[start + t] = e - rank * local;
-    for (int64_t r = start * tile + total; r < (start + tiles) * tile; ++r) meta[r] = -1;
-    if (e == (rank + 1) * local - 1) *num_row_tiles = static_cast<int32_t>(start + tiles);
+    for (int64_t t = lane; t < tiles; t += 32) tile_group[start + t] = e - rank * local;
+    for (int64_t r = start * tile + total + lane; r < (start + tiles) * tile; r += 32) meta[r] = -1;
+    if (last && lane == 0) *num_row_tiles = static_cast<int32_t>(start + tiles);
   }
 }
 
@@ -128,7 +136,21 @@ ep_dispatch_kernel(const IdT* __restrict__ ids, const float* __restrict__ weight
     const int64_t token = i / topk;
     const uint4* s = reinterpret_cast<const uint4*>(src + token * src_stride);
     uint4* dst = reinterpret_cast<uint4*>(peers.rows[d] + r * row_bytes);
-    for (int v = lane; v < row_bytes / 16; v += 32) dst[v] = s[v];
+    // eight 16-byte vectors per lane in flight (a 4 KB row in one round)
+    const int nv = row_bytes / 16;
+    for (int v0 = 0; v0 < nv; v0 += 256) {
+      uint4 t[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int v = v0 + u * 32 + lane;
+        if (v < nv) t[u] = s[v];
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int v = v0 + u * 32 + lane;
+        if (v < nv) dst[v] = t[u];
+      }
+    }
     if (aux_bytes > 0) {
       const uint4* sa = reinterpret_cast<const uint4*>(aux + token * aux_stride);
       uint4* da = reinterpret_cast<uint4*>(peers.aux[d] + r * aux_bytes);
