@@ -36,7 +36,7 @@ class B200KError(RuntimeError):
 class GemmConfig(Structure):
     _fields_ = [("kernel", c_int32), ("tile_n", c_int32), ("epilogue_store", c_int32),
                 ("split_k", c_int32), ("wait_budget_us", c_int32), ("withhold_arrival", c_int32),
-                ("programmatic_launch", c_int32)]
+                ("programmatic_launch", c_int32), ("group_m", c_int32)]
 
 
 class GemmArgs(Structure):

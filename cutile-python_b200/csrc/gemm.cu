@@ -717,6 +717,7 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
     const int bn = (want_bn == 128 && pair_plain && !(b_mn && elem_bytes == 1)) ? 128 : 256;
     pp.pair_bn = bn;
     pp.b_mn = b_mn ? 1 : 0;
+    pp.group_m = grouped ? kGroupM : pick_group_m(a->m, a->lda * elem_bytes, cfg.group_m);
     pp.tiles_n = static_cast<int>(ceil_div(a->n, bn));
     pp.idesc = make_idesc(fmt, fmt, false, b_mn, 256, bn);
     CUtensorMap tbp = tb;
@@ -869,6 +870,7 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
     GemmParams pp = p;
     pp.idesc = make_idesc_block_scaled(fmt, fmt, 256, BN, /*ue8m0=*/!fp4, 0, 0);
     pp.sfb_group_tiles = grouped ? static_cast<int>(a->stride_sfb / sfb_tile_bytes) : 0;
+    pp.group_m = grouped ? kGroupM : pick_group_m(a->m, lda_b + a->sf_k_atoms * 4, cfg.group_m);
     CUtensorMap tsa, tsb;
     const uint32_t atoms = fp4 ? 4 : 1;
     const uint64_t ka = static_cast<uint64_t>(a->sf_k_atoms);

@@ -59,6 +59,7 @@ struct GemmParams {
   uint64_t wait_budget_ns;
   int withhold_arrival;
   int programmatic_launch;   // host side only: launch with programmatic stream serialisation
+  int group_m;               // CTA-pair kernel: row tiles per raster band
   // CTA-pair kernel, grouped: output rows scattered over up to 16 buffers (peer-mapped or
   // local); row_map values are then buffer * c_peer_rows + row
   int num_c_peers;
@@ -115,21 +116,40 @@ struct TileCoord {
   int batch, pid_m, pid_n;
 };
 
-// Grouped raster order: consecutive tile ids walk kGroupM row tiles before moving to
-// the next column tile, which keeps a band of A and one B tile hot in L2.
-__device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles_n) {
+// Grouped raster order: consecutive tile ids walk `group_m` row tiles before moving to
+// the next column tile, which keeps a band of A and one B tile hot in L2 (the reference's
+// GROUP_SIZE_M = 8, test/kernels/matmul.py:13-23; here the band height is a launch parameter,
+// chosen from the operand sizes: see pick_group_m).
+__device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles_n, int group_m = kGroupM) {
   int per_batch = tiles_m * tiles_n;
   TileCoord c;
   c.batch = tile / per_batch;
   int t = tile - c.batch * per_batch;
-  int group_tiles = kGroupM * tiles_n;
+  int group_tiles = group_m * tiles_n;
   int group = t / group_tiles;
-  int first_m = group * kGroupM;
-  int rows = min(kGroupM, tiles_m - first_m);
+  int first_m = group * group_m;
+  int rows = min(group_m, tiles_m - first_m);
   int in_group = t - group * group_tiles;
   c.pid_m = first_m + in_group % rows;
   c.pid_n = in_group / rows;
   return c;
+}
+
+// Band height of the raster for the CTA-pair kernel: as many 256-row tiles of A as fit a
+// quarter of the L2 (with their scale factors), at least the reference's 8.  Every band
+// re-reads B once, so a taller band cuts B's traffic from DRAM: NVFP4 8192 x 28672 x 8192
+// holds all of A (36 MB) and reads B once instead of four times.
+inline int pick_group_m(int64_t m, int64_t a_row_bytes, int forced) {
+  if (forced > 0) return forced;
+  const int64_t tile_bytes = 256 * a_row_bytes;
+  const int64_t budget = 40ll << 20;
+  int64_t g = tile_bytes > 0 ? budget / tile_bytes : kGroupM;
+  if (g < kGroupM) g = kGroupM;
+  const int64_t tiles_m = (m + 255) / 256;
+  if (g >= tiles_m) return static_cast<int>(tiles_m > 0 ? tiles_m : 1);
+  const int64_t bands = (tiles_m + g - 1) / g;      // bands of equal height
+  g = (tiles_m + bands - 1) / bands;
+  return static_cast<int>(g);
 }
 
 template <int OUT>

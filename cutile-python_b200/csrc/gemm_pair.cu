@@ -143,7 +143,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t it = 0;
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
+        const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n, p.group_m);
         int group = tc.batch, a_batch = tc.batch;
         if (p.tile_group != nullptr) {
           group = p.tile_group[tc.pid_m];
@@ -217,7 +217,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       if (q >= p.k_iters) ok = false;   // a single k-step: nothing for the second issuer
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        if (p.tile_group != nullptr && p.tile_group[tile_coord(tile, tiles_m, p.tiles_n).pid_m] < 0) continue;
+        if (p.tile_group != nullptr && p.tile_group[tile_coord(tile, tiles_m, p.tiles_n, p.group_m).pid_m] < 0) continue;
         const int w = lt & 1;
         if (!mbar_wait(acc_empty_bar(w), ((lt >> 1) & 1) ^ 1, abort_flag, p.wait_budget_ns)) {
           report_status(p.status, 52, 100 + w);
@@ -333,7 +333,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t lead_ovl = map_to_cta(ovl_free_bar, 0);
     uint32_t lt = 0;
     for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
-      const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n);
+      const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n, p.group_m);
       if (p.tile_group != nullptr && p.tile_group[tc.pid_m] < 0) continue;
       const int w = lt & 1;
       if (!mbar_wait_relaxed(acc_full_bar(w), (lt >> 1) & 1, abort_flag, 64, p.wait_budget_ns)) {
@@ -621,6 +621,7 @@ int launch_gemm_pair(int kind, int out_dtype, const CUtensorMap* maps, const Gem
   GemmParams p = p_in;
   if (p.pair_bn != 128) p.pair_bn = 256;
   if (p.wait_budget_ns == 0) p.wait_budget_ns = kWaitBudgetNs;
+  if (p.group_m <= 0) p.group_m = kGroupM;
   // Stores staged through shared memory unless the caller asks for the direct form: direct
   // stores take about 8000 cycles per tile (16-bit output; twice the store instructions for
   // fp32) against about 530 per k-step, which decides short-K problems, and measured on

@@ -96,6 +96,10 @@ typedef struct {
    * predecessor before it touches global memory).  0 = ordinary launch.  The Python wrappers
    * set it for plain dense GEMMs. */
   int32_t programmatic_launch;
+  /* CTA-pair kernel, plain problems: 256-row tiles of A per band of the tile raster (the
+   * reference's GROUP_SIZE_M, test/kernels/matmul.py:13-23).  0 = from the operand sizes: as
+   * many as fit a quarter of the L2, at least 8. */
+  int32_t group_m;
 } b200k_gemm_config;
 
 /* ---- dense GEMM -------------------------------------------------------

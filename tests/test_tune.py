@@ -88,7 +88,7 @@ def test_config_validation_and_c_mirror():
     cfg = tune.GemmConfig(kernel=2, tile_n=128, epilogue_store=2, split_k=1)
     c = cfg.to_c()
     assert (c.kernel, c.tile_n, c.epilogue_store, c.split_k) == (2, 128, 2, 1)
-    assert ctypes.sizeof(c) == 28 and (c.wait_budget_us, c.withhold_arrival, c.programmatic_launch) == (0, 0, 0)
+    assert ctypes.sizeof(c) == 32 and (c.wait_budget_us, c.withhold_arrival, c.programmatic_launch) == (0, 0, 0)
     assert tune.GemmConfig.from_dict({"kernel": 1}) == tune.GemmConfig(kernel=1)
     for bad in (dict(kernel=3), dict(tile_n=64), dict(epilogue_store=5), dict(split_k=-1)):
         with pytest.raises(ValueError):
