@@ -1491,9 +1491,9 @@ def run_ref_shapes(args):
 # from one ncu capture of that kernel (None until captured).  The two AllGather / plain NVFP4
 # entries are the same kernel on the same problem.
 TRAFFIC_BYTES: dict[str, float | None] = {
-    "mxfp8_gemm_8192x8192x8192_bf16out": 477.0e6,
-    "nvfp4_gemm_8192x28672x8192_bf16out": 1007.0e6,
-    "allgather_nvfp4_gemm_8192x28672x8192_bf16out": 1007.0e6,
+    "mxfp8_gemm_8192x8192x8192_bf16out": 377.0e6,
+    "nvfp4_gemm_8192x28672x8192_bf16out": 726.0e6,
+    "allgather_nvfp4_gemm_8192x28672x8192_bf16out": 726.0e6,
     "fmha_causal_bf16_b4_h32_s8192_d128": 1066.0e6,
     "mxfp8_quantize_bf16_8192x8192": 173.0e6,
     "dense_f16_gemm_2048x2048x2048": 16.8e6,
