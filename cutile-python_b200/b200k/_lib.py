@@ -53,6 +53,7 @@ class GemmArgs(Structure):
         ("workspace", c_void_p), ("workspace_bytes", c_int64),
         ("config", POINTER(GemmConfig)),
         ("c_peers", POINTER(c_void_p)), ("num_c_peers", c_int32), ("c_peer_rows", c_int64),
+        ("skip_rows_begin", c_int64), ("skip_rows_count", c_int64),
     ]
 
 
@@ -84,6 +85,7 @@ class BlockScaledGemmArgs(Structure):
         ("config", POINTER(GemmConfig)),
         ("c_scale", c_void_p),
         ("c_peers", POINTER(c_void_p)), ("num_c_peers", c_int32), ("c_peer_rows", c_int64),
+        ("skip_rows_begin", c_int64), ("skip_rows_count", c_int64),
     ]
 
 

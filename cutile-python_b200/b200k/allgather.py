@@ -171,6 +171,8 @@ class Nvfp4GatherMatmul:
         self.sf_own = _as_u8(a_sf)
         self.side = torch.cuda.Stream(dev)
         self.gathered = torch.cuda.Event()
+        # whole 256-row tiles per rank: the other ranks' rows go through one GEMM launch
+        self.one_remote_launch = self.m % 256 == 0
 
     def gather(self):
         peer_gather(self.q_peers, self.rank, out=self.q)
@@ -205,11 +207,17 @@ class Nvfp4GatherMatmul:
             main.wait_event(self.gathered)
             tiles = self.sf_shape[0]       # 128-row scale tiles per rank
             sf = self.sf.reshape(world * tiles, *self.sf_shape[1:])
-            for lo, hi in ((0, rank), (rank + 1, world)):
-                if hi > lo:
-                    _scaled_gemm(self.q[lo * m:hi * m], sf[lo * tiles:hi * tiles], wq, wsf,
-                                 out[lo * m:hi * m], fp4=True, alpha_b=w_ts,
-                                 row_scale=self.row_scale[lo * m:hi * m])
+            if self.one_remote_launch:
+                # every other rank's rows in one launch over the gathered A: the row tiles of
+                # this rank's own shard are left out of the raster
+                _scaled_gemm(self.q, sf, wq, wsf, out, fp4=True, alpha_b=w_ts, row_scale=self.row_scale,
+                             skip_rows=(rank * m, m))
+            else:
+                for lo, hi in ((0, rank), (rank + 1, world)):
+                    if hi > lo:
+                        _scaled_gemm(self.q[lo * m:hi * m], sf[lo * tiles:hi * tiles], wq, wsf,
+                                     out[lo * m:hi * m], fp4=True, alpha_b=w_ts,
+                                     row_scale=self.row_scale[lo * m:hi * m])
         return out
 
 

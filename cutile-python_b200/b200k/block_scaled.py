@@ -171,16 +171,18 @@ _SCALED_LAUNCHES = _lib.LaunchCache("b200k_block_scaled_gemm")
 
 
 def _scaled_gemm(a_km, sfa, b_nk, sfb, c, *, fp4: bool, alpha: float = 1.0, alpha_a=None,
-                 alpha_b=None, max_ctas: int = 0, row_scale=None, c_sf=None, c_scale=None):
+                 alpha_b=None, max_ctas: int = 0, row_scale=None, c_sf=None, c_scale=None,
+                 skip_rows: tuple[int, int] = (0, 0)):
     """a_km (M, Kp), b_nk (N, Kp) K-contiguous byte tensors (Kp = K or K/2 bytes);
-    sfa/sfb swizzled 4-D byte tensors."""
+    sfa/sfb swizzled 4-D byte tensors.  ``skip_rows`` = (first, count): rows of A / C left out
+    of the product (whole 256-row tiles)."""
     key = None
     if not tune.in_use():
         ptr = _lib.ptr
         key = (a_km.data_ptr(), b_nk.data_ptr(), c.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), a_km.shape,
                a_km.stride(), b_nk.shape, b_nk.stride(), c.stride(), sfa.shape, sfb.shape, a_km.dtype, c.dtype,
                fp4, alpha, ptr(alpha_a), ptr(alpha_b), max_ctas, ptr(row_scale), ptr(c_sf),
-               None if c_sf is None else c_sf.shape, ptr(c_scale))
+               None if c_sf is None else c_sf.shape, ptr(c_scale), skip_rows)
         plan = _SCALED_LAUNCHES.get(key)
         if plan is not None:
             _SCALED_LAUNCHES.launch(plan, c.device)
@@ -208,6 +210,7 @@ def _scaled_gemm(a_km, sfa, b_nk, sfb, c, *, fp4: bool, alpha: float = 1.0, alph
     args.alpha_b = _lib.ptr(alpha_b)
     args.max_ctas = max_ctas
     args.row_scale = _lib.ptr(row_scale)
+    args.skip_rows_begin, args.skip_rows_count = skip_rows
     if c_sf is not None:
         args.c_sf, args.c_sf_k_atoms = c_sf.data_ptr(), c_sf.shape[1]
     cfg = tune.config_for("block_scaled_gemm", args.ab_dtype, args.c_dtype, _lib.B_NK, m, n, k, 1)

@@ -543,6 +543,20 @@ int set_c_peers(GemmParams* p, const void* const* c_peers, int32_t n, int64_t ro
   return B200K_OK;
 }
 
+// Rows left out of a plain product on the CTA-pair kernel (whole 256-row tiles).
+int set_skip_rows(GemmParams* p, int64_t begin, int64_t count, int64_t m, bool plain_pair_single) {
+  if (count == 0) return B200K_OK;
+  if (!plain_pair_single)
+    return fail(B200K_UNSUPPORTED, "skip_rows needs a plain problem (no groups, batch 1, store epilogue) on the "
+                "CTA-pair kernel");
+  if (begin < 0 || count < 0 || begin % 256 || count % 256 || begin + count > m)
+    return fail(B200K_INVALID_ARG, "skip_rows [%lld, +%lld) must be whole 256-row tiles inside M = %lld",
+                static_cast<long long>(begin), static_cast<long long>(count), static_cast<long long>(m));
+  p->skip_tile0 = static_cast<int>(begin / 256);
+  p->skip_tiles = static_cast<int>(count / 256);
+  return B200K_OK;
+}
+
 // The caller's b200k_gemm_config, or, where it leaves a choice open, the process-wide
 // diagnostic switches: B200K_SINGLE_CTA=1 (one-CTA kernels), B200K_PAIR_BN=128 (narrow
 // pair tiles), B200K_EPILOGUE=c|d (staged / direct stores).
@@ -662,7 +676,8 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
   if (a->max_ctas > 0 && grid > a->max_ctas) grid = a->max_ctas;
 
   const int out = a->c_dtype;
-  if (!grouped && a->epilogue == B200K_EPI_STORE && a->row_map == nullptr && a->workspace != nullptr) {
+  if (!grouped && a->epilogue == B200K_EPI_STORE && a->row_map == nullptr && a->workspace != nullptr &&
+      a->skip_rows_count == 0) {
     // a caller that asks for the CTA-pair kernel gets no split (the split kernel is one-CTA)
     const SplitPlan plan = plan_split_k(a->m, a->n, a->batch, p.k_iters, sms,
                                         cfg.kernel == 2 && cfg.split_k == 0 ? 1 : cfg.split_k);
@@ -717,6 +732,8 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
     const int bn = (want_bn == 128 && pair_plain && !(b_mn && elem_bytes == 1)) ? 128 : 256;
     pp.pair_bn = bn;
     pp.b_mn = b_mn ? 1 : 0;
+    if (int rc = set_skip_rows(&pp, a->skip_rows_begin, a->skip_rows_count, a->m, pair_plain && a->batch == 1))
+      return rc;
     pp.group_m = grouped ? kGroupM : pick_group_m(a->m, a->lda * elem_bytes, cfg.group_m);
     pp.tiles_n = static_cast<int>(ceil_div(a->n, bn));
     pp.idesc = make_idesc(fmt, fmt, false, b_mn, 256, bn);
@@ -730,6 +747,7 @@ extern "C" int b200k_gemm(const b200k_gemm_args* a, b200k_stream stream_) {
     const CUtensorMap maps[4] = {ta, tbp, ta, ta};
     return launch_gemm_pair(kind, out, maps, pp, sms, stream);
   }
+  if (int rc = set_skip_rows(&p, a->skip_rows_begin, a->skip_rows_count, a->m, false)) return rc;
   if (grouped && a->tile_rows != 0 && a->tile_rows != 128)
     return fail(B200K_UNSUPPORTED, "tile_rows %d: 256-row tiles need B stored (N, K) and the CTA-pair "
                 "kernels, otherwise tile_group entries are per 128 rows", a->tile_rows);
@@ -870,6 +888,7 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
     GemmParams pp = p;
     pp.idesc = make_idesc_block_scaled(fmt, fmt, 256, BN, /*ue8m0=*/!fp4, 0, 0);
     pp.sfb_group_tiles = grouped ? static_cast<int>(a->stride_sfb / sfb_tile_bytes) : 0;
+    if (int rc = set_skip_rows(&pp, a->skip_rows_begin, a->skip_rows_count, a->m, pair_plain)) return rc;
     pp.group_m = grouped ? kGroupM : pick_group_m(a->m, lda_b + a->sf_k_atoms * 4, cfg.group_m);
     CUtensorMap tsa, tsb;
     const uint32_t atoms = fp4 ? 4 : 1;
@@ -887,6 +906,7 @@ extern "C" int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* a,
     const CUtensorMap maps[4] = {ta, tb, tsa, tsb};
     return launch_gemm_pair(fp4 ? kKindNVF4 : kKindMXF8, a->c_dtype, maps, pp, sms, stream);
   }
+  if (int rc = set_skip_rows(&p, a->skip_rows_begin, a->skip_rows_count, a->m, false)) return rc;
   if (mx_out || nv_out)
     return fail(B200K_UNSUPPORTED, "quantised output is produced by the CTA-pair kernel only (plain "
                 "problems, or grouped ones with tile_rows = 256)");

@@ -62,6 +62,8 @@ struct GemmParams {
   int group_m;               // CTA-pair kernel: row tiles per raster band
   // CTA-pair kernel, grouped: output rows scattered over up to 16 buffers (peer-mapped or
   // local); row_map values are then buffer * c_peer_rows + row
+  int skip_tile0;      // CTA-pair kernel, plain problems: 256-row tiles [skip_tile0, skip_tile0 +
+  int skip_tiles;      // skip_tiles) of A and C take no part in the product
   int num_c_peers;
   int64_t c_peer_rows;
   void* c_peers[16];

@@ -128,6 +128,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   // grouped mode: 256-row tiles, the live count comes from the device
   int tiles_m = (p.m + 255) / 256;
   if (p.num_row_tiles != nullptr) tiles_m = min(tiles_m, *p.num_row_tiles);
+  // rows left out of the product (the AllGather GEMM's own shard, multiplied earlier from
+  // the rank's own buffer): the raster runs over the remaining tile rows
+  tiles_m -= p.skip_tiles;
+  auto coord_of = [&](int tile) {
+    TileCoord c = tile_coord(tile, tiles_m, p.tiles_n, p.group_m);
+    if (c.pid_m >= p.skip_tile0) c.pid_m += p.skip_tiles;
+    return c;
+  };
   const int num_tiles = tiles_m * p.tiles_n * p.batch;
   const bool swiglu = p.epilogue == B200K_EPI_SWIGLU;
   const int bn = p.pair_bn;         // tile width: 256, or 128 when that wastes less of the last wave
@@ -143,7 +151,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t it = 0;
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n, p.group_m);
+        const TileCoord tc = coord_of(tile);
         int group = tc.batch, a_batch = tc.batch;
         if (p.tile_group != nullptr) {
           group = p.tile_group[tc.pid_m];
@@ -217,7 +225,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       if (q >= p.k_iters) ok = false;   // a single k-step: nothing for the second issuer
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        if (p.tile_group != nullptr && p.tile_group[tile_coord(tile, tiles_m, p.tiles_n, p.group_m).pid_m] < 0) continue;
+        if (p.tile_group != nullptr && p.tile_group[coord_of(tile).pid_m] < 0) continue;
         const int w = lt & 1;
         if (!mbar_wait(acc_empty_bar(w), ((lt >> 1) & 1) ^ 1, abort_flag, p.wait_budget_ns)) {
           report_status(p.status, 52, 100 + w);
@@ -333,7 +341,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t lead_ovl = map_to_cta(ovl_free_bar, 0);
     uint32_t lt = 0;
     for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
-      const TileCoord tc = tile_coord(tile, tiles_m, p.tiles_n, p.group_m);
+      const TileCoord tc = coord_of(tile);
       if (p.tile_group != nullptr && p.tile_group[tc.pid_m] < 0) continue;
       const int w = lt & 1;
       if (!mbar_wait_relaxed(acc_full_bar(w), (lt >> 1) & 1, abort_flag, 64, p.wait_budget_ns)) {

@@ -153,6 +153,13 @@ typedef struct {
   const void* const* c_peers;
   int32_t num_c_peers;
   int64_t c_peer_rows;
+  /* Rows [skip_rows_begin, skip_rows_begin + skip_rows_count) of A take no part in the product
+   * and the same rows of C are not written (plain problems on the CTA-pair kernel, batch 1;
+   * both multiples of 256).  The AllGather GEMM multiplies the rows a rank owns out of its own
+   * buffer while the others arrive, then every other row in ONE launch over the gathered A
+   * (samples/AllGatherMatmul.py:28-120 computes all rows in one kernel).  0 = none. */
+  int64_t skip_rows_begin;
+  int64_t skip_rows_count;
 } b200k_gemm_args;
 
 int b200k_gemm(const b200k_gemm_args* args, b200k_stream stream);
@@ -249,6 +256,9 @@ typedef struct {
   const void* const* c_peers;
   int32_t num_c_peers;
   int64_t c_peer_rows;
+  /* as in b200k_gemm_args */
+  int64_t skip_rows_begin;
+  int64_t skip_rows_count;
 } b200k_block_scaled_gemm_args;
 
 int b200k_block_scaled_gemm(const b200k_block_scaled_gemm_args* args, b200k_stream stream);

@@ -286,11 +286,12 @@ def test_gather_matmul_emulated_ranks_one_gpu(world, dtype, device_ok):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("m", [128, 256, 512])   # 128: two remote GEMMs; 256, 512: one that skips the own rows
 @pytest.mark.parametrize("world", [2, 4])
-def test_gather_matmul_nvfp4_emulated_ranks_one_gpu(world, device_ok):
+def test_gather_matmul_nvfp4_emulated_ranks_one_gpu(world, m, device_ok):
     import b200k
-    g = torch.Generator().manual_seed(200 + world)
-    m, k, n = 256, 1024, 512
+    g = torch.Generator().manual_seed(200 + world + m)
+    k, n = 1024, 512
     shards = [(torch.randn(m, k, generator=g) * (1 + p)).bfloat16() for p in range(world)]
     wn = (0.02 * torch.randn(n, k, generator=g)).bfloat16()
     quant = [b200k.nvfp4_quantize(s.cuda()) for s in shards]     # each rank quantises its own rows

@@ -235,3 +235,47 @@ def test_quantise_in_epilogue_equals_two_steps(m, n, k, device_ok):
     q2, s2 = b200k.block_quantize(c_bf16, 32)
     assert torch.equal(q2.view(torch.uint8), q.view(torch.uint8))
     assert torch.equal(s2.cpu().view(torch.uint8), s_ref.view(torch.uint8))
+
+
+@pytest.mark.parametrize("fp4", [False, True])
+@pytest.mark.parametrize("skip", [(0, 256), (256, 512), (768, 256)])
+def test_skip_rows_leaves_whole_tiles_out(fp4, skip, device_ok):
+    """skip_rows of b200k_block_scaled_gemm_args (the AllGather GEMM multiplies a rank's own
+    rows separately): the skipped rows of C keep their contents, every other row is bit for
+    bit the row of the full product."""
+    from b200k.block_scaled import _as_u8, _scaled_gemm
+    g = torch.Generator().manual_seed(31 + skip[0] + fp4)
+    m, n, k = 1024, 768, 512
+    a = torch.randn(m, k, generator=g).bfloat16().cuda()
+    w = (0.05 * torch.randn(n, k, generator=g)).bfloat16().cuda()
+    if fp4:
+        aq, asf, ats = b200k.nvfp4_quantize(a)
+        wq, wsf, wts = b200k.nvfp4_quantize(w)
+        kw = dict(fp4=True, alpha_a=ats, alpha_b=wts)
+    else:
+        aq, asf = b200k.block_quantize(a, swizzled_scale=True)
+        wq, wsf = b200k.block_quantize(w, swizzled_scale=True)
+        kw = dict(fp4=False)
+    ops = (_as_u8(aq) if fp4 else aq, _as_u8(asf), _as_u8(wq) if fp4 else wq, _as_u8(wsf))
+    full = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    _scaled_gemm(*ops, full, **kw)
+    part = torch.full((m, n), 7.0, dtype=torch.bfloat16, device="cuda")
+    _scaled_gemm(*ops, part, skip_rows=skip, **kw)
+    lo, cnt = skip
+    assert torch.all(part[lo:lo + cnt] == 7.0)
+    keep = torch.ones(m, dtype=torch.bool, device="cuda")
+    keep[lo:lo + cnt] = False
+    assert torch.equal(part[keep], full[keep])
+    assert b200k.device_status() == (0, 0)
+
+
+def test_skip_rows_validation(device_ok):
+    from b200k.block_scaled import _as_u8, _scaled_gemm
+    a = torch.randn(512, 256, device="cuda").bfloat16()
+    w = torch.randn(256, 256, device="cuda").bfloat16()
+    aq, asf = b200k.block_quantize(a, swizzled_scale=True)
+    wq, wsf = b200k.block_quantize(w, swizzled_scale=True)
+    c = torch.empty(512, 256, dtype=torch.bfloat16, device="cuda")
+    for bad in [(128, 256), (0, 100), (256, 512), (-256, 256)]:
+        with pytest.raises(b200k.B200KError):
+            _scaled_gemm(aq, _as_u8(asf), wq, _as_u8(wsf), c, fp4=False, skip_rows=bad)
