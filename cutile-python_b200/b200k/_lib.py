@@ -203,6 +203,8 @@ SIGNATURES = {
                                c_int32, c_int32, c_void_p]),
     "b200k_peer_gather": (c_int, [POINTER(PeerGatherArgs), c_void_p]),
     "b200k_peer_scalar_expand": (c_int, [POINTER(c_void_p), c_int32, c_int64, c_void_p, c_void_p]),
+    "b200k_peer_gather_batch": (c_int, [POINTER(PeerGatherArgs), c_int32, POINTER(c_void_p), c_int64, c_void_p,
+                                        c_void_p]),
     "b200k_moe_sparse": (c_int, [POINTER(MoeSparseArgs), c_void_p]),
     "b200k_moe_ep_capacity_rows": (c_int64, [c_int64, c_int32, c_int32, c_int32]),
     "b200k_moe_ep_count": (c_int, [POINTER(MoeEpCountArgs), c_void_p]),

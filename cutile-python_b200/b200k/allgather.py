@@ -173,16 +173,44 @@ class Nvfp4GatherMatmul:
         self.gathered = torch.cuda.Event()
         # whole 256-row tiles per rank: the other ranks' rows go through one GEMM launch
         self.one_remote_launch = self.m % 256 == 0
+        self._batch = None
+
+    def _batch_args(self):
+        """Packed operand and scale atoms as one batch of two dense gathers, plus the pointer
+        table of the tensor scales; built once, the buffers never move."""
+        args = (_lib.PeerGatherArgs * 2)()
+        keep = []
+        for a, shards, out in ((args[0], self.q_peers, self.q), (args[1], self.sf_peers, self.sf)):
+            mine = shards[self.rank]
+            ptrs = (ctypes.c_void_p * self.world)(*[s.data_ptr() for s in shards])
+            keep.append(ptrs)
+            a.shards = ctypes.cast(ptrs, ctypes.POINTER(ctypes.c_void_p))
+            a.dst = out.data_ptr()
+            a.rows, a.row_bytes = mine.shape[0], mine.shape[1] * mine.element_size()
+            a.src_stride_bytes = mine.stride(0) * mine.element_size()
+            a.dst_stride_bytes = out.stride(0) * out.element_size()
+            a.world, a.rank, a.round_tf32 = self.world, self.rank, 0
+        ts = (ctypes.c_void_p * self.world)(*[t.data_ptr() for t in self.ts_peers])
+        keep.append(ts)
+        dense = all(a.src_stride_bytes == a.row_bytes == a.dst_stride_bytes for a in args)
+        return args, ctypes.cast(ts, ctypes.POINTER(ctypes.c_void_p)), keep, dense
 
     def gather(self):
-        peer_gather(self.q_peers, self.rank, out=self.q)
-        peer_gather(self.sf_peers, self.rank, out=self.sf)
-        ptrs = (ctypes.c_void_p * self.world)(*[t.data_ptr() for t in self.ts_peers])
+        """One launch for the packed operand, the scale atoms and the per-row expansion of the
+        peers' tensor scales (three launches where a shard is not dense)."""
+        if self._batch is None:
+            self._batch = self._batch_args()
+        args, ts, _, dense = self._batch
         dev = self.q.device
         with torch.cuda.device(dev):
-            _lib.check(_lib.lib().b200k_peer_scalar_expand(
-                ctypes.cast(ptrs, ctypes.POINTER(ctypes.c_void_p)), self.world, self.m,
-                self.row_scale.data_ptr(), _lib.stream_ptr(dev)))
+            if dense:
+                _lib.check(_lib.lib().b200k_peer_gather_batch(args, 2, ts, self.m, self.row_scale.data_ptr(),
+                                                              _lib.stream_ptr(dev)))
+                return
+            peer_gather(self.q_peers, self.rank, out=self.q)
+            peer_gather(self.sf_peers, self.rank, out=self.sf)
+            _lib.check(_lib.lib().b200k_peer_scalar_expand(ts, self.world, self.m, self.row_scale.data_ptr(),
+                                                           _lib.stream_ptr(dev)))
 
     def run(self, w_q, w_sf, w_ts, out: torch.Tensor | None = None,
             out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:

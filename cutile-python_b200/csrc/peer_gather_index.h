@@ -10,6 +10,8 @@
 //   chunk# = run / world
 //   peer   = (rank + 1 + slot) % world    remote shards first, this rank's own shard last
 //
+// The kernel gives a run to a block of kPeerGatherChunkVecs threads (item = run, thread), so the
+// divisions by `world` are per block and only the row / column split is per thread.
 // Items whose vector index falls behind the end of the shard (the last chunk's tail) are
 // invalid.  Every (peer, vector) pair is produced by exactly one valid item.
 #ifndef B200K_PEER_GATHER_INDEX_H_
@@ -42,15 +44,30 @@ B200K_HD int64_t peer_gather_items(int world, int64_t rows, int64_t row_vecs) {
   return chunks * world * kPeerGatherChunkVecs;
 }
 
+// A run of kPeerGatherChunkVecs consecutive items: one peer, consecutive vectors of its shard.
+struct PeerGatherRun {
+  int peer;
+  int64_t first_vec;   // flat vector index inside the shard of the run's first item
+};
+
+B200K_HD int64_t peer_gather_runs(int world, int64_t rows, int64_t row_vecs) {
+  return peer_gather_items(world, rows, row_vecs) / kPeerGatherChunkVecs;
+}
+
+B200K_HD PeerGatherRun peer_gather_run(int64_t run, int world, int rank) {
+  PeerGatherRun r;
+  const int slot = static_cast<int>(run % world);
+  r.peer = (rank + 1 + slot) % world;
+  r.first_vec = (run / world) * kPeerGatherChunkVecs;
+  return r;
+}
+
 B200K_HD PeerGatherItem peer_gather_item(int64_t i, int world, int rank, int64_t rows, int64_t row_vecs) {
   PeerGatherItem it;
-  const int64_t within = i % kPeerGatherChunkVecs;
-  const int64_t run = i / kPeerGatherChunkVecs;
-  const int slot = static_cast<int>(run % world);
-  const int64_t chunk = run / world;
-  const int64_t v = chunk * kPeerGatherChunkVecs + within;
+  const PeerGatherRun r = peer_gather_run(i / kPeerGatherChunkVecs, world, rank);
+  const int64_t v = r.first_vec + i % kPeerGatherChunkVecs;
   it.valid = v < rows * row_vecs;
-  it.peer = (rank + 1 + slot) % world;
+  it.peer = r.peer;
   it.row = v / row_vecs;
   it.col = v - it.row * row_vecs;
   return it;

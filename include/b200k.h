@@ -439,6 +439,15 @@ int b200k_peer_gather(const b200k_peer_gather_args* args, b200k_stream stream);
 int b200k_peer_scalar_expand(const void* const* shards, int32_t world, int64_t rows, float* out,
                              b200k_stream stream);
 
+/* Up to 4 gathers and (optionally, scalar_shards != NULL) one scalar expansion in ONE launch:
+ * what the NVFP4 form of the gather GEMM needs per step (packed operand, scale atoms, tensor
+ * scales).  Every gather must be dense (both strides == row_bytes), without rounding, and of
+ * the same world and rank; otherwise B200K_UNSUPPORTED and nothing is enqueued.  One launch
+ * instead of three keeps the gather ahead of the GEMM it runs beside. */
+int b200k_peer_gather_batch(const b200k_peer_gather_args* args, int32_t count,
+                            const void* const* scalar_shards, int64_t scalar_rows, float* scalar_out,
+                            b200k_stream stream);
+
 /* ---- expert-parallel MoE (experts and tokens sharded over the ranks of one node) --------
  * No counterpart in the reference, whose only multi-GPU code is the AllGather sample; the
  * single-GPU pipeline these calls must reproduce is cutile_moe (samples/MoE.py:197-288).

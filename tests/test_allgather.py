@@ -286,6 +286,56 @@ def test_gather_matmul_emulated_ranks_one_gpu(world, dtype, device_ok):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 5, 8])
+@pytest.mark.parametrize("rows,cols", [(256, 4096), (100, 48), (7, 16), (1024, 512)])
+def test_peer_gather_kernel_forms(world, rows, cols, device_ok, monkeypatch):
+    """The bulk-copy form (dense shards), the load / store form (forced, and taken by itself
+    for strided shards) and the batch entry give the byte-exact concatenation; shard sizes
+    that end inside a 4 KB run included."""
+    import ctypes
+    import b200k
+    from b200k import _lib
+    g = torch.Generator().manual_seed(rows + cols + world)
+    shards = [torch.randint(0, 256, (rows, cols), generator=g, dtype=torch.uint8).cuda() for _ in range(world)]
+    want = torch.cat(shards)
+    for rank in (0, world - 1):
+        assert torch.equal(b200k.peer_gather(shards, rank), want)
+        monkeypatch.setenv("B200K_GATHER", "ldst")
+        assert torch.equal(b200k.peer_gather(shards, rank), want)
+        monkeypatch.delenv("B200K_GATHER")
+    # strided shards: views into wider buffers
+    wide = [torch.zeros(rows, cols + 32, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    for w, sh in zip(wide, shards):
+        w[:, :cols].copy_(sh)
+    assert torch.equal(b200k.peer_gather([w[:, :cols] for w in wide], 1), want)
+    # the batch entry: two gathers and a scalar expansion in one launch
+    other = [torch.randint(0, 256, (rows, 32), generator=g, dtype=torch.uint8).cuda() for _ in range(world)]
+    scal = [torch.full((1,), 1.5 + p, device="cuda") for p in range(world)]
+    out_a, out_b = torch.zeros_like(want), torch.zeros(world * rows, 32, dtype=torch.uint8, device="cuda")
+    out_s = torch.zeros(world * rows, device="cuda")
+    args = (_lib.PeerGatherArgs * 2)()
+    keep = []
+    for a, sh, out in ((args[0], shards, out_a), (args[1], other, out_b)):
+        ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in sh])
+        keep.append(ptrs)
+        a.shards = ctypes.cast(ptrs, ctypes.POINTER(ctypes.c_void_p))
+        a.dst, a.rows, a.row_bytes = out.data_ptr(), rows, sh[0].shape[1]
+        a.src_stride_bytes = a.dst_stride_bytes = a.row_bytes
+        a.world, a.rank = world, world - 1
+    sp = (ctypes.c_void_p * world)(*[t.data_ptr() for t in scal])
+    _lib.check(_lib.lib().b200k_peer_gather_batch(args, 2, ctypes.cast(sp, ctypes.POINTER(ctypes.c_void_p)), rows,
+                                                  out_s.data_ptr(), _lib.stream_ptr(want.device)))
+    torch.cuda.synchronize()
+    assert torch.equal(out_a, want) and torch.equal(out_b, torch.cat(other))
+    assert torch.equal(out_s, torch.cat([s.expand(rows) for s in scal]))
+    # a strided member is refused before anything is enqueued
+    args[1].dst_stride_bytes = 64
+    with pytest.raises(b200k.B200KError):
+        _lib.check(_lib.lib().b200k_peer_gather_batch(args, 2, None, 0, None, _lib.stream_ptr(want.device)))
+    assert b200k.device_status() == (0, 0)
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("m", [128, 256, 512])   # 128: two remote GEMMs; 256, 512: one that skips the own rows
 @pytest.mark.parametrize("world", [2, 4])
 def test_gather_matmul_nvfp4_emulated_ranks_one_gpu(world, m, device_ok):
