@@ -385,6 +385,8 @@ class AgNvfp4Gemm(Nvfp4Gemm):
     def launches(self):
         if self.world == 1:
             return 1
+        if (self.M // self.world) % 256 == 0:
+            return 3        # one gather launch, the GEMM of the own rows, one GEMM of every other row
         return 3 + 1 + (1 if self.rank in (0, self.world - 1) else 2)   # gathers, local GEMM, remote GEMMs
 
     def gathered_bytes(self):
