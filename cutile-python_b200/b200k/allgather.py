@@ -170,7 +170,6 @@ class Nvfp4GatherMatmul:
         self.row_scale = torch.empty(self.world * self.m, dtype=torch.float32, device=dev)
         self.sf_own = _as_u8(a_sf)
         self.side = torch.cuda.Stream(dev)
-        self.gathered = torch.cuda.Event()
         # whole 256-row tiles per rank: the other ranks' rows go through one GEMM launch
         self.one_remote_launch = self.m % 256 == 0
         self._batch = None
@@ -214,9 +213,12 @@ class Nvfp4GatherMatmul:
 
     def run(self, w_q, w_sf, w_ts, out: torch.Tensor | None = None,
             out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-        """The gather runs on a side stream while the rows this rank owns are multiplied
-        straight out of its own buffers; the remote rows follow once the gather has landed
-        (an event, no kernel waits on another)."""
+        """The gather and, behind it, the GEMM of the other ranks' rows run on a side stream
+        while the rows this rank owns are multiplied straight out of its own buffers on the
+        caller's stream: stream order is the only dependency (no kernel waits on another), and
+        the CTAs of the second GEMM move in as those of the first leave, so the partly filled
+        last round of the first costs nothing.  The caller's stream waits for the side stream
+        before the call returns."""
         n = w_q.shape[0]
         dev = self.q.device
         m, world, rank = self.m, self.world, self.rank
@@ -225,27 +227,26 @@ class Nvfp4GatherMatmul:
         wq, wsf = _as_u8(w_q), _as_u8(w_sf)
         main = torch.cuda.current_stream(dev)
         if world > 1:
-            self.side.wait_stream(main)    # the previous call's GEMMs are done with the staging
+            self.side.wait_stream(main)    # operands are ready; the previous call is done with the staging
             with torch.cuda.stream(self.side):
                 self.gather()
-                self.gathered.record(self.side)
+                tiles = self.sf_shape[0]       # 128-row scale tiles per rank
+                sf = self.sf.reshape(world * tiles, *self.sf_shape[1:])
+                if self.one_remote_launch:
+                    # every other rank's rows in one launch over the gathered A: the row tiles of
+                    # this rank's own shard are left out of the raster
+                    _scaled_gemm(self.q, sf, wq, wsf, out, fp4=True, alpha_b=w_ts, row_scale=self.row_scale,
+                                 skip_rows=(rank * m, m))
+                else:
+                    for lo, hi in ((0, rank), (rank + 1, world)):
+                        if hi > lo:
+                            _scaled_gemm(self.q[lo * m:hi * m], sf[lo * tiles:hi * tiles], wq, wsf,
+                                         out[lo * m:hi * m], fp4=True, alpha_b=w_ts,
+                                         row_scale=self.row_scale[lo * m:hi * m])
         _scaled_gemm(self.q_peers[rank], self.sf_own, wq, wsf, out[rank * m:(rank + 1) * m], fp4=True,
                      alpha_a=self.ts_peers[rank], alpha_b=w_ts)
         if world > 1:
-            main.wait_event(self.gathered)
-            tiles = self.sf_shape[0]       # 128-row scale tiles per rank
-            sf = self.sf.reshape(world * tiles, *self.sf_shape[1:])
-            if self.one_remote_launch:
-                # every other rank's rows in one launch over the gathered A: the row tiles of
-                # this rank's own shard are left out of the raster
-                _scaled_gemm(self.q, sf, wq, wsf, out, fp4=True, alpha_b=w_ts, row_scale=self.row_scale,
-                             skip_rows=(rank * m, m))
-            else:
-                for lo, hi in ((0, rank), (rank + 1, world)):
-                    if hi > lo:
-                        _scaled_gemm(self.q[lo * m:hi * m], sf[lo * tiles:hi * tiles], wq, wsf,
-                                     out[lo * m:hi * m], fp4=True, alpha_b=w_ts,
-                                     row_scale=self.row_scale[lo * m:hi * m])
+            main.wait_stream(self.side)
         return out
 
 
