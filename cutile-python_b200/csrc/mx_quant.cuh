@@ -93,22 +93,26 @@ __device__ __forceinline__ uint8_t nvfp4_block(const float (&v)[16], float six_s
   }
   // x / denom as x * (1 / denom), both correctly rounded: one reciprocal per block instead
   // of sixteen divisions.  A subnormal denom (reciprocal not finite) keeps the division.
-  const float inv = (denom >= 1.17549435e-38f) ? __frcp_rn(denom) : 0.0f;
-  uint32_t lo = 0, hi = 0;
+  // One branch per block, not per pair: the three cases run their own straight-line loops.
+  uint32_t code[8];
+  if (denom >= 1.17549435e-38f) {
+    const float inv = __frcp_rn(denom);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    float a = 0.0f, b = 0.0f;
-    if (inv > 0.0f) {
-      a = __fmul_rn(v[2 * i], inv);
-      b = __fmul_rn(v[2 * i + 1], inv);
-    } else if (denom > 0.0f) {
-      a = __fdiv_rn(v[2 * i], denom);
-      b = __fdiv_rn(v[2 * i + 1], denom);
-    }
-    const uint32_t byte = __nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest);
-    if (i < 4) lo |= (byte & 0xff) << (8 * i);
-    else hi |= (byte & 0xff) << (8 * (i - 4));
+    for (int i = 0; i < 8; ++i)
+      code[i] = __nv_cvt_float2_to_fp4x2(make_float2(__fmul_rn(v[2 * i], inv), __fmul_rn(v[2 * i + 1], inv)),
+                                         __NV_E2M1, cudaRoundNearest);
+  } else if (denom > 0.0f) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      code[i] = __nv_cvt_float2_to_fp4x2(make_float2(__fdiv_rn(v[2 * i], denom), __fdiv_rn(v[2 * i + 1], denom)),
+                                         __NV_E2M1, cudaRoundNearest);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) code[i] = 0;     // the codes of (+0, +0)
   }
+  // four code bytes per word with three byte permutes
+  const uint32_t lo = __byte_perm(__byte_perm(code[0], code[1], 0x0040), __byte_perm(code[2], code[3], 0x0040), 0x5410);
+  const uint32_t hi = __byte_perm(__byte_perm(code[4], code[5], 0x0040), __byte_perm(code[6], code[7], 0x0040), 0x5410);
   *lo_out = lo;
   *hi_out = hi;
   return sf_byte;
