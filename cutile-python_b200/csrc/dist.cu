@@ -97,7 +97,7 @@ peer_gather_kernel(PeerPtrs peers, int world, int rank, int64_t rows, int64_t ro
 constexpr int kBulkStages = 4;
 constexpr int kBulkRunBytes = kPeerGatherChunkVecs * 16;
 
-constexpr int kMaxBatch = 4;
+constexpr int kMaxBatch = kPeerGatherMaxBatch;
 
 struct BulkJob {
   PeerPtrs peers;
@@ -231,7 +231,7 @@ int launch_bulk_batch(const b200k_peer_gather_args* args, int count, const void*
   int sms = current_sm_count();
   if (sms <= 0) return fail(B200K_CUDA_ERROR, "no current CUDA device");
   BulkBatch b = {};
-  int64_t runs[kMaxBatch] = {}, total = 0;
+  int64_t runs[kMaxBatch] = {};
   for (int j = 0; j < count; ++j) {
     const b200k_peer_gather_args* a = &args[j];
     if (a->rows == 0 || a->row_bytes == 0) continue;
@@ -240,31 +240,16 @@ int launch_bulk_batch(const b200k_peer_gather_args* args, int count, const void*
     job.shard_bytes = a->rows * a->row_bytes;
     job.dst = static_cast<uint8_t*>(a->dst);
     runs[b.jobs] = peer_gather_runs(a->world, job.shard_bytes / 16, 1);
-    total += runs[b.jobs];
     b.world = a->world;
     b.rank = a->rank;
     ++b.jobs;
   }
   if (b.jobs == 0 && scalar_out == nullptr) return B200K_OK;
-  int grid = 0;
-  if (b.jobs == 0) {
-    grid = 1;
-  } else {
-    // one block per SM in all (the grid is then resident at once, beside a GEMM's CTAs too), dealt
-    // in proportion to the runs, at least one block per job
-    int64_t want = total < sms ? total : sms;
-    if (want < b.jobs) want = b.jobs;
-    int64_t left_blocks = want, left_runs = total;
-    for (int j = 0; j < b.jobs; ++j) {
-      b.job[j].first_block = grid;
-      const int jobs_after = b.jobs - 1 - j;
-      int64_t share = left_runs > 0 ? (runs[j] * left_blocks + left_runs / 2) / left_runs : 1;
-      if (share < 1) share = 1;
-      if (share > left_blocks - jobs_after) share = left_blocks - jobs_after;
-      grid += static_cast<int>(share);
-      left_blocks -= share;
-      left_runs -= runs[j];
-    }
+  int grid = 1;
+  if (b.jobs > 0) {
+    int first[kMaxBatch];
+    grid = peer_gather_batch_blocks(runs, b.jobs, sms, first);
+    for (int j = 0; j < b.jobs; ++j) b.job[j].first_block = first[j];
   }
   if (scalar_out != nullptr) {
     b.world = args[0].world;

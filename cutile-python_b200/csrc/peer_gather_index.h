@@ -73,5 +73,32 @@ B200K_HD PeerGatherItem peer_gather_item(int64_t i, int world, int rank, int64_t
   return it;
 }
 
+// A batch launch (several gathers in one grid of one-warp blocks): the blocks are dealt over the
+// jobs in proportion to their runs - one block per SM in all and never more, so that the whole
+// grid is resident at once beside another kernel's CTAs, at least one block per job.  Block b
+// of a job that owns `blocks` blocks takes the job's runs b, b + blocks, b + 2 * blocks, ...
+// Returns the grid size; first_block[j] is job j's first block.
+constexpr int kPeerGatherMaxBatch = 4;
+
+B200K_HD int peer_gather_batch_blocks(const int64_t* runs, int jobs, int sms, int* first_block) {
+  int64_t total = 0;
+  for (int j = 0; j < jobs; ++j) total += runs[j];
+  int64_t want = total < sms ? total : sms;
+  if (want < jobs) want = jobs;
+  int64_t left_blocks = want, left_runs = total;
+  int grid = 0;
+  for (int j = 0; j < jobs; ++j) {
+    first_block[j] = grid;
+    const int jobs_after = jobs - 1 - j;
+    int64_t share = left_runs > 0 ? (runs[j] * left_blocks + left_runs / 2) / left_runs : 1;
+    if (share < 1) share = 1;
+    if (share > left_blocks - jobs_after) share = left_blocks - jobs_after;
+    grid += static_cast<int>(share);
+    left_blocks -= share;
+    left_runs -= runs[j];
+  }
+  return grid;
+}
+
 }  // namespace b200k
 #endif  // B200K_PEER_GATHER_INDEX_H_

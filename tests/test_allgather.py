@@ -57,6 +57,36 @@ extern "C" void host_peer_gather(const uint8_t* const* shards, int world, int ra
     }
   }
 }
+
+// The bulk-copy kernel's loop nest on the host for a batch of dense gathers: blocks dealt over
+// the jobs by peer_gather_batch_blocks, block b of a job walking its runs b, b + blocks, ...
+// Returns the grid size, or -1 when a job got no block or the grid exceeds `sms` (+ jobs).
+extern "C" int host_bulk_batch(const uint8_t* const* const* shards, uint8_t* const* dst,
+                               const int64_t* shard_bytes, int jobs, int world, int rank, int sms,
+                               int32_t* const* hits) {
+  int64_t runs[b200k::kPeerGatherMaxBatch];
+  int first[b200k::kPeerGatherMaxBatch + 1];
+  for (int j = 0; j < jobs; ++j) runs[j] = b200k::peer_gather_runs(world, shard_bytes[j] / 16, 1);
+  const int grid = b200k::peer_gather_batch_blocks(runs, jobs, sms, first);
+  first[jobs] = grid;
+  if (grid > (sms > jobs ? sms : jobs)) return -1;
+  for (int j = 0; j < jobs; ++j) {
+    const int blocks = first[j + 1] - first[j];
+    if (blocks < 1) return -1;
+    for (int block = 0; block < blocks; ++block) {
+      for (int64_t run = block; run < runs[j]; run += blocks) {
+        const b200k::PeerGatherRun r = b200k::peer_gather_run(run, world, rank);
+        const int64_t off = r.first_vec * 16;
+        if (off >= shard_bytes[j]) return -2;          // every run holds at least one vector
+        const int64_t left = shard_bytes[j] - off;
+        const int64_t bytes = left < 4096 ? left : 4096;
+        memcpy(dst[j] + int64_t(r.peer) * shard_bytes[j] + off, shards[j][r.peer] + off, bytes);
+        for (int64_t v = 0; v < bytes / 16; ++v) hits[j][(int64_t(r.peer) * shard_bytes[j] + off) / 16 + v] += 1;
+      }
+    }
+  }
+  return grid;
+}
 """
 
 
@@ -77,7 +107,8 @@ def host_gather(tmp_path_factory):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     subprocess.run([cxx, "-O1", "-shared", "-fPIC", "-I", os.path.join(root, "cutile-python_b200", "csrc"),
                     str(src), "-o", str(lib)], check=True)
-    fn = ctypes.CDLL(str(lib)).host_peer_gather
+    handle = ctypes.CDLL(str(lib))
+    fn = handle.host_peer_gather
     fn.restype = None
 
     def run(shards, rank, threads, dst_cols=None):
@@ -95,6 +126,8 @@ def host_gather(tmp_path_factory):
            ctypes.c_void_p(hits.data_ptr()), ctypes.c_void_p(first.data_ptr()))
         return dst, hits, first
 
+    run.batch = handle.host_bulk_batch
+    run.batch.restype = ctypes.c_int
     return run
 
 
@@ -120,6 +153,36 @@ def test_peer_gather_index_math_on_fake_shards(host_gather, world, rows, cols):
                 assert int(first[256 * slot]) == (rank + 1 + slot) % world
         if world > 1:
             assert int(first[0]) != rank and int(first[256 * (world - 1)]) == rank
+
+
+@pytest.mark.parametrize("world", [1, 2, 5, 8])
+@pytest.mark.parametrize("sizes,sms", [((4096 * 50, 4096 * 3), 148), ((4096 * 1024, 4096 * 128 + 48), 148),
+                                       ((16, 16, 16, 16), 148), ((4096 * 9 + 160, 4096 * 200), 16),
+                                       ((4096 * 3,), 2), ((4096 * 7, 32, 4096 * 40 + 16), 3)])
+def test_bulk_batch_covers_every_vector_once(host_gather, world, sizes, sms):
+    """The block distribution and run walk of the bulk-copy gather (one launch for several
+    tensors): every 16-byte vector of every shard of every job is copied exactly once, every
+    job owns at least one block, and the grid never exceeds one block per SM."""
+    import ctypes
+    g = torch.Generator().manual_seed(world + len(sizes) + sms)
+    jobs = len(sizes)
+    shards = [[torch.randint(0, 256, (nbytes,), generator=g, dtype=torch.uint8) for _ in range(world)] for nbytes in sizes]
+    dst = [torch.zeros(world * nbytes, dtype=torch.uint8) for nbytes in sizes]
+    hits = [torch.zeros(world * nbytes // 16, dtype=torch.int32) for nbytes in sizes]
+    per_job = [(ctypes.c_void_p * world)(*[t.data_ptr() for t in job]) for job in shards]
+    shard_tab = (ctypes.c_void_p * jobs)(*[ctypes.addressof(p) for p in per_job])
+    dst_tab = (ctypes.c_void_p * jobs)(*[t.data_ptr() for t in dst])
+    hit_tab = (ctypes.c_void_p * jobs)(*[t.data_ptr() for t in hits])
+    size_tab = (ctypes.c_int64 * jobs)(*sizes)
+    for rank in (0, world - 1):
+        for t in dst + hits:
+            t.zero_()
+        grid = host_gather.batch(shard_tab, dst_tab, size_tab, ctypes.c_int(jobs), ctypes.c_int(world),
+                                 ctypes.c_int(rank), ctypes.c_int(sms), hit_tab)
+        assert 1 <= grid <= max(sms, jobs)
+        for j in range(jobs):
+            assert torch.equal(dst[j], torch.cat(shards[j]))
+            assert bool((hits[j] == 1).all())
 
 
 def _gloo_worker(rank, world, port, q):
