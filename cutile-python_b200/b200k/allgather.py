@@ -68,6 +68,19 @@ def peer_gather(shards: list[torch.Tensor], rank: int, *, round_tf32: bool = Fal
     return out
 
 
+_SIDE_STREAMS: dict = {}
+
+
+def _side_stream(device) -> torch.cuda.Stream:
+    """One side stream per device for the gather and the GEMM that follows it."""
+    idx = torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    if idx not in _SIDE_STREAMS:
+        _SIDE_STREAMS[idx] = torch.cuda.Stream(torch.device("cuda", idx))
+    return _SIDE_STREAMS[idx]
+
+
 def _round_tf32(t: torch.Tensor) -> torch.Tensor:
     """fp32 -> nearest tf32 value (ties away from zero), still stored as fp32."""
     bits = t.contiguous().view(torch.int32)
@@ -112,6 +125,23 @@ def cutile_gather_matmul(inp: torch.Tensor, w: torch.Tensor, group=None, *,
     if transport == "p2p":
         if peers is None:
             peers = [inp] if world == 1 else peer_buffers(inp, group)
+        if (world > 1 and not fp32 and m % 256 == 0 and m * n * k > 0 and inp.stride(1) == 1
+                and (inp.stride(0) * inp.element_size()) % 16 == 0 and inp.data_ptr() % 16 == 0):
+            # 16-bit shards of whole 256-row tiles: the own rows are multiplied straight out of
+            # the rank's buffer while, on a side stream, the other shards arrive and are
+            # multiplied in one launch whose raster leaves the own row tiles out
+            out = torch.empty((world * m, n), dtype=inp.dtype, device=inp.device)
+            staged = torch.empty((world * m, k), dtype=inp.dtype, device=inp.device)
+            main = torch.cuda.current_stream(inp.device)
+            side = _side_stream(inp.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                peer_gather(peers, rank, out=staged)
+                _gemm(staged, w, out, skip_rows=(rank * m, m))
+            _gemm(inp, w, out[rank * m:(rank + 1) * m])
+            main.wait_stream(side)
+            staged.record_stream(side)
+            return out
         staged = peer_gather(peers, rank, round_tf32=fp32)
     elif transport == "nccl":
         staged = torch.empty((world * m, k), dtype=inp.dtype, device=inp.device)

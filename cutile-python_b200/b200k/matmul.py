@@ -38,12 +38,14 @@ _GEMM_LAUNCHES = _lib.LaunchCache("b200k_gemm")
 
 
 def _gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, alpha: float = 1.0,
-          max_ctas: int = 0) -> torch.Tensor:
-    """a: (B, M, K) or (M, K); b: (B, K, N) or (K, N) as a view; c likewise (M, N)."""
+          max_ctas: int = 0, skip_rows: tuple[int, int] = (0, 0)) -> torch.Tensor:
+    """a: (B, M, K) or (M, K); b: (B, K, N) or (K, N) as a view; c likewise (M, N).
+    ``skip_rows`` = (first, count): rows of a / c left out of the product (whole 256-row tiles,
+    plain 2-D problems)."""
     key = None
     if not tune.in_use():
         key = (a.data_ptr(), b.data_ptr(), c.data_ptr(), a.shape, a.stride(), b.shape, b.stride(),
-               c.stride(), a.dtype, b.dtype, c.dtype, alpha, max_ctas)
+               c.stride(), a.dtype, b.dtype, c.dtype, alpha, max_ctas, skip_rows)
         plan = _GEMM_LAUNCHES.get(key)
         if plan is not None:
             _GEMM_LAUNCHES.launch(plan, c.device)
@@ -93,6 +95,7 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, alpha: float = 1
     args.epilogue = _lib.EPI_STORE
     args.alpha = alpha
     args.max_ctas = max_ctas
+    args.skip_rows_begin, args.skip_rows_count = skip_rows
     cfg = tune.config_for("gemm", args.ab_dtype, args.c_dtype, layout, m, n, k, nb)
     # plain dense GEMMs launch programmatically: a chain of short ones on one stream then runs
     # without launch gaps (2048 cubed fp16: 20.2 -> 18.0 us per call, the CUDA-graph figure)
@@ -102,8 +105,8 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, alpha: float = 1
     with torch.cuda.device(a.device):
         # a few output tiles with a long K: split-K over the idle SMs needs fp32 scratch
         workspace = None
-        if (cfg is not None and cfg.split_k > 1) or (
-                -(-m // 128) * -(-n // 256) * nb * 4 <= 256 and k * a3.element_size() >= 1024):
+        if skip_rows[1] == 0 and ((cfg is not None and cfg.split_k > 1) or (
+                -(-m // 128) * -(-n // 256) * nb * 4 <= 256 and k * a3.element_size() >= 1024)):
             ws_bytes = _lib.lib().b200k_gemm_workspace_bytes(ctypes.byref(args))
             if ws_bytes > 0:
                 workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)

@@ -330,6 +330,8 @@ def test_gather_matmul_emulated_ranks_one_gpu(world, dtype, device_ok):
     import b200k
     g = torch.Generator().manual_seed(52 + world)
     m, k, n = (256, 1024, 512) if dtype == torch.float32 else (384, 512, 768)
+    if dtype == torch.bfloat16 and world == 3:
+        m = 512      # whole 256-row tiles per rank: own rows and the other ranks' rows as two overlapped GEMMs
     draw = torch.rand if dtype == torch.float32 else torch.randn    # the sample feeds uniform fp32
     shards = [draw(m, k, generator=g).to(dtype) for _ in range(world)]
     w = draw(k, n, generator=g).to(dtype)
@@ -346,6 +348,29 @@ def test_gather_matmul_emulated_ranks_one_gpu(world, dtype, device_ok):
     for rank in (0, world - 1):
         staged = b200k.peer_gather(dev_shards, rank)
         assert torch.equal(staged.cpu(), torch.cat(shards))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 8])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_gather_matmul_whole_tile_shards_overlap(world, dtype, device_ok):
+    """Shards of whole 256-row tiles: own rows and the other ranks' rows are two GEMMs on two
+    streams (the second skips the own row tiles).  Against one GEMM over the concatenation
+    (which may split K for so small a problem: another summation order) to a rounding step of
+    the 16-bit output, and against the oracle."""
+    import b200k
+    g = torch.Generator().manual_seed(77 + world)
+    m, k, n = 256, 384, 640
+    shards = [torch.randn(m, k, generator=g).to(dtype).cuda() for _ in range(world)]
+    w = torch.randn(k, n, generator=g).to(dtype).cuda()
+    whole = b200k.cutile_matmul(torch.cat(shards), w)
+    want = oracle.matmul_ref(torch.cat(shards).cpu(), w.cpu())
+    for rank in range(world):
+        out = b200k.cutile_gather_matmul(shards[rank], w, peers=shards, rank=rank)
+        assert out.shape == (m * world, n) and out.dtype == dtype
+        torch.testing.assert_close(out.float(), whole.float(), atol=2e-2 * float(want.abs().max()), rtol=1e-2)
+        torch.testing.assert_close(out.float().cpu(), want, atol=2e-1, rtol=2e-2)
+    assert b200k.device_status() == (0, 0)
 
 
 @pytest.mark.gpu
