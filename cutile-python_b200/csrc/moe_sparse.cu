@@ -11,8 +11,9 @@
 //   moe_sparse_down  y[r, h]   = w[r] * (W2[e][h, :] . act[r, :])
 // with r = t * topk + slot and e = topk_ids[r]; replicas routed outside [0, experts) give
 // zero rows.  A group of G lanes (G = 4, 8, 16 or 32 by the length of a weight row) owns one
-// output element and walks its weight row in 16-byte vectors; the input vector sits in
-// shared memory as fp32.
+// output element and walks its weight row in 16-byte vectors against the input vector in
+// shared memory (in its own type, unpacked to fp32 at use); rows of at most four vectors take
+// one lane per row with the input in registers.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -58,20 +59,48 @@ template <> __device__ __forceinline__ float from_f32<float>(float v) { return v
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 
-// dot of one weight row (k elements, 16-byte aligned) with the fp32 vector in shared memory,
-// over the G lanes of a group; every lane of the group returns the sum.
+// dot of one weight row (k elements, 16-byte aligned) with the input vector in shared memory
+// (kept in its own type: a 16-byte weight vector meets one 16-byte read of the input), over
+// the G lanes of a group; every lane of the group returns the sum.
 template <typename T, int G>
-__device__ __forceinline__ float group_dot(const T* __restrict__ row, const float* __restrict__ vec, int k,
+__device__ __forceinline__ float group_dot(const T* __restrict__ row, const T* __restrict__ vec, int k,
                                            int lane_in_group) {
   constexpr int E = Vec16<T>::kElems;
   float acc = 0.0f;
   const uint4* r4 = reinterpret_cast<const uint4*>(row);
+  const uint4* v4 = reinterpret_cast<const uint4*>(vec);
   for (int v = lane_in_group; v * E < k; v += G) {
     const uint4 q = __ldg(r4 + v);
-    float f[E];
+    float f[E], x[E];
     unpack16<T>(q, f);
+    unpack16<T>(v4[v], x);
 #pragma unroll
-    for (int i = 0; i < E; ++i) acc = fmaf(f[i], vec[v * E + i], acc);
+    for (int i = 0; i < E; ++i) acc = fmaf(f[i], x[i], acc);
+  }
+#pragma unroll
+  for (int o = G / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o, G);
+  return acc;
+}
+
+// The same dot product with the lane's share of the input vector held in registers: lane l of
+// a group owns the 16-byte vectors l, l + G, ... of every row, VPL of them, so its slice of
+// the (fp32) input is loaded once per block instead of being read from shared memory for
+// every weight vector (twice the bytes of the weights themselves).
+template <typename T, int G, int VPL>
+__device__ __forceinline__ float group_dot_reg(const T* __restrict__ row,
+                                               const float (&xr)[VPL * Vec16<T>::kElems], int lane_in_group) {
+  constexpr int E = Vec16<T>::kElems;
+  const uint4* r4 = reinterpret_cast<const uint4*>(row);
+  uint4 q[VPL];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) q[j] = __ldg(r4 + lane_in_group + j * G);
+  float acc = 0.0f;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    float f[E];
+    unpack16<T>(q[j], f);
+#pragma unroll
+    for (int i = 0; i < E; ++i) acc = fmaf(f[i], xr[j * E + i], acc);
   }
 #pragma unroll
   for (int o = G / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o, G);
@@ -85,12 +114,16 @@ __device__ __forceinline__ long long load_id(const void* ids, int64_t r) {
 
 // grid (row blocks, replicas); UP: rows are the I (gate, up) pairs of W1, k = hidden;
 // otherwise rows are the hidden rows of W2, k = intermediate.
-template <typename T, int G, bool UP>
+// VPL > 0: a weight row is exactly G * VPL 16-byte vectors and the lane's slice of the input
+// lives in registers (used with G = 1: short rows); VPL == 0: any row length, input in shared
+// memory.
+template <typename T, int G, bool UP, int VPL>
 __global__ void __launch_bounds__(256)
 moe_sparse_kernel(const T* __restrict__ in, int64_t in_stride, const T* __restrict__ w, int64_t w_stride_e,
                   int64_t w_ld, const void* __restrict__ ids, int ids_are_int64, const float* __restrict__ route_w,
                   int topk, int experts, int rows, int k, T* __restrict__ out, int64_t out_stride, int* status) {
-  extern __shared__ float s_vec[];
+  extern __shared__ __align__(16) uint8_t s_raw[];
+  T* s_vec = reinterpret_cast<T*>(s_raw);
   const int64_t r = blockIdx.y;
   const long long e = ids_are_int64 ? load_id<long long>(ids, r) : load_id<int>(ids, r);
   const bool live = e >= 0 && e < experts;
@@ -107,8 +140,25 @@ moe_sparse_kernel(const T* __restrict__ in, int64_t in_stride, const T* __restri
   }
   // UP reads token r / topk of the hidden states, DOWN reads replica r of the activations
   const T* v = in + (UP ? r / topk : r) * in_stride;
-  for (int i = threadIdx.x; i < k; i += blockDim.x) s_vec[i] = to_f32<T>(v[i]);
-  __syncthreads();
+  constexpr int E = Vec16<T>::kElems;
+  float xr[(VPL > 0 ? VPL : 1) * E];
+  if constexpr (VPL > 0) {
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const uint4 q = *reinterpret_cast<const uint4*>(v + static_cast<int64_t>(lg + j * G) * E);
+      float f[E];
+      unpack16<T>(q, f);
+#pragma unroll
+      for (int i = 0; i < E; ++i) xr[j * E + i] = f[i];
+    }
+  } else {
+    for (int i = threadIdx.x; i < k; i += blockDim.x) s_vec[i] = v[i];
+    __syncthreads();
+  }
+  auto dot = [&](const T* row) {
+    if constexpr (VPL > 0) return group_dot_reg<T, G, VPL>(row, xr, lg);
+    else return group_dot<T, G>(row, s_vec, k, lg);
+  };
   const T* we = w + e * w_stride_e;
   const float scale = UP ? 1.0f : (route_w != nullptr ? route_w[r] : 1.0f);
   // every group of a warp takes the same number of trips (the shuffles inside group_dot are
@@ -117,12 +167,12 @@ moe_sparse_kernel(const T* __restrict__ in, int64_t in_stride, const T* __restri
     const bool mine = j0 + g < row1;
     const int j = mine ? j0 + g : row1 - 1;
     if constexpr (UP) {
-      const float gate = group_dot<T, G>(we + static_cast<int64_t>(j) * w_ld, s_vec, k, lg);
-      const float up = group_dot<T, G>(we + static_cast<int64_t>(rows + j) * w_ld, s_vec, k, lg);
+      const float gate = dot(we + static_cast<int64_t>(j) * w_ld);
+      const float up = dot(we + static_cast<int64_t>(rows + j) * w_ld);
       // rounded to the activation type exactly where the dense path rounds it
       if (mine && lg == 0) o[j] = from_f32<T>(__fdividef(gate, 1.0f + __expf(-gate)) * up);
     } else {
-      const float y = group_dot<T, G>(we + static_cast<int64_t>(j) * w_ld, s_vec, k, lg);
+      const float y = dot(we + static_cast<int64_t>(j) * w_ld);
       if (mine && lg == 0) o[j] = from_f32<T>(y * scale);
     }
   }
@@ -144,22 +194,37 @@ int launch_sparse(const b200k_moe_sparse_args* a, cudaStream_t stream) {
   // rows per block: enough blocks to fill the GPU, no fewer than one pass of the block's groups
   int sms = current_sm_count();
   if (sms <= 0) sms = 148;
-  auto launch = [&](auto group_tag) {
+  // the input vector must be readable as 16-byte vectors for the register form
+  const bool in_vec_ok = reinterpret_cast<uintptr_t>(in) % 16 == 0 && (in_stride * sizeof(T)) % 16 == 0;
+  auto launch = [&](auto group_tag, auto vpl_tag) {
     constexpr int G = decltype(group_tag)::value;
+    constexpr int VPL = decltype(vpl_tag)::value;
     const int groups = 256 / G;
     int64_t want_blocks = ceil_div(static_cast<int64_t>(sms) * 8, replicas);
     const int64_t max_blocks = ceil_div(rows, groups);
     if (want_blocks > max_blocks) want_blocks = max_blocks;
     if (want_blocks < 1) want_blocks = 1;
     const dim3 grid(static_cast<unsigned>(want_blocks), static_cast<unsigned>(replicas));
-    moe_sparse_kernel<T, G, UP><<<grid, 256, static_cast<size_t>(k) * sizeof(float), stream>>>(
+    const size_t smem = VPL > 0 ? 0 : static_cast<size_t>(k) * sizeof(T);
+    moe_sparse_kernel<T, G, UP, VPL><<<grid, 256, smem, stream>>>(
         in, in_stride, w, w_stride_e, w_ld, a->topk_ids, a->ids_are_int64, a->topk_weights, a->topk,
         a->num_experts, rows, k, out, out_stride, device_status_word());
   };
-  if (vecs >= 32) launch(std::integral_constant<int, 32>());
-  else if (vecs >= 16) launch(std::integral_constant<int, 16>());
-  else if (vecs >= 8) launch(std::integral_constant<int, 8>());
-  else launch(std::integral_constant<int, 4>());
+  using std::integral_constant;
+  // rows of at most four vectors (the down projection of a narrow expert): one lane per row, no
+  // shuffles, the whole input in registers; longer rows: a lane group per row, the input in
+  // shared memory in its own type (held as fp32 there it cost twice the bytes of the weights;
+  // a lane's slice held in registers instead leaves too few warps per SM: 131 against 108 us
+  // for the whole step at 256 tokens x 1408 experts x top-6)
+  if (in_vec_ok && vecs >= 1 && vecs <= 4 && vecs != 3) {
+    if (vecs == 4) launch(integral_constant<int, 1>(), integral_constant<int, 4>());
+    else if (vecs == 2) launch(integral_constant<int, 1>(), integral_constant<int, 2>());
+    else launch(integral_constant<int, 1>(), integral_constant<int, 1>());
+  }
+  else if (vecs >= 32) launch(integral_constant<int, 32>(), integral_constant<int, 0>());
+  else if (vecs >= 16) launch(integral_constant<int, 16>(), integral_constant<int, 0>());
+  else if (vecs >= 8) launch(integral_constant<int, 8>(), integral_constant<int, 0>());
+  else launch(integral_constant<int, 4>(), integral_constant<int, 0>());
   B200K_CHECK_LAUNCH("moe_sparse launch");
   return B200K_OK;
 }
