@@ -12,7 +12,7 @@
 // with r = t * topk + slot and e = topk_ids[r]; replicas routed outside [0, experts) give
 // zero rows.  A group of G lanes (G = 4, 8, 16 or 32 by the length of a weight row) owns one
 // output element and walks its weight row in 16-byte vectors against the input vector in
-// shared memory (in its own type, unpacked to fp32 at use); rows of at most four vectors take
+// shared memory (in its own type, unpacked to fp32 at use); rows of at most eight vectors take
 // one lane per row with the input in registers.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -211,13 +211,14 @@ int launch_sparse(const b200k_moe_sparse_args* a, cudaStream_t stream) {
         a->num_experts, rows, k, out, out_stride, device_status_word());
   };
   using std::integral_constant;
-  // rows of at most four vectors (the down projection of a narrow expert): one lane per row, no
+  // rows of at most eight vectors (the down projection of a narrow expert): one lane per row, no
   // shuffles, the whole input in registers; longer rows: a lane group per row, the input in
   // shared memory in its own type (held as fp32 there it cost twice the bytes of the weights;
   // a lane's slice held in registers instead leaves too few warps per SM: 131 against 108 us
   // for the whole step at 256 tokens x 1408 experts x top-6)
-  if (in_vec_ok && vecs >= 1 && vecs <= 4 && vecs != 3) {
-    if (vecs == 4) launch(integral_constant<int, 1>(), integral_constant<int, 4>());
+  if (in_vec_ok && (vecs == 1 || vecs == 2 || vecs == 4 || vecs == 8)) {
+    if (vecs == 8) launch(integral_constant<int, 1>(), integral_constant<int, 8>());
+    else if (vecs == 4) launch(integral_constant<int, 1>(), integral_constant<int, 4>());
     else if (vecs == 2) launch(integral_constant<int, 1>(), integral_constant<int, 2>());
     else launch(integral_constant<int, 1>(), integral_constant<int, 1>());
   }
