@@ -197,6 +197,8 @@ SIGNATURES = {
     "b200k_moe_align": (c_int, [POINTER(MoeAlignArgs), c_void_p]),
     "b200k_gather_rows": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int32, c_void_p,
                                   c_int32, c_int64, c_void_p, c_int64, c_void_p]),
+    "b200k_gather_rows_by_source": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int32, c_void_p,
+                                            c_int32, c_int64, c_void_p, c_int64, c_void_p, c_void_p]),
     "b200k_silu_and_mul": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int32,
                                    c_void_p]),
     "b200k_topk_sum": (c_int, [c_void_p, c_void_p, c_int64, c_int32, c_int64, c_void_p, c_int32, c_void_p,

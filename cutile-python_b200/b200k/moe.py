@@ -87,11 +87,24 @@ def moe_align_tile_size_torch(topk_ids: torch.Tensor, tile_m: int, num_experts: 
 
 
 def _gather_rows(src: torch.Tensor, index: torch.Tensor, divisor: int, rows: int,
-                 num_blocks: torch.Tensor | None, tile: int = ROW_TILE) -> torch.Tensor:
+                 num_blocks: torch.Tensor | None, tile: int = ROW_TILE, *,
+                 by_source: bool = False) -> torch.Tensor:
+    """dst row i = src row index[i] // divisor (zero rows for sentinels).  ``by_source``: the
+    valid entries of ``index`` are distinct replica ids (the alignment's output); every source
+    row is then read once and stored to all its places."""
     if src.stride(1) != 1 or (src.stride(0) * src.element_size()) % 16 or src.data_ptr() % 16 \
             or (src.shape[1] * src.element_size()) % 16:
         raise ValueError("gather source rows must be contiguous multiples of 16 bytes")
     dst = torch.empty((rows, src.shape[1]), dtype=src.dtype, device=src.device)
+    if by_source:
+        scratch = torch.empty(max(src.shape[0] * divisor, 1), dtype=torch.int32, device=src.device)
+        with torch.cuda.device(src.device):
+            _lib.check(_lib.lib().b200k_gather_rows_by_source(
+                src.data_ptr(), src.shape[0], src.shape[1] * src.element_size(),
+                src.stride(0) * src.element_size(), index.data_ptr(), divisor,
+                _lib.ptr(num_blocks), tile, rows, dst.data_ptr(),
+                dst.stride(0) * dst.element_size(), scratch.data_ptr(), _lib.stream_ptr(src.device)))
+        return dst
     with torch.cuda.device(src.device):
         _lib.check(_lib.lib().b200k_gather_rows(
             src.data_ptr(), src.shape[0], src.shape[1] * src.element_size(),
@@ -266,7 +279,7 @@ def cutile_moe(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
     tile = _moe_tile(tokens * topk, experts)
     sorted_ids, expert_ids, num_blocks = moe_align_device(topk_ids, tile, experts)
     cap = sorted_ids.numel()
-    a_sorted = _gather_rows(x, sorted_ids, topk, cap, num_blocks, tile)
+    a_sorted = _gather_rows(x, sorted_ids, topk, cap, num_blocks, tile, by_source=topk > 1)
     act = torch.empty((cap, inter), dtype=dtype, device=dev)
     if inter % 128 == 0:
         _grouped_gemm(a_sorted, w1c, act, expert_ids, num_blocks=num_blocks, swiglu=True, tile=tile)

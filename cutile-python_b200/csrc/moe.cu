@@ -195,7 +195,12 @@ moe_scatter_kernel(const IdT* __restrict__ ids, int64_t total, int num_experts,
   }
 }
 
-// One block per destination row; 16-byte copies.
+// A block copies four destination rows at a time with 16-byte vectors: their four indices are
+// fetched together and every thread has four loads in flight before its first store (one row
+// at a time, the chain index -> row load -> store of each row ran back to back and the copy
+// was bound by that latency: 332 us for 1.07 GB of rows where the memory system takes 200).
+constexpr int kGatherRowsPerTrip = 4;
+
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint8_t* __restrict__ src, int64_t src_rows, int64_t row_bytes,
                    int64_t src_stride, const int* __restrict__ index, int divisor,
@@ -207,15 +212,99 @@ gather_rows_kernel(const uint8_t* __restrict__ src, int64_t src_rows, int64_t ro
     const int64_t live = static_cast<int64_t>(*num_blocks) * tile_m;
     rows = live < rows ? live : rows;
   }
-  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
-    const int64_t s = index[r] / divisor;
-    uint4* out = reinterpret_cast<uint4*>(dst + r * dst_stride);
+  const int64_t vecs = row_bytes / 16;
+  for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * kGatherRowsPerTrip; r0 < rows;
+       r0 += static_cast<int64_t>(gridDim.x) * kGatherRowsPerTrip) {
+    const uint4* in[kGatherRowsPerTrip];
+    uint4* out[kGatherRowsPerTrip];
+#pragma unroll
+    for (int u = 0; u < kGatherRowsPerTrip; ++u) {
+      const int64_t r = r0 + u;
+      in[u] = nullptr;
+      out[u] = nullptr;
+      if (r < rows) {
+        const int ix = index[r];
+        const int64_t s = ix / divisor;
+        out[u] = reinterpret_cast<uint4*>(dst + r * dst_stride);
+        if (ix >= 0 && s < src_rows) in[u] = reinterpret_cast<const uint4*>(src + s * src_stride);
+      }
+    }
+    for (int64_t i = threadIdx.x; i < vecs; i += blockDim.x) {
+      uint4 v[kGatherRowsPerTrip];
+#pragma unroll
+      for (int u = 0; u < kGatherRowsPerTrip; ++u) v[u] = in[u] != nullptr ? in[u][i] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < kGatherRowsPerTrip; ++u)
+        if (out[u] != nullptr) out[u][i] = v[u];
+    }
+  }
+}
+
+// ---- the same gather, source row by source row ---------------------------------------
+// With top-k replicas every source row has k destinations scattered over the sorted order.
+// Walking the destinations reads the source k times at random (134 MB of tokens do not stay in
+// the L2 under 1 GB of streaming stores: the copy then moves 2 GB through DRAM); walking the
+// sources reads each row once and stores it k times.  That needs the inverse of `index`.
+
+// inv[id] = position of replica id in the sorted order (inv is preset to -1); rows whose index
+// is a sentinel are zero-filled here, so that the destination is fully defined.
+__global__ void __launch_bounds__(256)
+invert_index_kernel(const int* __restrict__ index, int64_t ids, const int* __restrict__ num_blocks, int tile_m,
+                    int64_t max_rows, int* __restrict__ inv, uint8_t* __restrict__ dst, int64_t dst_stride,
+                    int64_t row_bytes) {
+  pdl_wait();
+  int64_t rows = max_rows;
+  if (num_blocks != nullptr) {
+    const int64_t live = static_cast<int64_t>(*num_blocks) * tile_m;
+    rows = live < rows ? live : rows;
+  }
+  __shared__ int s_id[256];
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * 256; base < rows; base += static_cast<int64_t>(gridDim.x) * 256) {
+    const int64_t pos = base + threadIdx.x;
+    int id = -1;
+    if (pos < rows) {
+      id = index[pos];
+      if (id >= 0 && id < ids) inv[id] = static_cast<int>(pos);
+      else id = -1;
+    }
+    s_id[threadIdx.x] = (pos < rows) ? id : 0;      // past the end: nothing to fill
+    __syncthreads();
     const int64_t vecs = row_bytes / 16;
-    if (s >= 0 && s < src_rows && index[r] >= 0) {
-      const uint4* in = reinterpret_cast<const uint4*>(src + s * src_stride);
-      for (int64_t i = threadIdx.x; i < vecs; i += blockDim.x) out[i] = in[i];
-    } else {
-      for (int64_t i = threadIdx.x; i < vecs; i += blockDim.x) out[i] = make_uint4(0, 0, 0, 0);
+    for (int j = 0; j < 256; ++j) {
+      if (s_id[j] >= 0) continue;
+      uint4* out = reinterpret_cast<uint4*>(dst + (base + j) * dst_stride);
+      for (int64_t i = threadIdx.x; i < vecs; i += 256) out[i] = make_uint4(0, 0, 0, 0);
+    }
+    __syncthreads();
+  }
+}
+
+// One block per source row: the row is read once into registers (up to four 16-byte vectors per
+// thread; longer rows in passes) and stored to each of its `divisor` destinations.
+__global__ void __launch_bounds__(256)
+scatter_rows_kernel(const uint8_t* __restrict__ src, int64_t src_rows, int64_t row_bytes, int64_t src_stride,
+                    const int* __restrict__ inv, int divisor, uint8_t* __restrict__ dst, int64_t dst_stride) {
+  pdl_wait();
+  const int64_t vecs = row_bytes / 16;
+  for (int64_t s = blockIdx.x; s < src_rows; s += gridDim.x) {
+    const uint4* in = reinterpret_cast<const uint4*>(src + s * src_stride);
+    for (int64_t i0 = 0; i0 < vecs; i0 += 4 * 256) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t i = i0 + u * 256 + threadIdx.x;
+        if (i < vecs) v[u] = in[i];
+      }
+      for (int k = 0; k < divisor; ++k) {
+        const int pos = inv[s * divisor + k];
+        if (pos < 0) continue;                         // a replica that is not in the sorted order
+        uint4* out = reinterpret_cast<uint4*>(dst + static_cast<int64_t>(pos) * dst_stride);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int64_t i = i0 + u * 256 + threadIdx.x;
+          if (i < vecs) out[i] = v[u];
+        }
+      }
     }
   }
 }
@@ -466,12 +555,43 @@ extern "C" int b200k_gather_rows(const void* src, int64_t src_rows, int64_t row_
   if (row_bytes % 16 || src_stride_bytes % 16 || dst_stride_bytes % 16 ||
       (reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) % 16)
     return fail(B200K_UNSUPPORTED, "rows must be multiples of 16 bytes on 16-byte boundaries");
-  const int grid = blocks_for(max_rows * 256, 256, 16);
+  const int grid = blocks_for(ceil_div(max_rows, kGatherRowsPerTrip) * 256, 256, 16);
   const cudaError_t e = launch_after_predecessor(gather_rows_kernel, dim3(grid), dim3(256), 0, stream,
                                                  static_cast<const uint8_t*>(src), src_rows, row_bytes,
                                                  src_stride_bytes, index, divisor, num_blocks, tile_m, max_rows,
                                                  static_cast<uint8_t*>(dst), dst_stride_bytes);
   if (e != cudaSuccess) return fail(B200K_CUDA_ERROR, "gather_rows launch: %s", cudaGetErrorString(e));
+  return B200K_OK;
+}
+
+extern "C" int b200k_gather_rows_by_source(const void* src, int64_t src_rows, int64_t row_bytes,
+                                           int64_t src_stride_bytes, const int32_t* index, int32_t divisor,
+                                           const int32_t* num_blocks, int32_t tile_m, int64_t max_rows,
+                                           void* dst, int64_t dst_stride_bytes, int32_t* scratch,
+                                           b200k_stream stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (src_rows < 0 || row_bytes < 0 || max_rows < 0 || divisor <= 0)
+    return fail(B200K_INVALID_ARG, "bad sizes");
+  if (max_rows == 0 || row_bytes == 0) return B200K_OK;
+  if (!src || !index || !dst || !scratch) return fail(B200K_INVALID_ARG, "null pointer");
+  if (row_bytes % 16 || src_stride_bytes % 16 || dst_stride_bytes % 16 ||
+      (reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) % 16)
+    return fail(B200K_UNSUPPORTED, "rows must be multiples of 16 bytes on 16-byte boundaries");
+  const int64_t ids = src_rows * divisor;
+  if (ids > INT32_MAX || max_rows > INT32_MAX) return fail(B200K_UNSUPPORTED, "more than 2^31 rows");
+  if (ids > 0) {
+    const cudaError_t em = cudaMemsetAsync(scratch, 0xff, static_cast<size_t>(ids) * sizeof(int32_t), stream);
+    if (em != cudaSuccess) return fail(B200K_CUDA_ERROR, "memset: %s", cudaGetErrorString(em));
+  }
+  invert_index_kernel<<<blocks_for(max_rows, 256, 8), 256, 0, stream>>>(
+      index, ids, num_blocks, tile_m, max_rows, scratch, static_cast<uint8_t*>(dst), dst_stride_bytes, row_bytes);
+  B200K_CHECK_LAUNCH("invert_index launch");
+  if (src_rows > 0) {
+    scatter_rows_kernel<<<blocks_for(src_rows * 256, 256, 8), 256, 0, stream>>>(
+        static_cast<const uint8_t*>(src), src_rows, row_bytes, src_stride_bytes, scratch, divisor,
+        static_cast<uint8_t*>(dst), dst_stride_bytes);
+    B200K_CHECK_LAUNCH("scatter_rows launch");
+  }
   return B200K_OK;
 }
 

@@ -375,6 +375,17 @@ int b200k_gather_rows(const void* src, int64_t src_rows, int64_t row_bytes,
                       const int32_t* num_blocks, int32_t tile_m, int64_t max_rows, void* dst,
                       int64_t dst_stride_bytes, b200k_stream stream);
 
+/* The same destination as b200k_gather_rows, produced source row by source row: every source row
+ * is read once and stored to each position index sends it to, instead of being read once per
+ * destination row (with top-k replicas the sources do not stay in the L2 under the streaming
+ * stores).  Needs the valid entries of `index` to be distinct values in [0, src_rows * divisor),
+ * as b200k_moe_align produces them, and `scratch`: src_rows * divisor int32 of device memory,
+ * contents irrelevant before and after. */
+int b200k_gather_rows_by_source(const void* src, int64_t src_rows, int64_t row_bytes,
+                                int64_t src_stride_bytes, const int32_t* index, int32_t divisor,
+                                const int32_t* num_blocks, int32_t tile_m, int64_t max_rows, void* dst,
+                                int64_t dst_stride_bytes, int32_t* scratch, b200k_stream stream);
+
 /* C[r, j] = silu(AB[r, j]) * AB[r, j + n], f16/bf16/f32; replaces silu_and_mul_kernel
  * (reference: test/kernels/fused_moe.py:85-108). */
 int b200k_silu_and_mul(const void* ab, int64_t rows, int64_t n, int64_t ld_ab, void* c,

@@ -224,3 +224,29 @@ def test_sparse_routing_path_drops_entries_outside_the_expert_range(monkeypatch)
     assert code != 0 and (info >> 8) & 0xff == 40
     ref = oracle.moe_ref(x, w1, w2, tw_eff, bad.clamp(0, 63))
     assert oracle.rel_frobenius(out, ref) < 2e-2
+
+
+@pytest.mark.parametrize("tokens,hidden,experts,topk", [(300, 512, 8, 2), (64, 4096, 16, 8), (17, 264, 5, 3)])
+def test_gather_rows_by_source_equals_gather_rows(tokens, hidden, experts, topk, device_ok):
+    """b200k_gather_rows_by_source (every token row read once, stored to all its places) fills the
+    destination exactly as b200k_gather_rows does (one read per destination row), padding rows
+    and entries routed outside the experts included."""
+    from b200k import moe
+    g = torch.Generator().manual_seed(tokens + hidden)
+    x = torch.randn(tokens, hidden, generator=g).bfloat16().cuda()
+    ids = torch.stack([torch.randperm(experts, generator=g)[:topk] for _ in range(tokens)]).int()
+    ids[0, 0] = experts + 3                      # dropped entries: not in the sorted order
+    ids[tokens - 1, topk - 1] = -1
+    sorted_ids, _, num_blocks = moe.moe_align_device(ids.cuda(), 128, experts)
+    cap = sorted_ids.numel()
+    a = moe._gather_rows(x, sorted_ids, topk, cap, num_blocks, 128)
+    b = moe._gather_rows(x, sorted_ids, topk, cap, num_blocks, 128, by_source=True)
+    live = int(num_blocks.item()) * 128
+    assert torch.equal(a[:live], b[:live])
+    # without the live-row bound every row of the capacity is produced
+    a = moe._gather_rows(x, sorted_ids[:live], topk, live, None, 128)
+    b = moe._gather_rows(x, sorted_ids[:live], topk, live, None, 128, by_source=True)
+    assert torch.equal(a, b)
+    torch.cuda.synchronize()
+    code, info = b200k.device_status()           # the alignment records the dropped entries; reading clears
+    assert code != 0 and (info >> 8) & 0xff == 40
