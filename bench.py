@@ -1230,6 +1230,9 @@ def run_ours(args, w):
         os.environ.setdefault("MASTER_PORT", "29531")
         os.environ.setdefault("RANK", "0")
         os.environ.setdefault("WORLD_SIZE", "1")
+        # NCCL only carries barriers and the max over ranks here; without NVLink multicast objects a
+        # rank that dies cannot fault its peers' GPUs
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=device)
     w.world, w.rank = world, rank
 
